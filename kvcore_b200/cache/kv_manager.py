@@ -1,0 +1,268 @@
+"""Cache manager: pages per group of layers, a block table per request and group, and a
+state slot per request.  Pure bookkeeping on the host; it never touches device tensors.
+
+What the reference does per layer (one manager and one block list per layer over a common
+pool: kvcore/kv/kv_manager.py:105-113, 179-257; single_type_kv_manager.py:104-182;
+block_table.py:87-236) is done here per *group*: schedule entries whose mixers have the same
+cache needs (kv heads, head size, window) share one pool and one block table, and every
+entry of the group stores its keys/values under the same page id in its own slice of the
+group's storage.  A group that keeps all keys holds a request's pages until it ends; a
+windowed group hands back pages that lie wholly behind the window while the request lives
+(table entry becomes the null page).  Freed pages go to the tail of the free queue, a
+finished request's pages in reverse order, so pages are used again.
+
+Tables are persistent numpy rows indexed by the request's state slot and updated
+incrementally; the step function gathers the rows of the requests it runs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .page_pool import NULL_PAGE, PagePool
+from .state_slots import StateSlotPool
+
+
+@dataclass(frozen=True)
+class CacheGroupSpec:
+    """One group of schedule entries with equal cache needs."""
+
+    group_id: int
+    entries: tuple[int, ...]
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+    @property
+    def kind(self) -> str:
+        return "full" if self.window is None else "window"
+
+
+@dataclass
+class _RequestState:
+    slot: int
+    num_computed: int = 0
+    # per group: number of logical blocks in the table (freed ones included) and how many
+    # leading blocks were already handed back
+    num_blocks: list[int] = field(default_factory=list)
+    num_released: list[int] = field(default_factory=list)
+
+
+class KVManagerError(RuntimeError):
+    pass
+
+
+class KVManager:
+    def __init__(
+        self,
+        groups: list[CacheGroupSpec],
+        *,
+        num_pages: int | list[int],
+        page_size: int,
+        max_num_seqs: int,
+        max_model_len: int,
+    ) -> None:
+        if page_size <= 0:
+            raise ValueError(f"page_size must be positive, got {page_size}")
+        self.groups = list(groups)
+        self.page_size = int(page_size)
+        self.max_model_len = int(max_model_len)
+        self.max_blocks_per_seq = -(-self.max_model_len // self.page_size)
+        counts = [num_pages] * len(self.groups) if isinstance(num_pages, int) else list(num_pages)
+        if len(counts) != len(self.groups):
+            raise ValueError("num_pages must give one count per group")
+        self.pools = [PagePool(count) for count in counts]
+        self.slots = StateSlotPool(max_num_seqs)
+        self.tables = [
+            np.zeros((max_num_seqs, self.max_blocks_per_seq), dtype=np.int32) for _ in self.groups
+        ]
+        self._requests: dict[str, _RequestState] = {}
+        self._fresh_slots: list[int] = []
+
+    # ---- queries ---------------------------------------------------------------------------
+    def has_request(self, request_id: str) -> bool:
+        return request_id in self._requests
+
+    def num_computed(self, request_id: str) -> int:
+        state = self._requests.get(request_id)
+        return 0 if state is None else state.num_computed
+
+    def state_slot(self, request_id: str) -> int:
+        return self._requests[request_id].slot
+
+    def live_requests(self) -> list[str]:
+        return list(self._requests)
+
+    def num_free_pages(self) -> list[int]:
+        return [pool.num_free for pool in self.pools]
+
+    def block_ids(self, request_id: str) -> tuple[tuple[int, ...], ...]:
+        """Per group, the request's table row up to the blocks it has (0 = handed back)."""
+        state = self._requests[request_id]
+        return tuple(
+            tuple(int(x) for x in self.tables[g][state.slot, : state.num_blocks[g]])
+            for g in range(len(self.groups))
+        )
+
+    def _new_pages_needed(self, state: _RequestState | None, num_new_tokens: int) -> list[int]:
+        computed = 0 if state is None else state.num_computed
+        total = computed + num_new_tokens
+        target = -(-total // self.page_size)
+        return [
+            max(target - (0 if state is None else state.num_blocks[g]), 0)
+            for g in range(len(self.groups))
+        ]
+
+    def pages_needed(self, request_id: str, num_new_tokens: int) -> list[int]:
+        return self._new_pages_needed(self._requests.get(request_id), num_new_tokens)
+
+    def can_fit(self, request_id: str, num_new_tokens: int) -> bool:
+        """Whether ``num_new_tokens`` more tokens of the request can be given pages (and, for a
+        request not yet seen, a state slot) right now.  Admission math as the reference's
+        ``can_fit`` (kv_manager.py:179-201) per group instead of per layer."""
+        state = self._requests.get(request_id)
+        computed = 0 if state is None else state.num_computed
+        if computed + num_new_tokens > self.max_model_len:
+            return False
+        if state is None and self.slots.num_free == 0:
+            return False
+        needed = self._new_pages_needed(state, num_new_tokens)
+        return all(need <= pool.num_free for need, pool in zip(needed, self.pools))
+
+    # ---- changes ---------------------------------------------------------------------------
+    def allocate_slots(self, request_id: str, num_new_tokens: int) -> bool:
+        """Give the request pages for ``num_new_tokens`` tokens beyond those computed.
+        Returns False (and changes nothing) if they do not fit."""
+        if num_new_tokens <= 0:
+            raise ValueError(f"num_new_tokens must be positive, got {num_new_tokens}")
+        if not self.can_fit(request_id, num_new_tokens):
+            return False
+        state = self._requests.get(request_id)
+        if state is None:
+            slot = self.slots.allocate(request_id)
+            state = _RequestState(
+                slot=slot,
+                num_blocks=[0] * len(self.groups),
+                num_released=[0] * len(self.groups),
+            )
+            self._requests[request_id] = state
+            self._fresh_slots.append(slot)
+            for table in self.tables:
+                table[slot, :] = NULL_PAGE
+        needed = self._new_pages_needed(state, num_new_tokens)
+        for g, need in enumerate(needed):
+            if need:
+                pages = self.pools[g].allocate(need)
+                begin = state.num_blocks[g]
+                self.tables[g][state.slot, begin : begin + need] = pages
+                state.num_blocks[g] = begin + need
+        return True
+
+    def advance(self, request_id: str, num_tokens: int) -> None:
+        """Record that ``num_tokens`` more tokens are computed; windowed groups hand back the
+        pages that no later query can see (all positions < num_computed - window + 1)."""
+        state = self._requests[request_id]
+        state.num_computed += num_tokens
+        for g, group in enumerate(self.groups):
+            capacity = state.num_blocks[g] * self.page_size
+            if state.num_computed > capacity:
+                raise KVManagerError(
+                    f"request {request_id!r} computed {state.num_computed} tokens but group "
+                    f"{group.group_id} holds pages for only {capacity}"
+                )
+            if group.window is None:
+                continue
+            first_visible = state.num_computed - group.window + 1
+            releasable = max(first_visible, 0) // self.page_size
+            releasable = min(releasable, state.num_blocks[g])
+            if releasable > state.num_released[g]:
+                row = self.tables[g][state.slot]
+                pages = [int(p) for p in row[state.num_released[g] : releasable] if p != NULL_PAGE]
+                self.pools[g].free(pages)
+                row[state.num_released[g] : releasable] = NULL_PAGE
+                state.num_released[g] = releasable
+
+    def free(self, request_id: str) -> None:
+        """Return everything the request holds: pages in reverse order, and its slot."""
+        state = self._requests.pop(request_id, None)
+        if state is None:
+            return
+        for g in range(len(self.groups)):
+            row = self.tables[g][state.slot]
+            pages = [int(p) for p in row[: state.num_blocks[g]] if p != NULL_PAGE]
+            self.pools[g].free(reversed(pages))
+            row[:] = NULL_PAGE
+        self.slots.free(state.slot)
+        if state.slot in self._fresh_slots:
+            self._fresh_slots.remove(state.slot)
+
+    def take_fresh_slots(self) -> list[int]:
+        """Slots handed to new requests since the last call; their state must start at zero."""
+        fresh, self._fresh_slots = self._fresh_slots, []
+        return fresh
+
+    # ---- checks ----------------------------------------------------------------------------
+    def check_invariants(self) -> None:
+        """No page lost, none held twice, tables and pools agree (used by tests)."""
+        for g, pool in enumerate(self.pools):
+            seen: dict[int, str] = {}
+            for request_id, state in self._requests.items():
+                row = self.tables[g][state.slot]
+                if np.any(row[state.num_blocks[g] :] != NULL_PAGE):
+                    raise KVManagerError(f"request {request_id!r} has pages beyond its block count")
+                for page in row[: state.num_blocks[g]]:
+                    page = int(page)
+                    if page == NULL_PAGE:
+                        continue
+                    if page in seen:
+                        raise KVManagerError(
+                            f"page {page} of group {g} is held by {seen[page]!r} and {request_id!r}"
+                        )
+                    if not pool.is_held(page):
+                        raise KVManagerError(f"page {page} of group {g} is in a table but free")
+                    seen[page] = request_id
+            free = pool.free_pages()
+            if len(set(free)) != len(free):
+                raise KVManagerError(f"group {g}: a page is in the free queue twice")
+            if set(free) & set(seen):
+                raise KVManagerError(f"group {g}: a page is both free and held")
+            if len(free) + len(seen) != pool.num_usable:
+                raise KVManagerError(
+                    f"group {g}: {pool.num_usable - len(free) - len(seen)} page(s) lost"
+                )
+
+
+def group_entries(requirements) -> tuple[list[CacheGroupSpec], dict[int, int]]:
+    """Partition schedule entries into cache groups by equal ``CacheSpec``.
+
+    ``requirements`` are the model's ``EntryRequirement``s.  Returns the groups and a map
+    from entry index to group id; an entry that borrows a cache maps to its owner's group.
+    """
+    by_spec: dict[tuple, list[int]] = {}
+    for req in requirements:
+        if req.cache_spec is None or req.cache_of is not None:
+            continue
+        key = (req.cache_spec.num_kv_heads, req.cache_spec.head_dim, req.cache_spec.window)
+        by_spec.setdefault(key, []).append(req.entry)
+    groups = [
+        CacheGroupSpec(group_id, tuple(entries), key[0], key[1], key[2])
+        for group_id, (key, entries) in enumerate(by_spec.items())
+    ]
+    entry_group: dict[int, int] = {}
+    for group in groups:
+        for entry in group.entries:
+            entry_group[entry] = group.group_id
+    for req in requirements:
+        if req.cache_of is not None and req.cache_spec is not None:
+            owner = requirements[req.cache_of]
+            if owner.cache_spec != req.cache_spec:
+                raise ValueError(
+                    f"schedule entry {req.entry} borrows the cache of entry {req.cache_of}, "
+                    "whose cache layout differs"
+                )
+            entry_group[req.entry] = entry_group[req.cache_of]
+    return groups, entry_group
+
+
+__all__ = ["CacheGroupSpec", "KVManager", "KVManagerError", "group_entries"]

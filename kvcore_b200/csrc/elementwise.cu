@@ -1,0 +1,304 @@
+// Memory-bound kernels of the step: row gather (token embedding, logits rows), RMS norm with
+// the residual sum folded in, SiLU(gate)*up, and rotary encoding fused with the cache write.
+// Each is templated on the activation type (float for the 32-bit path, bf16 for serving) and
+// does its arithmetic in 32-bit.  16-byte vector loads are used when the row size and the
+// pointers allow, scalar loops otherwise, so every width is accepted.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// Row gather: out[i, :] = table[ids[i], :].  An id outside [0, rows) writes zeros and sets the
+// BAD_TOKEN status bit instead of reading out of bounds.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ table,
+                                   const int* __restrict__ ids, int width, int rows, int vec_ok,
+                                   int* status) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool valid = id >= 0 && id < rows;
+  if (!valid && threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_TOKEN);
+  T* dst = out + (size_t)row * width;
+  const T* src = table + (size_t)(valid ? id : 0) * width;
+  if (vec_ok) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) {
+      Vec16<T> v;
+      if (valid) v.load(src + i); else v.raw = make_uint4(0, 0, 0, 0);
+      v.store(dst + i);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      dst[i] = valid ? src[i] : from_float<T>(0.0f);
+  }
+}
+
+extern "C" int kvb_gather_rows(void* out, const void* table, const int* ids, int count, int width,
+                               int rows, int dtype, cudaStream_t stream) {
+  if (count == 0) return 0;
+  KVB_REQUIRE(width > 0 && rows > 0, "gather_rows: empty table");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "gather_rows: no status word");
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const int vec_ok = ((size_t)width * esize) % 16 == 0 && aligned16(out) && aligned16(table);
+  const int threads = 128;
+  if (dtype == KVB_F32)
+    gather_rows_kernel<float><<<count, threads, 0, stream>>>((float*)out, (const float*)table, ids,
+                                                             width, rows, vec_ok, status);
+  else
+    gather_rows_kernel<bf16><<<count, threads, 0, stream>>>((bf16*)out, (const bf16*)table, ids,
+                                                           width, rows, vec_ok, status);
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// RMS norm.  One block of 256 threads per row, whatever the batch: the reduction tree depends
+// on the width only, so a row's result does not depend on what else is in the batch.
+//   ADD: s = h + residual (rounded to T, stored back as the new residual), else s = h
+//   out = T( w * (s * rsqrt(mean(s^2) + eps)) ), everything between in 32-bit.
+// ------------------------------------------------------------------------------------------
+template <typename T, typename W, bool ADD, bool VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ h,
+               const W* __restrict__ weight, int width, float eps) {
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * width;
+  const T* hr = h + base;
+  T* rr = ADD ? residual + base : nullptr;
+  T* orow = out + base;
+  float sq = 0.0f;
+  if (VEC) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = threadIdx.x * N; i < width; i += 256 * N) {
+      Vec16<T> a;
+      a.load(hr + i);
+      if (ADD) {
+        Vec16<T> r;
+        r.load(rr + i);
+#pragma unroll
+        for (int j = 0; j < N; ++j) a.set(j, a.get(j) + r.get(j));
+        a.store(rr + i);
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) { const float x = a.get(j); sq += x * x; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += 256) {
+      float x = to_float(hr[i]);
+      if (ADD) {
+        const T s = from_float<T>(x + to_float(rr[i]));
+        rr[i] = s;
+        x = to_float(s);
+      }
+      sq += x * x;
+    }
+  }
+  const float total = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)width + eps);
+  const T* src = ADD ? rr : hr;  // each thread re-reads exactly what it wrote itself
+  if (VEC) {
+    constexpr int N = Vec16<T>::N;
+    for (int i = threadIdx.x * N; i < width; i += 256 * N) {
+      Vec16<T> a, o;
+      a.load(src + i);
+#pragma unroll
+      for (int j = 0; j < N; ++j) o.set(j, to_float(weight[i + j]) * (a.get(j) * inv));
+      o.store(orow + i);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += 256)
+      orow[i] = from_float<T>(to_float(weight[i]) * (to_float(src[i]) * inv));
+  }
+}
+
+template <typename T, typename W>
+static void launch_rmsnorm(void* out, void* residual, const void* h, const void* w, int rows,
+                           int width, float eps, bool add, bool vec, cudaStream_t stream) {
+#define KVB_RMS(ADD_, VEC_)                                                                   \
+  rmsnorm_kernel<T, W, ADD_, VEC_><<<rows, 256, 0, stream>>>((T*)out, (T*)residual, (const T*)h, \
+                                                             (const W*)w, width, eps)
+  if (add) { if (vec) KVB_RMS(true, true); else KVB_RMS(true, false); }
+  else { if (vec) KVB_RMS(false, true); else KVB_RMS(false, false); }
+#undef KVB_RMS
+}
+
+// residual == nullptr: plain norm of h.  Otherwise residual is updated in place to h + residual.
+extern "C" int kvb_rmsnorm(void* out, void* residual, const void* h, const void* weight, int rows,
+                           int width, float eps, int dtype, int weight_dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  KVB_REQUIRE(width > 0, "rmsnorm: width must be positive");
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const bool add = residual != nullptr;
+  const bool vec = ((size_t)width * esize) % 16 == 0 && aligned16(out) && aligned16(h) &&
+                   (!add || aligned16(residual));
+  if (dtype == KVB_F32) {
+    KVB_REQUIRE(weight_dtype == KVB_F32, "rmsnorm: a 32-bit model needs 32-bit norm weights");
+    launch_rmsnorm<float, float>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+  } else if (weight_dtype == KVB_F32) {
+    launch_rmsnorm<bf16, float>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+  } else {
+    launch_rmsnorm<bf16, bf16>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+  }
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+template <typename T, bool VEC>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter,
+                                long long total_vecs) {
+  constexpr int N = VEC ? Vec16<T>::N : 1;
+  const int per_row = inter / N;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vecs;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long row = v / per_row;
+    const int col = (int)(v % per_row) * N;
+    const T* g = gu + row * 2 * inter + col;
+    T* o = out + row * inter + col;
+    if (VEC) {
+      Vec16<T> a, b, r;
+      a.load(g);
+      b.load(g + inter);
+#pragma unroll
+      for (int j = 0; j < Vec16<T>::N; ++j) {
+        // the product is formed from the rounded activation, as silu(gate) * up in T would be
+        const float s = to_float(from_float<T>(silu(a.get(j))));
+        r.set(j, s * b.get(j));
+      }
+      r.store(o);
+    } else {
+      const float s = to_float(from_float<T>(silu(to_float(g[0]))));
+      o[0] = from_float<T>(s * to_float(g[inter]));
+    }
+  }
+}
+
+extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter, int dtype,
+                            cudaStream_t stream) {
+  if (rows == 0) return 0;
+  KVB_REQUIRE(inter > 0, "silu_mul: width must be positive");
+  const int esize = dtype == KVB_F32 ? 4 : 2;
+  const bool vec = ((size_t)inter * esize) % 16 == 0 && aligned16(out) && aligned16(gate_up);
+  const int n = vec ? 16 / esize : 1;
+  const long long total = (long long)rows * (inter / n);
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
+                                                                     : 148 * 16);
+  if (dtype == KVB_F32) {
+    if (vec) silu_mul_kernel<float, true><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+    else silu_mul_kernel<float, false><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+  } else {
+    if (vec) silu_mul_kernel<bf16, true><<<blocks, threads, 0, stream>>>((bf16*)out, (const bf16*)gate_up, inter, total);
+    else silu_mul_kernel<bf16, false><<<blocks, threads, 0, stream>>>((bf16*)out, (const bf16*)gate_up, inter, total);
+  }
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Rotary encoding of q and k (half-rotation layout) fused with the write of k and v into the
+// paged cache.  qkv is [T, (H + 2*KVH) * D]: q heads, then k heads, then v heads.
+//   angle = float(position) * inv_freq[j]  (32-bit), j in [0, D/2)
+//   x'[j] = x[j]*cos - x[j+D/2]*sin ;  x'[j+D/2] = x[j+D/2]*cos + x[j]*sin
+// q and k are rotated in place; rotated k and v go to page table[req, pos / page] at offset
+// pos % page of a cache laid out [pages, KVH, page, D].  inv_freq == nullptr: no rotation.
+// k_cache == nullptr: nothing is written (an entry that reads another entry's cache).
+// One block per token: threadIdx.x = j, threadIdx.y strides over heads.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
+                                     const int* __restrict__ positions,
+                                     const int* __restrict__ req_index,
+                                     const float* __restrict__ inv_freq,
+                                     const int* __restrict__ table, int table_stride,
+                                     T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int KVH,
+                                     int D, int page_size, int num_pages, int rotate_k,
+                                     int* status) {
+  const int token = blockIdx.x;
+  const int half = D >> 1;
+  const int pos = positions[token];
+  T* row = qkv + (size_t)token * qkv_stride;
+
+  size_t cache_base = 0;
+  bool write = k_cache != nullptr;
+  if (write) {
+    const int page = table[(size_t)req_index[token] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && threadIdx.y == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      write = false;
+    }
+    cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
+  }
+  const size_t head_stride = (size_t)page_size * D;  // between kv heads inside a page
+
+  const int j = threadIdx.x;
+  if (j < half) {
+    float c = 1.0f, s = 0.0f;
+    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[j], &s, &c);
+    const int rotated_heads = H + KVH;
+    for (int head = threadIdx.y; head < rotated_heads; head += blockDim.y) {
+      T* x = row + (size_t)head * D;
+      float a = to_float(x[j]), b = to_float(x[j + half]);
+      if (inv_freq != nullptr && (head < H || rotate_k)) {
+        const float ra = a * c - b * s;
+        const float rb = b * c + a * s;
+        a = to_float(from_float<T>(ra));
+        b = to_float(from_float<T>(rb));
+        x[j] = from_float<T>(ra);
+        x[j + half] = from_float<T>(rb);
+      }
+      if (head >= H && write) {
+        T* dst = k_cache + cache_base + (size_t)(head - H) * head_stride;
+        dst[j] = from_float<T>(a);
+        dst[j + half] = from_float<T>(b);
+      }
+    }
+  }
+  if (write) {
+    const T* v = row + (size_t)(H + KVH) * D;
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+    const int nthreads = blockDim.x * blockDim.y;
+    for (int i = tid; i < KVH * D; i += nthreads) {
+      const int head = i / D, d = i % D;
+      v_cache[cache_base + (size_t)head * head_stride + d] = v[i];
+    }
+  }
+}
+
+extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* positions,
+                                 const int* req_index,
+                                 const float* inv_freq, const int* table, int table_stride,
+                                 void* k_cache, void* v_cache, int tokens, int H, int KVH, int D,
+                                 int page_size, int num_pages, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  KVB_REQUIRE(D > 0 && D % 2 == 0 && D <= 1024, "rope_kv_write: head_dim must be even and <= 1024");
+  KVB_REQUIRE(H >= 0 && KVH >= 0 && H + KVH > 0, "rope_kv_write: no heads to encode");
+  KVB_REQUIRE(KVH > 0 || k_cache == nullptr, "rope_kv_write: a cache write needs kv heads");
+  KVB_REQUIRE(qkv_stride >= (long long)(H + 2 * KVH) * D || (k_cache == nullptr && qkv_stride >= (long long)(H + KVH) * D),
+              "rope_kv_write: row stride is smaller than the row");
+  KVB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "rope_kv_write: give both caches or none");
+  KVB_REQUIRE(k_cache == nullptr || (table != nullptr && page_size > 0), "rope_kv_write: a cache write needs a block table");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "rope_kv_write: no status word");
+  const int half = D / 2;
+  int tx = 1;
+  while (tx < half) tx <<= 1;           // threads along j, a power of two >= D/2
+  int ty = 256 / tx;
+  if (ty < 1) ty = 1;
+  if (ty > H + KVH) ty = H + KVH;
+  dim3 block(tx, ty);
+  if (dtype == KVB_F32)
+    rope_kv_write_kernel<float><<<tokens, block, 0, stream>>>(
+        (float*)qkv, qkv_stride, positions, req_index, inv_freq, table, table_stride, (float*)k_cache,
+        (float*)v_cache, H, KVH, D, page_size, num_pages, 1, status);
+  else
+    rope_kv_write_kernel<bf16><<<tokens, block, 0, stream>>>(
+        (bf16*)qkv, qkv_stride, positions, req_index, inv_freq, table, table_stride, (bf16*)k_cache,
+        (bf16*)v_cache, H, KVH, D, page_size, num_pages, 1, status);
+  KVB_CHECK_LAUNCH();
+  return 0;
+}

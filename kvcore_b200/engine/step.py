@@ -1,0 +1,318 @@
+"""The step function: one batch of (request, its next tokens) run through the model from
+the cache, returning 32-bit logits at the wanted places.
+
+A step may mix portions of prompts with single decoded tokens, cut anywhere.  It runs only
+the tokens it is given; everything earlier is read from the pages that earlier steps wrote.
+The reference spreads this over its model runner (kvcore/model/model_runner.py:208-306,
+411-580: flatten inputs, build metadata with per-layer block tables and slot mappings,
+forward, gather logits rows).  Here the whole step's metadata is packed into one pinned
+host buffer and uploaded with a single copy: per request its query start, cached length,
+total length and state slot; per token its id, position and request row; the wanted rows;
+and one block-table slice per cache group.  Kernels compute cache slots from the block
+table and the position themselves, so no slot mapping is built.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.kv_manager import CacheGroupSpec, KVManager
+from ..parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens, and which of them need logits."""
+
+    request_id: str
+    token_ids: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+@dataclass
+class LayerCache:
+    """What one schedule entry's mixer sees of the cache."""
+
+    group: int | None
+    k: torch.Tensor | None
+    v: torch.Tensor | None
+    owner: bool
+    state: torch.Tensor | None
+    page_size: int
+
+
+class StepContext:
+    """Device-side description of the step's batch, handed to every part."""
+
+    def __init__(self) -> None:
+        self.num_tokens = 0
+        self.num_reqs = 0
+        self.num_logits = 0
+        self.page_size = 0
+        self.token_ids: torch.Tensor | None = None
+        self.positions: torch.Tensor | None = None
+        self.req_index: torch.Tensor | None = None
+        self.query_start: torch.Tensor | None = None
+        self.context_lens: torch.Tensor | None = None
+        self.seq_lens: torch.Tensor | None = None
+        self.state_slots: torch.Tensor | None = None
+        self.logits_indices: torch.Tensor | None = None
+        self.tables: list[torch.Tensor] = []
+        self.table_width = 0
+        self.max_query_len = 0
+        self.max_seq_len = 0
+        self.decode_only = False
+        # host copies, for parts that plan their launches (or toy parts written in torch)
+        self.host_query_lens: list[int] = []
+        self.host_context_lens: list[int] = []
+        self.host_state_slots: list[int] = []
+
+    def block_table(self, group: int | None) -> torch.Tensor | None:
+        """``[num_reqs, table_width]`` int32 page ids of the step's requests for ``group``."""
+        return None if group is None else self.tables[group]
+
+
+class CacheStorage:
+    """Device tensors behind the cache manager's bookkeeping.
+
+    Per group one tensor ``[entries, 2, pages, kv_heads, page_size, head_dim]`` (keys at
+    index 0, values at 1): every entry of the group stores a page id's tokens in its own
+    slice.  Per schedule entry with a ``StateSpec`` one tensor ``[slots, *shape]``.
+    """
+
+    def __init__(
+        self,
+        model: DecoderModel,
+        groups: list[CacheGroupSpec],
+        entry_group: dict[int, int],
+        *,
+        num_pages: list[int],
+        page_size: int,
+        num_slots: int,
+        dtype: torch.dtype,
+        device: torch.device,
+    ) -> None:
+        self.page_size = page_size
+        self.group_tensors: list[torch.Tensor] = []
+        for group, pages in zip(groups, num_pages):
+            self.group_tensors.append(
+                torch.zeros(
+                    len(group.entries), 2, pages, group.num_kv_heads, page_size, group.head_dim,
+                    dtype=dtype, device=device,
+                )
+            )
+        self.layer_caches: list[LayerCache] = []
+        self.state_tensors: list[torch.Tensor] = []
+        for req in model.entry_requirements():
+            k = v = None
+            group_id = entry_group.get(req.entry)
+            owner = req.cache_of is None
+            if group_id is not None:
+                owner_entry = req.entry if owner else req.cache_of
+                index = groups[group_id].entries.index(owner_entry)
+                k = self.group_tensors[group_id][index, 0]
+                v = self.group_tensors[group_id][index, 1]
+            state = None
+            if req.state_spec is not None:
+                state = torch.zeros(
+                    (num_slots, *req.state_spec.shape), dtype=req.state_spec.dtype, device=device
+                )
+                self.state_tensors.append(state)
+            self.layer_caches.append(LayerCache(group_id, k, v, owner, state, page_size))
+
+    def zero_slots(self, slots: Sequence[int]) -> None:
+        if not slots or not self.state_tensors:
+            return
+        index = torch.as_tensor(list(slots), dtype=torch.long, device=self.state_tensors[0].device)
+        for state in self.state_tensors:
+            state.index_fill_(0, index, 0)
+
+    def bytes_per_page(self) -> list[int]:
+        return [
+            t.shape[0] * 2 * t.shape[3] * t.shape[4] * t.shape[5] * t.element_size()
+            for t in self.group_tensors
+        ]
+
+
+def _round4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepFunction:
+    def __init__(
+        self,
+        model: DecoderModel,
+        kv_manager: KVManager,
+        storage: CacheStorage,
+        *,
+        max_num_tokens: int,
+        max_num_seqs: int,
+    ) -> None:
+        self.model = model
+        self.kv = kv_manager
+        self.storage = storage
+        self.device = model.device
+        self.max_num_tokens = int(max_num_tokens)
+        self.max_num_seqs = int(max_num_seqs)
+        self.vocab_size = model.spec.vocab_size
+        width = kv_manager.max_blocks_per_seq
+        capacity = (
+            4 * _round4(self.max_num_seqs + 1)
+            + 4 * _round4(self.max_num_tokens)
+            + len(kv_manager.groups) * _round4(self.max_num_seqs * width)
+        )
+        self._capacity = capacity
+        self._device_meta = torch.zeros(capacity, dtype=torch.int32, device=self.device)
+        pin = self.device.type == "cuda"
+        self._host_meta = [torch.zeros(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._host_events: list[torch.cuda.Event | None] = [None, None]
+        self._turn = 0
+        self.last_context: StepContext | None = None
+        self.num_steps = 0
+
+    # ---- packing -----------------------------------------------------------------------------
+    def _pack(self, entries: Sequence[StepEntry]) -> StepContext:
+        kv = self.kv
+        num_reqs = len(entries)
+        if num_reqs == 0:
+            raise ValueError("a step needs at least one entry")
+        if num_reqs > self.max_num_seqs:
+            raise ValueError(f"{num_reqs} requests in one step exceed max_num_seqs {self.max_num_seqs}")
+        query_lens = [len(entry.token_ids) for entry in entries]
+        num_tokens = sum(query_lens)
+        if num_tokens > self.max_num_tokens:
+            raise ValueError(
+                f"{num_tokens} tokens in one step exceed max_num_scheduled_tokens {self.max_num_tokens}"
+            )
+        seen: set[str] = set()
+        context_lens: list[int] = []
+        slots: list[int] = []
+        for entry, n in zip(entries, query_lens):
+            if n == 0:
+                raise ValueError(f"request {entry.request_id!r} brings no tokens to the step")
+            if entry.request_id in seen:
+                raise ValueError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            if not kv.has_request(entry.request_id) or any(kv.pages_needed(entry.request_id, n)):
+                raise RuntimeError(
+                    f"request {entry.request_id!r} has no pages for its next {n} tokens: "
+                    "allocate_slots must succeed before the step"
+                )
+            context_lens.append(kv.num_computed(entry.request_id))
+            slots.append(kv.state_slot(entry.request_id))
+        seq_lens = [c + n for c, n in zip(context_lens, query_lens)]
+        max_seq_len = max(seq_lens)
+        width = -(-max_seq_len // kv.page_size)
+        width = max(1, min(_round4(width), kv.max_blocks_per_seq))
+        num_logits = sum(len(entry.want) for entry in entries)
+
+        # layout (int32 counts, each array starting on a 16-byte boundary)
+        r4, t4 = _round4(num_reqs + 1), _round4(num_tokens)
+        off_query_start = 0
+        off_context = r4
+        off_seq = 2 * r4
+        off_slots = 3 * r4
+        off_tokens = 4 * r4
+        off_positions = off_tokens + t4
+        off_req_index = off_positions + t4
+        off_logits = off_req_index + t4
+        off_tables = off_logits + _round4(max(num_logits, 1))
+        table_len = _round4(num_reqs * width)
+        used = off_tables + len(kv.groups) * table_len
+        if used > self._capacity:
+            raise RuntimeError("step metadata exceeds its buffer")  # cannot happen by construction
+
+        turn = self._turn
+        self._turn ^= 1
+        event = self._host_events[turn]
+        if event is not None:
+            event.synchronize()
+        host = self._host_meta[turn].numpy()
+
+        starts = np.zeros(num_reqs + 1, dtype=np.int32)
+        np.cumsum(query_lens, out=starts[1:])
+        host[off_query_start : off_query_start + num_reqs + 1] = starts
+        host[off_context : off_context + num_reqs] = context_lens
+        host[off_seq : off_seq + num_reqs] = seq_lens
+        host[off_slots : off_slots + num_reqs] = slots
+        cursor = 0
+        logit_rows: list[int] = []
+        for row, (entry, n, context) in enumerate(zip(entries, query_lens, context_lens)):
+            ids = np.asarray(entry.token_ids, dtype=np.int64)
+            if ids.min() < 0 or ids.max() >= self.vocab_size:
+                raise ValueError(
+                    f"request {entry.request_id!r} has a token id outside [0, {self.vocab_size})"
+                )
+            host[off_tokens + cursor : off_tokens + cursor + n] = ids
+            host[off_positions + cursor : off_positions + cursor + n] = np.arange(
+                context, context + n, dtype=np.int32
+            )
+            host[off_req_index + cursor : off_req_index + cursor + n] = row
+            for place in entry.want:
+                if not 0 <= place < n:
+                    raise ValueError(
+                        f"request {entry.request_id!r} wants logits at place {place} of {n} tokens"
+                    )
+                logit_rows.append(cursor + int(place))
+            cursor += n
+        if logit_rows:
+            host[off_logits : off_logits + num_logits] = logit_rows
+        slot_index = np.asarray(slots, dtype=np.int64)
+        for g in range(len(kv.groups)):
+            begin = off_tables + g * table_len
+            host[begin : begin + num_reqs * width] = kv.tables[g][slot_index, :width].reshape(-1)
+
+        device_meta = self._device_meta
+        device_meta[:used].copy_(self._host_meta[turn][:used], non_blocking=True)
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+            self._host_events[turn] = event
+
+        ctx = StepContext()
+        ctx.num_tokens, ctx.num_reqs, ctx.num_logits = num_tokens, num_reqs, num_logits
+        ctx.page_size = kv.page_size
+        ctx.query_start = device_meta[off_query_start : off_query_start + num_reqs + 1]
+        ctx.context_lens = device_meta[off_context : off_context + num_reqs]
+        ctx.seq_lens = device_meta[off_seq : off_seq + num_reqs]
+        ctx.state_slots = device_meta[off_slots : off_slots + num_reqs]
+        ctx.token_ids = device_meta[off_tokens : off_tokens + num_tokens]
+        ctx.positions = device_meta[off_positions : off_positions + num_tokens]
+        ctx.req_index = device_meta[off_req_index : off_req_index + num_tokens]
+        ctx.logits_indices = device_meta[off_logits : off_logits + num_logits]
+        ctx.tables = [
+            device_meta[off_tables + g * table_len : off_tables + g * table_len + num_reqs * width].view(
+                num_reqs, width
+            )
+            for g in range(len(kv.groups))
+        ]
+        ctx.table_width = width
+        ctx.max_query_len = max(query_lens)
+        ctx.max_seq_len = max_seq_len
+        ctx.decode_only = ctx.max_query_len == 1
+        ctx.host_query_lens = query_lens
+        ctx.host_context_lens = context_lens
+        ctx.host_state_slots = slots
+        return ctx
+
+    # ---- the step ------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        """Run one batch; returns ``[wanted, vocab]`` 32-bit logits on the device (``None`` if
+        nothing is wanted), rows in the order of the entries and of each entry's ``want``."""
+        ctx = self._pack(entries)
+        self.storage.zero_slots(self.kv.take_fresh_slots())
+        h, residual = self.model.forward(ctx, self.storage.layer_caches)
+        logits = None
+        if ctx.num_logits:
+            logits = self.model.compute_logits(h, residual, ctx.logits_indices)
+        for entry in entries:
+            self.kv.advance(entry.request_id, len(entry.token_ids))
+        self.last_context = ctx
+        self.num_steps += 1
+        return logits
+
+
+__all__ = ["CacheStorage", "LayerCache", "StepContext", "StepEntry", "StepFunction"]

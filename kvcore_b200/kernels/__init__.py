@@ -1,0 +1,39 @@
+"""Hand-written sm_100a CUDA kernels and their Python wrappers.
+
+Parts call these through ``kvcore_b200.kernels.<name>`` at call time.
+"""
+from .api import (
+    KernelError,
+    add_rmsnorm,
+    check_attention_shape,
+    ensure_built,
+    gather_rows,
+    library_is_loaded,
+    linear,
+    paged_attention,
+    read_status,
+    require_device,
+    rmsnorm,
+    rope_inplace,
+    rope_kv_write,
+    sample,
+    silu_mul,
+)
+
+__all__ = [
+    "KernelError",
+    "add_rmsnorm",
+    "check_attention_shape",
+    "ensure_built",
+    "gather_rows",
+    "library_is_loaded",
+    "linear",
+    "paged_attention",
+    "read_status",
+    "require_device",
+    "rmsnorm",
+    "rope_inplace",
+    "rope_kv_write",
+    "sample",
+    "silu_mul",
+]

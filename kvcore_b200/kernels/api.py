@@ -1,0 +1,354 @@
+"""Python face of the CUDA library: one function per kernel, taking torch tensors.
+
+Each wrapper checks device, dtype, contiguity and sizes, then calls the exported C entry
+point with raw device pointers on torch's current stream.  There is no CPU path and no
+fallback: a tensor that is not on a CUDA device, or a library that cannot be built or
+loaded, raises.  Library matrix products (cuBLAS through torch) stand in for the bf16
+linear layers, as the reference uses a library for them (kvcore/model/layer/linear.py:6-12).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from . import build as _build
+
+_F32, _BF16 = 0, 1
+_lib: ctypes.CDLL | None = None
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+_ll = ctypes.c_longlong
+_float = ctypes.c_float
+
+
+class KernelError(RuntimeError):
+    """A kernel entry point refused its arguments or its launch failed."""
+
+
+def ensure_built(verbose: bool = False) -> str:
+    """Build (if needed) and load the CUDA library; returns its path."""
+    global _lib
+    if _lib is not None:
+        return _lib._name
+    path = _build.build(verbose=verbose)
+    lib = ctypes.CDLL(str(path))
+    lib.kvb_last_error.restype = ctypes.c_char_p
+    lib.kvb_status_word.restype = _vp
+    signatures: dict[str, list[Any]] = {
+        "kvb_gather_rows": [_vp, _vp, _vp, _int, _int, _int, _int, _vp],
+        "kvb_rmsnorm": [_vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _vp],
+        "kvb_silu_mul": [_vp, _vp, _int, _int, _int, _vp],
+        "kvb_rope_kv_write": [_vp, _ll, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
+                              _int, _int, _int, _vp],
+        "kvb_paged_attention_rows": [_vp, _int, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int,
+                                     _int, _int, _int, _int, _float, _int, _int, _vp],
+        "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
+        "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
+        "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
+    }
+    for name, argtypes in signatures.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _int
+    _lib = lib
+    return str(path)
+
+
+def library_is_loaded() -> bool:
+    return _lib is not None
+
+
+def require_device(device: torch.device | str) -> None:
+    """Fail loudly unless ``device`` is a usable CUDA device and the library loads."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise KernelError(f"kvcore_b200 runs on CUDA devices only, got device {device}")
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available; kvcore_b200 has no CPU path")
+    ensure_built()
+    with torch.cuda.device(device):
+        if not _lib.kvb_status_word():
+            raise KernelError("cannot allocate the device status word")
+
+
+def _call(name: str, *args: Any) -> None:
+    if _lib is None:
+        ensure_built()
+    code = getattr(_lib, name)(*args)
+    if code != 0:
+        raise KernelError(f"{name}: {_lib.kvb_last_error().decode()}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"unsupported tensor dtype {t.dtype}: kernels take float32 or bfloat16")
+
+
+def _check(t: torch.Tensor, name: str, *, dtype: torch.dtype | None = None, contiguous: bool = True) -> None:
+    if t.device.type != "cuda":
+        raise KernelError(f"{name} must be on a CUDA device, got {t.device}: there is no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def read_status(reset: bool = True) -> int:
+    """Status bits set by kernels (1 bad token id, 2 bad page id, 4 bounded wait ran out)."""
+    out = ctypes.c_int(0)
+    _call("kvb_read_status", int(reset), ctypes.byref(out))
+    return out.value
+
+
+# ---- shape policy -------------------------------------------------------------------------------
+def check_attention_shape(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
+    """Refuse, with a clear error, head shapes the attention kernels do not take."""
+    if head_dim <= 0 or head_dim % 2 or head_dim > 256:
+        raise ValueError(f"head_dim must be even and at most 256, got {head_dim}")
+    if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
+        raise ValueError(
+            f"num_heads {num_heads} must be a positive multiple of num_kv_heads {num_kv_heads}"
+        )
+    if dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"attention runs in float32 or bfloat16, got {dtype}")
+
+
+# ---- kernels --------------------------------------------------------------------------------------
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[i] = table[ids[i]]`` for int32 ``ids``; used for the embedding and for logits rows."""
+    _check(table, "table")
+    _check(ids, "ids", dtype=torch.int32)
+    if table.dim() != 2:
+        raise KernelError(f"table must be [rows, width], got {tuple(table.shape)}")
+    count, (rows, width) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((count, width), dtype=table.dtype, device=table.device)
+    _call("kvb_gather_rows", out.data_ptr(), table.data_ptr(), ids.data_ptr(), count, width, rows,
+          _dtype_code(table), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _check(x, "x")
+    _check(weight, "weight")
+    rows, width = x.shape
+    if weight.numel() != width:
+        raise KernelError(f"norm weight has {weight.numel()} entries for rows of width {width}")
+    out = torch.empty_like(x)
+    _call("kvb_rmsnorm", out.data_ptr(), None, x.data_ptr(), weight.data_ptr(), rows, width,
+          float(eps), _dtype_code(x), _dtype_code(weight), _stream())
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``residual += h`` in place, returns ``norm(residual) * weight``."""
+    _check(h, "h")
+    _check(residual, "residual", dtype=h.dtype)
+    _check(weight, "weight")
+    if h.shape != residual.shape:
+        raise KernelError(f"h {tuple(h.shape)} and residual {tuple(residual.shape)} differ in shape")
+    rows, width = h.shape
+    if weight.numel() != width:
+        raise KernelError(f"norm weight has {weight.numel()} entries for rows of width {width}")
+    out = torch.empty_like(h)
+    _call("kvb_rmsnorm", out.data_ptr(), residual.data_ptr(), h.data_ptr(), weight.data_ptr(), rows,
+          width, float(eps), _dtype_code(h), _dtype_code(weight), _stream())
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    _check(gate_up, "gate_up")
+    rows, two_inter = gate_up.shape
+    if two_inter % 2:
+        raise KernelError(f"gate_up must have an even width, got {two_inter}")
+    inter = two_inter // 2
+    out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _call("kvb_silu_mul", out.data_ptr(), gate_up.data_ptr(), rows, inter, _dtype_code(gate_up), _stream())
+    return out
+
+
+def rope_kv_write(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    req_index: torch.Tensor,
+    inv_freq: torch.Tensor | None,
+    table: torch.Tensor | None,
+    k_cache: torch.Tensor | None,
+    v_cache: torch.Tensor | None,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    *,
+    write_kv: bool = True,
+) -> None:
+    """Rotate q and k of ``qkv [T, (H+2KVH)*D]`` in place and write k, v into their pages."""
+    _check(qkv, "qkv", contiguous=False)
+    _check(positions, "positions", dtype=torch.int32)
+    _check(req_index, "req_index", dtype=torch.int32)
+    tokens = qkv.shape[0]
+    if qkv.stride(1) != 1:
+        raise KernelError("qkv rows must be contiguous")
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {qkv.shape[1]} does not match the head layout")
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", dtype=torch.float32)
+        if inv_freq.numel() != head_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.numel()} entries for head_dim {head_dim}")
+    k_ptr = v_ptr = table_ptr = None
+    table_stride = page_size = num_pages = 0
+    if write_kv:
+        if k_cache is None or v_cache is None or table is None:
+            raise KernelError("a cache write needs k_cache, v_cache and a block table")
+        _check(k_cache, "k_cache", dtype=qkv.dtype)
+        _check(v_cache, "v_cache", dtype=qkv.dtype)
+        _check(table, "block table", dtype=torch.int32, contiguous=False)
+        num_pages, kvh, page_size, d = k_cache.shape
+        if (kvh, d) != (num_kv_heads, head_dim) or v_cache.shape != k_cache.shape:
+            raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match the head layout")
+        if table.stride(1) != 1:
+            raise KernelError("block table rows must be contiguous")
+        k_ptr, v_ptr, table_ptr = k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr()
+        table_stride = table.stride(0)
+    if inv_freq is None and not write_kv:
+        return
+    _call("kvb_rope_kv_write", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), req_index.data_ptr(),
+          None if inv_freq is None else inv_freq.data_ptr(), table_ptr, table_stride, k_ptr, v_ptr,
+          tokens, num_heads, num_kv_heads, head_dim, page_size, num_pages, _dtype_code(qkv), _stream())
+
+
+def rope_inplace(q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tensor, inv_freq: torch.Tensor) -> None:
+    """Rotate ``q [T, H, D]`` (and ``k [T, KVH, D]``) in place without touching a cache; rows may
+    be views into a wider buffer as long as heads are contiguous."""
+    _check(positions, "positions", dtype=torch.int32)
+    _check(inv_freq, "inv_freq", dtype=torch.float32)
+    for x in (q, k):
+        if x is None:
+            continue
+        _check(x, "q/k", contiguous=False)
+        tokens, heads, head_dim = x.shape
+        if x.stride(2) != 1 or x.stride(1) != head_dim:
+            raise KernelError("rope_inplace: heads must be contiguous within a row")
+        if inv_freq.numel() != head_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.numel()} entries for head_dim {head_dim}")
+        _call("kvb_rope_kv_write", x.data_ptr(), x.stride(0), positions.data_ptr(), positions.data_ptr(),
+              inv_freq.data_ptr(), None, 0, None, None, tokens, heads, 0, head_dim, 0, 0,
+              _dtype_code(x), _stream())
+
+
+def paged_attention(
+    qkv: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    table: torch.Tensor,
+    ctx,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    scale: float,
+    window: int | None,
+) -> torch.Tensor:
+    """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
+
+    Returns ``[T, H*D]``.  ``ctx`` gives positions and request rows of the tokens.
+    """
+    _check(qkv, "qkv")
+    _check(k_cache, "k_cache", dtype=qkv.dtype)
+    _check(v_cache, "v_cache", dtype=qkv.dtype)
+    _check(table, "block table", dtype=torch.int32, contiguous=False)
+    tokens = qkv.shape[0]
+    num_pages, kvh, page_size, d = k_cache.shape
+    if (kvh, d) != (num_kv_heads, head_dim):
+        raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match the head layout")
+    out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+          k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
+          ctx.positions.data_ptr(), ctx.req_index.data_ptr(), tokens, num_heads, num_kv_heads,
+          head_dim, page_size, num_pages, float(scale), int(window or 0), _dtype_code(qkv), _stream())
+    return out
+
+
+_mm_out_dtype_ok: bool | None = None
+
+
+def linear(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    *,
+    out_dtype: torch.dtype | None = None,
+) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` for ``x [M, K]``, ``weight [N, K]``.
+
+    float32: this package's own FMA kernel (no tensor cores, fixed summation order).
+    bfloat16: the library matrix product with 32-bit accumulation.
+    ``out_dtype=float32`` keeps the accumulator's precision in the result (the logits).
+    """
+    global _mm_out_dtype_ok
+    _check(x, "x", contiguous=False)
+    _check(weight, "weight", dtype=x.dtype)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
+        raise KernelError(f"linear: x {tuple(x.shape)} does not match weight {tuple(weight.shape)}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    n = weight.shape[0]
+    if x.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        _call("kvb_gemm_f32", out.data_ptr(), x.data_ptr(), weight.data_ptr(),
+              None if bias is None else bias.data_ptr(), m, n, k, x.stride(0), out.stride(0), _stream())
+        return out
+    if out_dtype == torch.float32:
+        if _mm_out_dtype_ok is None:
+            try:
+                torch.mm(x[:1], weight[:1].t(), out_dtype=torch.float32)
+                _mm_out_dtype_ok = True
+            except (TypeError, RuntimeError):
+                _mm_out_dtype_ok = False
+        if _mm_out_dtype_ok:
+            out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        else:
+            out = torch.mm(x, weight.t()).float()
+        if bias is not None:
+            out = out + bias.float()
+        return out
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+def sample(logits: torch.Tensor, packed_params: torch.Tensor, eps: float) -> torch.Tensor:
+    """One token per row of ``logits [S, V]`` float32; ``packed_params [S, 6]`` float64 on the host:
+    temperature, top_k, top_p, seed low 32 bits, seed high 32 bits, index of the sampled token."""
+    _check(logits, "logits", dtype=torch.float32)
+    rows, vocab = logits.shape
+    params = packed_params.to(device=logits.device, dtype=torch.float64, non_blocking=False).contiguous()
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("kvb_sample", out.data_ptr(), logits.data_ptr(), params.data_ptr(), rows, vocab, float(eps), _stream())
+    return out
+
+
+__all__ = [
+    "KernelError",
+    "add_rmsnorm",
+    "check_attention_shape",
+    "ensure_built",
+    "gather_rows",
+    "library_is_loaded",
+    "linear",
+    "paged_attention",
+    "read_status",
+    "require_device",
+    "rmsnorm",
+    "rope_inplace",
+    "rope_kv_write",
+    "sample",
+    "silu_mul",
+]

@@ -1,0 +1,49 @@
+"""Arrangement of one layer: pre-norm mixer and feed-forward on a deferred residual.
+
+As the reference's decoder layer (kvcore/model/models/llama3.py:124-142): the running
+``residual`` and the last sub-layer output ``h`` stay separate and are summed inside the
+next norm; the first block starts with ``residual = h``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.model_spec import LayerSpec
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, WeightSlot
+
+
+class PreNormResidualBlock(Block):
+    def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: torch.device) -> None:
+        self.mixer_norm = NORMS.build(layer.norms["mixer_norm"], dtype=dtype, device=device)
+        self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
+        self.feed_forward_norm = NORMS.build(layer.norms["feed_forward_norm"], dtype=dtype, device=device)
+        self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def weight_slots(self) -> list[WeightSlot]:
+        slots: list[WeightSlot] = []
+        for part in self.parts():
+            slots += part.weight_slots()
+        return slots
+
+    def finalize_weights(self) -> None:
+        for part in self.parts():
+            part.finalize_weights()
+
+    def forward(self, h, residual, ctx, cache):
+        if residual is None:
+            residual = h
+            x = self.mixer_norm.forward(h)
+        else:
+            x, residual = self.mixer_norm.forward_residual(h, residual)
+        a = self.mixer.forward(x, ctx, cache)
+        x, residual = self.feed_forward_norm.forward_residual(a, residual)
+        h = self.feed_forward.forward(x, ctx)
+        return h, residual
+
+
+BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+
+__all__ = ["PreNormResidualBlock"]

@@ -1,0 +1,68 @@
+"""Next-token sampling from 32-bit logits: greedy, temperature, top-k, top-p, seeded.
+
+Rule as the reference's sampler (kvcore/sample/sampler.py:86-167): a temperature below
+1e-5 means greedy argmax; otherwise logits are divided by the temperature, all but the k
+largest are masked (top-k), then the smallest-probability tokens whose cumulative
+probability stays <= 1 - p are masked (top-p, the largest always kept), and the token is
+``argmax(softmax(logits) / q)`` with ``q ~ Exp(1)`` per vocabulary entry.
+
+Deliberate difference: the reference rebuilds a seeded generator at every call, so a
+seeded request sees the same noise at every decode step (sampler.py:53-57, 185-188).  Here
+the noise is a counter-based stream keyed by (request seed, index of the token being
+sampled, vocabulary entry), so a seeded request is reproducible and does not depend on
+what else is in the batch.  One kernel launch samples the whole batch.
+"""
+from __future__ import annotations
+
+import random
+from typing import Sequence
+
+import torch
+
+from .. import kernels as K
+from .params import SamplingParams
+
+SAMPLING_EPS = 1e-5  # sampler.py:11
+
+
+class Sampler:
+    def __init__(self, device: torch.device | str) -> None:
+        self.device = torch.device(device)
+
+    @staticmethod
+    def fresh_seed() -> int:
+        """A seed for a request that gave none."""
+        return random.getrandbits(62)
+
+    def sample(
+        self,
+        logits: torch.Tensor,
+        params: Sequence[SamplingParams],
+        seeds: Sequence[int],
+        token_indices: Sequence[int],
+    ) -> torch.Tensor:
+        """``logits [S, V]`` 32-bit -> int32 ``[S]`` token ids.
+
+        ``seeds[i]`` and ``token_indices[i]`` (how many tokens request i has sampled so far)
+        select the noise stream of row i.
+        """
+        if logits.dim() != 2:
+            raise ValueError(f"logits must be [rows, vocab], got {tuple(logits.shape)}")
+        rows, vocab = logits.shape
+        if not (len(params) == len(seeds) == len(token_indices) == rows):
+            raise ValueError("one SamplingParams, seed and token index per logits row is needed")
+        if logits.dtype != torch.float32:
+            logits = logits.float()
+        packed = torch.empty((rows, 6), dtype=torch.float64)
+        for row, (p, seed, index) in enumerate(zip(params, seeds, token_indices)):
+            top_k = vocab if p.top_k is None else min(p.top_k, vocab)
+            packed[row, 0] = p.temperature
+            packed[row, 1] = top_k
+            packed[row, 2] = p.top_p
+            packed[row, 3] = float(int(seed) & 0xFFFFFFFF)
+            packed[row, 4] = float((int(seed) >> 32) & 0xFFFFFFFF)
+            packed[row, 5] = index
+        return K.sample(logits, packed, SAMPLING_EPS)
+
+
+__all__ = ["SAMPLING_EPS", "Sampler"]
