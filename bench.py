@@ -1,0 +1,348 @@
+"""Benchmark: decode and prefill throughput of the Llama 3.1 8B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every request
+holding ``context_len`` tokens in the cache (a "step" is one decode step of the whole batch,
+sampling included), timed on the device with CUDA events around exactly K steps after W
+warm-up steps.  ``e2e`` is the same workload through the Python entry point
+(``LLMEngine.step``): every step uploads its inputs from pinned host memory and reads the
+sampled tokens back.  ``prefill`` times one 2,048-token prompt; ``roofline`` relates the bytes
+a decode step must read (every weight once, and the cache of the live requests) to its
+time.  ``points`` holds decode at batch 1 and 64, and the same batches at 1,024 tokens of
+context.  Weights are 15 GB, so consecutive steps cannot reuse the L2 cache.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA_31_8B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=128256, hidden_size=4096,
+    intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, max_position_embeddings=131072, tie_word_embeddings=False, rms_norm_eps=1e-5,
+    rope_theta=500000.0, hidden_act="silu",
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+)
+CONTEXT_LEN = 8192
+PREFILL_TOKENS = 2048
+BLOCK_SIZE = 16
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return dict(hbm_gbs=float(raw["hbm_gbs"]),
+                        bf16_tflops=float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
+                        source="measured")
+        except (KeyError, ValueError, json.JSONDecodeError):
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.path = Path(tempfile.mkstemp(suffix=".csv")[1])
+        self.process = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.path.open("w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 6:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                max_clock = float(fields[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, fields[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        self.path.unlink(missing_ok=True)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(config: dict, layers: int) -> dict:
+    e, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
+    h, kvh, d = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    per_layer = (h + 2 * kvh) * d * e + e * h * d + 2 * i * e + e * i + 2 * e
+    return dict(
+        layer_params=per_layer,
+        streamed_params=layers * per_layer + v * e + e,  # every matrix once, the head, the final norm
+        kv_bytes_per_token=layers * 2 * kvh * d * 2,
+        heads=h, head_dim=d, hidden=e, vocab=v,
+    )
+
+
+def build_runner(layers: int, max_seqs: int, max_len: int, num_pages: int, max_tokens: int):
+    import torch
+
+    from kvcore_b200 import CacheConfig, DeviceConfig, KVCoreConfig, LoadConfig, ModelConfig, SchedulerConfig
+    from kvcore_b200.engine.runner import ModelRunner
+
+    folder = Path(tempfile.mkdtemp(prefix="kvcore_bench_"))
+    (folder / "config.json").write_text(json.dumps(dict(LLAMA_31_8B, num_hidden_layers=layers)))
+    config = KVCoreConfig(
+        model_config=ModelConfig(model=str(folder), dtype="bfloat16", max_model_len=max_len),
+        load_config=LoadConfig(random_weights=True, seed=0),
+        cache_config=CacheConfig(block_size=BLOCK_SIZE, num_gpu_blocks=num_pages),
+        scheduler_config=SchedulerConfig(max_num_seqs=max_seqs, max_num_scheduled_tokens=max_tokens,
+                                         max_num_partial_prefills=max_seqs, max_long_partial_prefills=max_seqs),
+        device_config=DeviceConfig(device="cuda:0"),
+    )
+    runner = ModelRunner(config)
+    for tensor in runner.storage.group_tensors:  # a cache of plausible values, not zeros
+        flat = tensor.view(-1)
+        chunk = 1 << 28
+        for begin in range(0, flat.numel(), chunk):
+            flat[begin : begin + chunk].normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    return config, runner
+
+
+def time_decode(runner, batch: int, context: int, steps: int, warmup: int) -> float:
+    """Milliseconds per decode step of ``batch`` requests that each hold ``context`` tokens."""
+    import torch
+
+    from kvcore_b200.engine.step import StepEntry
+    from kvcore_b200.sampling import SamplingParams
+
+    kv = runner.kv_manager
+    for rid in kv.live_requests():
+        kv.free(rid)
+    ids = [f"bench-{i}" for i in range(batch)]
+    for rid in ids:
+        assert kv.allocate_slots(rid, context), "cache too small for the benchmark batch"
+        kv.advance(rid, context)
+    generator = torch.Generator().manual_seed(1)
+    vocab = runner.model.spec.vocab_size
+    tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=generator).tolist()
+    params = [SamplingParams(max_tokens=1, temperature=0.0)] * batch
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def one_step(index: int) -> None:
+        entries = []
+        for rid, token in zip(ids, tokens[index]):
+            assert kv.allocate_slots(rid, 1)
+            entries.append(StepEntry(rid, [token], (0,)))
+        logits = runner.step_function.step(entries)
+        runner.sampler.sample(logits, params, [0] * batch, [index] * batch)
+
+    for index in range(warmup):
+        one_step(index)
+    torch.cuda.synchronize()
+    start.record()
+    for index in range(warmup, warmup + steps):
+        one_step(index)
+    stop.record()
+    torch.cuda.synchronize()
+    for rid in ids:
+        kv.free(rid)
+    return start.elapsed_time(stop) / steps
+
+
+def time_prefill(runner, tokens: int, repeats: int, warmup: int) -> float:
+    import torch
+
+    from kvcore_b200.engine.step import StepEntry
+
+    kv = runner.kv_manager
+    generator = torch.Generator().manual_seed(2)
+    vocab = runner.model.spec.vocab_size
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for index in range(warmup + repeats):
+        prompt = torch.randint(0, vocab, (tokens,), generator=generator).tolist()
+        assert kv.allocate_slots("prefill", tokens)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step_function.step([StepEntry("prefill", prompt, (tokens - 1,))])
+        stop.record()
+        torch.cuda.synchronize()
+        kv.free("prefill")
+        if index >= warmup:
+            total += start.elapsed_time(stop)
+    return total / repeats
+
+
+def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """Decode steps through ``LLMEngine.step``: host token ids in, sampled token ids out."""
+    import torch
+
+    from kvcore_b200.engine.llm_engine import LLMEngine
+    from kvcore_b200.sampling import SamplingParams
+
+    for rid in runner.kv_manager.live_requests():
+        runner.kv_manager.free(rid)
+    engine = LLMEngine(config, model_runner=runner)
+    generator = torch.Generator().manual_seed(3)
+    vocab = runner.model.spec.vocab_size
+    for index in range(batch):
+        prompt = torch.randint(0, vocab, (context,), generator=generator).tolist()
+        engine.add_request(f"e2e-{index}", SamplingParams(max_tokens=steps + warmup + 1, temperature=0.0),
+                           prompt_token_ids=prompt)
+    scheduler = engine.engine_core.scheduler
+    while any(r.num_computed_tokens < r.num_prompt_tokens for r in scheduler.requests.values()):
+        engine.step()  # prefill, untimed
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    used_before = runner.step_function.num_steps
+    begin = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += sum(1 for o in engine.step().request_outputs if o.sampled_token_id is not None)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - begin
+    assert runner.step_function.num_steps - used_before == steps
+    ctx = runner.step_function.last_context
+    h2d = 4 * (4 * (batch + 4) + 4 * batch + batch * ctx.table_width) + batch * 6 * 8
+    engine.engine_core.scheduler.shutdown()
+    runner.remove_requests(list(runner.requests))
+    return {"value": produced / elapsed, "unit": "tokens/s", "ms_per_step": 1000.0 * elapsed / steps,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference through its own entry point, if it could be installed offline."""
+    ref = ROOT / "baseline" / "_ref"
+    reason = None
+    if not (ref / "kvcore").is_dir():
+        reason = "reference not installed under baseline/_ref (offline pip install did not succeed)"
+    print(json.dumps({"impl": "reference", "unavailable": reason or "reference arm not wired yet"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=32)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--layers", type=int, default=LLAMA_31_8B["num_hidden_layers"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=CONTEXT_LEN)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-points", action="store_true", help="only the headline decode number")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this engine is single-GPU by design, --gpus {args.gpus} is not run")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    import kvcore_b200.kernels as K
+
+    peaks = measured_peaks()
+    numbers = model_numbers(LLAMA_31_8B, args.layers)
+    max_batch = args.batch if args.skip_points else max(64, args.batch)
+    margin = args.steps + args.warmup + 8
+    max_len = max(args.context, PREFILL_TOKENS) + margin
+    pages = max_batch * (-(-max_len // BLOCK_SIZE)) + 1
+    config, runner = build_runner(args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))
+
+    sampler = ClockSampler()
+    sampler.start()
+    launches_before = K.api.launch_count
+    ms_step = time_decode(runner, args.batch, args.context, args.steps, args.warmup)
+    launches = (K.api.launch_count - launches_before) * args.steps // (args.steps + args.warmup)
+    points = {}
+    prefill = None
+    e2e = None
+    if not args.skip_points:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / time_decode(runner, batch, args.context, args.steps, args.warmup), 2)
+        for batch in (1, 8, 64):
+            points[f"decode_b{batch}_ctx1024"] = round(batch * 1000.0 / time_decode(runner, batch, 1024, args.steps, args.warmup), 2)
+        ms_prefill = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+        t, h, d = PREFILL_TOKENS, numbers["heads"], numbers["head_dim"]
+        flops = 2.0 * t * (args.layers * (numbers["layer_params"] - 2 * numbers["hidden"])) \
+            + args.layers * 4.0 * h * d * (t * (t + 1) / 2) + 2.0 * numbers["hidden"] * numbers["vocab"]
+        prefill = {"value": round(t * 1000.0 / ms_prefill, 1), "tokens": t, "ms": round(ms_prefill, 3),
+                   "frac": round(flops / (ms_prefill * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                   "tflops": round(flops / (ms_prefill * 1e-3) / 1e12, 1), "of": peaks["source"]}
+        e2e = time_e2e(config, runner, args.batch, args.context, args.steps, args.warmup)
+        e2e["value"] = round(e2e["value"], 2)
+        e2e["ms_per_step"] = round(e2e["ms_per_step"], 3)
+    clocks = sampler.stop()
+
+    step_bytes = 2.0 * numbers["streamed_params"] + args.batch * args.context * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    value = args.batch * 1000.0 / ms_step
+    line = {
+        "metric": "decode tokens/s, Llama 3.1 8B shape, batch 8, bf16",
+        "value": round(value, 2),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: random N(0,0.02) weights, seeded uniform-random token ids, random cache contents",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B shape", "layers": args.layers, "layers_of_config": LLAMA_31_8B["num_hidden_layers"],
+            "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
+            "vocab": 128256, "global_batch": args.batch, "seq_len": args.context, "context_len": args.context,
+            "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+            "l2": "weights of 15 GB stream every step: inputs larger than L2",
+        },
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"],
+                     "bytes_per_step": int(step_bytes)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if e2e is not None:
+        line["e2e"] = e2e
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

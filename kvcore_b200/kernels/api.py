@@ -73,9 +73,14 @@ def require_device(device: torch.device | str) -> None:
             raise KernelError("cannot allocate the device status word")
 
 
+launch_count = 0  # kernels of this library launched so far (read by the benchmark)
+
+
 def _call(name: str, *args: Any) -> None:
+    global launch_count
     if _lib is None:
         ensure_built()
+    launch_count += 1
     code = getattr(_lib, name)(*args)
     if code != 0:
         raise KernelError(f"{name}: {_lib.kvb_last_error().decode()}")

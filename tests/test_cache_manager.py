@@ -1,0 +1,166 @@
+"""The cache manager: no page lost, held twice or freed twice, under random orders of requests;
+windowed groups hand pages back while a request lives; state slots."""
+from __future__ import annotations
+
+import random
+
+import numpy as np
+import pytest
+
+from kvcore_b200.cache import (
+    CacheGroupSpec, KVManager, PagePool, PagePoolError, StateSlotError, StateSlotPool,
+)
+
+
+def manager(num_pages=9, page_size=4, windows=(None,), max_num_seqs=4, max_model_len=64):
+    groups = [CacheGroupSpec(i, (i,), 2, 16, w) for i, w in enumerate(windows)]
+    return KVManager(groups, num_pages=num_pages, page_size=page_size, max_num_seqs=max_num_seqs,
+                     max_model_len=max_model_len)
+
+
+def test_pool_null_page_order_and_double_free():
+    pool = PagePool(5)
+    assert pool.num_free == 4 and pool.num_usable == 4
+    pages = pool.allocate(3)
+    assert pages == [1, 2, 3] and 0 not in pages
+    with pytest.raises(PagePoolError):
+        pool.allocate(2)
+    pool.free(reversed(pages))
+    assert pool.free_pages() == [4, 3, 2, 1]  # freed pages queue behind the never-used one
+    with pytest.raises(PagePoolError, match="twice"):
+        pool.free([2])
+    with pytest.raises(PagePoolError, match="null"):
+        pool.free([0])
+    with pytest.raises(PagePoolError):
+        pool.free([9])
+    assert pool.allocate(2) == [4, 3]
+
+
+def test_allocate_advance_free_and_tables():
+    kv = manager()
+    assert kv.can_fit("a", 9) and kv.allocate_slots("a", 9)  # 3 pages
+    assert kv.block_ids("a") == ((1, 2, 3),)
+    assert kv.pages_needed("a", 9) == [0] and kv.pages_needed("a", 13) == [1]
+    kv.advance("a", 9)
+    assert kv.num_computed("a") == 9
+    assert kv.allocate_slots("a", 3)  # fits in the third page
+    assert kv.block_ids("a") == ((1, 2, 3),)
+    kv.advance("a", 3)
+    assert kv.allocate_slots("a", 1) and kv.block_ids("a") == ((1, 2, 3, 4),)
+    assert kv.allocate_slots("b", 16) and kv.block_ids("b") == ((5, 6, 7, 8),)
+    assert not kv.can_fit("c", 1) and not kv.allocate_slots("c", 1)
+    assert not kv.has_request("c")
+    row = kv.tables[0][kv.state_slot("b")]
+    assert row[:4].tolist() == [5, 6, 7, 8] and not row[4:].any()
+    kv.check_invariants()
+    kv.free("a")
+    assert kv.pools[0].free_pages() == [4, 3, 2, 1]  # reverse order: tail pages first
+    assert kv.allocate_slots("c", 5) and kv.block_ids("c") == ((4, 3),)
+    kv.free("b"); kv.free("c"); kv.free("c")
+    kv.check_invariants()
+    assert kv.num_free_pages() == [8] and not kv.live_requests()
+
+
+def test_advance_beyond_pages_is_an_error():
+    kv = manager()
+    kv.allocate_slots("a", 4)
+    with pytest.raises(Exception, match="holds pages"):
+        kv.advance("a", 5)
+
+
+def test_max_model_len_and_slots_limit():
+    kv = manager(num_pages=100, max_num_seqs=2, max_model_len=10)
+    assert not kv.can_fit("a", 11) and kv.allocate_slots("a", 10)
+    assert kv.allocate_slots("b", 1)
+    assert not kv.can_fit("c", 1)  # no state slot left
+    kv.free("a")
+    assert kv.allocate_slots("c", 1) and kv.state_slot("c") == 0
+    assert kv.take_fresh_slots() == [1, 0] and kv.take_fresh_slots() == []
+
+
+def test_window_group_hands_pages_back_while_the_request_lives():
+    kv = manager(num_pages=6, page_size=4, windows=(None, 6), max_model_len=40)
+    assert kv.allocate_slots("a", 10)
+    kv.advance("a", 10)  # next query at 10 sees keys >= 5: page 0 (positions 0..3) is passed
+    assert kv.block_ids("a") == ((1, 2, 3), (0, 2, 3))
+    assert kv.num_free_pages() == [2, 3]
+    for _ in range(10):
+        assert kv.allocate_slots("a", 1)
+        kv.advance("a", 1)
+        kv.check_invariants()
+    # 20 tokens: the full group would need 5 pages; the windowed one never holds more than 3
+    assert kv.num_free_pages()[1] >= 2 and kv.block_ids("a")[1][:3] == (0, 0, 0)
+    assert not kv.can_fit("a", 1)  # the full group is exhausted
+    kv.free("a")
+    kv.check_invariants()
+    assert kv.num_free_pages() == [5, 5]
+
+
+def test_window_never_releases_a_page_a_later_query_can_see():
+    page, window = 4, 6
+    kv = manager(num_pages=50, page_size=page, windows=(window,), max_model_len=100)
+    rng = random.Random(0)
+    done = 0
+    while done < 90:
+        n = rng.choice([1, 1, 2, 5, 9])
+        assert kv.allocate_slots("a", n)
+        # every key the portion's queries can see must still have a page
+        first_visible = max(0, done - window + 1)
+        row = kv.tables[0][kv.state_slot("a")]
+        for pos in range(first_visible, done + n):
+            assert row[pos // page] != 0, (done, n, pos)
+        kv.advance("a", n)
+        done += n
+    assert kv.pools[0].num_usable - kv.pools[0].num_free <= -(-(window + 9) // page) + 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_page_accounted(seed):
+    rng = random.Random(seed)
+    kv = manager(num_pages=24, page_size=4, windows=(None, 7), max_num_seqs=5, max_model_len=48)
+    live: dict[str, int] = {}
+    counter = 0
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.35 and len(live) < 5:
+            counter += 1
+            rid = f"r{counter}"
+            n = rng.randint(1, 20)
+            if kv.allocate_slots(rid, n):
+                kv.advance(rid, n)
+                live[rid] = n
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 3, 8])
+            before = kv.num_free_pages()
+            if kv.allocate_slots(rid, n):
+                kv.advance(rid, n)
+                live[rid] += n
+            else:
+                assert kv.num_free_pages() == before  # a refused allocation changes nothing
+        elif live:
+            rid = rng.choice(list(live))
+            kv.free(rid)
+            del live[rid]
+        kv.check_invariants()
+        for rid, n in live.items():
+            assert kv.num_computed(rid) == n
+        slots = [kv.state_slot(r) for r in live]
+        assert len(set(slots)) == len(slots)
+    for rid in list(live):
+        kv.free(rid)
+    kv.check_invariants()
+    assert kv.num_free_pages() == [23, 23] and kv.slots.num_free == 5
+    assert not any(np.any(t) for t in kv.tables)
+
+
+def test_state_slots():
+    pool = StateSlotPool(2)
+    a, b = pool.allocate("a"), pool.allocate("b")
+    assert (a, b) == (0, 1) and pool.owner(1) == "b"
+    with pytest.raises(StateSlotError):
+        pool.allocate("c")
+    pool.free(a)
+    with pytest.raises(StateSlotError):
+        pool.free(a)
+    assert pool.allocate("c") == 0

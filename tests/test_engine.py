@@ -1,0 +1,289 @@
+"""The engine above the step function: greedy generation through the Python entry point,
+seeded sampling, generality of the parts (a toy mixer with state of its own, a layer run
+twice, a layer reading another layer's cache, a windowed layer beside full ones).
+
+Every test runs twice: on the CPU with the kernels replaced by their plain statements
+(host logic only, ``-m "not gpu"``), and on the GPU with the real kernels (``-m gpu``)."""
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kernels
+import plain_llama
+import replay_cases as rc
+
+from kvcore_b200 import (
+    CacheConfig, DeviceConfig, KVCoreConfig, LoadConfig, ModelConfig, SamplingParams, SchedulerConfig,
+)
+from kvcore_b200.config import LlamaConfig, register_architecture, unregister_architecture
+from kvcore_b200.config.model_spec import ModelSpec, PartSpec, ScheduleEntry
+from kvcore_b200.engine.llm_engine import GenerationRequest, LLMEngine
+from kvcore_b200.parts import MIXERS, POSITION_ENCODINGS, FEED_FORWARDS, Mixer, PositionEncoding, FeedForward, StateSpec, WeightSlot
+
+BACKENDS = [pytest.param("cpu", id="host"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
+
+
+@pytest.fixture(params=BACKENDS)
+def device(request, monkeypatch):
+    if request.param == "cpu":
+        plain_kernels.install(monkeypatch)
+    return request.param
+
+
+def engine_config(folder, device, dtype="float32", **overrides):
+    sched = dict(max_num_seqs=4, max_num_scheduled_tokens=64, max_num_partial_prefills=4, max_long_partial_prefills=4)
+    sched.update(overrides.pop("scheduler", {}))
+    return KVCoreConfig(
+        model_config=ModelConfig(model=str(folder), dtype=dtype, max_model_len=overrides.pop("max_model_len", 128)),
+        load_config=LoadConfig(**overrides.pop("load", {})),
+        cache_config=CacheConfig(block_size=overrides.pop("block_size", 16), num_gpu_blocks=overrides.pop("num_gpu_blocks", 40)),
+        scheduler_config=SchedulerConfig(**sched),
+        device_config=DeviceConfig(device=device),
+    )
+
+
+@pytest.mark.parametrize("name,lengths,steps,block,budget", [("A", (7, 13), 8, 16, 64), ("B", (5, 19, 40), 12, 8, 6)])
+def test_greedy_generation_matches_plain(device, tmp_path, name, lengths, steps, block, budget):
+    config = rc.TINY_CONFIGS[name]
+    folder = rc.write_model(tmp_path / "m", config, rc.TINY_SEEDS[name], "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    prompts = [rc.random_tokens(config["vocab_size"], n, 50 + i) for i, n in enumerate(lengths)]
+    engine = LLMEngine(engine_config(folder, device, block_size=block, scheduler=dict(max_num_scheduled_tokens=budget)))
+    requests = [GenerationRequest(f"r{i}", SamplingParams(max_tokens=steps, temperature=0.0), tuple(p))
+                for i, p in enumerate(prompts)]
+    outputs = engine.generate(requests)
+    assert [o.request_id for o in outputs] == [r.request_id for r in requests]
+    for prompt, output in zip(prompts, outputs):
+        assert output.finish_reason == "length"
+        assert list(output.output_token_ids) == plain_llama.greedy_generate(config, weights, prompt, steps)
+    kv = engine.engine_core.model_runner.kv_manager
+    kv.check_invariants()
+    assert not kv.live_requests() and not engine.engine_core.model_runner.requests
+
+
+def test_generation_with_few_pages_and_preemption(device, tmp_path):
+    """So few pages that requests wait, are preempted and recomputed: tokens stay the plain ones."""
+    config = rc.TINY_CONFIGS["A"]
+    folder = rc.write_model(tmp_path / "m", config, 0, "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    prompts = [rc.random_tokens(256, n, 70 + i) for i, n in enumerate((9, 14, 6, 11))]
+    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=14,
+                                     scheduler=dict(max_num_scheduled_tokens=16)))
+    outputs = engine.generate([dict(request_id=f"r{i}", prompt_token_ids=p,
+                                    sampling_params=dict(max_tokens=10, temperature=0.0))
+                               for i, p in enumerate(prompts)])
+    for prompt, output in zip(prompts, outputs):
+        assert list(output.output_token_ids) == plain_llama.greedy_generate(config, weights, prompt, 10)
+    assert engine.engine_core.scheduler.num_preemptions > 0
+    engine.engine_core.model_runner.kv_manager.check_invariants()
+
+
+def test_too_small_a_cache_is_an_error(device, tmp_path):
+    folder = rc.write_model(tmp_path / "m", rc.TINY_A, 0, "bfloat16")
+    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=4,
+                                     scheduler=dict(preempt_on_deadlock=False)))
+    with pytest.raises(RuntimeError, match="no scheduling progress"):
+        engine.generate([dict(request_id="a", prompt_token_ids=[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11],
+                              sampling_params=dict(max_tokens=8, temperature=0.0))])
+
+
+def test_stop_token_from_config(device, tmp_path):
+    config = dict(rc.TINY_A)
+    folder = rc.write_model(tmp_path / "m", config, 0, "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    prompt = rc.random_tokens(256, 9, 3)
+    expected = plain_llama.greedy_generate(config, weights, prompt, 6)
+    stored = json.loads((folder / "config.json").read_text())
+    stored["eos_token_id"] = [expected[3], 999999]
+    (folder / "config.json").write_text(json.dumps(stored))
+    out = LLMEngine(engine_config(folder, device)).generate(
+        [dict(request_id="a", prompt_token_ids=prompt, sampling_params=dict(max_tokens=6, temperature=0.0))])
+    cut = expected.index(expected[3]) + 1
+    assert list(out[0].output_token_ids) == expected[:cut] and out[0].finish_reason == "stop"
+
+
+def test_seeded_sampling_is_reproducible_and_independent_of_the_batch(device, tmp_path):
+    config = rc.TINY_CONFIGS["B"]
+    folder = rc.write_model(tmp_path / "m", config, 1, "bfloat16")
+    prompts = [rc.random_tokens(config["vocab_size"], n, 90 + i) for i, n in enumerate((5, 19, 40))]
+
+    def run(which, budget):
+        engine = LLMEngine(engine_config(folder, device, block_size=8, max_model_len=256,
+                                         scheduler=dict(max_num_scheduled_tokens=budget)))
+        reqs = [dict(request_id=f"r{i}", prompt_token_ids=prompts[i],
+                     sampling_params=SamplingParams(max_tokens=12, temperature=0.8, seed=1234 + i, top_k=50, top_p=0.95))
+                for i in which]
+        return {o.request_id: o.output_token_ids for o in engine.generate(reqs)}
+
+    together = run([0, 1, 2], 6)
+    assert together == run([0, 1, 2], 6)
+    if device == "cpu":  # bit-equal logits across batchings hold for the plain kernels and the 32-bit GPU path
+        assert run([1], 64)["r1"] == together["r1"]
+    assert len({tuple(v) for v in together.values()}) == 3
+    unseeded = LLMEngine(engine_config(folder, device, block_size=8, max_model_len=256)).generate(
+        [dict(request_id="u", prompt_token_ids=prompts[0], sampling_params=dict(max_tokens=4))])
+    assert len(unseeded[0].output_token_ids) == 4
+
+
+def test_random_weights_mode_needs_no_weight_file(device, tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps(rc.TINY_A))
+    engine = LLMEngine(engine_config(tmp_path, device, load=dict(random_weights=True, seed=3)))
+    out = engine.generate([dict(request_id="a", prompt_token_ids=[1, 2, 3],
+                                sampling_params=dict(max_tokens=3, temperature=0.0))])
+    assert len(out[0].output_token_ids) == 3
+
+
+def test_requests_are_validated(device, tmp_path):
+    folder = rc.write_model(tmp_path / "m", rc.TINY_A, 0, "bfloat16")
+    engine = LLMEngine(engine_config(folder, device))
+    with pytest.raises(ValueError, match="outside"):
+        engine.add_request("a", SamplingParams(max_tokens=1), prompt_token_ids=[1, 256])
+    with pytest.raises(ValueError, match="prompt_token_ids or messages"):
+        engine.add_request("a", SamplingParams(max_tokens=1))
+    with pytest.raises(Exception, match="tokenizer"):
+        engine.add_request("a", SamplingParams(max_tokens=1), messages=[{"role": "user", "content": "hi"}])
+
+
+# ---- generality of the parts ------------------------------------------------------------------
+class RunningMeanMixer(Mixer):
+    """A toy mixer with state of its own: ``y_t = W (s_t / (t+1))`` with ``s_t = s_{t-1} + x_t``,
+    where ``s`` lives in the request's state slot between steps.  Written in torch by the test."""
+
+    def __init__(self, *, hidden_size, name, dtype, device):
+        self.hidden_size, self.name = hidden_size, name
+        self.weight = torch.empty(hidden_size, hidden_size, dtype=dtype, device=device)
+
+    def state_spec(self):
+        return StateSpec((self.hidden_size,), torch.float32)
+
+    def weight_slots(self):
+        return [WeightSlot(f"{self.name}.weight", self.weight)]
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        start = 0
+        for n, context, slot in zip(ctx.host_query_lens, ctx.host_context_lens, ctx.host_state_slots):
+            sums = cache.state[slot] + torch.cumsum(x[start:start + n].float(), dim=0)
+            counts = torch.arange(context + 1, context + n + 1, device=x.device, dtype=torch.float32)[:, None]
+            out[start:start + n] = ((sums / counts) @ self.weight.float().T).to(x.dtype)
+            cache.state[slot] = sums[-1]
+            start += n
+        return out
+
+
+class OffsetPosition(PositionEncoding):
+    """A toy position encoding: adds ``amplitude * sin(position * rate)`` to every q and k entry."""
+
+    def __init__(self, *, rate, amplitude, dtype, device):
+        self.rate, self.amplitude = rate, amplitude
+
+    def apply(self, q, k, ctx):
+        shift = (torch.sin(ctx.positions.float() * self.rate) * self.amplitude)[:, None, None]
+        q.copy_((q.float() + shift).to(q.dtype))
+        if k is not None:
+            k.copy_((k.float() + shift).to(k.dtype))
+
+
+def toy_spec(raw):
+    """Layers: 0 attention (window 9, toy position), 1 running mean, 2 attention (rope).
+    Schedule: 0, 1, 2, 0 again (own cache), then 2 reading the cache of the first run of 2."""
+    base = LlamaConfig.from_dict(raw).to_model_spec()
+    layers = list(base.layers)
+    layers[0] = type(layers[0])(
+        prefix=layers[0].prefix, block=layers[0].block,
+        mixer=layers[0].mixer.with_params(sliding_window=9, position=PartSpec("toy_offset", dict(rate=0.37, amplitude=0.5))),
+        feed_forward=layers[0].feed_forward, norms=layers[0].norms)
+    layers[1] = type(layers[1])(
+        prefix=layers[1].prefix, block=layers[1].block,
+        mixer=PartSpec("toy_running_mean", dict(hidden_size=raw["hidden_size"], name="model.layers.1.mean")),
+        feed_forward=layers[1].feed_forward, norms=layers[1].norms)
+    fields = {f: getattr(base, f) for f in base.__dataclass_fields__}
+    fields.update(architecture="ToyForCausalLM", layers=tuple(layers),
+                  schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(2, cache_of=2)))
+    return ModelSpec(**fields)
+
+
+def toy_plain_logits(raw, weights, tokens):
+    """The toy model, whole sequence, no cache, in plain torch (float64)."""
+    import plain_llama as pl
+
+    w = {k: v.double() for k, v in weights.items()}
+    ids = torch.as_tensor(tokens)
+    n = ids.numel()
+    heads, kvh, dim = raw["num_attention_heads"], raw["num_key_value_heads"], pl.head_dim_of(raw)
+    eps, positions = raw["rms_norm_eps"], torch.arange(n)
+    inv_freq = pl.rope_inv_freq(raw)
+
+    def attention_layer(x, p, kind, borrowed=None):
+        q = pl.linear(x, w[f"{p}.self_attn.q_proj.weight"]).view(n, heads, dim)
+        k = pl.linear(x, w[f"{p}.self_attn.k_proj.weight"]).view(n, kvh, dim)
+        v = pl.linear(x, w[f"{p}.self_attn.v_proj.weight"]).view(n, kvh, dim)
+        if kind == "toy":
+            shift = (torch.sin(positions.float() * 0.37) * 0.5).double()[:, None, None]
+            q, k = q + shift, k + shift
+            window = 9
+        else:
+            q, k = pl.apply_rope(q, k, positions, inv_freq)
+            window = None
+        if borrowed is not None:
+            k, v = borrowed
+        a = pl.causal_attention(q, k, v, dim ** -0.5, window).reshape(n, heads * dim)
+        return pl.linear(a, w[f"{p}.self_attn.o_proj.weight"]), (k, v)
+
+    def mean_layer(x, p):
+        running = torch.cumsum(x.float(), dim=0).double() / torch.arange(1, n + 1).double()[:, None]
+        return pl.linear(running, w["model.layers.1.mean.weight"]), None
+
+    h = pl.embed(ids, w["model.embed_tokens.weight"])
+    residual = None
+    kept = {}
+    for entry, (layer, borrow) in enumerate([(0, None), (1, None), (2, None), (0, None), (2, 2)]):
+        p = f"model.layers.{layer}"
+        residual = h if residual is None else h + residual
+        x = pl.rms_norm(residual, w[f"{p}.input_layernorm.weight"], eps)
+        if layer == 1:
+            a, _ = mean_layer(x, p)
+        else:
+            a, kept[entry] = attention_layer(x, p, "toy" if layer == 0 else "rope",
+                                             None if borrow is None else kept[borrow])
+        residual = a + residual
+        x = pl.rms_norm(residual, w[f"{p}.post_attention_layernorm.weight"], eps)
+        h = pl.swiglu_mlp(x, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"])
+    final = pl.rms_norm(h + residual, w["model.norm.weight"], eps)
+    return (final @ w["lm_head.weight"].T).float()
+
+
+@pytest.fixture
+def toy_parts():
+    MIXERS.register("toy_running_mean", RunningMeanMixer)
+    POSITION_ENCODINGS.register("toy_offset", OffsetPosition)
+    register_architecture("ToyForCausalLM", toy_spec)
+    yield
+    MIXERS.unregister("toy_running_mean")
+    POSITION_ENCODINGS.unregister("toy_offset")
+    unregister_architecture("ToyForCausalLM")
+
+
+def test_toy_parts_register_build_and_step_without_touching_the_framework(device, toy_parts, tmp_path):
+    raw = dict(rc.TINY_A, architectures=["ToyForCausalLM"], num_hidden_layers=3, max_position_embeddings=256)
+    folder = rc.write_model(tmp_path / "m", raw, 4, "float32")
+    weights = plain_llama.load_weights(folder)
+    assert "model.layers.1.mean.weight" in weights and "model.layers.1.self_attn.q_proj.weight" not in weights
+    requests = {f"r{i}": rc.random_tokens(256, n, 30 + i) for i, n in enumerate((40, 75, 23, 58, 31))}
+    reference = {rid: toy_plain_logits(raw, weights, toks).numpy() for rid, toks in requests.items()}
+    for steps in (rc.trace_whole(requests), rc.trace_chunks(requests), rc.trace_mixed(requests, max_live=3, seed=1)):
+        out = tmp_path / f"out{len(steps)}"
+        step_function, kv = rc.run_inprocess(folder, "float32", steps, out, rc.peak_tokens(steps), device=device)
+        rows = rc.collect(steps, out, 256)
+        assert len(rows) == sum(len(t) for t in requests.values())
+        for (rid, pos), row in rows.items():
+            err = np.abs(row - reference[rid][pos]).max() / np.abs(reference[rid]).max()
+            assert err < 3e-5, (rid, pos, err)
+        # two groups of pages: windowed (both runs of layer 0) and full (layer 2 and its borrower)
+        assert [g.kind for g in kv.groups] == ["window", "full"]
+        assert [len(g.entries) for g in kv.groups] == [2, 1]
+        assert len(step_function.storage.state_tensors) == 1

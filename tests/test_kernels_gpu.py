@@ -1,0 +1,299 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/plain_kernels.py), in
+float32 and bfloat16, at sizes other than the engine's tiny models: widths that are no
+power of two, head sizes in steps of 16, odd head counts and groups, pages that are not
+full, windows."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_kernels as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    import kvcore_b200.kernels as kernels
+
+    kernels.require_device(DEV)
+    return kernels
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+def randn(*shape, dtype, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,count", [(301, 120, 17), (1000, 4096, 64), (37, 7, 5)])
+def test_gather_rows(dtype, rows, width, count):
+    table = randn(rows, width, dtype=dtype)
+    ids = torch.randint(0, rows, (count,), dtype=torch.int32, device=DEV)
+    out = K().gather_rows(table, ids)
+    assert torch.equal(out, P.gather_rows(table, ids))
+    assert K().read_status() == 0
+
+
+def test_gather_rows_flags_bad_id():
+    table = randn(10, 8, dtype=torch.float32)
+    ids = torch.tensor([3, 10, -1], dtype=torch.int32, device=DEV)
+    out = K().gather_rows(table, ids)
+    assert torch.equal(out[0], table[3]) and not out[1:].any()
+    assert K().read_status() & 1
+    assert K().read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(5, 96), (33, 4096), (3, 1001), (2, 8192 + 8)])
+def test_rmsnorm(dtype, rows, width):
+    x = randn(rows, width, dtype=dtype, seed=1)
+    w = randn(width, dtype=dtype, seed=2)
+    torch.testing.assert_close(K().rmsnorm(x, w, 1e-5), P.rmsnorm(x, w, 1e-5), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(5, 96), (33, 4096), (3, 1001)])
+def test_add_rmsnorm(dtype, rows, width):
+    h = randn(rows, width, dtype=dtype, seed=1)
+    res = randn(rows, width, dtype=dtype, seed=3)
+    w = randn(width, dtype=dtype, seed=2)
+    res_ref = res.clone()
+    want = P.add_rmsnorm(h, res_ref, w, 1e-6)
+    got = K().add_rmsnorm(h, res, w, 1e-6)
+    assert torch.equal(res, res_ref)  # the sum is a single correctly rounded addition
+    torch.testing.assert_close(got, want, **tol(dtype))
+
+
+def test_rmsnorm_keeps_32bit_weight_in_bf16_model():
+    x = randn(7, 200, dtype=torch.bfloat16, seed=1)
+    w = randn(200, dtype=torch.float32, seed=2)
+    want = (w * (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5))).to(torch.bfloat16)
+    torch.testing.assert_close(K().rmsnorm(x, w, 1e-5), want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(9, 160), (64, 14336), (3, 37)])
+def test_silu_mul(dtype, rows, inter):
+    gu = randn(rows, 2 * inter, dtype=dtype, seed=4)
+    torch.testing.assert_close(K().silu_mul(gu), P.silu_mul(gu), **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (13, 200, 96), (70, 130, 257), (64, 64, 16), (3, 515, 96)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_f32(m, n, k, bias):
+    x = randn(m, k, dtype=torch.float32, seed=5)
+    w = randn(n, k, dtype=torch.float32, seed=6)
+    b = randn(n, dtype=torch.float32, seed=7) if bias else None
+    want = x.double() @ w.double().T + (b.double() if bias else 0)
+    got = K().linear(x, w, b)
+    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_f32_rows_do_not_depend_on_batch():
+    """A row's product is bit-identical whether it is computed alone or inside a larger batch."""
+    x = randn(150, 300, dtype=torch.float32, seed=8)
+    w = randn(130, 300, dtype=torch.float32, seed=9)
+    full = K().linear(x, w)
+    for rows in ([0], [149], [3, 77], list(range(64, 129))):
+        part = K().linear(x[rows].contiguous(), w)
+        assert torch.equal(part, full[rows])
+
+
+@pytest.mark.parametrize("m,n,k", [(5, 96, 64), (77, 515, 96)])
+def test_linear_bf16_and_32bit_logits(m, n, k):
+    x = randn(m, k, dtype=torch.bfloat16, seed=5)
+    w = randn(n, k, dtype=torch.bfloat16, seed=6, scale=0.1)
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(K().linear(x, w).float(), want, rtol=2e-2, atol=2e-2)
+    logits = K().linear(x, w, out_dtype=torch.float32)
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits, want, rtol=1e-3, atol=1e-3)
+
+
+def _cache_case(dtype, heads, kv_heads, dim, page_size, lens, seed=0, window=None):
+    """A batch of requests with contexts already in the cache plus new query tokens."""
+    g = torch.Generator().manual_seed(seed)
+    num_reqs = len(lens)
+    total_pages = sum(-(-(c + q) // page_size) for c, q in lens) + 1
+    perm = (torch.randperm(total_pages - 1, generator=g) + 1).tolist()  # scattered page ids
+    width = max(-(-(c + q) // page_size) for c, q in lens)
+    table = torch.zeros((num_reqs, width), dtype=torch.int32)
+    cursor = 0
+    for r, (c, q) in enumerate(lens):
+        n = -(-(c + q) // page_size)
+        table[r, :n] = torch.tensor(perm[cursor : cursor + n], dtype=torch.int32)
+        cursor += n
+    k_cache = randn(total_pages, kv_heads, page_size, dim, dtype=dtype, seed=seed + 1)
+    v_cache = randn(total_pages, kv_heads, page_size, dim, dtype=dtype, seed=seed + 2)
+    positions, req_index = [], []
+    for r, (c, q) in enumerate(lens):
+        positions += list(range(c, c + q))
+        req_index += [r] * q
+    tokens = len(positions)
+    qkv = randn(tokens, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=seed + 3)
+    return dict(
+        qkv=qkv, table=table.to(DEV), k_cache=k_cache, v_cache=v_cache,
+        positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+        req_index=torch.tensor(req_index, dtype=torch.int32, device=DEV),
+    )
+
+
+class _Ctx:
+    def __init__(self, case):
+        self.positions, self.req_index = case["positions"], case["req_index"]
+
+
+ATTN_SHAPES = [
+    # heads, kv_heads, dim, page, [(context, query), ...], window
+    (4, 2, 16, 16, [(0, 7), (20, 1), (5, 13)], None),
+    (3, 1, 32, 8, [(0, 40), (39, 1)], None),
+    (6, 3, 48, 16, [(17, 30), (0, 1), (100, 2)], None),
+    (5, 5, 80, 4, [(9, 9)], None),
+    (8, 2, 128, 16, [(300, 1), (0, 64), (129, 3)], None),
+    (4, 4, 256, 32, [(31, 34)], None),
+    (4, 2, 64, 16, [(0, 50), (70, 1), (33, 5)], 24),
+    (2, 1, 112, 16, [(40, 8)], 5),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,page,lens,window", ATTN_SHAPES)
+def test_paged_attention(dtype, heads, kv_heads, dim, page, lens, window):
+    case = _cache_case(dtype, heads, kv_heads, dim, page, lens)
+    scale = dim ** -0.5
+    got = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], _Ctx(case),
+                              heads, kv_heads, dim, scale, window)
+    want = P.paged_attention_plain(case["qkv"], case["k_cache"], case["v_cache"], case["table"],
+                                   case["positions"], case["req_index"], heads, kv_heads, dim, scale, window)
+    torch.testing.assert_close(got, want, **(dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32
+                                             else dict(rtol=2e-2, atol=2e-2)))
+    assert K().read_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_a_far_key(dtype):
+    """One key among hundreds is made to dominate: the output must be that key's value."""
+    heads, kv_heads, dim, page = 4, 2, 64, 16
+    case = _cache_case(dtype, heads, kv_heads, dim, page, [(700, 1)], seed=3)
+    far = 37  # position of the dominating key, on another page than the query
+    q = case["qkv"][:, : heads * dim].view(1, heads, dim)
+    page_id = int(case["table"][0, far // page])
+    for head in range(heads):
+        g = head // (heads // kv_heads)
+        case["k_cache"][page_id, g, far % page] = (q[0, head].float() * 4.0).to(dtype)
+    out = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], _Ctx(case),
+                              heads, kv_heads, dim, 1.0, None).view(1, heads, dim)
+    for head in range(heads):
+        g = head // (heads // kv_heads)
+        if head % (heads // kv_heads) == heads // kv_heads - 1:  # the head whose query the key copies last
+            torch.testing.assert_close(out[0, head].float(), case["v_cache"][page_id, g, far % page].float(),
+                                       rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,page", [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (32, 8, 128, 16)])
+def test_rope_kv_write(dtype, heads, kv_heads, dim, page):
+    lens = [(0, 9), (33, 1), (7, 12)]
+    case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=5)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))).float().to(DEV)
+    ref = {k: v.clone() for k, v in case.items()}
+    P.rope_kv_write(ref["qkv"], ref["positions"], ref["req_index"], inv_freq, ref["table"],
+                    ref["k_cache"], ref["v_cache"], heads, kv_heads, dim)
+    K().rope_kv_write(case["qkv"], case["positions"], case["req_index"], inv_freq, case["table"],
+                      case["k_cache"], case["v_cache"], heads, kv_heads, dim)
+    t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+    torch.testing.assert_close(case["qkv"], ref["qkv"], **t)
+    torch.testing.assert_close(case["k_cache"], ref["k_cache"], **t)
+    assert torch.equal(case["v_cache"], ref["v_cache"])
+    assert K().read_status() == 0
+
+
+def test_rope_large_positions_fp32():
+    """Angles of tens of thousands of radians keep full float accuracy."""
+    dim, heads = 64, 2
+    positions = torch.tensor([0, 1, 8191, 65535, 131071], dtype=torch.int32, device=DEV)
+    q = randn(5, heads, dim, dtype=torch.float32, seed=1)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))).float().to(DEV)
+    want = P._rotate(q.cpu(), positions.cpu(), inv_freq.cpu())
+    K().rope_inplace(q, None, positions, inv_freq)
+    torch.testing.assert_close(q.cpu(), want, rtol=1e-5, atol=2e-6)
+
+
+def test_kernels_refuse_cpu_tensors():
+    import kvcore_b200.kernels as kernels
+
+    with pytest.raises(kernels.KernelError, match="no CPU path"):
+        kernels.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5)
+    with pytest.raises(kernels.KernelError):
+        kernels.require_device("cpu")
+
+
+# ---- sampling ---------------------------------------------------------------------------------
+def _packed(rows):
+    return torch.tensor(rows, dtype=torch.float64)
+
+
+def test_sample_greedy_is_argmax_with_lowest_index():
+    logits = randn(6, 515, dtype=torch.float32, seed=11)
+    logits[2, 100] = logits[2, 400] = 50.0  # a tie: the lower index wins
+    params = _packed([[0.0, 515, 1.0, 1, 0, 0]] * 6)
+    got = K().sample(logits, params, 1e-5).cpu()
+    want = logits.argmax(dim=-1).cpu()
+    want[2] = 100
+    assert got.tolist() == want.tolist()
+
+
+def test_sample_matches_plain_noise_and_masks():
+    vocab = 301
+    logits = randn(8, vocab, dtype=torch.float32, seed=12, scale=2.0)
+    rows = [
+        [0.8, vocab, 1.0, 123, 0, 0],
+        [0.8, vocab, 1.0, 123, 0, 1],
+        [1.0, 5, 1.0, 7, 9, 3],
+        [1.3, vocab, 0.7, 7, 9, 4],
+        [0.5, 40, 0.9, 2**31 + 5, 2**31 + 1, 1000],
+        [0.0, vocab, 1.0, 1, 1, 1],
+        [2.0, 1, 1.0, 5, 5, 5],
+        [1.0, vocab, 0.05, 5, 5, 6],
+    ]
+    got = K().sample(logits, _packed(rows), 1e-5).cpu().tolist()
+    for row, (temperature, top_k, top_p, lo, hi, index) in enumerate(rows):
+        seed = int(lo) | (int(hi) << 32)
+        token, scores = P.sample_row(logits[row].cpu(), temperature, int(top_k), top_p, seed, int(index))
+        if scores is None:
+            assert got[row] == token
+            continue
+        assert torch.isfinite(scores[got[row]]), "sampled a masked token"
+        # same token, or an exact near-tie of the noisy scores (rounding of exp/log differs)
+        assert got[row] == token or abs(float(scores[got[row]] - scores[token])) < 1e-4
+    assert got[0] != got[1] or True  # different token index -> different noise (may still coincide)
+
+
+def test_sample_seeded_rows_do_not_depend_on_the_batch():
+    vocab = 1000
+    logits = randn(5, vocab, dtype=torch.float32, seed=13)
+    rows = [[0.9, vocab, 1.0, 40 + r, 1, r] for r in range(5)]
+    together = K().sample(logits, _packed(rows), 1e-5).cpu().tolist()
+    alone = [K().sample(logits[r : r + 1].contiguous(), _packed([rows[r]]), 1e-5).item() for r in range(5)]
+    assert together == alone
+    again = K().sample(logits, _packed(rows), 1e-5).cpu().tolist()
+    assert again == together
+
+
+def test_sample_follows_the_distribution():
+    vocab, draws = 16, 4000
+    base = torch.linspace(-2.0, 2.0, vocab)
+    logits = base.repeat(draws, 1).to(DEV).contiguous()
+    rows = [[1.0, vocab, 1.0, 99, 0, i] for i in range(draws)]
+    got = K().sample(logits, _packed(rows), 1e-5).cpu()
+    counts = torch.bincount(got.long(), minlength=vocab).double()
+    expected = torch.softmax(base.double(), dim=-1) * draws
+    chi2 = float(((counts - expected) ** 2 / expected).sum())
+    assert chi2 < 50.0, chi2  # 15 degrees of freedom: 50 is far in the tail

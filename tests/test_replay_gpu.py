@@ -1,0 +1,156 @@
+"""Trace replay on the GPU against the plain implementation, in 32-bit and in bfloat16:
+each request alone and whole; most of it in one step and the last 32 tokens one by one;
+portions of changing size down to two (and one) tokens; and mixed, up to four live requests
+with so few pages that pages are used again.  In 32-bit the cuttings must also agree with
+each other bit for bit, because every kernel of that path sums in an order that depends on
+the position only."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import replay_cases as rc
+
+pytestmark = pytest.mark.gpu
+
+# largest |difference| allowed, as a fraction of the largest |logit| of the request.
+# bfloat16: a faithful bfloat16 evaluation of the same formulas differs from 32-bit by about
+# 0.5% of the largest logit on these models; the bound is four times that.
+TOLERANCE = {"float32": 2e-5, "bfloat16": 2e-2}
+LENGTHS = (45, 70, 33, 101, 64, 17, 128)
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def model_case(request, tmp_path_factory):
+    name = request.param
+    config = rc.TINY_CONFIGS[name]
+    folder = tmp_path_factory.mktemp(f"model_{name}")
+    rc.write_model(folder, config, rc.TINY_SEEDS[name], "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    requests = {f"r{i}": rc.random_tokens(config["vocab_size"], n, 10 + i) for i, n in enumerate(LENGTHS)}
+    reference = {rid: plain_llama.forward_logits(config, weights, toks).numpy() for rid, toks in requests.items()}
+    return dict(name=name, config=config, folder=folder, requests=requests, reference=reference)
+
+
+def _compare(rows, reference, dtype):
+    assert rows
+    worst = 0.0
+    for (rid, pos), row in rows.items():
+        ref = reference[rid][pos]
+        assert np.isfinite(row).all(), f"non-finite logits for {rid}@{pos}"
+        err = np.abs(row - ref).max() / np.abs(reference[rid]).max()
+        if err > TOLERANCE[dtype]:
+            first = min(p for (r, p), v in rows.items() if r == rid
+                        and np.abs(v - reference[rid][p]).max() / np.abs(reference[rid]).max() > TOLERANCE[dtype])
+            raise AssertionError(f"{rid}: first wrong position {first} (error {err:.3e} at {pos})")
+        worst = max(worst, err)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuttings_match_plain_implementation(model_case, dtype, tmp_path):
+    config, requests = model_case["config"], model_case["requests"]
+    vocab = config["vocab_size"]
+    expected_rows = sum(len(t) for t in requests.values())
+    results = {}
+    traces = {
+        "whole": rc.trace_whole(requests),
+        "tail": rc.trace_decode_tail(requests, tail=32),
+        "chunks": rc.trace_chunks(requests),
+        "mixed": rc.trace_mixed(requests, max_live=4, seed=3),
+    }
+    for name, steps in traces.items():
+        out = tmp_path / name
+        peak = rc.peak_tokens(steps)
+        rc.run_inprocess(model_case["folder"], dtype, steps, out, peak)
+        rows = rc.collect(steps, out, vocab)
+        assert len(rows) == expected_rows
+        _compare(rows, model_case["reference"], dtype)
+        results[name] = rows
+    if dtype == "float32":
+        for name in ("tail", "chunks", "mixed"):
+            for key, row in results["whole"].items():
+                assert np.array_equal(row, results[name][key]), f"{name} differs from whole at {key}"
+    import kvcore_b200.kernels as K
+
+    assert K.read_status() == 0
+
+
+def test_pages_are_used_again(model_case, tmp_path):
+    """The mixed trace needs more pages over its life than the pool has."""
+    steps = rc.trace_mixed(model_case["requests"], max_live=4, seed=3)
+    peak = rc.peak_tokens(steps)
+    total = sum(-(-len(t) // 16) for t in model_case["requests"].values())
+    assert total * 16 > peak, "the trace would fit without reuse; make it longer"
+    step_function, kv = rc.run_inprocess(model_case["folder"], "float32", steps, tmp_path / "o", peak)
+    assert kv.pools[0].num_free == kv.pools[0].num_usable
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_case, dtype, tmp_path):
+    """The program itself, as a user drives it: a step, its ``done`` line, the next step."""
+    if model_case["name"] != "B":
+        pytest.skip("one configuration is enough for the subprocess run")
+    requests = dict(list(model_case["requests"].items())[:4])
+    steps = rc.trace_mixed(requests, max_live=3, seed=5)
+    steps.insert(1, {"step": 1000, "entries": [], "end": []})  # a step that brings nothing
+    out = tmp_path / "out"
+    rc.run_subprocess(model_case["folder"], dtype, steps, out, rc.peak_tokens(steps))
+    rows = rc.collect(steps, out, model_case["config"]["vocab_size"])
+    assert len(rows) == sum(len(t) for t in requests.values())
+    _compare(rows, model_case["reference"], dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_and_first_tokens(dtype, tmp_path):
+    """A prompt of two tokens, then hundreds of single-token steps across many pages; the first
+    positions (one and two keys) are compared like the rest."""
+    config = rc.TINY_CONFIGS["B"]
+    folder = tmp_path / "m"
+    rc.write_model(folder, config, 7, "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    tokens = rc.random_tokens(config["vocab_size"], 400, 21)
+    reference = {"long": plain_llama.forward_logits(config, weights, tokens).numpy()}
+    steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens[:2], "want": [0, 1]}], "end": []}]
+    for pos in range(2, len(tokens)):
+        steps.append({"step": pos, "entries": [{"id": "long", "tokens": [tokens[pos]], "want": [0]}],
+                      "end": ["long"] if pos == len(tokens) - 1 else []})
+    rc.run_inprocess(folder, dtype, steps, tmp_path / "o", 448)
+    rows = rc.collect(steps, tmp_path / "o", config["vocab_size"])
+    assert len(rows) == len(tokens)
+    _compare(rows, reference, dtype)
+
+
+def test_far_key_is_seen_through_the_cache(tmp_path):
+    """Weights made so that one far key decides the answer: with a strong o/v path a wrong or
+    missing page would change the logits far beyond rounding."""
+    config = dict(rc.TINY_CONFIGS["A"], max_position_embeddings=1024)
+    folder = tmp_path / "m"
+    from kvcore_b200.weights import random_state_dict, write_safetensors
+    import json
+
+    weights = random_state_dict(config, 3, 0.02, "float32")
+    for layer in range(config["num_hidden_layers"]):
+        # sharpen attention: larger q/k make single keys stand out among hundreds
+        weights[f"model.layers.{layer}.self_attn.q_proj.weight"] *= 12.0
+        weights[f"model.layers.{layer}.self_attn.k_proj.weight"] *= 12.0
+        weights[f"model.layers.{layer}.self_attn.v_proj.weight"] *= 4.0
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(config))
+    write_safetensors(folder / "model.safetensors", weights)
+    tokens = rc.random_tokens(config["vocab_size"], 600, 5)
+    reference = {"r": plain_llama.forward_logits(config, weights, tokens).numpy()}
+    requests = {"r": tokens}
+    for steps in (rc.trace_chunks(requests, sizes=(200, 3, 150, 2, 97)), rc.trace_decode_tail(requests, 32)):
+        out = tmp_path / f"o{len(steps)}"
+        rc.run_inprocess(folder, "float32", steps, out, 640)
+        _compare(rc.collect(steps, out, config["vocab_size"]), reference, "float32")
+
+
+def test_replay_refuses_when_pages_run_out(model_case, tmp_path):
+    tokens = model_case["requests"]["r3"]
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": tokens, "want": [0]}], "end": []}]
+    with pytest.raises(RuntimeError, match="no pages"):
+        rc.run_inprocess(model_case["folder"], "float32", steps, tmp_path / "o", 64)

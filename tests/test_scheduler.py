@@ -1,0 +1,187 @@
+"""The scheduler's decisions: portions under a token budget, running before waiting, the limit
+on partial prefills, finishing and freeing, and what happens when pages run out."""
+from __future__ import annotations
+
+import pytest
+
+from kvcore_b200.cache import CacheGroupSpec, KVManager
+from kvcore_b200.config import SchedulerConfig
+from kvcore_b200.engine.request import FinishReason, Request, RequestStatus
+from kvcore_b200.engine.scheduler import Scheduler
+from kvcore_b200.sampling import SamplingParams
+
+
+def make(num_pages=33, page_size=4, max_model_len=64, **cfg):
+    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=num_pages, page_size=page_size,
+                   max_num_seqs=cfg.get("max_num_seqs", 8), max_model_len=max_model_len)
+    return Scheduler(SchedulerConfig(**cfg), kv), kv
+
+
+def request(rid, n, max_tokens=4, **params):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, temperature=0.0, **params))
+
+
+def run_step(sched, kv, tokens=None, stop=None):
+    """schedule + pretend the model ran + update; returns (output, update)."""
+    out = sched.schedule()
+    sampled = {}
+    for rid, n in out.num_scheduled_tokens.items():
+        kv.advance(rid, n)
+        sampled[rid] = (tokens or {}).get(rid, 7)
+    return out, sched.update_from_outputs(out, sampled, stop_token_ids=stop)
+
+
+def test_chunked_prefill_then_decode_then_finish():
+    sched, kv = make(max_num_scheduled_tokens=5, max_num_seqs=4)
+    sched.add_request(request("a", 12, max_tokens=2))
+    out, upd = run_step(sched, kv)
+    assert out.scheduled_new_reqs[0].req_id == "a" and out.num_scheduled_tokens == {"a": 5}
+    assert out.scheduled_new_reqs[0].num_computed_tokens == 0
+    assert upd.step_outputs[0].sampled_token_id is None  # a middle portion samples nothing
+    out, upd = run_step(sched, kv)
+    assert out.scheduled_cached_reqs.req_ids == ("a",) and out.scheduled_cached_reqs.new_token_ids == ((6, 7, 8, 9, 10),)
+    assert out.scheduled_cached_reqs.num_computed_tokens == (5,)
+    out, upd = run_step(sched, kv)
+    assert out.num_scheduled_tokens == {"a": 2} and upd.step_outputs[0].sampled_token_id == 7
+    out, upd = run_step(sched, kv)  # decode: one token
+    assert out.num_scheduled_tokens == {"a": 1} and out.scheduled_cached_reqs.new_token_ids == ((7,),)
+    assert upd.finished_requests[0].finish_reason == FinishReason.LENGTH
+    assert upd.finished_requests[0].output_token_ids == (7, 7)
+    assert not sched.has_unfinished_requests() and kv.num_free_pages() == [32]
+    out = sched.schedule()
+    assert out.finished_req_ids == frozenset({"a"}) and out.total_num_scheduled_tokens == 0
+
+
+def test_running_requests_go_first_and_budget_is_shared():
+    sched, kv = make(max_num_scheduled_tokens=8, max_num_partial_prefills=4, max_long_partial_prefills=4)
+    sched.add_request(request("a", 3))
+    sched.add_request(request("b", 20))
+    out, _ = run_step(sched, kv)
+    assert out.num_scheduled_tokens == {"a": 3, "b": 5}
+    out, _ = run_step(sched, kv)  # a decodes (1), b takes the rest of the budget
+    assert list(out.num_scheduled_tokens.items()) == [("a", 1), ("b", 7)]
+
+
+def test_partial_prefill_limit_skips_to_a_later_request():
+    sched, kv = make(max_num_scheduled_tokens=6, max_num_partial_prefills=1)
+    sched.add_request(request("a", 10))
+    sched.add_request(request("b", 10))
+    out, _ = run_step(sched, kv)
+    assert out.num_scheduled_tokens == {"a": 6}  # one prefill at a time
+    out, _ = run_step(sched, kv)
+    assert out.num_scheduled_tokens == {"a": 4}
+    out, _ = run_step(sched, kv)  # a decodes, b may now start
+    assert out.num_scheduled_tokens == {"a": 1, "b": 5}
+    assert [r.request_id for r in sched.running] == ["a", "b"]
+
+
+def test_long_prefill_threshold_caps_a_portion():
+    sched, kv = make(max_num_scheduled_tokens=100, long_prefill_token_threshold=4, max_num_partial_prefills=2,
+                     max_long_partial_prefills=1)
+    sched.add_request(request("a", 10))
+    sched.add_request(request("b", 10))
+    sched.add_request(request("c", 2))
+    out, _ = run_step(sched, kv)
+    assert out.num_scheduled_tokens == {"a": 4, "c": 2}  # b is a second long prefill: skipped, c is short
+
+
+def test_max_num_seqs():
+    sched, kv = make(max_num_seqs=2, max_num_scheduled_tokens=100, max_num_partial_prefills=8)
+    for rid in "abc":
+        sched.add_request(request(rid, 3))
+    out, _ = run_step(sched, kv)
+    assert set(out.num_scheduled_tokens) == {"a", "b"}
+
+
+def test_stop_token_and_abort():
+    sched, kv = make(max_num_scheduled_tokens=100, max_num_partial_prefills=8)
+    sched.add_request(request("a", 3, max_tokens=10))
+    sched.add_request(request("b", 3, max_tokens=10))
+    _, upd = run_step(sched, kv, tokens={"a": 99, "b": 5}, stop={99})
+    assert [f.request_id for f in upd.finished_requests] == ["a"]
+    assert upd.finished_requests[0].finish_reason == FinishReason.STOP
+    finished = sched.finish_requests("b", RequestStatus.FINISHED_ABORTED)
+    assert finished[0].finish_reason == FinishReason.ABORT and kv.num_free_pages() == [32]
+    assert not sched.has_unfinished_requests()
+
+
+def test_admission_checks():
+    sched, kv = make(num_pages=5, page_size=4, max_model_len=32)
+    with pytest.raises(ValueError, match="never"):
+        sched.add_request(request("big", 20))
+    with pytest.raises(ValueError, match="max_model_len"):
+        sched.add_request(request("long", 32))
+    sched.add_request(request("a", 3))
+    with pytest.raises(ValueError, match="Duplicate"):
+        sched.add_request(request("a", 3))
+    with pytest.raises(ValueError):
+        Request("empty", [], SamplingParams(max_tokens=1))
+
+
+def test_generation_stops_at_max_model_len():
+    sched, kv = make(max_model_len=6, max_num_scheduled_tokens=100)
+    sched.add_request(request("a", 4, max_tokens=50))
+    reasons = []
+    while sched.has_unfinished_requests():
+        _, upd = run_step(sched, kv)
+        reasons += [f.finish_reason for f in upd.finished_requests]
+    assert reasons == [FinishReason.LENGTH]
+
+
+def test_waiting_request_waits_when_pages_run_out():
+    sched, kv = make(num_pages=6, page_size=4, max_num_scheduled_tokens=100, max_num_partial_prefills=8)
+    sched.add_request(request("a", 12, max_tokens=2))  # 3 pages (+1 for the second token)
+    sched.add_request(request("b", 12, max_tokens=2))
+    out, _ = run_step(sched, kv)
+    assert set(out.num_scheduled_tokens) == {"a"}  # b does not fit: it stays queued, untouched
+    assert [r.request_id for r in sched.waiting] == ["b"] and not kv.has_request("b")
+    run_step(sched, kv)
+    assert not kv.has_request("a")  # finished and freed
+    out, _ = run_step(sched, kv)
+    assert set(out.num_scheduled_tokens) == {"b"}  # on pages that a held before
+    kv.check_invariants()
+
+
+def test_deadlock_preempts_the_youngest_and_recomputes_it():
+    sched, kv = make(num_pages=5, page_size=4, max_num_scheduled_tokens=100, max_num_partial_prefills=8)
+    sched.add_request(request("a", 7, max_tokens=8))
+    sched.add_request(request("b", 7, max_tokens=8))
+    run_step(sched, kv)  # both prefilled: 2 pages each, pool empty; both sampled a token
+    out, _ = run_step(sched, kv)  # both fit their 8th token in the second page
+    assert set(out.num_scheduled_tokens) == {"a", "b"}
+    out, _ = run_step(sched, kv)  # token 9 needs a third page each: none free -> preempt b
+    assert out.preempted_req_ids == ("b",) and set(out.num_scheduled_tokens) == {"a"}
+    assert sched.num_preemptions == 1 and not kv.has_request("b")
+    b = sched.requests["b"]
+    assert b.status == RequestStatus.PREEMPTED and b.num_computed_tokens == 0 and b.num_output_tokens == 2
+    outputs = {}
+    guard = 0
+    while sched.has_unfinished_requests():
+        out, upd = run_step(sched, kv)
+        for new in out.scheduled_new_reqs:  # b comes back as a new request carrying all its tokens
+            assert new.req_id == "b" and len(new.prompt_token_ids) == 7 + new.num_output_tokens
+        for f in upd.finished_requests:
+            outputs[f.request_id] = f.output_token_ids
+        guard += 1
+        assert guard < 50
+        kv.check_invariants()
+    assert len(outputs["a"]) == 8 and len(outputs["b"]) == 8
+
+
+def test_no_progress_is_reported_when_preemption_is_off_or_impossible():
+    sched, kv = make(num_pages=5, page_size=4, max_num_scheduled_tokens=100, max_num_partial_prefills=8,
+                     preempt_on_deadlock=False)
+    sched.add_request(request("a", 7, max_tokens=8))
+    sched.add_request(request("b", 7, max_tokens=8))
+    run_step(sched, kv)
+    run_step(sched, kv)
+    out = sched.schedule()
+    assert out.total_num_scheduled_tokens == 0 and sched.last_no_progress_state is not None
+    assert "no progress" in sched.last_no_progress_state.format_message()
+    # a lone request that outgrows the whole pool cannot be helped by preemption either
+    sched2, kv2 = make(num_pages=3, page_size=4, max_num_scheduled_tokens=100)
+    sched2.add_request(request("a", 7, max_tokens=8))
+    run_step(sched2, kv2)
+    run_step(sched2, kv2)
+    out = sched2.schedule()
+    assert out.total_num_scheduled_tokens == 0 and sched2.last_no_progress_state.running == ("a",)
