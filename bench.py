@@ -215,7 +215,8 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
     vocab = runner.model.spec.vocab_size
     for index in range(batch):
         prompt = torch.randint(0, vocab, (context,), generator=generator).tolist()
-        engine.add_request(f"e2e-{index}", SamplingParams(max_tokens=steps + warmup + 1, temperature=0.0),
+        # requests admitted early decode while later ones still prefill: leave room for that
+        engine.add_request(f"e2e-{index}", SamplingParams(max_tokens=1_000_000, temperature=0.0),
                            prompt_token_ids=prompt)
     scheduler = engine.engine_core.scheduler
     while any(r.num_computed_tokens < r.num_prompt_tokens for r in scheduler.requests.values()):
@@ -231,6 +232,7 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - begin
     assert runner.step_function.num_steps - used_before == steps
+    assert produced == steps * batch, f"{produced} tokens from {steps} steps of {batch} requests"
     ctx = runner.step_function.last_context
     h2d = 4 * (4 * (batch + 4) + 4 * batch + batch * ctx.table_width) + batch * 6 * 8
     engine.engine_core.scheduler.shutdown()
@@ -274,7 +276,8 @@ def main() -> int:
     peaks = measured_peaks()
     numbers = model_numbers(LLAMA_31_8B, args.layers)
     max_batch = args.batch if args.skip_points else max(64, args.batch)
-    margin = args.steps + args.warmup + 8
+    prefill_steps = -(-max(args.context, PREFILL_TOKENS) // PREFILL_TOKENS)
+    margin = args.steps + args.warmup + 8 + args.batch * prefill_steps  # e2e: early requests decode during prefill
     max_len = max(args.context, PREFILL_TOKENS) + margin
     pages = max_batch * (-(-max_len // BLOCK_SIZE)) + 1
     config, runner = build_runner(args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))

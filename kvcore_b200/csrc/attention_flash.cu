@@ -1,0 +1,448 @@
+// Paged flash attention for bf16 on tensor cores (mma.sync m16n8k16, fp32 accumulate), head
+// sizes in steps of 16 up to 128.  One kernel body, two shapes:
+//
+//  * TILE mode (prompt portions, mixed batches): a block of 4 warps owns 64 query rows of one
+//    (request, kv head); a row is a (token, query head of the group) pair, so the G heads that
+//    share a kv head reuse every K/V tile.  Each warp owns 16 rows and walks all 64 keys of
+//    each K/V tile.
+//  * SPLIT mode (decode: at most 16 rows per request and kv head): the key range of a request
+//    is cut into `num_splits` contiguous chunks, one block each; inside a block the 4 warps
+//    take 16 keys each of every 64-key tile and merge their partial (max, sum, output)
+//    through shared memory.  With more than one split the block writes its partial result to
+//    scratch and a second kernel combines the splits.
+//
+// K/V tiles of 64 keys are gathered page by page through the block table with 16-byte
+// cp.async copies into padded shared-memory rows (double buffered); fragments come from
+// ldmatrix.  Scores, softmax and accumulation are 32-bit.  Keys outside the request, pages
+// that were handed back (table entry 0) and rows beyond the batch are zero-filled or masked,
+// never read as garbage.
+//
+// Cache layout [pages, KVH, page_size, D]; q rows at q + token*q_stride + head*D.
+#include "common.cuh"
+
+#define FA_KEYS 64          // keys per K/V tile
+#define FA_THREADS 128
+#define FA_PAD 8            // bf16 elements of padding per shared-memory row (16 bytes)
+
+struct FlashParams {
+  bf16* out; long long out_stride;
+  const bf16* q; long long q_stride;
+  const bf16* k_cache; const bf16* v_cache;
+  const int* table; int table_stride;
+  const int* query_start; const int* context_lens;
+  int num_reqs, H, KVH, G, page_size, num_pages, window;
+  float scale_log2;          // scale * log2(e)
+  int num_splits;
+  float* partial_o;          // [reqs, KVH, splits, 16, D]
+  float* partial_ml;         // [reqs, KVH, splits, 16, 2]
+  int* status;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// Gather one 64-key tile of K and V (keys [key0, key0+64)) into shared memory.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const FlashParams& p, const int* pages,
+                                             int kvh, int key0, int key_lo, int key_hi) {
+  constexpr int ROW = D + FA_PAD;
+  constexpr int CHUNKS = D / 8;
+  const size_t head_off = (size_t)kvh * p.page_size * D;
+  const size_t page_elems = (size_t)p.KVH * p.page_size * D;
+  for (int i = threadIdx.x; i < FA_KEYS * CHUNKS; i += FA_THREADS) {
+    const int row = i / CHUNKS, chunk = i % CHUNKS;
+    const int key = key0 + row;
+    bool valid = key >= key_lo && key < key_hi;
+    size_t off = 0;
+    if (valid) {
+      const int page = pages[key / p.page_size];
+      if (page <= 0 || page >= p.num_pages) {
+        if (page != 0) atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+        valid = false;
+      } else {
+        off = (size_t)page * page_elems + head_off + (size_t)(key % p.page_size) * D + chunk * 8;
+      }
+    }
+    cp_async16(ks + row * ROW + chunk * 8, p.k_cache + off, valid);
+    cp_async16(vs + row * ROW + chunk * 8, p.v_cache + off, valid);
+  }
+}
+
+template <int D, bool SPLIT>
+__global__ void __launch_bounds__(FA_THREADS)
+flash_paged_kernel(const FlashParams p) {
+  constexpr int ROW = D + FA_PAD;
+  constexpr int TILE_M = SPLIT ? 16 : 64;
+  constexpr int KSTEPS = D / 16;   // k-steps of Q.K^T
+  constexpr int DBLOCKS = D / 8;   // n-blocks of the output
+  constexpr int WARP_KEYS = SPLIT ? 16 : 64;   // keys of a tile one warp scores
+  constexpr int NB = WARP_KEYS / 8;            // score n-blocks per warp
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);
+  bf16* ks = qs + TILE_M * ROW;
+  bf16* vs = ks + 2 * FA_KEYS * ROW;
+
+  const int req = blockIdx.z, kvh = blockIdx.y;
+  const int tile = SPLIT ? 0 : blockIdx.x;
+  const int split = SPLIT ? blockIdx.x : 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_begin = p.query_start[req];
+  const int q_len = p.query_start[req + 1] - q_begin;
+  const int context = p.context_lens[req];
+  const int rows_total = q_len * p.G;
+  const int row0 = tile * TILE_M;
+  if (row0 >= rows_total) return;  // whole block: this request has fewer rows
+  const int* pages = p.table + (size_t)req * p.table_stride;
+
+  // rows of this block: flat row r -> token r / G, head kvh*G + r % G
+  const int last_row = min(row0 + TILE_M, rows_total) - 1;
+  const int first_pos = context + row0 / p.G;
+  const int last_pos = context + last_row / p.G;
+  int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  int key_hi = last_pos + 1;
+  if (SPLIT) {
+    const int tiles = (key_hi - (key_lo / FA_KEYS) * FA_KEYS + FA_KEYS - 1) / FA_KEYS;
+    const int per = (tiles + p.num_splits - 1) / p.num_splits;
+    const int base = (key_lo / FA_KEYS) * FA_KEYS;
+    const int lo = base + split * per * FA_KEYS;
+    const int hi = min(key_hi, lo + per * FA_KEYS);
+    key_lo = max(key_lo, lo);
+    key_hi = hi;
+  }
+  const int tile_begin = key_lo / FA_KEYS;
+  const int tile_end = key_hi > key_lo ? (key_hi + FA_KEYS - 1) / FA_KEYS : tile_begin;
+
+  // ---- Q tile into shared memory, then into A fragments --------------------------------
+  for (int i = threadIdx.x; i < TILE_M * (D / 8); i += FA_THREADS) {
+    const int r = i / (D / 8), chunk = i % (D / 8);
+    const int flat = row0 + r;
+    const bool valid = flat < rows_total;
+    const int token = q_begin + (valid ? flat / p.G : 0);
+    const int head = kvh * p.G + (valid ? flat % p.G : 0);
+    cp_async16(qs + r * ROW + chunk * 8, p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8, valid);
+  }
+  cp_async_commit();
+  if (tile_begin < tile_end)
+    load_kv_tile<D>(ks, vs, p, pages, kvh, tile_begin * FA_KEYS, key_lo, key_hi);
+  cp_async_commit();
+  cp_async_wait<1>();
+  __syncthreads();
+
+  const int wrow = SPLIT ? 0 : warp * 16;  // first row of this warp inside the block's tile
+  unsigned qf[KSTEPS][4];
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    const int r = wrow + (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int c = k * 16 + 8 * (lane >> 4);
+    ldmatrix_x4(qf[k], qs + r * ROW + c);
+  }
+  // positions of this lane's two rows (lane/4 and lane/4 + 8)
+  int row_pos[2];
+  bool row_valid[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int flat = row0 + wrow + (lane >> 2) + 8 * h;
+    row_valid[h] = flat < rows_total;
+    row_pos[h] = context + (row_valid[h] ? flat / p.G : 0);
+  }
+
+  float o[DBLOCKS][4];
+#pragma unroll
+  for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+
+  for (int t = tile_begin; t < tile_end; ++t) {
+    const int buf = (t - tile_begin) & 1;
+    bf16* kt = ks + buf * FA_KEYS * ROW;
+    bf16* vt = vs + buf * FA_KEYS * ROW;
+    if (t + 1 < tile_end)
+      load_kv_tile<D>(ks + (buf ^ 1) * FA_KEYS * ROW, vs + (buf ^ 1) * FA_KEYS * ROW, p, pages, kvh,
+                      (t + 1) * FA_KEYS, key_lo, key_hi);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const int wkey = SPLIT ? warp * 16 : 0;  // first key of the tile this warp scores
+    float s[NB][4];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+      for (int j = 0; j < NB; j += 2) {
+        unsigned kb[4];
+        const int key = wkey + j * 8 + (lane & 7) + 8 * (lane >> 4);
+        const int c = k * 16 + 8 * ((lane >> 3) & 1);
+        ldmatrix_x4(kb, kt + key * ROW + c);
+        mma_bf16(s[j], qf[k], kb[0], kb[1]);
+        mma_bf16(s[j + 1], qf[k], kb[2], kb[3]);
+      }
+    }
+    // mask and online softmax (base-2 exponent)
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = t * FA_KEYS + wkey + j * 8 + (lane & 3) * 2 + (e & 1);
+        const bool seen = row_valid[h] && key >= key_lo && key < key_hi && key <= row_pos[h] &&
+                          (p.window <= 0 || key > row_pos[h] - p.window);
+        const float v = seen ? s[j][e] * p.scale_log2 : -INFINITY;
+        s[j][e] = v;
+        tile_max[h] = fmaxf(tile_max[h], v);
+      }
+    }
+    float correction[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float m = tile_max[h];
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      const float new_max = fmaxf(row_max[h], m);
+      correction[h] = (row_max[h] == -INFINITY) ? 0.0f : exp2f(row_max[h] - new_max);
+      row_max[h] = new_max;
+      row_sum[h] *= correction[h];
+    }
+#pragma unroll
+    for (int j = 0; j < DBLOCKS; ++j) {
+      o[j][0] *= correction[0]; o[j][1] *= correction[0];
+      o[j][2] *= correction[1]; o[j][3] *= correction[1];
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const float pv = (s[j][e] == -INFINITY) ? 0.0f : exp2f(s[j][e] - row_max[h]);
+        s[j][e] = pv;
+        row_sum[h] += pv;
+      }
+    }
+    // O += P V over this warp's keys, 16 keys per step
+#pragma unroll
+    for (int kk = 0; kk < NB / 2; ++kk) {
+      unsigned pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int j = 0; j < DBLOCKS; j += 2) {
+        unsigned vb[4];
+        const int key = wkey + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int c = j * 8 + 8 * (lane >> 4);
+        ldmatrix_x4_trans(vb, vt + key * ROW + c);
+        mma_bf16(o[j], pa, vb[0], vb[1]);
+        mma_bf16(o[j + 1], pa, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();  // everyone is done with this buffer before it is refilled
+  }
+  cp_async_wait<0>();
+
+  // row sums live spread over the 4 lanes of a quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+  }
+
+  if (!SPLIT) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!row_valid[h]) continue;
+      const int flat = row0 + wrow + (lane >> 2) + 8 * h;
+      const int token = q_begin + flat / p.G;
+      const int head = kvh * p.G + flat % p.G;
+      const float inv = row_sum[h] > 0.0f ? 1.0f / row_sum[h] : 0.0f;
+      bf16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * D + (lane & 3) * 2;
+#pragma unroll
+      for (int j = 0; j < DBLOCKS; ++j)
+        *reinterpret_cast<unsigned*>(dst + j * 8) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+    }
+    return;
+  }
+
+  // ---- SPLIT: merge the four warps (each saw other keys of the same 16 rows) -------------
+  __syncthreads();
+  float* merge_o = reinterpret_cast<float*>(ks);            // [4 warps][16 rows][D]
+  float* merge_ml = merge_o + 4 * 16 * D;                   // [4 warps][16 rows][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+    for (int j = 0; j < DBLOCKS; ++j) {
+      float* dst = merge_o + ((size_t)(warp * 16 + r)) * D + j * 8 + (lane & 3) * 2;
+      dst[0] = o[j][2 * h];
+      dst[1] = o[j][2 * h + 1];
+    }
+    if ((lane & 3) == 0) {
+      merge_ml[(warp * 16 + r) * 2 + 0] = row_max[h];
+      merge_ml[(warp * 16 + r) * 2 + 1] = row_sum[h];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 16 * D; i += FA_THREADS) {
+    const int r = i / D, d = i % D;
+    if (r >= rows_total) continue;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    float total = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = merge_ml[(w * 16 + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+      total += merge_ml[(w * 16 + r) * 2 + 1] * f;
+      acc += merge_o[((size_t)(w * 16 + r)) * D + d] * f;
+    }
+    if (p.num_splits == 1) {
+      const int token = q_begin + r / p.G;
+      const int head = kvh * p.G + r % p.G;
+      p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+          __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+    } else {
+      const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
+      p.partial_o[(slot * 16 + r) * D + d] = acc;
+      if (d == 0) {
+        p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
+        p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
+      }
+    }
+  }
+}
+
+// Merge the splits of every (request, kv head, row): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+template <int D>
+__global__ void flash_combine_kernel(const FlashParams p) {
+  const int req = blockIdx.y, kvh = blockIdx.x;
+  const int q_begin = p.query_start[req];
+  const int rows_total = (p.query_start[req + 1] - q_begin) * p.G;
+  const size_t base = ((size_t)req * p.KVH + kvh) * p.num_splits;
+  for (int i = threadIdx.x; i < 16 * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    if (r >= rows_total) continue;
+    float m = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.partial_ml[((base + s) * 16 + r) * 2]);
+    float total = 0.0f, acc = 0.0f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float ms = p.partial_ml[((base + s) * 16 + r) * 2];
+      const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
+      total += p.partial_ml[((base + s) * 16 + r) * 2 + 1] * f;
+      acc += p.partial_o[((base + s) * 16 + r) * D + d] * f;
+    }
+    const int token = q_begin + r / p.G;
+    const int head = kvh * p.G + r % p.G;
+    p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+        __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+  }
+}
+
+template <int D>
+static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cudaStream_t stream) {
+  constexpr int ROW = D + FA_PAD;
+  if (split_mode) {
+    size_t smem = (size_t)(16 + 4 * FA_KEYS) * ROW * sizeof(bf16);
+    const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+    if (smem < 16 * ROW * sizeof(bf16) + merge) smem = 16 * ROW * sizeof(bf16) + merge;
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, true>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(p.num_splits, p.KVH, p.num_reqs);
+    flash_paged_kernel<D, true><<<grid, FA_THREADS, smem, stream>>>(p);
+    KVB_CHECK_LAUNCH();
+    if (p.num_splits > 1) {
+      dim3 cgrid(p.KVH, p.num_reqs);
+      flash_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
+      KVB_CHECK_LAUNCH();
+    }
+  } else {
+    const size_t smem = (size_t)(64 + 4 * FA_KEYS) * ROW * sizeof(bf16);
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((max_rows + 63) / 64, p.KVH, p.num_reqs);
+    flash_paged_kernel<D, false><<<grid, FA_THREADS, smem, stream>>>(p);
+    KVB_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+// Scratch floats needed for `num_splits` splits: partial outputs then partial (max, sum).
+extern "C" long long kvb_flash_scratch_floats(int num_reqs, int KVH, int num_splits, int D) {
+  if (num_splits <= 1) return 0;
+  return (long long)num_reqs * KVH * num_splits * 16 * (D + 2);
+}
+
+// max_query_len: the longest portion in the batch.  split mode is used when every request has
+// at most 16 (token, head) rows per kv head; otherwise num_splits must be 1.
+extern "C" int kvb_flash_paged_attention(void* out, long long out_stride, const void* q,
+                                         long long q_stride, const void* k_cache, const void* v_cache,
+                                         const int* table, int table_stride, const int* query_start,
+                                         const int* context_lens, int num_reqs, int max_query_len,
+                                         int H, int KVH, int D, int page_size, int num_pages,
+                                         float scale, int window, int num_splits, float* scratch,
+                                         cudaStream_t stream) {
+  if (num_reqs == 0) return 0;
+  KVB_REQUIRE(D % 16 == 0 && D >= 16 && D <= 128, "flash attention: head_dim must be a multiple of 16 up to 128");
+  KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "flash attention: H must be a multiple of KVH");
+  KVB_REQUIRE(page_size > 0 && num_pages > 1, "flash attention: empty cache");
+  KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "flash attention: batch too large for one launch");
+  KVB_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && (q_stride % 8) == 0,
+              "flash attention: q and the caches must be 16-byte aligned");
+  FlashParams p;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.table = table; p.table_stride = table_stride;
+  p.query_start = query_start; p.context_lens = context_lens;
+  p.num_reqs = num_reqs; p.H = H; p.KVH = KVH; p.G = H / KVH;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = kvb_status_word();
+  KVB_REQUIRE(p.status != nullptr, "flash attention: no status word");
+  const int max_rows = max_query_len * p.G;
+  const bool split_mode = max_rows <= 16;
+  KVB_REQUIRE(split_mode || num_splits <= 1, "flash attention: splits need at most 16 rows per kv head");
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  KVB_REQUIRE(p.num_splits == 1 || scratch != nullptr, "flash attention: splits need scratch memory");
+  p.partial_o = scratch;
+  p.partial_ml = scratch ? scratch + (size_t)num_reqs * KVH * p.num_splits * 16 * D : nullptr;
+  switch (D) {
+    case 16: return launch_flash<16>(p, split_mode, max_rows, stream);
+    case 32: return launch_flash<32>(p, split_mode, max_rows, stream);
+    case 48: return launch_flash<48>(p, split_mode, max_rows, stream);
+    case 64: return launch_flash<64>(p, split_mode, max_rows, stream);
+    case 80: return launch_flash<80>(p, split_mode, max_rows, stream);
+    case 96: return launch_flash<96>(p, split_mode, max_rows, stream);
+    case 112: return launch_flash<112>(p, split_mode, max_rows, stream);
+    case 128: return launch_flash<128>(p, split_mode, max_rows, stream);
+  }
+  return kvb_fail(-1, "flash attention: unsupported head_dim", __FILE__, __LINE__);
+}

@@ -2,11 +2,14 @@
 
 Parts call these through ``kvcore_b200.kernels.<name>`` at call time.
 """
+from . import api
 from .api import (
     KernelError,
     add_rmsnorm,
     check_attention_shape,
+    decode_splits,
     ensure_built,
+    flash_attention_supported,
     gather_rows,
     library_is_loaded,
     linear,
@@ -24,7 +27,9 @@ __all__ = [
     "KernelError",
     "add_rmsnorm",
     "check_attention_shape",
+    "decode_splits",
     "ensure_built",
+    "flash_attention_supported",
     "gather_rows",
     "library_is_loaded",
     "linear",

@@ -44,6 +44,8 @@ def ensure_built(verbose: bool = False) -> str:
                               _int, _int, _int, _vp],
         "kvb_paged_attention_rows": [_vp, _int, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int,
                                      _int, _int, _int, _int, _float, _int, _int, _vp],
+        "kvb_flash_paged_attention": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int,
+                                      _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
@@ -250,6 +252,23 @@ def rope_inplace(q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tenso
               _dtype_code(x), _stream())
 
 
+SM_COUNT = 148  # B200
+_FLASH_CTAS_PER_SM = 3
+
+
+def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether the tensor-core kernel takes this shape (else the general kernel runs)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
+    """How many chunks each request's keys are cut into so that the GPU is filled."""
+    blocks = max(1, num_reqs * num_kv_heads)
+    wanted = -(-SM_COUNT * _FLASH_CTAS_PER_SM // blocks)
+    longest = max(1, -(-max_seq_len // 256))  # a split of fewer than 256 keys is not worth a block
+    return max(1, min(wanted, longest, 64))
+
+
 def paged_attention(
     qkv: torch.Tensor,
     k_cache: torch.Tensor,
@@ -261,12 +280,18 @@ def paged_attention(
     head_dim: int,
     scale: float,
     window: int | None,
+    *,
+    force_general: bool = False,
+    num_splits: int | None = None,
 ) -> torch.Tensor:
     """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
 
-    Returns ``[T, H*D]``.  ``ctx`` gives positions and request rows of the tokens.
+    Returns ``[T, H*D]``.  ``ctx`` describes the batch: positions and request rows of the
+    tokens, and per request its query start and cached length.  bfloat16 with a head size in
+    steps of 16 up to 128 runs on the tensor-core kernel (split over the keys for decode
+    batches); everything else, and all of float32, runs on the general kernel.
     """
-    _check(qkv, "qkv")
+    _check(qkv, "qkv", contiguous=False)
     _check(k_cache, "k_cache", dtype=qkv.dtype)
     _check(v_cache, "v_cache", dtype=qkv.dtype)
     _check(table, "block table", dtype=torch.int32, contiguous=False)
@@ -275,6 +300,22 @@ def paged_attention(
     if (kvh, d) != (num_kv_heads, head_dim):
         raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match the head layout")
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0:
+        group = num_heads // num_kv_heads
+        split_mode = ctx.max_query_len * group <= 16
+        splits = 1
+        if split_mode:
+            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, ctx.max_seq_len)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
+                                  dtype=torch.float32, device=qkv.device)
+        _call("kvb_flash_paged_attention", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+              k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
+              ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+              num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
+              splits, None if scratch is None else scratch.data_ptr(), _stream())
+        return out
     _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
           ctx.positions.data_ptr(), ctx.req_index.data_ptr(), tokens, num_heads, num_kv_heads,
@@ -345,6 +386,8 @@ __all__ = [
     "add_rmsnorm",
     "check_attention_shape",
     "ensure_built",
+    "decode_splits",
+    "flash_attention_supported",
     "gather_rows",
     "library_is_loaded",
     "linear",

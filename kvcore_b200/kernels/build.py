@@ -149,7 +149,7 @@ def build(verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
             objects = list(pool.map(_compile, files))
         library = target_dir / (_LIB_PREFIX + tag + ".so")
         partial = target_dir / (_LIB_PREFIX + tag + f".{os.getpid()}.tmp")
-        _run([nvcc, "-shared", "-o", str(partial), *map(str, objects)], "link", verbose)
+        _run([nvcc, "-Wno-deprecated-gpu-targets", "-shared", "-o", str(partial), *map(str, objects)], "link", verbose)
         os.replace(partial, library)
         for stale in target_dir.glob(_LIB_PREFIX + "*.so"):
             if stale != library:

@@ -87,7 +87,8 @@ def rope_kv_write(qkv, positions, req_index, inv_freq, table, k_cache, v_cache,
             v_cache[page, :, pos % page_size, :] = v[t]
 
 
-def paged_attention(qkv, k_cache, v_cache, table, ctx, num_heads, num_kv_heads, head_dim, scale, window):
+def paged_attention(qkv, k_cache, v_cache, table, ctx, num_heads, num_kv_heads, head_dim, scale, window,
+                    *, force_general=False, num_splits=None):
     return paged_attention_plain(qkv, k_cache, v_cache, table, ctx.positions, ctx.req_index,
                                  num_heads, num_kv_heads, head_dim, scale, window)
 

@@ -138,16 +138,26 @@ def _cache_case(dtype, heads, kv_heads, dim, page_size, lens, seed=0, window=Non
         req_index += [r] * q
     tokens = len(positions)
     qkv = randn(tokens, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=seed + 3)
+    starts = [0]
+    for _, q in lens:
+        starts.append(starts[-1] + q)
     return dict(
         qkv=qkv, table=table.to(DEV), k_cache=k_cache, v_cache=v_cache,
         positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
         req_index=torch.tensor(req_index, dtype=torch.int32, device=DEV),
+        query_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
+        context_lens=torch.tensor([c for c, _ in lens], dtype=torch.int32, device=DEV),
+        lens=lens,
     )
 
 
 class _Ctx:
     def __init__(self, case):
         self.positions, self.req_index = case["positions"], case["req_index"]
+        self.query_start, self.context_lens = case["query_start"], case["context_lens"]
+        self.num_reqs = len(case["lens"])
+        self.max_query_len = max(q for _, q in case["lens"])
+        self.max_seq_len = max(c + q for c, q in case["lens"])
 
 
 ATTN_SHAPES = [
@@ -175,6 +185,64 @@ def test_paged_attention(dtype, heads, kv_heads, dim, page, lens, window):
     torch.testing.assert_close(got, want, **(dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32
                                              else dict(rtol=2e-2, atol=2e-2)))
     assert K().read_status() == 0
+
+
+FLASH_SHAPES = [
+    # heads, kv_heads, dim, page, [(context, query), ...], window, forced splits
+    (32, 8, 128, 16, [(1000, 1), (17, 1), (4095, 1), (0, 1)], None, None),   # decode, split by the policy
+    (32, 8, 128, 16, [(1000, 1), (17, 1), (300, 1)], None, 1),
+    (32, 8, 128, 16, [(1000, 1), (17, 1), (300, 1)], None, 7),
+    (32, 8, 128, 16, [(700, 4), (0, 2), (63, 3)], None, 3),                  # short portions ride the split kernel
+    (8, 2, 64, 16, [(0, 200), (130, 77), (500, 1), (64, 64)], None, None),   # tiles, mixed with a decode
+    (6, 2, 96, 8, [(5, 150), (0, 3)], None, None),                           # 3 heads a group: tokens straddle tiles
+    (3, 1, 32, 8, [(0, 40), (39, 1)], None, None),
+    (5, 5, 80, 4, [(9, 9), (100, 30)], None, None),
+    (4, 4, 16, 32, [(31, 34), (0, 1)], None, None),
+    (14, 2, 112, 16, [(40, 70)], None, None),
+    (6, 3, 48, 16, [(17, 30), (0, 1), (100, 2)], None, None),
+    (4, 2, 64, 16, [(0, 150), (170, 1), (33, 5)], 24, None),                 # window
+    (8, 2, 128, 16, [(900, 1), (70, 1)], 100, 4),                            # window, decode, forced splits
+]
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page,lens,window,splits", FLASH_SHAPES)
+def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits):
+    """The tensor-core kernel (tile and split shapes) against the plain statement and the general kernel."""
+    dtype = torch.bfloat16
+    case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=7)
+    # pages the batch does not own hold NaN: reading one shows up in the output
+    owned = set(case["table"].flatten().tolist())
+    for page_id in range(case["k_cache"].shape[0]):
+        if page_id not in owned:
+            case["k_cache"][page_id] = float("nan")
+            case["v_cache"][page_id] = float("nan")
+    # so do slots of owned pages beyond each request's length
+    for r, (c, q) in enumerate(lens):
+        end = c + q
+        last_page = int(case["table"][r, (end - 1) // page])
+        if end % page:
+            case["k_cache"][last_page, :, end % page:] = float("nan")
+            case["v_cache"][last_page, :, end % page:] = float("nan")
+    scale = dim ** -0.5
+    ctx = _Ctx(case)
+    assert K().flash_attention_supported(dtype, dim)
+    got = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                              heads, kv_heads, dim, scale, window, num_splits=splits)
+    general = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                                  heads, kv_heads, dim, scale, window, force_general=True)
+    want = P.paged_attention_plain(case["qkv"], case["k_cache"], case["v_cache"], case["table"],
+                                   case["positions"], case["req_index"], heads, kv_heads, dim, scale, window)
+    assert torch.isfinite(got.float()).all()
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.float(), general.float(), rtol=2e-2, atol=2e-2)
+    assert K().read_status() == 0
+
+
+def test_flash_split_policy():
+    assert K().decode_splits(64, 8, 8192) == 1
+    assert K().decode_splits(8, 8, 8192) == 7
+    assert K().decode_splits(1, 8, 8192) == 32
+    assert K().decode_splits(1, 8, 100) == 1
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
