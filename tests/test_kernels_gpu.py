@@ -271,7 +271,7 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim, page):
     lens = [(0, 9), (33, 1), (7, 12)]
     case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=5)
     inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))).float().to(DEV)
-    ref = {k: v.clone() for k, v in case.items()}
+    ref = {k: v.clone() for k, v in case.items() if torch.is_tensor(v)}
     P.rope_kv_write(ref["qkv"], ref["positions"], ref["req_index"], inv_freq, ref["table"],
                     ref["k_cache"], ref["v_cache"], heads, kv_heads, dim)
     K().rope_kv_write(case["qkv"], case["positions"], case["req_index"], inv_freq, case["table"],
