@@ -36,12 +36,14 @@ class ModelConfig:
 
     ``model`` is a folder holding config.json and safetensors weights.  ``dtype`` selects
     the kernel family: "bfloat16" (serving precision) or "float32" (true 32-bit everywhere).
-    ``None`` takes the dtype named in config.json, else bfloat16.
+    ``None`` takes the dtype named in config.json, else bfloat16.  ``enforce_eager`` turns off
+    the CUDA graphs that decode-only steps otherwise replay.
     """
 
     model: str | Path
     dtype: str | None = None
     max_model_len: int | None = None
+    enforce_eager: bool = False
 
     def __post_init__(self) -> None:
         if self.max_model_len is not None and self.max_model_len <= 0:

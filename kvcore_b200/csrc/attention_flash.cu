@@ -67,28 +67,37 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const unsigned*>(&v);
 }
 
-// Gather one 64-key tile of K and V (keys [key0, key0+64)) into shared memory.
+// Element offset of every key row of a 64-key tile inside the cache (or -1: zero-fill), looked
+// up through the block table by the first 64 threads, one row each, so that the lookups of a
+// tile run in parallel and one tile ahead of the copies that use them.
 template <int D>
-__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const FlashParams& p, const int* pages,
-                                             int kvh, int key0, int key_lo, int key_hi) {
+__device__ __forceinline__ void lookup_tile_rows(long long* rows, const FlashParams& p, const int* pages,
+                                                 int kvh, int key0, int key_lo, int key_hi) {
+  if (threadIdx.x >= FA_KEYS) return;
+  const int key = key0 + threadIdx.x;
+  long long off = -1;
+  if (key >= key_lo && key < key_hi) {
+    const int page = pages[key / p.page_size];
+    if (page > 0 && page < p.num_pages)
+      off = ((long long)page * p.KVH + kvh) * p.page_size * D + (long long)(key % p.page_size) * D;
+    else if (page != 0)
+      atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+  }
+  rows[threadIdx.x] = off;
+}
+
+// Copy one 64-key tile of K and V into shared memory, 16 bytes per cp.async.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const FlashParams& p,
+                                             const long long* rows) {
   constexpr int ROW = D + FA_PAD;
   constexpr int CHUNKS = D / 8;
-  const size_t head_off = (size_t)kvh * p.page_size * D;
-  const size_t page_elems = (size_t)p.KVH * p.page_size * D;
+#pragma unroll 4
   for (int i = threadIdx.x; i < FA_KEYS * CHUNKS; i += FA_THREADS) {
     const int row = i / CHUNKS, chunk = i % CHUNKS;
-    const int key = key0 + row;
-    bool valid = key >= key_lo && key < key_hi;
-    size_t off = 0;
-    if (valid) {
-      const int page = pages[key / p.page_size];
-      if (page <= 0 || page >= p.num_pages) {
-        if (page != 0) atomicOr(p.status, KVB_STATUS_BAD_PAGE);
-        valid = false;
-      } else {
-        off = (size_t)page * page_elems + head_off + (size_t)(key % p.page_size) * D + chunk * 8;
-      }
-    }
+    const long long base = rows[row];
+    const bool valid = base >= 0;
+    const long long off = valid ? base + chunk * 8 : 0;
     cp_async16(ks + row * ROW + chunk * 8, p.k_cache + off, valid);
     cp_async16(vs + row * ROW + chunk * 8, p.v_cache + off, valid);
   }
@@ -105,7 +114,8 @@ flash_paged_kernel(const FlashParams p) {
   constexpr int NB = WARP_KEYS / 8;            // score n-blocks per warp
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);
+  long long* tile_rows = reinterpret_cast<long long*>(smem_raw);  // [2][FA_KEYS] row offsets
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw + 2 * FA_KEYS * sizeof(long long));
   bf16* ks = qs + TILE_M * ROW;
   bf16* vs = ks + 2 * FA_KEYS * ROW;
 
@@ -149,8 +159,13 @@ flash_paged_kernel(const FlashParams p) {
     cp_async16(qs + r * ROW + chunk * 8, p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8, valid);
   }
   cp_async_commit();
-  if (tile_begin < tile_end)
-    load_kv_tile<D>(ks, vs, p, pages, kvh, tile_begin * FA_KEYS, key_lo, key_hi);
+  if (tile_begin < tile_end) {
+    lookup_tile_rows<D>(tile_rows, p, pages, kvh, tile_begin * FA_KEYS, key_lo, key_hi);
+    if (tile_begin + 1 < tile_end)
+      lookup_tile_rows<D>(tile_rows + FA_KEYS, p, pages, kvh, (tile_begin + 1) * FA_KEYS, key_lo, key_hi);
+    __syncthreads();
+    load_kv_tile<D>(ks, vs, p, tile_rows);
+  }
   cp_async_commit();
   cp_async_wait<1>();
   __syncthreads();
@@ -183,11 +198,13 @@ flash_paged_kernel(const FlashParams p) {
     bf16* kt = ks + buf * FA_KEYS * ROW;
     bf16* vt = vs + buf * FA_KEYS * ROW;
     if (t + 1 < tile_end)
-      load_kv_tile<D>(ks + (buf ^ 1) * FA_KEYS * ROW, vs + (buf ^ 1) * FA_KEYS * ROW, p, pages, kvh,
-                      (t + 1) * FA_KEYS, key_lo, key_hi);
+      load_kv_tile<D>(ks + (buf ^ 1) * FA_KEYS * ROW, vs + (buf ^ 1) * FA_KEYS * ROW, p,
+                      tile_rows + (buf ^ 1) * FA_KEYS);
     cp_async_commit();
     cp_async_wait<1>();
-    __syncthreads();
+    __syncthreads();  // tile t has landed; the row offsets of tile t (slot buf) are spent
+    if (t + 2 < tile_end)  // offsets of tile t+2 go to slot buf; published by the barrier that ends this turn
+      lookup_tile_rows<D>(tile_rows + buf * FA_KEYS, p, pages, kvh, (t + 2) * FA_KEYS, key_lo, key_hi);
 
     const int wkey = SPLIT ? warp * 16 : 0;  // first key of the tile this warp scores
     float s[NB][4];
@@ -341,52 +358,62 @@ flash_paged_kernel(const FlashParams p) {
 }
 
 // Merge the splits of every (request, kv head, row): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// One thread per output element; grid.x covers the 16 rows x D elements of a (request, kv head).
 template <int D>
 __global__ void flash_combine_kernel(const FlashParams p) {
-  const int req = blockIdx.y, kvh = blockIdx.x;
+  const int req = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.query_start[req];
   const int rows_total = (p.query_start[req + 1] - q_begin) * p.G;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = i / D, d = i % D;
+  if (r >= rows_total || r >= 16) return;
   const size_t base = ((size_t)req * p.KVH + kvh) * p.num_splits;
-  for (int i = threadIdx.x; i < 16 * D; i += blockDim.x) {
-    const int r = i / D, d = i % D;
-    if (r >= rows_total) continue;
-    float m = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.partial_ml[((base + s) * 16 + r) * 2]);
-    float total = 0.0f, acc = 0.0f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float ms = p.partial_ml[((base + s) * 16 + r) * 2];
-      const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
-      total += p.partial_ml[((base + s) * 16 + r) * 2 + 1] * f;
-      acc += p.partial_o[((base + s) * 16 + r) * D + d] * f;
-    }
-    const int token = q_begin + r / p.G;
-    const int head = kvh * p.G + r % p.G;
-    p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
-        __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+  float m = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.partial_ml[((base + s) * 16 + r) * 2]);
+  float total = 0.0f, acc = 0.0f;
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float ms = p.partial_ml[((base + s) * 16 + r) * 2];
+    const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
+    total += p.partial_ml[((base + s) * 16 + r) * 2 + 1] * f;
+    acc += p.partial_o[((base + s) * 16 + r) * D + d] * f;
   }
+  const int token = q_begin + r / p.G;
+  const int head = kvh * p.G + r % p.G;
+  p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+      __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
 }
 
 template <int D>
 static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cudaStream_t stream) {
   constexpr int ROW = D + FA_PAD;
   if (split_mode) {
-    size_t smem = (size_t)(16 + 4 * FA_KEYS) * ROW * sizeof(bf16);
+    const size_t rows_bytes = 2 * FA_KEYS * sizeof(long long);
+    size_t smem = rows_bytes + (size_t)(16 + 4 * FA_KEYS) * ROW * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
-    if (smem < 16 * ROW * sizeof(bf16) + merge) smem = 16 * ROW * sizeof(bf16) + merge;
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, true>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem < rows_bytes + 16 * ROW * sizeof(bf16) + merge) smem = rows_bytes + 16 * ROW * sizeof(bf16) + merge;
+    static bool configured_split = false;  // set once (the first call is never inside a graph capture)
+    if (!configured_split) {
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured_split = true;
+    }
     dim3 grid(p.num_splits, p.KVH, p.num_reqs);
     flash_paged_kernel<D, true><<<grid, FA_THREADS, smem, stream>>>(p);
     KVB_CHECK_LAUNCH();
     if (p.num_splits > 1) {
-      dim3 cgrid(p.KVH, p.num_reqs);
+      const int rows = max_rows < 16 ? max_rows : 16;
+      dim3 cgrid((rows * D + 127) / 128, p.KVH, p.num_reqs);
       flash_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
       KVB_CHECK_LAUNCH();
     }
   } else {
-    const size_t smem = (size_t)(64 + 4 * FA_KEYS) * ROW * sizeof(bf16);
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const size_t smem = 2 * FA_KEYS * sizeof(long long) + (size_t)(64 + 4 * FA_KEYS) * ROW * sizeof(bf16);
+    static bool configured_tile = false;
+    if (!configured_tile) {
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured_tile = true;
+    }
     dim3 grid((max_rows + 63) / 64, p.KVH, p.num_reqs);
     flash_paged_kernel<D, false><<<grid, FA_THREADS, smem, stream>>>(p);
     KVB_CHECK_LAUNCH();

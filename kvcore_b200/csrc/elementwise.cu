@@ -200,24 +200,49 @@ extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter,
 }
 
 // ------------------------------------------------------------------------------------------
+// cos/sin of every (token, frequency) of the step: table[t, j] = (cos, sin)(float(pos_t) * inv_freq[j]).
+// Computed once per step and shared by all layers with the same frequency table.
+// ------------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int tokens, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * half) return;
+  const int t = i / half, j = i % half;
+  float s, c;
+  sincosf((float)positions[t] * inv_freq[j], &s, &c);
+  table[i] = make_float2(c, s);
+}
+
+extern "C" int kvb_rope_table(float* table, const int* positions, const float* inv_freq, int tokens,
+                              int half, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  KVB_REQUIRE(half > 0, "rope_table: head_dim must be positive");
+  const long long total = (long long)tokens * half;
+  rope_table_kernel<<<(int)((total + 255) / 256), 256, 0, stream>>>((float2*)table, positions, inv_freq,
+                                                                    tokens, half);
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
 // Rotary encoding of q and k (half-rotation layout) fused with the write of k and v into the
 // paged cache.  qkv is [T, (H + 2*KVH) * D]: q heads, then k heads, then v heads.
-//   angle = float(position) * inv_freq[j]  (32-bit), j in [0, D/2)
-//   x'[j] = x[j]*cos - x[j+D/2]*sin ;  x'[j+D/2] = x[j+D/2]*cos + x[j]*sin
+//   (c, s) = cos_sin[token, j]   (32-bit, from rope_table_kernel), j in [0, D/2)
+//   x'[j] = x[j]*c - x[j+D/2]*s ;  x'[j+D/2] = x[j+D/2]*c + x[j]*s
 // q and k are rotated in place; rotated k and v go to page table[req, pos / page] at offset
-// pos % page of a cache laid out [pages, KVH, page, D].  inv_freq == nullptr: no rotation.
+// pos % page of a cache laid out [pages, KVH, page, D].  cos_sin == nullptr: no rotation.
 // k_cache == nullptr: nothing is written (an entry that reads another entry's cache).
-// One block per token: threadIdx.x = j, threadIdx.y strides over heads.
+// grid (tokens, head groups): threadIdx.x = j, threadIdx.y = head within the group; the
+// blocks of a token share the copy of its v heads.
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
                                      const int* __restrict__ positions,
                                      const int* __restrict__ req_index,
-                                     const float* __restrict__ inv_freq,
+                                     const float2* __restrict__ cos_sin,
                                      const int* __restrict__ table, int table_stride,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int KVH,
-                                     int D, int page_size, int num_pages, int rotate_k,
-                                     int* status) {
+                                     int D, int page_size, int num_pages, int* status) {
   const int token = blockIdx.x;
   const int half = D >> 1;
   const int pos = positions[token];
@@ -228,7 +253,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
   if (write) {
     const int page = table[(size_t)req_index[token] * table_stride + pos / page_size];
     if (page <= 0 || page >= num_pages) {
-      if (threadIdx.x == 0 && threadIdx.y == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      if (threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.y == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
       write = false;
     }
     cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
@@ -236,44 +261,41 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
   const size_t head_stride = (size_t)page_size * D;  // between kv heads inside a page
 
   const int j = threadIdx.x;
-  if (j < half) {
-    float c = 1.0f, s = 0.0f;
-    if (inv_freq != nullptr) sincosf((float)pos * inv_freq[j], &s, &c);
-    const int rotated_heads = H + KVH;
-    for (int head = threadIdx.y; head < rotated_heads; head += blockDim.y) {
-      T* x = row + (size_t)head * D;
-      float a = to_float(x[j]), b = to_float(x[j + half]);
-      if (inv_freq != nullptr && (head < H || rotate_k)) {
-        const float ra = a * c - b * s;
-        const float rb = b * c + a * s;
-        a = to_float(from_float<T>(ra));
-        b = to_float(from_float<T>(rb));
-        x[j] = from_float<T>(ra);
-        x[j + half] = from_float<T>(rb);
-      }
-      if (head >= H && write) {
-        T* dst = k_cache + cache_base + (size_t)(head - H) * head_stride;
-        dst[j] = from_float<T>(a);
-        dst[j + half] = from_float<T>(b);
-      }
+  const int head = blockIdx.y * blockDim.y + threadIdx.y;
+  if (j < half && head < H + KVH) {
+    T* x = row + (size_t)head * D;
+    float a = to_float(x[j]), b = to_float(x[j + half]);
+    if (cos_sin != nullptr) {
+      const float2 cs = cos_sin[(size_t)token * half + j];
+      const float ra = a * cs.x - b * cs.y;
+      const float rb = b * cs.x + a * cs.y;
+      x[j] = from_float<T>(ra);
+      x[j + half] = from_float<T>(rb);
+      a = to_float(from_float<T>(ra));
+      b = to_float(from_float<T>(rb));
+    }
+    if (head >= H && write) {
+      T* dst = k_cache + cache_base + (size_t)(head - H) * head_stride;
+      dst[j] = from_float<T>(a);
+      dst[j + half] = from_float<T>(b);
     }
   }
   if (write) {
     const T* v = row + (size_t)(H + KVH) * D;
-    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
-    const int nthreads = blockDim.x * blockDim.y;
+    const int tid = (blockIdx.y * blockDim.y + threadIdx.y) * blockDim.x + threadIdx.x;
+    const int nthreads = gridDim.y * blockDim.y * blockDim.x;
     for (int i = tid; i < KVH * D; i += nthreads) {
-      const int head = i / D, d = i % D;
-      v_cache[cache_base + (size_t)head * head_stride + d] = v[i];
+      const int vh = i / D, d = i % D;
+      v_cache[cache_base + (size_t)vh * head_stride + d] = v[i];
     }
   }
 }
 
 extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* positions,
-                                 const int* req_index,
-                                 const float* inv_freq, const int* table, int table_stride,
-                                 void* k_cache, void* v_cache, int tokens, int H, int KVH, int D,
-                                 int page_size, int num_pages, int dtype, cudaStream_t stream) {
+                                 const int* req_index, const float* cos_sin, const int* table,
+                                 int table_stride, void* k_cache, void* v_cache, int tokens, int H,
+                                 int KVH, int D, int page_size, int num_pages, int dtype,
+                                 cudaStream_t stream) {
   if (tokens == 0) return 0;
   KVB_REQUIRE(D > 0 && D % 2 == 0 && D <= 1024, "rope_kv_write: head_dim must be even and <= 1024");
   KVB_REQUIRE(H >= 0 && KVH >= 0 && H + KVH > 0, "rope_kv_write: no heads to encode");
@@ -287,18 +309,20 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
   const int half = D / 2;
   int tx = 1;
   while (tx < half) tx <<= 1;           // threads along j, a power of two >= D/2
-  int ty = 256 / tx;
+  int ty = 128 / tx;
   if (ty < 1) ty = 1;
   if (ty > H + KVH) ty = H + KVH;
   dim3 block(tx, ty);
+  dim3 grid(tokens, (H + KVH + ty - 1) / ty);
+  KVB_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
   if (dtype == KVB_F32)
-    rope_kv_write_kernel<float><<<tokens, block, 0, stream>>>(
-        (float*)qkv, qkv_stride, positions, req_index, inv_freq, table, table_stride, (float*)k_cache,
-        (float*)v_cache, H, KVH, D, page_size, num_pages, 1, status);
+    rope_kv_write_kernel<float><<<grid, block, 0, stream>>>(
+        (float*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
+        (float*)k_cache, (float*)v_cache, H, KVH, D, page_size, num_pages, status);
   else
-    rope_kv_write_kernel<bf16><<<tokens, block, 0, stream>>>(
-        (bf16*)qkv, qkv_stride, positions, req_index, inv_freq, table, table_stride, (bf16*)k_cache,
-        (bf16*)v_cache, H, KVH, D, page_size, num_pages, 1, status);
+    rope_kv_write_kernel<bf16><<<grid, block, 0, stream>>>(
+        (bf16*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
+        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status);
   KVB_CHECK_LAUNCH();
   return 0;
 }

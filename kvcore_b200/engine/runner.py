@@ -136,6 +136,7 @@ class ModelRunner:
             self.storage,
             max_num_tokens=self.max_num_tokens,
             max_num_seqs=self.max_num_seqs,
+            use_cuda_graphs=not config.model_config.enforce_eager,
         )
         self.sampler = Sampler(self.device)
         self.requests: dict[str, CachedRequestState] = {}

@@ -19,6 +19,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
+from .. import kernels as K
 from ..cache.kv_manager import CacheGroupSpec, KVManager
 from ..parts.model import DecoderModel
 
@@ -64,11 +65,20 @@ class StepContext:
         self.table_width = 0
         self.max_query_len = 0
         self.max_seq_len = 0
+        self.max_seq_len_bound = 0  # table_width * page_size: a bound that is stable across steps
         self.decode_only = False
         # host copies, for parts that plan their launches (or toy parts written in torch)
         self.host_query_lens: list[int] = []
         self.host_context_lens: list[int] = []
         self.host_state_slots: list[int] = []
+        self._shared: dict = {}
+
+    def shared(self, key, make):
+        """A value computed once per step and shared by the layers that ask for it under
+        ``key`` (for example the cos/sin table of one rotary frequency table)."""
+        if key not in self._shared:
+            self._shared[key] = make()
+        return self._shared[key]
 
     def block_table(self, group: int | None) -> torch.Tensor | None:
         """``[num_reqs, table_width]`` int32 page ids of the step's requests for ``group``."""
@@ -150,6 +160,8 @@ class StepFunction:
         *,
         max_num_tokens: int,
         max_num_seqs: int,
+        use_cuda_graphs: bool = True,
+        max_graphs: int = 24,
     ) -> None:
         self.model = model
         self.kv = kv_manager
@@ -172,6 +184,12 @@ class StepFunction:
         self._turn = 0
         self.last_context: StepContext | None = None
         self.num_steps = 0
+        # decode-only steps of one shape (requests, wanted rows, table width) replay a CUDA graph
+        self.use_cuda_graphs = bool(use_cuda_graphs) and self.device.type == "cuda" and model.graph_safe
+        self.max_graphs = int(max_graphs)
+        self._graphs: dict[tuple[int, int, int], object] = {}
+        self._graph_seen: set[tuple[int, int, int]] = set()
+        self.num_graph_replays = 0
 
     # ---- packing -----------------------------------------------------------------------------
     def _pack(self, entries: Sequence[StepEntry]) -> StepContext:
@@ -206,7 +224,10 @@ class StepFunction:
         seq_lens = [c + n for c, n in zip(context_lens, query_lens)]
         max_seq_len = max(seq_lens)
         width = -(-max_seq_len // kv.page_size)
-        width = max(1, min(_round4(width), kv.max_blocks_per_seq))
+        # decode-only steps round the table width up coarsely so that one captured graph serves
+        # many consecutive steps (the width is part of the graph's shape)
+        grain = 16 if max(query_lens) == 1 else 4
+        width = max(1, min(-(-width // grain) * grain, kv.max_blocks_per_seq))
         num_logits = sum(len(entry.want) for entry in entries)
 
         # layout (int32 counts, each array starting on a 16-byte boundary)
@@ -292,6 +313,7 @@ class StepFunction:
         ctx.table_width = width
         ctx.max_query_len = max(query_lens)
         ctx.max_seq_len = max_seq_len
+        ctx.max_seq_len_bound = width * kv.page_size
         ctx.decode_only = ctx.max_query_len == 1
         ctx.host_query_lens = query_lens
         ctx.host_context_lens = context_lens
@@ -304,15 +326,53 @@ class StepFunction:
         nothing is wanted), rows in the order of the entries and of each entry's ``want``."""
         ctx = self._pack(entries)
         self.storage.zero_slots(self.kv.take_fresh_slots())
-        h, residual = self.model.forward(ctx, self.storage.layer_caches)
-        logits = None
-        if ctx.num_logits:
-            logits = self.model.compute_logits(h, residual, ctx.logits_indices)
+        if self.use_cuda_graphs and ctx.decode_only:
+            logits = self._step_with_graph(ctx)
+        else:
+            logits = self._forward(ctx)
         for entry in entries:
             self.kv.advance(entry.request_id, len(entry.token_ids))
         self.last_context = ctx
         self.num_steps += 1
         return logits
+
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor | None:
+        h, residual = self.model.forward(ctx, self.storage.layer_caches)
+        if not ctx.num_logits:
+            return None
+        return self.model.compute_logits(h, residual, ctx.logits_indices)
+
+    def _step_with_graph(self, ctx: StepContext) -> torch.Tensor | None:
+        """Decode-only step through a CUDA graph.
+
+        Every value a kernel takes from the host is fixed by the key (requests, wanted rows,
+        table width); everything else (token ids, positions, lengths, block tables) sits at
+        fixed addresses of the metadata buffer, which was just uploaded.  A shape is run
+        eagerly the first time, captured the second time and replayed from then on.  The
+        returned logits live in the graph's memory and are overwritten by its next replay.
+        """
+        key = (ctx.num_reqs, ctx.num_logits, ctx.table_width)
+        graph = self._graphs.get(key)
+        if graph is None:
+            if key not in self._graph_seen:
+                self._graph_seen.add(key)
+                return self._forward(ctx)
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            cuda_graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            launches_before = K.api.launch_count
+            with torch.cuda.graph(cuda_graph):
+                static_logits = self._forward(ctx)
+            graph = (cuda_graph, static_logits, K.api.launch_count - launches_before)
+            K.api.launch_count = launches_before  # capturing launches nothing; replays are counted
+            self._graphs[key] = graph
+        cuda_graph, static_logits, launches = graph
+        cuda_graph.replay()
+        K.api.launch_count += launches
+        self.num_graph_replays += 1
+        return static_logits
 
 
 __all__ = ["CacheStorage", "LayerCache", "StepContext", "StepEntry", "StepFunction"]

@@ -19,6 +19,7 @@ from .api import (
     rmsnorm,
     rope_inplace,
     rope_kv_write,
+    rope_table,
     sample,
     silu_mul,
 )
@@ -39,6 +40,7 @@ __all__ = [
     "rmsnorm",
     "rope_inplace",
     "rope_kv_write",
+    "rope_table",
     "sample",
     "silu_mul",
 ]

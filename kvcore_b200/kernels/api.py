@@ -40,6 +40,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_gather_rows": [_vp, _vp, _vp, _int, _int, _int, _int, _vp],
         "kvb_rmsnorm": [_vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _vp],
         "kvb_silu_mul": [_vp, _vp, _int, _int, _int, _vp],
+        "kvb_rope_table": [_vp, _vp, _vp, _int, _int, _vp],
         "kvb_rope_kv_write": [_vp, _ll, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                               _int, _int, _int, _vp],
         "kvb_paged_attention_rows": [_vp, _int, _vp, _int, _vp, _vp, _vp, _int, _vp, _vp, _int, _int,
@@ -184,11 +185,21 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """``[T, D/2, 2]`` float32 (cos, sin) of ``float(position) * inv_freq``: made once per step."""
+    _check(positions, "positions", dtype=torch.int32)
+    _check(inv_freq, "inv_freq", dtype=torch.float32)
+    tokens, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((tokens, half, 2), dtype=torch.float32, device=positions.device)
+    _call("kvb_rope_table", table.data_ptr(), positions.data_ptr(), inv_freq.data_ptr(), tokens, half, _stream())
+    return table
+
+
 def rope_kv_write(
     qkv: torch.Tensor,
     positions: torch.Tensor,
     req_index: torch.Tensor,
-    inv_freq: torch.Tensor | None,
+    cos_sin: torch.Tensor | None,
     table: torch.Tensor | None,
     k_cache: torch.Tensor | None,
     v_cache: torch.Tensor | None,
@@ -198,7 +209,8 @@ def rope_kv_write(
     *,
     write_kv: bool = True,
 ) -> None:
-    """Rotate q and k of ``qkv [T, (H+2KVH)*D]`` in place and write k, v into their pages."""
+    """Rotate q and k of ``qkv [T, (H+2KVH)*D]`` in place with the ``rope_table`` values
+    ``cos_sin`` (``None``: no rotation) and write k, v into their pages."""
     _check(qkv, "qkv", contiguous=False)
     _check(positions, "positions", dtype=torch.int32)
     _check(req_index, "req_index", dtype=torch.int32)
@@ -207,10 +219,10 @@ def rope_kv_write(
         raise KernelError("qkv rows must be contiguous")
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
         raise KernelError(f"qkv width {qkv.shape[1]} does not match the head layout")
-    if inv_freq is not None:
-        _check(inv_freq, "inv_freq", dtype=torch.float32)
-        if inv_freq.numel() != head_dim // 2:
-            raise KernelError(f"inv_freq has {inv_freq.numel()} entries for head_dim {head_dim}")
+    if cos_sin is not None:
+        _check(cos_sin, "cos_sin", dtype=torch.float32)
+        if tuple(cos_sin.shape) != (tokens, head_dim // 2, 2):
+            raise KernelError(f"cos_sin has shape {tuple(cos_sin.shape)} for {tokens} tokens of head_dim {head_dim}")
     k_ptr = v_ptr = table_ptr = None
     table_stride = page_size = num_pages = 0
     if write_kv:
@@ -226,18 +238,17 @@ def rope_kv_write(
             raise KernelError("block table rows must be contiguous")
         k_ptr, v_ptr, table_ptr = k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr()
         table_stride = table.stride(0)
-    if inv_freq is None and not write_kv:
+    if cos_sin is None and not write_kv:
         return
     _call("kvb_rope_kv_write", qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), req_index.data_ptr(),
-          None if inv_freq is None else inv_freq.data_ptr(), table_ptr, table_stride, k_ptr, v_ptr,
+          None if cos_sin is None else cos_sin.data_ptr(), table_ptr, table_stride, k_ptr, v_ptr,
           tokens, num_heads, num_kv_heads, head_dim, page_size, num_pages, _dtype_code(qkv), _stream())
 
 
 def rope_inplace(q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tensor, inv_freq: torch.Tensor) -> None:
     """Rotate ``q [T, H, D]`` (and ``k [T, KVH, D]``) in place without touching a cache; rows may
     be views into a wider buffer as long as heads are contiguous."""
-    _check(positions, "positions", dtype=torch.int32)
-    _check(inv_freq, "inv_freq", dtype=torch.float32)
+    cos_sin = rope_table(positions, inv_freq)
     for x in (q, k):
         if x is None:
             continue
@@ -248,7 +259,7 @@ def rope_inplace(q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tenso
         if inv_freq.numel() != head_dim // 2:
             raise KernelError(f"inv_freq has {inv_freq.numel()} entries for head_dim {head_dim}")
         _call("kvb_rope_kv_write", x.data_ptr(), x.stride(0), positions.data_ptr(), positions.data_ptr(),
-              inv_freq.data_ptr(), None, 0, None, None, tokens, heads, 0, head_dim, 0, 0,
+              cos_sin.data_ptr(), None, 0, None, None, tokens, heads, 0, head_dim, 0, 0,
               _dtype_code(x), _stream())
 
 
@@ -305,7 +316,8 @@ def paged_attention(
         split_mode = ctx.max_query_len * group <= 16
         splits = 1
         if split_mode:
-            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, ctx.max_seq_len)
+            bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
+            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound)
         scratch = None
         if splits > 1:
             scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
@@ -397,6 +409,7 @@ __all__ = [
     "rmsnorm",
     "rope_inplace",
     "rope_kv_write",
+    "rope_table",
     "sample",
     "silu_mul",
 ]

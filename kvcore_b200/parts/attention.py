@@ -19,6 +19,10 @@ from .rope import RotaryEncoding
 
 
 class PagedAttention(Mixer):
+    @property
+    def graph_safe(self) -> bool:
+        return self.position is None or self.position.graph_safe
+
     def __init__(
         self,
         *,
@@ -87,9 +91,10 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         qkv = K.linear(x, self.qkv_weight, self.qkv_bias)
         table = ctx.block_table(cache.group)
-        inv_freq = None
+        cos_sin = None
         if isinstance(self.position, RotaryEncoding):
-            inv_freq = self.position.inv_freq  # rotation fused with the cache write
+            # rotation fused with the cache write; its cos/sin table is made once per step
+            cos_sin = self.position.cos_sin(ctx)
         elif self.position is not None:
             tokens = qkv.shape[0]
             q = qkv[:, : self.q_size].view(tokens, self.num_heads, self.head_dim)
@@ -98,7 +103,7 @@ class PagedAttention(Mixer):
             )
             self.position.apply(q, k if cache.owner else None, ctx)
         K.rope_kv_write(
-            qkv, ctx.positions, ctx.req_index, inv_freq, table, cache.k, cache.v,
+            qkv, ctx.positions, ctx.req_index, cos_sin, table, cache.k, cache.v,
             self.num_heads, self.num_kv_heads, self.head_dim, write_kv=cache.owner,
         )
         out = K.paged_attention(

@@ -72,7 +72,15 @@ class StateSpec:
 
 
 class Part:
-    """Base of everything that may hold weights."""
+    """Base of everything that may hold weights.
+
+    ``graph_safe``: the part's forward launches the same kernels with the same host-side
+    arguments for every batch of a given shape and reads batch contents only from device
+    memory, so a decode step containing it may be captured in a CUDA graph and replayed.
+    A part that branches on host copies of the batch (``ctx.host_*``) must leave it False.
+    """
+
+    graph_safe = False
 
     def weight_slots(self) -> list[WeightSlot]:
         return []

@@ -22,6 +22,10 @@ class PreNormResidualBlock(Block):
     def parts(self):
         return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts())
+
     def weight_slots(self) -> list[WeightSlot]:
         slots: list[WeightSlot] = []
         for part in self.parts():

@@ -14,6 +14,8 @@ from .base import EMBEDDINGS, LM_HEADS, Part, WeightSlot
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, *, vocab_size: int, hidden_size: int, name: str, dtype, device) -> None:
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
@@ -28,6 +30,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(
         self,
         *,

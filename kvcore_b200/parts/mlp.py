@@ -12,6 +12,8 @@ from .base import FEED_FORWARDS, FeedForward, WeightSlot
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(
         self,
         *,

@@ -47,6 +47,11 @@ class DecoderModel:
         self.lm_head = LM_HEADS.build(spec.lm_head, tied_weight=tied_weight, dtype=dtype, device=device)
         self.schedule = spec.schedule
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be captured in a CUDA graph."""
+        return all(part.graph_safe for part in self._parts())
+
     # ---- weights -------------------------------------------------------------------------
     def _parts(self):
         return [self.embedding, *self.blocks, self.final_norm, self.lm_head]

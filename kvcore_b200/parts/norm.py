@@ -13,6 +13,8 @@ from .base import NORMS, Norm, WeightSlot
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, *, size: int, eps: float, name: str, dtype: torch.dtype, device: torch.device):
         self.size = int(size)
         self.eps = float(eps)

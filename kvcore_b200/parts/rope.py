@@ -55,6 +55,8 @@ def rope_inverse_frequencies(
 class RotaryEncoding(PositionEncoding):
     """Holds the frequency table; the attention mixer fuses its rotation with the cache write."""
 
+    graph_safe = True
+
     def __init__(
         self,
         *,
@@ -76,6 +78,11 @@ class RotaryEncoding(PositionEncoding):
             original_max_position_embeddings,
         )
         self.inv_freq = table if torch.device(device).type == "meta" else table.to(device)
+
+    def cos_sin(self, ctx) -> torch.Tensor:
+        """``[T, D/2, 2]`` (cos, sin) of this step's positions; one table per step and frequency table."""
+        key = ("rope", self.inv_freq.data_ptr(), self.inv_freq.numel())
+        return ctx.shared(key, lambda: K.rope_table(ctx.positions, self.inv_freq))
 
     def apply(self, q: torch.Tensor, k: torch.Tensor | None, ctx) -> None:
         K.rope_inplace(q, k, ctx.positions, self.inv_freq)

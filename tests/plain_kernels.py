@@ -67,16 +67,28 @@ def rope_inplace(q, k, positions, inv_freq):
         k.copy_(_rotate(k, positions, inv_freq))
 
 
-def rope_kv_write(qkv, positions, req_index, inv_freq, table, k_cache, v_cache,
+def rope_table(positions, inv_freq):
+    angles = positions.to(torch.float32)[:, None] * inv_freq[None, :].to(torch.float32)
+    return torch.stack((angles.cos(), angles.sin()), dim=-1)
+
+
+def _rotate_with(x, cos_sin):
+    half = x.shape[-1] // 2
+    cos, sin = cos_sin[:, None, :, 0], cos_sin[:, None, :, 1]
+    a, b = x[..., :half].float(), x[..., half:].float()
+    return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1).to(x.dtype)
+
+
+def rope_kv_write(qkv, positions, req_index, cos_sin, table, k_cache, v_cache,
                   num_heads, num_kv_heads, head_dim, *, write_kv=True):
     tokens = qkv.shape[0]
     q_size, kv_size = num_heads * head_dim, num_kv_heads * head_dim
     q = qkv[:, :q_size].view(tokens, num_heads, head_dim)
     k = qkv[:, q_size:q_size + kv_size].view(tokens, num_kv_heads, head_dim)
     v = qkv[:, q_size + kv_size:].view(tokens, num_kv_heads, head_dim)
-    if inv_freq is not None:
-        q.copy_(_rotate(q, positions, inv_freq))
-        k.copy_(_rotate(k, positions, inv_freq))
+    if cos_sin is not None:
+        q.copy_(_rotate_with(q, cos_sin))
+        k.copy_(_rotate_with(k, cos_sin))
     if write_kv:
         page_size = k_cache.shape[2]
         for t in range(tokens):
@@ -179,7 +191,7 @@ def sample(logits, packed_params, eps):
 
 _NAMES = [
     "require_device", "ensure_built", "read_status", "check_attention_shape", "gather_rows", "rmsnorm",
-    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_kv_write", "paged_attention", "linear", "sample",
+    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "sample",
 ]
 
 

@@ -272,9 +272,11 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim, page):
     case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=5)
     inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))).float().to(DEV)
     ref = {k: v.clone() for k, v in case.items() if torch.is_tensor(v)}
-    P.rope_kv_write(ref["qkv"], ref["positions"], ref["req_index"], inv_freq, ref["table"],
-                    ref["k_cache"], ref["v_cache"], heads, kv_heads, dim)
-    K().rope_kv_write(case["qkv"], case["positions"], case["req_index"], inv_freq, case["table"],
+    P.rope_kv_write(ref["qkv"], ref["positions"], ref["req_index"], P.rope_table(ref["positions"], inv_freq),
+                    ref["table"], ref["k_cache"], ref["v_cache"], heads, kv_heads, dim)
+    cos_sin = K().rope_table(case["positions"], inv_freq)
+    torch.testing.assert_close(cos_sin, P.rope_table(case["positions"], inv_freq), rtol=1e-6, atol=1e-6)
+    K().rope_kv_write(case["qkv"], case["positions"], case["req_index"], cos_sin, case["table"],
                       case["k_cache"], case["v_cache"], heads, kv_heads, dim)
     t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
     torch.testing.assert_close(case["qkv"], ref["qkv"], **t)
