@@ -261,6 +261,8 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT_LEN)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="only the headline decode number")
+    parser.add_argument("--only-prefill", action="store_true",
+                        help="time the 2,048-token prefill alone and print its line (for profiling)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -282,6 +284,11 @@ def main() -> int:
     pages = max_batch * (-(-max_len // BLOCK_SIZE)) + 1
     config, runner = build_runner(args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))
 
+    if args.only_prefill:
+        ms_prefill = time_prefill(runner, PREFILL_TOKENS, repeats=max(1, args.steps), warmup=2)
+        print(json.dumps({"prefill_ms": round(ms_prefill, 3), "layers": args.layers,
+                          "tokens_per_s": round(PREFILL_TOKENS * 1000.0 / ms_prefill, 1)}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     launches_before = K.api.launch_count
