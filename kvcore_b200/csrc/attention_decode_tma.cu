@@ -1,0 +1,495 @@
+// Split-KV paged attention for decode, fed by TMA (sm_100a).
+//
+// Decode reads every cached key and value once and does little arithmetic on them, so the
+// kernel is built to keep as many bytes in flight as one SM can hold.  One block per SM-sized
+// share of the work: a (request, kv head, split) triple.  A producer warp walks the split's
+// key range in tiles of 64 keys and, for each tile, looks the pages up in the block table and
+// issues one tiled TMA copy per page and 64-column half (cp.async.bulk.tensor.2d, 128-byte
+// swizzle) for K and for V into a ring of STAGES shared-memory stages; each stage has a
+// "full" mbarrier that the copies complete and an "empty" mbarrier that the consumers
+// release.  Four consumer warps each score 16 keys of a tile against the (at most 16) query
+// rows of the request with mma.sync m16n8k16, keep a running 32-bit softmax, and accumulate
+// their part of the output; at the end the warps merge through shared memory and the block
+// writes either the final rows (one split) or a partial (max, sum, output) to scratch that
+// flash_combine merges.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the thread sets the
+// WAIT_TIMEOUT bit of the status word, the block stops waiting, drains the copies it
+// issued (bounded again) and returns, so a fault in the pipeline cannot hang the GPU.
+//
+// Whole pages are copied, so slots of a request's last page beyond its length and the null
+// page reach shared memory; their scores are masked and their probability is exactly zero.
+// Cache memory is zero-initialised and only ever holds finite values, so 0 * value = 0.
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#define TD_KEYS 64
+#define TD_STAGES 6
+#define TD_CONSUMERS 4
+#define TD_THREADS ((TD_CONSUMERS + 1) * 32)
+#define TD_SPIN_LIMIT (1u << 22)
+
+struct DecodeParams {
+  bf16* out; long long out_stride;
+  const bf16* q; long long q_stride;
+  const int* table; int table_stride;
+  const int* query_start; const int* context_lens;
+  int num_reqs, H, KVH, G, page_size, num_pages, window;
+  float scale_log2;
+  int num_splits;
+  float* partial_o;   // [reqs, KVH, splits, 16, D]
+  float* partial_ml;  // [reqs, KVH, splits, 16, 2]
+  int* status;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Waits for the phase of `parity` to complete; gives up after TD_SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+  for (unsigned spin = 0; spin < TD_SPIN_LIMIT; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (spin > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void td_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void td_ldmatrix_x4_trans(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void td_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned td_pack(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// Byte offset of element (row, d) inside one stage's K (or V) area: D/64 halves of
+// [64 rows][128 bytes], 16-byte chunks XOR-swizzled with the row (TMA's 128-byte swizzle).
+__device__ __forceinline__ unsigned swz(int row, int d) {
+  const int half = d >> 6, chunk = (d & 63) >> 3;
+  return (unsigned)(half * (TD_KEYS * 128) + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int D>
+__global__ void __launch_bounds__(TD_THREADS, 1)
+flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                        const DecodeParams p) {
+  constexpr int HALVES = D / 64;
+  constexpr int KV_BYTES = TD_KEYS * D * 2;        // one of K or V of a stage
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  constexpr int QROW = D + 8;
+  constexpr int KSTEPS = D / 16, DBLOCKS = D / 8;
+
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment for the swizzled stages
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* stages = base;
+  bf16* qs = reinterpret_cast<bf16*>(base + TD_STAGES * STAGE_BYTES);
+  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(qs + 16 * QROW);
+  unsigned long long* empty_bar = full_bar + TD_STAGES;
+  int* abort_flag = reinterpret_cast<int*>(empty_bar + TD_STAGES);
+
+  const int req = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_begin = p.query_start[req];
+  const int q_len = p.query_start[req + 1] - q_begin;
+  const int context = p.context_lens[req];
+  const int rows_total = min(q_len * p.G, 16);
+  const int last_pos = context + (rows_total - 1) / p.G;
+  int key_lo = p.window > 0 ? max(0, context - p.window + 1) : 0;
+  int key_hi = last_pos + 1;
+  {
+    const int first_tile_key = (key_lo / TD_KEYS) * TD_KEYS;
+    const int tiles = (key_hi - first_tile_key + TD_KEYS - 1) / TD_KEYS;
+    const int per = (tiles + p.num_splits - 1) / p.num_splits;
+    const int lo = first_tile_key + split * per * TD_KEYS;
+    key_hi = min(key_hi, lo + per * TD_KEYS);
+    key_lo = max(key_lo, lo);
+  }
+  const int tile_begin = key_lo / TD_KEYS;
+  const int tile_end = key_hi > key_lo ? (key_hi + TD_KEYS - 1) / TD_KEYS : tile_begin;
+  const int num_tiles = tile_end - tile_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TD_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], TD_CONSUMERS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G)
+  for (int i = threadIdx.x; i < 16 * (D / 8); i += TD_THREADS) {
+    const int r = i / (D / 8), chunk = i % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows_total) {
+      const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8);
+    }
+    *reinterpret_cast<uint4*>(qs + r * QROW + chunk * 8) = v;
+  }
+  __syncthreads();
+
+  float o[DBLOCKS][4];
+#pragma unroll
+  for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+
+  if (warp == TD_CONSUMERS) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int* pages = p.table + (size_t)req * p.table_stride;
+      const int pages_per_tile = TD_KEYS / p.page_size;
+      int issued = 0;
+      for (int it = 0; it < num_tiles; ++it) {
+        const int stage = it % TD_STAGES;
+        if (it >= TD_STAGES) {
+          const unsigned parity = ((it / TD_STAGES) & 1) ^ 1;
+          if (!mbar_wait_bounded(&empty_bar[stage], parity)) {
+            atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+            atomicExch(abort_flag, 1);
+            break;
+          }
+        }
+        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+        unsigned char* kdst = stages + stage * STAGE_BYTES;
+        unsigned char* vdst = kdst + KV_BYTES;
+        mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+        const int key0 = (tile_begin + it) * TD_KEYS;
+        for (int pg = 0; pg < pages_per_tile; ++pg) {
+          const int key = key0 + pg * p.page_size;
+          int page = 0;
+          if (key < key_hi) {
+            page = pages[key / p.page_size];
+            if (page < 0 || page >= p.num_pages) {
+              atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+              page = 0;
+            }
+          }
+          const int row = (page * p.KVH + kvh) * p.page_size;
+          const int dst_off = pg * p.page_size * 128;
+#pragma unroll
+          for (int half = 0; half < HALVES; ++half) {
+            tma_load_2d(kdst + half * (TD_KEYS * 128) + dst_off, &k_map, half * 64, row, &full_bar[stage]);
+            tma_load_2d(vdst + half * (TD_KEYS * 128) + dst_off, &v_map, half * 64, row, &full_bar[stage]);
+          }
+        }
+        issued = it + 1;
+      }
+      // on an aborted run, let the copies already issued land before the block may exit
+      if (*reinterpret_cast<volatile int*>(abort_flag)) {
+        for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
+          mbar_wait_bounded(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int k = 0; k < KSTEPS; ++k) {
+      const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+      const int c = k * 16 + 8 * (lane >> 4);
+      td_ldmatrix_x4(qf[k], smem_u32(qs + r * QROW + c));
+    }
+    int row_pos[2];
+    bool row_valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+      row_valid[h] = r < rows_total;
+      row_pos[h] = context + (row_valid[h] ? r / p.G : 0);
+    }
+    const int wkey = warp * 16;
+    for (int it = 0; it < num_tiles; ++it) {
+      const int stage = it % TD_STAGES;
+      if (!mbar_wait_bounded(&full_bar[stage], (it / TD_STAGES) & 1)) {
+        atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+        atomicExch(abort_flag, 1);
+        break;
+      }
+      const unsigned kbase = smem_u32(stages + stage * STAGE_BYTES);
+      const unsigned vbase = kbase + KV_BYTES;
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k) {
+        unsigned kb[4];
+        const int key = wkey + (lane & 7) + 8 * (lane >> 4);
+        const int d = k * 16 + 8 * ((lane >> 3) & 1);
+        td_ldmatrix_x4(kb, kbase + swz(key, d));
+        td_mma(s[0], qf[k], kb[0], kb[1]);
+        td_mma(s[1], qf[k], kb[2], kb[3]);
+      }
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int key = (tile_begin + it) * TD_KEYS + wkey + j * 8 + (lane & 3) * 2 + (e & 1);
+          const bool seen = row_valid[h] && key >= key_lo && key < key_hi && key <= row_pos[h] &&
+                            (p.window <= 0 || key > row_pos[h] - p.window);
+          const float v = seen ? s[j][e] * p.scale_log2 : -INFINITY;
+          s[j][e] = v;
+          tile_max[h] = fmaxf(tile_max[h], v);
+        }
+      }
+      float correction[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float m = tile_max[h];
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        const float new_max = fmaxf(row_max[h], m);
+        correction[h] = (row_max[h] == -INFINITY) ? 0.0f : exp2f(row_max[h] - new_max);
+        row_max[h] = new_max;
+        row_sum[h] *= correction[h];
+      }
+#pragma unroll
+      for (int j = 0; j < DBLOCKS; ++j) {
+        o[j][0] *= correction[0]; o[j][1] *= correction[0];
+        o[j][2] *= correction[1]; o[j][3] *= correction[1];
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const float pv = (s[j][e] == -INFINITY) ? 0.0f : exp2f(s[j][e] - row_max[h]);
+          s[j][e] = pv;
+          row_sum[h] += pv;
+        }
+      }
+      unsigned pa[4];
+      pa[0] = td_pack(s[0][0], s[0][1]);
+      pa[1] = td_pack(s[0][2], s[0][3]);
+      pa[2] = td_pack(s[1][0], s[1][1]);
+      pa[3] = td_pack(s[1][2], s[1][3]);
+#pragma unroll
+      for (int j = 0; j < DBLOCKS; j += 2) {
+        unsigned vb[4];
+        const int key = wkey + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int d = j * 8 + 8 * (lane >> 4);
+        td_ldmatrix_x4_trans(vb, vbase + swz(key, d));
+        td_mma(o[j], pa, vb[0], vb[1]);
+        td_mma(o[j + 1], pa, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+    }
+  }
+
+  // ---- merge the four consumer warps through the (now idle) stage memory -------------------
+  __syncthreads();
+  float* merge_o = reinterpret_cast<float*>(stages);          // [4][16][D]
+  float* merge_ml = merge_o + TD_CONSUMERS * 16 * D;          // [4][16][2]
+  if (warp < TD_CONSUMERS) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+#pragma unroll
+      for (int j = 0; j < DBLOCKS; ++j) {
+        float* dst = merge_o + ((size_t)(warp * 16 + r)) * D + j * 8 + (lane & 3) * 2;
+        dst[0] = o[j][2 * h];
+        dst[1] = o[j][2 * h + 1];
+      }
+      if ((lane & 3) == 0) {
+        merge_ml[(warp * 16 + r) * 2 + 0] = row_max[h];
+        merge_ml[(warp * 16 + r) * 2 + 1] = row_sum[h];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows_total * D; i += TD_THREADS) {
+    const int r = i / D, d = i % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < TD_CONSUMERS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    float total = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < TD_CONSUMERS; ++w) {
+      const float mw = merge_ml[(w * 16 + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+      total += merge_ml[(w * 16 + r) * 2 + 1] * f;
+      acc += merge_o[((size_t)(w * 16 + r)) * D + d] * f;
+    }
+    if (p.num_splits == 1) {
+      const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+      p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+          __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+    } else {
+      const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
+      p.partial_o[(slot * 16 + r) * D + d] = acc;
+      if (d == 0) {
+        p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
+        p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
+      }
+    }
+  }
+}
+
+// Same merge of splits as the cp.async kernel's, for this kernel's scratch layout.
+template <int D>
+__global__ void flash_decode_combine_kernel(const DecodeParams p) {
+  const int req = blockIdx.z, kvh = blockIdx.y;
+  const int q_begin = p.query_start[req];
+  const int rows_total = min((p.query_start[req + 1] - q_begin) * p.G, 16);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = i / D, d = i % D;
+  if (r >= rows_total) return;
+  const size_t base = ((size_t)req * p.KVH + kvh) * p.num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.partial_ml[((base + s) * 16 + r) * 2]);
+  float total = 0.0f, acc = 0.0f;
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float ms = p.partial_ml[((base + s) * 16 + r) * 2];
+    const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
+    total += p.partial_ml[((base + s) * 16 + r) * 2 + 1] * f;
+    acc += p.partial_o[((base + s) * 16 + r) * D + d] * f;
+  }
+  const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+  p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+      __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Writes a 128-byte tensor map describing one layer's K (or V) cache [pages, KVH, page, D] bf16
+// as a 2-D tensor [pages*KVH*page rows, D columns] with boxes of [page rows, 64 columns].
+extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long long num_pages, int KVH,
+                                      int page_size, int D) {
+  KVB_REQUIRE(D == 64 || D == 128, "kv tensor map: head_dim must be 64 or 128");
+  KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
+              "kv tensor map: page size must be 8, 16, 32 or 64");
+  KVB_REQUIRE(aligned16(cache), "kv tensor map: the cache must be 16-byte aligned");
+  EncodeTiledFn encode = encode_tiled_fn();
+  KVB_REQUIRE(encode != nullptr, "kv tensor map: the driver does not export cuTensorMapEncodeTiled");
+  alignas(64) CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * KVH * page_size};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
+  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
+                             box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  KVB_REQUIRE(rc == CUDA_SUCCESS, "kv tensor map: cuTensorMapEncodeTiled failed");
+  memcpy(map_out, &map, sizeof(map));
+  return 0;
+}
+
+template <int D>
+static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
+                             int max_rows, cudaStream_t stream) {
+  constexpr size_t SMEM = 1024 + TD_STAGES * 2 * TD_KEYS * D * 2 + 16 * (D + 8) * 2 + 2 * TD_STAGES * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)SMEM));
+    configured = true;
+  }
+  dim3 grid(p.num_splits, p.KVH, p.num_reqs);
+  flash_decode_tma_kernel<D><<<grid, TD_THREADS, SMEM, stream>>>(k_map, v_map, p);
+  KVB_CHECK_LAUNCH();
+  if (p.num_splits > 1) {
+    const int rows = max_rows < 16 ? max_rows : 16;
+    dim3 cgrid((rows * D + 127) / 128, p.KVH, p.num_reqs);
+    flash_decode_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
+    KVB_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void* q, long long q_stride,
+                                    const void* k_map_host, const void* v_map_host, const int* table,
+                                    int table_stride, const int* query_start, const int* context_lens,
+                                    int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
+                                    int num_pages, float scale, int window, int num_splits, float* scratch,
+                                    cudaStream_t stream) {
+  if (num_reqs == 0) return 0;
+  KVB_REQUIRE(D == 64 || D == 128, "decode attention (TMA): head_dim must be 64 or 128");
+  KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
+              "decode attention (TMA): page size must be 8, 16, 32 or 64");
+  KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "decode attention (TMA): H must be a multiple of KVH");
+  KVB_REQUIRE(max_query_len * (H / KVH) <= 16, "decode attention (TMA): at most 16 rows per request and kv head");
+  KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "decode attention (TMA): batch too large for one launch");
+  KVB_REQUIRE(aligned16(q) && (q_stride % 8) == 0, "decode attention (TMA): q must be 16-byte aligned");
+  KVB_REQUIRE(k_map_host != nullptr && v_map_host != nullptr, "decode attention (TMA): tensor maps are missing");
+  DecodeParams p;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.table = table; p.table_stride = table_stride;
+  p.query_start = query_start; p.context_lens = context_lens;
+  p.num_reqs = num_reqs; p.H = H; p.KVH = KVH; p.G = H / KVH;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_splits = num_splits < 1 ? 1 : num_splits;
+  KVB_REQUIRE(p.num_splits == 1 || scratch != nullptr, "decode attention (TMA): splits need scratch memory");
+  p.partial_o = scratch;
+  p.partial_ml = scratch ? scratch + (size_t)num_reqs * KVH * p.num_splits * 16 * D : nullptr;
+  p.status = kvb_status_word();
+  KVB_REQUIRE(p.status != nullptr, "decode attention (TMA): no status word");
+  alignas(64) CUtensorMap k_map, v_map;
+  memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
+  memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
+  const int max_rows = max_query_len * p.G;
+  if (D == 64) return launch_decode_tma<64>(k_map, v_map, p, max_rows, stream);
+  return launch_decode_tma<128>(k_map, v_map, p, max_rows, stream);
+}

@@ -8,6 +8,8 @@ from .api import (
     add_rmsnorm,
     check_attention_shape,
     decode_splits,
+    decode_splits_tma,
+    tma_decode_supported,
     ensure_built,
     flash_attention_supported,
     gather_rows,
@@ -29,6 +31,8 @@ __all__ = [
     "add_rmsnorm",
     "check_attention_shape",
     "decode_splits",
+    "decode_splits_tma",
+    "tma_decode_supported",
     "ensure_built",
     "flash_attention_supported",
     "gather_rows",

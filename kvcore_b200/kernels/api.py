@@ -47,6 +47,9 @@ def ensure_built(verbose: bool = False) -> str:
                                      _int, _int, _int, _int, _float, _int, _int, _vp],
         "kvb_flash_paged_attention": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int,
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
+        "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
+        "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
+                                 _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
@@ -280,6 +283,41 @@ def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
     return max(1, min(wanted, longest, 64))
 
 
+def tma_decode_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether the TMA-fed decode kernel takes this cache shape."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size in (8, 16, 32, 64)
+
+
+def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
+    """Splits for the TMA decode kernel, which keeps one block per SM: the count that fills whole
+    waves of SM_COUNT blocks best, with at least four 64-key tiles per split."""
+    base = max(1, num_reqs * num_kv_heads)
+    tiles = max(1, -(-max_seq_len // 64))
+    best, best_eff = 1, 0.0
+    for splits in range(1, max(1, min(64, tiles // 4)) + 1):
+        blocks = base * splits
+        eff = blocks / (-(-blocks // SM_COUNT) * SM_COUNT)
+        if eff > best_eff + 0.02:
+            best, best_eff = splits, eff
+    return best
+
+
+_kv_tensor_maps: dict[tuple, tuple] = {}
+
+
+def _kv_tensor_map_pair(k_cache: torch.Tensor, v_cache: torch.Tensor) -> tuple:
+    """Host-side TMA descriptors of one layer's K and V cache, made once per tensor."""
+    key = (k_cache.data_ptr(), v_cache.data_ptr(), tuple(k_cache.shape))
+    maps = _kv_tensor_maps.get(key)
+    if maps is None:
+        num_pages, kvh, page_size, d = k_cache.shape
+        maps = (ctypes.create_string_buffer(128), ctypes.create_string_buffer(128))
+        for buffer, cache in zip(maps, (k_cache, v_cache)):
+            _call("kvb_make_kv_tensor_map", ctypes.addressof(buffer), cache.data_ptr(), num_pages, kvh, page_size, d)
+        _kv_tensor_maps[key] = maps
+    return maps
+
+
 def paged_attention(
     qkv: torch.Tensor,
     k_cache: torch.Tensor,
@@ -294,6 +332,7 @@ def paged_attention(
     *,
     force_general: bool = False,
     num_splits: int | None = None,
+    use_tma: bool = True,
 ) -> torch.Tensor:
     """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
 
@@ -314,9 +353,22 @@ def paged_attention(
     if not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0:
         group = num_heads // num_kv_heads
         split_mode = ctx.max_query_len * group <= 16
+        bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
+        if split_mode and use_tma and tma_decode_supported(qkv.dtype, head_dim, page_size):
+            splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound)
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
+                                      dtype=torch.float32, device=qkv.device)
+            k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache)
+            _call("kvb_flash_decode_tma", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+                  ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
+                  ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+                  num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
+                  splits, None if scratch is None else scratch.data_ptr(), _stream())
+            return out
         splits = 1
         if split_mode:
-            bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
             splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound)
         scratch = None
         if splits > 1:
@@ -399,7 +451,9 @@ __all__ = [
     "check_attention_shape",
     "ensure_built",
     "decode_splits",
+    "decode_splits_tma",
     "flash_attention_supported",
+    "tma_decode_supported",
     "gather_rows",
     "library_is_loaded",
     "linear",

@@ -202,6 +202,10 @@ FLASH_SHAPES = [
     (6, 3, 48, 16, [(17, 30), (0, 1), (100, 2)], None, None),
     (4, 2, 64, 16, [(0, 150), (170, 1), (33, 5)], 24, None),                 # window
     (8, 2, 128, 16, [(900, 1), (70, 1)], 100, 4),                            # window, decode, forced splits
+    (8, 2, 128, 16, [(3000, 1), (1, 1), (640, 1)], None, 5),                 # TMA decode: ring wraps many times
+    (16, 4, 64, 8, [(777, 1), (64, 2), (0, 1)], None, 3),                    # TMA decode: D=64, pages of 8
+    (4, 1, 128, 64, [(500, 3), (63, 1)], None, 2),                           # TMA decode: pages of 64
+    (2, 2, 64, 32, [(100, 9)], 17, None),                                    # TMA decode: 9 rows, window
 ]
 
 
@@ -216,18 +220,22 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
         if page_id not in owned:
             case["k_cache"][page_id] = float("nan")
             case["v_cache"][page_id] = float("nan")
-    # so do slots of owned pages beyond each request's length
+    # slots of owned pages beyond each request's length hold large stale values (finite, as
+    # anything a kernel ever wrote to the cache is): they must not leak into the result
     for r, (c, q) in enumerate(lens):
         end = c + q
         last_page = int(case["table"][r, (end - 1) // page])
         if end % page:
-            case["k_cache"][last_page, :, end % page:] = float("nan")
-            case["v_cache"][last_page, :, end % page:] = float("nan")
+            case["k_cache"][last_page, :, end % page:] = 3.0e4
+            case["v_cache"][last_page, :, end % page:] = -3.0e4
     scale = dim ** -0.5
     ctx = _Ctx(case)
     assert K().flash_attention_supported(dtype, dim)
     got = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
                               heads, kv_heads, dim, scale, window, num_splits=splits)
+    no_tma = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                                 heads, kv_heads, dim, scale, window, num_splits=splits, use_tma=False)
+    torch.testing.assert_close(got.float(), no_tma.float(), rtol=2e-2, atol=2e-2)
     general = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
                                   heads, kv_heads, dim, scale, window, force_general=True)
     want = P.paged_attention_plain(case["qkv"], case["k_cache"], case["v_cache"], case["table"],
@@ -243,6 +251,13 @@ def test_flash_split_policy():
     assert K().decode_splits(8, 8, 8192) == 7
     assert K().decode_splits(1, 8, 8192) == 32
     assert K().decode_splits(1, 8, 100) == 1
+    assert K().decode_splits_tma(8, 8, 8192) == 9     # 576 blocks: 3.9 waves of 148
+    assert K().decode_splits_tma(64, 8, 8192) == 2
+    assert K().decode_splits_tma(1, 8, 8192) == 18
+    assert K().decode_splits_tma(4, 8, 100) == 1
+    assert K().tma_decode_supported(torch.bfloat16, 128, 16)
+    assert not K().tma_decode_supported(torch.bfloat16, 96, 16)
+    assert not K().tma_decode_supported(torch.float32, 128, 16)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

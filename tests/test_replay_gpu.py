@@ -179,7 +179,7 @@ def test_decode_graphs_replay_and_match_eager(dtype, tmp_path):
             results[eager] = rc.collect(trace, out, config["vocab_size"])
             if not eager:
                 assert step_function.num_graph_replays > 20
-                assert len(step_function._graphs) >= 2
+                assert len(step_function._graphs) >= (2 if name == "mixed" else 1)
         for key, row in results[True].items():
             if dtype == "float32":
                 assert np.array_equal(row, results[False][key]), key
