@@ -173,50 +173,63 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 
   if (warp == TD_CONSUMERS) {
     // ---------------- producer ----------------
-    if (lane == 0) {
-      const int* pages = p.table + (size_t)req * p.table_stride;
-      const int pages_per_tile = TD_KEYS / p.page_size;
-      int issued = 0;
-      for (int it = 0; it < num_tiles; ++it) {
-        const int stage = it % TD_STAGES;
-        if (it >= TD_STAGES) {
-          const unsigned parity = ((it / TD_STAGES) & 1) ^ 1;
-          if (!mbar_wait_bounded(&empty_bar[stage], parity)) {
-            atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
-            atomicExch(abort_flag, 1);
-            break;
-          }
+    // The whole warp walks the tiles.  Page ids are fetched 32 table entries at a time, one
+    // lane each (a coalesced load), a batch ahead of their use, so no copy waits on a table
+    // lookup.  Lane 0 owns the barriers; lanes 0..pages_per_tile-1 each issue one page's copies.
+    const int* pages = p.table + (size_t)req * p.table_stride;
+    const int ppt = TD_KEYS / p.page_size;            // pages per tile: 1, 2, 4 or 8
+    const int first_entry = tile_begin * ppt;
+    const int total_entries = num_tiles * ppt;
+    auto fetch = [&](int entry) -> int {             // table entry `entry` of this split, 0 beyond it
+      if (entry >= total_entries) return 0;
+      const int index = first_entry + entry;
+      if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
+      const int page = pages[index];
+      if (page < 0 || page >= p.num_pages) {
+        atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+        return 0;
+      }
+      return page;
+    };
+    int cur = fetch(lane), nxt = fetch(32 + lane);
+    int issued = 0;
+    for (int it = 0; it < num_tiles; ++it) {
+      const int stage = it % TD_STAGES;
+      const int e0 = it * ppt;
+      if (e0 > 0 && (e0 & 31) == 0) {                 // crossed into the next batch of entries
+        cur = nxt;
+        nxt = fetch(e0 + 32 + lane);
+      }
+      int ok = 1;
+      if (lane == 0) {
+        if (it >= TD_STAGES && !mbar_wait_bounded(&empty_bar[stage], ((it / TD_STAGES) & 1) ^ 1)) {
+          atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+          atomicExch(abort_flag, 1);
+          ok = 0;
         }
-        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+        if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
+        if (ok) mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int page = __shfl_sync(0xffffffffu, cur, (e0 + lane) & 31);
+      if (lane < ppt) {
         unsigned char* kdst = stages + stage * STAGE_BYTES;
         unsigned char* vdst = kdst + KV_BYTES;
-        mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-        const int key0 = (tile_begin + it) * TD_KEYS;
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
-          const int key = key0 + pg * p.page_size;
-          int page = 0;
-          if (key < key_hi) {
-            page = pages[key / p.page_size];
-            if (page < 0 || page >= p.num_pages) {
-              atomicOr(p.status, KVB_STATUS_BAD_PAGE);
-              page = 0;
-            }
-          }
-          const int row = (page * p.KVH + kvh) * p.page_size;
-          const int dst_off = pg * p.page_size * 128;
+        const int row = (page * p.KVH + kvh) * p.page_size;
+        const int dst_off = lane * p.page_size * 128;
 #pragma unroll
-          for (int half = 0; half < HALVES; ++half) {
-            tma_load_2d(kdst + half * (TD_KEYS * 128) + dst_off, &k_map, half * 64, row, &full_bar[stage]);
-            tma_load_2d(vdst + half * (TD_KEYS * 128) + dst_off, &v_map, half * 64, row, &full_bar[stage]);
-          }
+        for (int half = 0; half < HALVES; ++half) {
+          tma_load_2d(kdst + half * (TD_KEYS * 128) + dst_off, &k_map, half * 64, row, &full_bar[stage]);
+          tma_load_2d(vdst + half * (TD_KEYS * 128) + dst_off, &v_map, half * 64, row, &full_bar[stage]);
         }
-        issued = it + 1;
       }
-      // on an aborted run, let the copies already issued land before the block may exit
-      if (*reinterpret_cast<volatile int*>(abort_flag)) {
-        for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
-          mbar_wait_bounded(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
-      }
+      issued = it + 1;
+    }
+    // on an aborted run, let the copies already issued land before the block may exit
+    if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
+      for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
+        mbar_wait_bounded(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
     }
   } else {
     // ---------------- consumers ----------------

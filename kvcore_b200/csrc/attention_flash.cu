@@ -23,6 +23,7 @@
 #define FA_KEYS 64          // keys per K/V tile
 #define FA_THREADS 128
 #define FA_PAD 8            // bf16 elements of padding per shared-memory row (16 bytes)
+#define FA_PAGE_IDS 1024    // block-table entries staged in shared memory at a time
 
 struct FlashParams {
   bf16* out; long long out_stride;
@@ -67,17 +68,25 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const unsigned*>(&v);
 }
 
-// Element offset of every key row of a 64-key tile inside the cache (or -1: zero-fill), looked
-// up through the block table by the first 64 threads, one row each, so that the lookups of a
-// tile run in parallel and one tile ahead of the copies that use them.
+// Stage the block-table entries [first, first + FA_PAGE_IDS) of this request in shared memory
+// (one coalesced sweep by the whole block), so that no tile waits on a table lookup.
+__device__ __forceinline__ void stage_page_ids(int* ids, const FlashParams& p, const int* pages, int first) {
+  for (int i = threadIdx.x; i < FA_PAGE_IDS; i += FA_THREADS) {
+    const int index = first + i;
+    ids[i] = index < p.table_stride ? pages[index] : 0;
+  }
+}
+
+// Element offset of every key row of a 64-key tile inside the cache (or -1: zero-fill), from
+// the staged page ids; done by the first 64 threads, one row each.
 template <int D>
-__device__ __forceinline__ void lookup_tile_rows(long long* rows, const FlashParams& p, const int* pages,
-                                                 int kvh, int key0, int key_lo, int key_hi) {
+__device__ __forceinline__ void lookup_tile_rows(long long* rows, const FlashParams& p, const int* ids,
+                                                 int ids_first, int kvh, int key0, int key_lo, int key_hi) {
   if (threadIdx.x >= FA_KEYS) return;
   const int key = key0 + threadIdx.x;
   long long off = -1;
   if (key >= key_lo && key < key_hi) {
-    const int page = pages[key / p.page_size];
+    const int page = ids[key / p.page_size - ids_first];
     if (page > 0 && page < p.num_pages)
       off = ((long long)page * p.KVH + kvh) * p.page_size * D + (long long)(key % p.page_size) * D;
     else if (page != 0)
@@ -115,7 +124,8 @@ flash_paged_kernel(const FlashParams p) {
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   long long* tile_rows = reinterpret_cast<long long*>(smem_raw);  // [2][FA_KEYS] row offsets
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw + 2 * FA_KEYS * sizeof(long long));
+  int* page_ids = reinterpret_cast<int*>(smem_raw + 2 * FA_KEYS * sizeof(long long));  // [FA_PAGE_IDS]
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw + 2 * FA_KEYS * sizeof(long long) + FA_PAGE_IDS * sizeof(int));
   bf16* ks = qs + TILE_M * ROW;
   bf16* vs = ks + 2 * FA_KEYS * ROW;
 
@@ -159,10 +169,17 @@ flash_paged_kernel(const FlashParams p) {
     cp_async16(qs + r * ROW + chunk * 8, p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8, valid);
   }
   cp_async_commit();
+  // Page ids are staged FA_PAGE_IDS entries at a time; tiles_per_stage tiles fit one staging.
+  const int tiles_per_staging = FA_PAGE_IDS * p.page_size / FA_KEYS;
+  int ids_first = (tile_begin * FA_KEYS) / p.page_size;   // table entry held in page_ids[0]
+  int restage_tile = tile_begin + tiles_per_staging;       // first tile that needs the next staging
+  if (p.page_size > FA_KEYS || FA_KEYS % p.page_size) restage_tile = tile_begin + max(1, tiles_per_staging - 1);
   if (tile_begin < tile_end) {
-    lookup_tile_rows<D>(tile_rows, p, pages, kvh, tile_begin * FA_KEYS, key_lo, key_hi);
+    stage_page_ids(page_ids, p, pages, ids_first);
+    __syncthreads();
+    lookup_tile_rows<D>(tile_rows, p, page_ids, ids_first, kvh, tile_begin * FA_KEYS, key_lo, key_hi);
     if (tile_begin + 1 < tile_end)
-      lookup_tile_rows<D>(tile_rows + FA_KEYS, p, pages, kvh, (tile_begin + 1) * FA_KEYS, key_lo, key_hi);
+      lookup_tile_rows<D>(tile_rows + FA_KEYS, p, page_ids, ids_first, kvh, (tile_begin + 1) * FA_KEYS, key_lo, key_hi);
     __syncthreads();
     load_kv_tile<D>(ks, vs, p, tile_rows);
   }
@@ -203,8 +220,16 @@ flash_paged_kernel(const FlashParams p) {
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();  // tile t has landed; the row offsets of tile t (slot buf) are spent
-    if (t + 2 < tile_end)  // offsets of tile t+2 go to slot buf; published by the barrier that ends this turn
-      lookup_tile_rows<D>(tile_rows + buf * FA_KEYS, p, pages, kvh, (t + 2) * FA_KEYS, key_lo, key_hi);
+    if (t + 2 < tile_end) {  // offsets of tile t+2 go to slot buf; published by the barrier that ends this turn
+      if (t + 2 >= restage_tile) {  // uniform: the staged ids run out, fetch the next stretch
+        ids_first = ((t + 2) * FA_KEYS) / p.page_size;
+        restage_tile = t + 2 + max(1, tiles_per_staging - 1);
+        __syncthreads();
+        stage_page_ids(page_ids, p, pages, ids_first);
+        __syncthreads();
+      }
+      lookup_tile_rows<D>(tile_rows + buf * FA_KEYS, p, page_ids, ids_first, kvh, (t + 2) * FA_KEYS, key_lo, key_hi);
+    }
 
     const int wkey = SPLIT ? warp * 16 : 0;  // first key of the tile this warp scores
     float s[NB][4];
@@ -387,7 +412,7 @@ template <int D>
 static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cudaStream_t stream) {
   constexpr int ROW = D + FA_PAD;
   if (split_mode) {
-    const size_t rows_bytes = 2 * FA_KEYS * sizeof(long long);
+    const size_t rows_bytes = 2 * FA_KEYS * sizeof(long long) + FA_PAGE_IDS * sizeof(int);
     size_t smem = rows_bytes + (size_t)(16 + 4 * FA_KEYS) * ROW * sizeof(bf16);
     const size_t merge = (size_t)(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
     if (smem < rows_bytes + 16 * ROW * sizeof(bf16) + merge) smem = rows_bytes + 16 * ROW * sizeof(bf16) + merge;
@@ -407,7 +432,8 @@ static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cud
       KVB_CHECK_LAUNCH();
     }
   } else {
-    const size_t smem = 2 * FA_KEYS * sizeof(long long) + (size_t)(64 + 4 * FA_KEYS) * ROW * sizeof(bf16);
+    const size_t smem = 2 * FA_KEYS * sizeof(long long) + FA_PAGE_IDS * sizeof(int) +
+                        (size_t)(64 + 4 * FA_KEYS) * ROW * sizeof(bf16);
     static bool configured_tile = false;
     if (!configured_tile) {
       KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_paged_kernel<D, false>,

@@ -290,11 +290,11 @@ def tma_decode_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> b
 
 def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
     """Splits for the TMA decode kernel, which keeps one block per SM: the count that fills whole
-    waves of SM_COUNT blocks best, with at least four 64-key tiles per split."""
+    waves of SM_COUNT blocks best, with at least eight 64-key tiles per split."""
     base = max(1, num_reqs * num_kv_heads)
     tiles = max(1, -(-max_seq_len // 64))
     best, best_eff = 1, 0.0
-    for splits in range(1, max(1, min(64, tiles // 4)) + 1):
+    for splits in range(1, max(1, min(64, tiles // 8)) + 1):
         blocks = base * splits
         eff = blocks / (-(-blocks // SM_COUNT) * SM_COUNT)
         if eff > best_eff + 0.02:
