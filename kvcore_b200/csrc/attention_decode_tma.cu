@@ -7,11 +7,13 @@
 // issues one tiled TMA copy per page and 64-column half (cp.async.bulk.tensor.2d, 128-byte
 // swizzle) for K and for V into a ring of STAGES shared-memory stages; each stage has a
 // "full" mbarrier that the copies complete and an "empty" mbarrier that the consumers
-// release.  Four consumer warps each score 16 keys of a tile against the (at most 16) query
-// rows of the request with mma.sync m16n8k16, keep a running 32-bit softmax, and accumulate
-// their part of the output; at the end the warps merge through shared memory and the block
-// writes either the final rows (one split) or a partial (max, sum, output) to scratch that
-// flash_combine merges.
+// release.  Two groups of four consumer warps take alternate tiles (the per-tile chain of
+// score, softmax and accumulate is latency-bound, so two tiles are worked at once); each
+// warp scores 16 keys of its group's tile against the (at most 16) query rows of the request
+// with mma.sync m16n8k16, keeps a running 32-bit softmax, and accumulates its part of the
+// output; at the end all warps merge through shared memory and the block writes either the
+// final rows (one split) or a partial (max, sum, output) to scratch that a second kernel
+// merges over the splits.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the thread sets the
 // WAIT_TIMEOUT bit of the status word, the block stops waiting, drains the copies it
@@ -27,7 +29,9 @@
 
 #define TD_KEYS 64
 #define TD_STAGES 6
-#define TD_CONSUMERS 4
+#define TD_GROUPS 2        // consumer groups; group g takes the tiles t with t % TD_GROUPS == g
+#define TD_GROUP_WARPS 4   // warps of a group; warp w of a group scores keys [16w, 16w+16) of a tile
+#define TD_CONSUMERS (TD_GROUPS * TD_GROUP_WARPS)
 #define TD_THREADS ((TD_CONSUMERS + 1) * 32)
 #define TD_SPIN_LIMIT (1u << 22)
 
@@ -148,7 +152,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < TD_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], TD_CONSUMERS);
+      mbar_init(&empty_bar[s], TD_GROUP_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -248,8 +252,9 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       row_valid[h] = r < rows_total;
       row_pos[h] = context + (row_valid[h] ? r / p.G : 0);
     }
-    const int wkey = warp * 16;
-    for (int it = 0; it < num_tiles; ++it) {
+    const int group = warp / TD_GROUP_WARPS;
+    const int wkey = (warp % TD_GROUP_WARPS) * 16;
+    for (int it = group; it < num_tiles; it += TD_GROUPS) {
       const int stage = it % TD_STAGES;
       if (!mbar_wait_bounded(&full_bar[stage], (it / TD_STAGES) & 1)) {
         atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
@@ -258,18 +263,30 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
       const unsigned kbase = smem_u32(stages + stage * STAGE_BYTES);
       const unsigned vbase = kbase + KV_BYTES;
-      float s[2][4];
+      float s[2][4], s2[2][4];  // two accumulation chains (even and odd k-steps) halve the latency
 #pragma unroll
-      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+      for (int j = 0; j < 2; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+        s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.0f;
+      }
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k) {
         unsigned kb[4];
         const int key = wkey + (lane & 7) + 8 * (lane >> 4);
         const int d = k * 16 + 8 * ((lane >> 3) & 1);
         td_ldmatrix_x4(kb, kbase + swz(key, d));
-        td_mma(s[0], qf[k], kb[0], kb[1]);
-        td_mma(s[1], qf[k], kb[2], kb[3]);
+        if (k & 1) {
+          td_mma(s2[0], qf[k], kb[0], kb[1]);
+          td_mma(s2[1], qf[k], kb[2], kb[3]);
+        } else {
+          td_mma(s[0], qf[k], kb[0], kb[1]);
+          td_mma(s[1], qf[k], kb[2], kb[3]);
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] += s2[j][e];
       float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int j = 0; j < 2; ++j) {

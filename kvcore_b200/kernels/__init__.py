@@ -15,6 +15,7 @@ from .api import (
     gather_rows,
     library_is_loaded,
     linear,
+    linear_skinny,
     paged_attention,
     read_status,
     require_device,
@@ -38,6 +39,7 @@ __all__ = [
     "gather_rows",
     "library_is_loaded",
     "linear",
+    "linear_skinny",
     "paged_attention",
     "read_status",
     "require_device",

@@ -51,6 +51,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                  _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
+        "kvb_gemm_skinny_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
     }
@@ -388,6 +389,46 @@ def paged_attention(
 
 
 _mm_out_dtype_ok: bool | None = None
+SKINNY_GEMM = True          # bf16 layers of at most SKINNY_MAX_ROWS tokens stream weights through TMA
+SKINNY_MAX_ROWS = 64
+_skinny_counters: dict[int, torch.Tensor] = {}
+
+
+def skinny_ksplit(n: int, k: int) -> int:
+    """Chunks K is cut into so that a skinny layer has work for every SM (each at least 4 stages)."""
+    n_tiles, kblocks = -(-n // 64), -(-k // 128)
+    return max(1, min(-(-2 * SM_COUNT // n_tiles), kblocks // 4, 16))
+
+
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
+                  out_dtype: torch.dtype | None = None, ksplit: int | None = None) -> torch.Tensor:
+    """``x @ weight.T`` for at most 64 rows of bf16 ``x``: the weight-streaming TMA kernel."""
+    _check(x, "x", dtype=torch.bfloat16, contiguous=False)
+    _check(weight, "weight", dtype=torch.bfloat16)
+    m, k = x.shape
+    n = weight.shape[0]
+    if not 0 < m <= SKINNY_MAX_ROWS or k % 8 or x.stride(1) != 1 or x.stride(0) % 8:
+        raise KernelError(f"linear_skinny: unsupported shape x {tuple(x.shape)} strides {x.stride()}")
+    if bias is not None:
+        _check(bias, "bias", dtype=torch.bfloat16)
+    out = torch.empty((m, n), dtype=out_dtype or torch.bfloat16, device=x.device)
+    splits = ksplit or skinny_ksplit(n, k)
+    splits = max(1, min(splits, -(-k // 128), 16))
+    scratch = counters = None
+    if splits > 1:
+        mb = 8 if m <= 8 else 16 if m <= 16 else 32 if m <= 32 else 64
+        scratch = torch.empty(splits * mb * (-(-n // 64) * 64), dtype=torch.float32, device=x.device)
+        index = x.device.index or 0
+        counters = _skinny_counters.get(index)
+        if counters is None or counters.numel() < -(-n // 64):
+            counters = torch.zeros(max(4096, -(-n // 64)), dtype=torch.int32, device=x.device)
+            _skinny_counters[index] = counters
+    _call("kvb_gemm_skinny_bf16", out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
+          x.data_ptr(), x.stride(0), weight.data_ptr(), None if bias is None else bias.data_ptr(),
+          m, n, k, splits, None if scratch is None else scratch.data_ptr(),
+          None if counters is None else counters.data_ptr(), SM_COUNT, _stream())
+    return out
+
 
 
 def linear(
@@ -417,6 +458,9 @@ def linear(
         _call("kvb_gemm_f32", out.data_ptr(), x.data_ptr(), weight.data_ptr(),
               None if bias is None else bias.data_ptr(), m, n, k, x.stride(0), out.stride(0), _stream())
         return out
+    if (SKINNY_GEMM and m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.stride(0) % 8 == 0
+            and weight.is_contiguous() and x.data_ptr() % 16 == 0):
+        return linear_skinny(x, weight, bias, out_dtype=out_dtype)
     if out_dtype == torch.float32:
         if _mm_out_dtype_ok is None:
             try:
@@ -457,6 +501,7 @@ __all__ = [
     "gather_rows",
     "library_is_loaded",
     "linear",
+    "linear_skinny",
     "paged_attention",
     "read_status",
     "require_device",

@@ -73,6 +73,9 @@ class RotaryEncoding(PositionEncoding):
         if head_dim % 2:
             raise ValueError(f"rotary encoding needs an even head_dim, got {head_dim}")
         self.head_dim = int(head_dim)
+        # layers with the same frequency parameters share one cos/sin table per step
+        self.table_key = ("rope", int(head_dim), float(theta), str(rope_type), float(factor),
+                          float(low_freq_factor), float(high_freq_factor), int(original_max_position_embeddings))
         table = rope_inverse_frequencies(
             head_dim, theta, rope_type, factor, low_freq_factor, high_freq_factor,
             original_max_position_embeddings,
@@ -81,8 +84,7 @@ class RotaryEncoding(PositionEncoding):
 
     def cos_sin(self, ctx) -> torch.Tensor:
         """``[T, D/2, 2]`` (cos, sin) of this step's positions; one table per step and frequency table."""
-        key = ("rope", self.inv_freq.data_ptr(), self.inv_freq.numel())
-        return ctx.shared(key, lambda: K.rope_table(ctx.positions, self.inv_freq))
+        return ctx.shared(self.table_key, lambda: K.rope_table(ctx.positions, self.inv_freq))
 
     def apply(self, q: torch.Tensor, k: torch.Tensor | None, ctx) -> None:
         K.rope_inplace(q, k, ctx.positions, self.inv_freq)

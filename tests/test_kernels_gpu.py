@@ -382,3 +382,33 @@ def test_sample_follows_the_distribution():
     expected = torch.softmax(base.double(), dim=-1) * draws
     chi2 = float(((counts - expected) ** 2 / expected).sum())
     assert chi2 < 50.0, chi2  # 15 degrees of freedom: 50 is far in the tail
+
+
+# ---- weight-streaming linear layer (decode) ---------------------------------------------------
+@pytest.mark.parametrize("m,n,k,ksplit", [
+    (1, 64, 128, 1), (3, 200, 96, 1), (8, 4096, 4096, None), (8, 4096, 4096, 1), (8, 6144, 4096, 5),
+    (9, 515, 1000, 2), (16, 130, 8, 1), (33, 1024, 2048, 4), (64, 96, 14336, 16), (64, 4096, 1024, None),
+    (5, 28672, 1024, None), (2, 70, 520, 3),
+])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_skinny(m, n, k, ksplit, bias):
+    x = randn(m, k, dtype=torch.bfloat16, seed=20)
+    w = randn(n, k, dtype=torch.bfloat16, seed=21, scale=0.05)
+    b = randn(n, dtype=torch.bfloat16, seed=22) if bias else None
+    want = x.float() @ w.float().T + (b.float() if bias else 0)
+    got = K().linear_skinny(x, w, b, ksplit=ksplit)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=2e-2)
+    wide = K().linear_skinny(x, w, b, out_dtype=torch.float32, ksplit=ksplit)
+    torch.testing.assert_close(wide, want, rtol=1e-3, atol=2e-3)
+    again = K().linear_skinny(x, w, b, out_dtype=torch.float32, ksplit=ksplit)
+    assert torch.equal(wide, again)  # split-K partials are added in a fixed order
+    assert K().read_status() == 0
+
+
+def test_linear_skinny_takes_row_views():
+    """x may be a column slice of a wider buffer (rows 16-byte aligned), as q inside qkv is."""
+    full = randn(6, 512 + 256, dtype=torch.bfloat16, seed=23)
+    x = full[:, 256:]
+    w = randn(300, 512, dtype=torch.bfloat16, seed=24, scale=0.05)
+    torch.testing.assert_close(K().linear(x, w).float(), x.float() @ w.float().T, rtol=1.6e-2, atol=2e-2)
