@@ -4,8 +4,8 @@
 // kernel is built to keep as many bytes in flight as one SM can hold.  One block per SM-sized
 // share of the work: a (request, kv head, split) triple.  A producer warp walks the split's
 // key range in tiles of 64 keys and, for each tile, looks the pages up in the block table and
-// issues one tiled TMA copy per page and 64-column half (cp.async.bulk.tensor.2d, 128-byte
-// swizzle) for K and for V into a ring of STAGES shared-memory stages; each stage has a
+// issues one tiled TMA copy per page (cp.async.bulk.tensor.2d, 128-byte swizzle; the block of
+// one page and kv head is contiguous in the cache) for K and for V into a ring of STAGES shared-memory stages; each stage has a
 // "full" mbarrier that the copies complete and an "empty" mbarrier that the consumers
 // release.  Two groups of four consumer warps take alternate tiles (the per-tile chain of
 // score, softmax and accumulate is latency-bound, so two tiles are worked at once); each
@@ -102,11 +102,14 @@ __device__ __forceinline__ unsigned td_pack(float lo, float hi) {
   return *reinterpret_cast<const unsigned*>(&v);
 }
 
-// Byte offset of element (row, d) inside one stage's K (or V) area: D/64 halves of
-// [64 rows][128 bytes], 16-byte chunks XOR-swizzled with the row (TMA's 128-byte swizzle).
-__device__ __forceinline__ unsigned swz(int row, int d) {
-  const int half = d >> 6, chunk = (d & 63) >> 3;
-  return (unsigned)(half * (TD_KEYS * 128) + row * 128 + ((chunk ^ (row & 7)) << 4));
+// Byte offset of element (key, d) inside one stage's K (or V) area.  The cache is described to
+// TMA as rows of 64 elements (128 bytes), so a key of D = 64*HALVES elements is HALVES
+// consecutive rows and a whole page of a head is one contiguous box.  Shared-memory row
+// r = key*HALVES + d/64 holds 8 chunks of 16 bytes, XOR-swizzled with r (128-byte swizzle).
+template <int HALVES>
+__device__ __forceinline__ unsigned swz(int key, int d) {
+  const int r = key * HALVES + (d >> 6), chunk = (d & 63) >> 3;
+  return (unsigned)(r * 128 + ((chunk ^ (r & 7)) << 4));
 }
 
 template <int D>
@@ -220,13 +223,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       if (lane < ppt) {
         unsigned char* kdst = stages + stage * STAGE_BYTES;
         unsigned char* vdst = kdst + KV_BYTES;
-        const int row = (page * p.KVH + kvh) * p.page_size;
-        const int dst_off = lane * p.page_size * 128;
-#pragma unroll
-        for (int half = 0; half < HALVES; ++half) {
-          tma_load_2d(kdst + half * (TD_KEYS * 128) + dst_off, &k_map, half * 64, row, &full_bar[stage]);
-          tma_load_2d(vdst + half * (TD_KEYS * 128) + dst_off, &v_map, half * 64, row, &full_bar[stage]);
-        }
+        const int row = (page * p.KVH + kvh) * p.page_size * HALVES;   // in rows of 64 elements
+        const int dst_off = lane * p.page_size * HALVES * 128;
+        tma_load_2d(kdst + dst_off, &k_map, 0, row, &full_bar[stage]);     // one contiguous page of a head
+        tma_load_2d(vdst + dst_off, &v_map, 0, row, &full_bar[stage]);
       }
       issued = it + 1;
     }
@@ -274,7 +274,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         unsigned kb[4];
         const int key = wkey + (lane & 7) + 8 * (lane >> 4);
         const int d = k * 16 + 8 * ((lane >> 3) & 1);
-        td_ldmatrix_x4(kb, kbase + swz(key, d));
+        td_ldmatrix_x4(kb, kbase + swz<HALVES>(key, d));
         if (k & 1) {
           td_mma(s2[0], qf[k], kb[0], kb[1]);
           td_mma(s2[1], qf[k], kb[2], kb[3]);
@@ -337,7 +337,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         unsigned vb[4];
         const int key = wkey + (lane & 7) + 8 * ((lane >> 3) & 1);
         const int d = j * 8 + 8 * (lane >> 4);
-        td_ldmatrix_x4_trans(vb, vbase + swz(key, d));
+        td_ldmatrix_x4_trans(vb, vbase + swz<HALVES>(key, d));
         td_mma(o[j], pa, vb[0], vb[1]);
         td_mma(o[j + 1], pa, vb[2], vb[3]);
       }
@@ -443,7 +443,8 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // Writes a 128-byte tensor map describing one layer's K (or V) cache [pages, KVH, page, D] bf16
-// as a 2-D tensor [pages*KVH*page rows, D columns] with boxes of [page rows, 64 columns].
+// as a 2-D tensor of 64-element rows [pages*KVH*page*(D/64) rows, 64 columns] with boxes of
+// [page*(D/64) rows, 64 columns]: one box is the contiguous block of one page and kv head.
 extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long long num_pages, int KVH,
                                       int page_size, int D) {
   KVB_REQUIRE(D == 64 || D == 128, "kv tensor map: head_dim must be 64 or 128");
@@ -453,9 +454,10 @@ extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long lon
   EncodeTiledFn encode = encode_tiled_fn();
   KVB_REQUIRE(encode != nullptr, "kv tensor map: the driver does not export cuTensorMapEncodeTiled");
   alignas(64) CUtensorMap map;
-  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * KVH * page_size};
-  const cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
-  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  const int halves = D / 64;
+  const cuuint64_t dims[2] = {64, (cuuint64_t)num_pages * KVH * page_size * halves};
+  const cuuint64_t strides[1] = {64 * sizeof(bf16)};
+  const cuuint32_t box[2] = {64, (cuuint32_t)(page_size * halves)};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
