@@ -458,9 +458,9 @@ def linear(
         _call("kvb_gemm_f32", out.data_ptr(), x.data_ptr(), weight.data_ptr(),
               None if bias is None else bias.data_ptr(), m, n, k, x.stride(0), out.stride(0), _stream())
         return out
-    # Measured on B200: the streaming kernel beats the library product for few rows and narrow
-    # outputs (where K can be cut); elsewhere the library is as fast or faster.
-    if (SKINNY_GEMM and m <= 16 and n <= 8192 and k % 8 == 0 and x.stride(0) % 8 == 0
+    # Measured on B200: the streaming kernel beats the library product only for very few rows
+    # and narrow outputs (where K can be cut in two); elsewhere the library is as fast or faster.
+    if (SKINNY_GEMM and m <= 4 and n <= 4096 and k % 8 == 0 and x.stride(0) % 8 == 0
             and weight.is_contiguous() and x.data_ptr() % 16 == 0):
         return linear_skinny(x, weight, bias, out_dtype=out_dtype, ksplit=2 if k >= 2048 else 1)
     if out_dtype == torch.float32:
