@@ -499,3 +499,96 @@ extern "C" int kvb_flash_paged_attention(void* out, long long out_stride, const 
   }
   return kvb_fail(-1, "flash attention: unsupported head_dim", __FILE__, __LINE__);
 }
+
+// ------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate (see no_alloc_api.h): scratch and
+// status word live in this file's own device arrays.
+// ------------------------------------------------------------------------------------------
+#include "no_alloc_api.h"
+
+static __device__ __align__(256) float kvb_static_scratch[KVB_STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) int kvb_static_status_word[64];
+
+// In host code the two names above are only stand-ins for the device arrays; the addresses a
+// kernel can use come from cudaGetSymbolAddress, looked up once per device.
+static float* g_static_scratch_ptr[64] = {nullptr};
+static int* g_static_status_ptr[64] = {nullptr};
+
+static int static_arrays(float** scratch, int** status) {
+  int device = 0;
+  KVB_CHECK_CUDA(cudaGetDevice(&device));
+  KVB_REQUIRE(device >= 0 && device < 64, "static attention: device index out of range");
+  if (g_static_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    KVB_CHECK_CUDA(cudaGetSymbolAddress(&ptr, kvb_static_scratch));
+    KVB_REQUIRE(ptr != nullptr, "static attention: no device address for the scratch array");
+    void* word = nullptr;
+    KVB_CHECK_CUDA(cudaGetSymbolAddress(&word, kvb_static_status_word));
+    KVB_REQUIRE(word != nullptr, "static attention: no device address for the status word");
+    g_static_status_ptr[device] = static_cast<int*>(word);
+    g_static_scratch_ptr[device] = static_cast<float*>(ptr);
+  }
+  *scratch = g_static_scratch_ptr[device];
+  *status = g_static_status_ptr[device];
+  return 0;
+}
+
+extern "C" int kvb_flash_paged_attention_static(void* out, long long out_stride, const void* q,
+                                                long long q_stride, const void* k_cache, const void* v_cache,
+                                                const int* table, int table_stride, const int* query_start,
+                                                const int* context_lens, int num_reqs, int max_query_len,
+                                                int H, int KVH, int D, int page_size, int num_pages,
+                                                float scale, int window, int num_splits, cudaStream_t stream) {
+  if (num_reqs == 0) return 0;
+  KVB_REQUIRE(D % 16 == 0 && D >= 16 && D <= 128, "static attention: head_dim must be a multiple of 16 up to 128");
+  KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "static attention: H must be a multiple of KVH");
+  KVB_REQUIRE(page_size > 0 && num_pages > 1, "static attention: empty cache");
+  KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "static attention: batch too large for one launch");
+  KVB_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && (q_stride % 8) == 0,
+              "static attention: q and the caches must be 16-byte aligned");
+  const int splits = num_splits < 1 ? 1 : num_splits;
+  const int max_rows = max_query_len * (H / KVH);
+  const bool split_mode = max_rows <= 16;
+  KVB_REQUIRE(split_mode || splits == 1, "static attention: splits need at most 16 rows per kv head");
+  const long long needed = splits > 1 ? (long long)num_reqs * KVH * splits * 16 * (D + 2) : 0;
+  KVB_REQUIRE(needed <= (long long)KVB_STATIC_SCRATCH_FLOATS,
+              "static attention: num_reqs * KVH * num_splits * 16 * (D + 2) exceeds the built-in scratch "
+              "of KVB_STATIC_SCRATCH_FLOATS floats");
+  float* scratch = nullptr;
+  int* status = nullptr;
+  if (int rc = static_arrays(&scratch, &status)) return rc;
+  KVB_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int), stream));  // the one thing that must start at zero
+  FlashParams p;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.table = table; p.table_stride = table_stride;
+  p.query_start = query_start; p.context_lens = context_lens;
+  p.num_reqs = num_reqs; p.H = H; p.KVH = KVH; p.G = H / KVH;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  p.num_splits = splits;
+  p.partial_o = scratch;
+  p.partial_ml = scratch + (size_t)num_reqs * KVH * splits * 16 * D;
+  switch (D) {
+    case 16: return launch_flash<16>(p, split_mode, max_rows, stream);
+    case 32: return launch_flash<32>(p, split_mode, max_rows, stream);
+    case 48: return launch_flash<48>(p, split_mode, max_rows, stream);
+    case 64: return launch_flash<64>(p, split_mode, max_rows, stream);
+    case 80: return launch_flash<80>(p, split_mode, max_rows, stream);
+    case 96: return launch_flash<96>(p, split_mode, max_rows, stream);
+    case 112: return launch_flash<112>(p, split_mode, max_rows, stream);
+    case 128: return launch_flash<128>(p, split_mode, max_rows, stream);
+  }
+  return kvb_fail(-1, "static attention: unsupported head_dim", __FILE__, __LINE__);
+}
+
+extern "C" int kvb_static_status(int* out) {
+  float* scratch = nullptr;
+  int* status = nullptr;
+  if (int rc = static_arrays(&scratch, &status)) return rc;
+  KVB_CHECK_CUDA(cudaMemcpy(out, status, sizeof(int), cudaMemcpyDeviceToHost));
+  KVB_CHECK_CUDA(cudaMemset(status, 0, sizeof(int)));
+  return 0;
+}
