@@ -28,8 +28,8 @@
 #include "common.cuh"
 
 #define TD_KEYS 64
-#define TD_STAGES 6
-#define TD_GROUPS 2        // consumer groups; group g takes the tiles t with t % TD_GROUPS == g
+#define TD_STAGES 3
+#define TD_GROUPS 1        // consumer groups; group g takes the tiles t with t % TD_GROUPS == g
 #define TD_GROUP_WARPS 4   // warps of a group; warp w of a group scores keys [16w, 16w+16) of a tile
 #define TD_CONSUMERS (TD_GROUPS * TD_GROUP_WARPS)
 #define TD_THREADS ((TD_CONSUMERS + 1) * 32)
@@ -113,7 +113,7 @@ __device__ __forceinline__ unsigned swz(int key, int d) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(TD_THREADS, 1)
+__global__ void __launch_bounds__(TD_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const DecodeParams p) {
   constexpr int HALVES = D / 64;

@@ -290,19 +290,15 @@ def tma_decode_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> b
 
 
 def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Splits for the TMA decode kernel, which keeps one block per SM: the count that fills whole
-    waves of SM_COUNT blocks best, with at least eight 64-key tiles per split."""
+    """Splits for the TMA decode kernel, which keeps two blocks per SM: as many as still fit one
+    wave of blocks (measured best on B200), with at least eight 64-key tiles per split."""
     base = max(1, num_reqs * num_kv_heads)
     tiles = max(1, -(-max_seq_len // 64))
-    best, best_eff = 1, 0.0
-    for splits in range(1, max(1, min(64, tiles // 8)) + 1):
-        blocks = base * splits
-        eff = blocks / (-(-blocks // SM_COUNT) * SM_COUNT)
-        if eff > best_eff + 0.02:
-            best, best_eff = splits, eff
-    return best
+    wave = SM_COUNT * TMA_DECODE_BLOCKS_PER_SM
+    return max(1, min(wave // base, tiles // 8, 64))
 
 
+TMA_DECODE_BLOCKS_PER_SM = 2
 _kv_tensor_maps: dict[tuple, tuple] = {}
 
 

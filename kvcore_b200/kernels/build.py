@@ -157,6 +157,9 @@ def build(verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
                     stale.unlink()
                 except OSError:
                     pass
+        for stale in (target_dir / "_build").iterdir():  # object files of older source states
+            if stale.is_dir() and stale != objects_dir:
+                shutil.rmtree(stale, ignore_errors=True)
         print(f"[kvcore_b200] built {library.name} in {time.time() - started:.0f}s",
               file=sys.stderr, flush=True)
         return library

@@ -251,8 +251,8 @@ def test_flash_split_policy():
     assert K().decode_splits(8, 8, 8192) == 7
     assert K().decode_splits(1, 8, 8192) == 32
     assert K().decode_splits(1, 8, 100) == 1
-    assert K().decode_splits_tma(8, 8, 8192) == 9     # 576 blocks: 3.9 waves of 148
-    assert K().decode_splits_tma(64, 8, 8192) == 2
+    assert K().decode_splits_tma(8, 8, 8192) == 4     # 256 blocks: one wave of 2 x 148
+    assert K().decode_splits_tma(64, 8, 8192) == 1
     assert K().decode_splits_tma(1, 8, 8192) == 16
     assert K().decode_splits_tma(4, 8, 100) == 1
     assert K().tma_decode_supported(torch.bfloat16, 128, 16)
