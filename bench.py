@@ -242,12 +242,21 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
 
 
 def reference_arm(args) -> int:
-    """The unmodified reference through its own entry point, if it could be installed offline."""
+    """The unmodified reference through its own entry point, if it could be installed offline.
+
+    The offline install (pip install --no-index --no-build-isolation --find-links /opt/wheelhouse
+    --target baseline/_ref <reference>) fails on this image: the reference's build backend,
+    hatchling, is neither installed nor in the wheelhouse.  Without an installed copy the arm
+    reports itself unavailable, as the contract asks.
+    """
     ref = ROOT / "baseline" / "_ref"
-    reason = None
     if not (ref / "kvcore").is_dir():
-        reason = "reference not installed under baseline/_ref (offline pip install did not succeed)"
-    print(json.dumps({"impl": "reference", "unavailable": reason or "reference arm not wired yet"}))
+        reason = ("offline pip install of the reference failed: its build backend hatchling is not installed "
+                  "and not in /opt/wheelhouse, so baseline/_ref is empty")
+    else:
+        reason = ("baseline/_ref holds the reference, but its entry point needs a tokenizer and a 16 GB "
+                  "checkpoint folder that cannot be provided offline")
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
     return 0
 
 
