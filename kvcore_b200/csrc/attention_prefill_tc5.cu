@@ -1,0 +1,526 @@
+// Paged flash attention for prompt portions on the 5th-generation tensor cores (sm_100a):
+// tcgen05.mma with accumulators in tensor memory, operands staged by TMA.  bf16, head size 128.
+//
+// A block owns 128 query rows of one (request, kv head); a row is a (token, query head of the
+// group) pair, so the G heads that share a kv head reuse every K/V tile.  It walks the keys in
+// tiles of 128.  Six warps:
+//   warps 0-3  softmax: thread t owns row t = TMEM lane t.  Per tile it reads its row of
+//              S = Q.K^T from TMEM (tcgen05.ld), masks, keeps the running max and sum (32-bit),
+//              writes P = exp2(...) as bf16 into shared memory in the swizzled K-major operand
+//              layout, and rescales its row of O in TMEM when the max moved.
+//   warp 4     producer: looks pages up in the block table (batched, a batch ahead) and issues
+//              the tiled TMA copies of K and V (two 64-column boxes per page, 128-byte swizzle)
+//              into two-stage rings.
+//   warp 5     one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
+//              softmax warps work on S(j), then O += P(j).V(j) (V as an MN-major operand).
+// mbarriers: k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S
+// buffers), p_ready (softmax -> MMA), pv_done (MMA -> softmax).  tcgen05.commit arrives on the
+// barriers that follow MMAs.  Every wait is bounded: on a time-out the thread sets the
+// WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it returns.
+//
+// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O [256,384).
+// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB | P 32 KB (all 1024-byte aligned, 128B swizzle).
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#define T5_BM 128
+#define T5_BN 128
+#define T5_D 128
+#define T5_THREADS 192
+#define T5_SPIN_LIMIT (1u << 22)
+#define T5_HALF_BYTES (128 * 128)        // one 64-column half of a 128-row operand tile
+#define T5_TILE_BYTES (2 * T5_HALF_BYTES)
+
+struct Tc5Params {
+  bf16* out; long long out_stride;
+  const bf16* q; long long q_stride;
+  const int* table; int table_stride;
+  const int* query_start; const int* context_lens;
+  int num_reqs, H, KVH, G, page_size, num_pages, window;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned t5_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void t5_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void t5_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(t5_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity) {
+  for (unsigned spin = 0; spin < T5_SPIN_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(t5_smem(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if (spin > 32) __nanosleep(32);
+  }
+  return false;
+}
+__device__ __forceinline__ void t5_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(t5_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(t5_smem(bar))
+      : "memory");
+}
+// Shared-memory matrix descriptor: 128-byte swizzle, version 1 (sm_100).
+__device__ __forceinline__ unsigned long long t5_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(lbo_bytes >> 4) << 16) |
+         ((unsigned long long)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// D[tmem] (+)= A[smem] . B[smem], one elected thread.
+__device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void t5_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned* r = reinterpret_cast<unsigned*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void t5_st32(unsigned taddr, const float (&v)[32]) {
+  const unsigned* r = reinterpret_cast<const unsigned*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void t5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Byte offset of the 16-byte chunk `chunk16` (0..15 across the 128 columns) of row `r` in a
+// [128 rows x 128 columns] bf16 operand tile stored as two swizzled 64-column halves.
+__device__ __forceinline__ unsigned t5_chunk_off(int r, int chunk16) {
+  return (unsigned)((chunk16 >> 3) * T5_HALF_BYTES + r * 128 + (((chunk16 & 7) ^ (r & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(T5_THREADS, 1)
+flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                         const Tc5Params p) {
+  extern __shared__ unsigned char t5_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_smem = base;
+  unsigned char* k_smem = q_smem + T5_TILE_BYTES;           // 2 stages
+  unsigned char* v_smem = k_smem + 2 * T5_TILE_BYTES;       // 2 stages
+  unsigned char* p_smem = v_smem + 2 * T5_TILE_BYTES;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_smem + T5_TILE_BYTES);
+  unsigned long long* k_full = bars;        // [2]
+  unsigned long long* k_empty = bars + 2;   // [2]
+  unsigned long long* v_full = bars + 4;    // [2]
+  unsigned long long* v_empty = bars + 6;   // [2]
+  unsigned long long* s_full = bars + 8;    // [2]
+  unsigned long long* s_free = bars + 10;   // [2]
+  unsigned long long* p_ready = bars + 12;
+  unsigned long long* pv_done = bars + 13;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int req = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_begin = p.query_start[req];
+  const int q_len = p.query_start[req + 1] - q_begin;
+  const int context = p.context_lens[req];
+  const int rows_total = q_len * p.G;
+  const int row0 = tile * T5_BM;
+  if (row0 >= rows_total) return;  // whole block, before any barrier or allocation
+
+  const int last_row = min(row0 + T5_BM, rows_total) - 1;
+  const int first_pos = context + row0 / p.G;
+  const int last_pos = context + last_row / p.G;
+  const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int key_hi = last_pos + 1;
+  const int tile_begin = key_lo / T5_BN;
+  const int num_tiles = (key_hi + T5_BN - 1) / T5_BN - tile_begin;   // >= 1
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      t5_mbar_init(&k_full[i], 1);
+      t5_mbar_init(&k_empty[i], 1);
+      t5_mbar_init(&v_full[i], 1);
+      t5_mbar_init(&v_empty[i], 1);
+      t5_mbar_init(&s_full[i], 1);
+      t5_mbar_init(&s_free[i], 128);
+    }
+    t5_mbar_init(p_ready, 128);
+    t5_mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 5) {  // tensor memory: 512 columns for this block
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_smem(tmem_slot)), "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  // Q rows -> shared memory in the swizzled K-major operand layout (thread t of warps 0-3: row t)
+  if (warp < 4) {
+    const int r = threadIdx.x;
+    const int flat = row0 + r;
+    const bool valid = flat < rows_total;
+    const bf16* src = p.q + (size_t)(q_begin + (valid ? flat / p.G : 0)) * p.q_stride +
+                      (size_t)(kvh * p.G + (valid ? flat % p.G : 0)) * T5_D;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+      *reinterpret_cast<uint4*>(q_smem + t5_chunk_off(r, c)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the MMA's reads
+  }
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+  const unsigned tmem_o = tmem_base + 256;
+
+  if (warp == 4) {
+    // ================= producer =================
+    const int* pages = p.table + (size_t)req * p.table_stride;
+    const int ppt = T5_BN / p.page_size;          // pages per tile: 2..16
+    const int first_entry = tile_begin * ppt;
+    const int total_entries = num_tiles * ppt;
+    auto fetch = [&](int entry) -> int {
+      if (entry >= total_entries) return 0;
+      const int index = first_entry + entry;
+      if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
+      const int page = pages[index];
+      if (page < 0 || page >= p.num_pages) {
+        atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+        return 0;
+      }
+      return page;
+    };
+    int cur = fetch(lane), nxt = fetch(32 + lane);
+    int issued_k = 0, issued_v = 0;
+    for (int j = 0; j < num_tiles; ++j) {
+      const int s = j & 1;
+      const int e0 = j * ppt;
+      if (e0 > 0 && (e0 & 31) == 0) {
+        cur = nxt;
+        nxt = fetch(e0 + 32 + lane);
+      }
+      const int page = __shfl_sync(0xffffffffu, cur, (e0 + lane) & 31);
+      const int row = (page * p.KVH + kvh) * p.page_size;
+      const int dst_off = lane * p.page_size * 128;
+      // K(j)
+      int ok = 1;
+      if (lane == 0) {
+        if (j >= 2 && !t5_wait(&k_empty[s], ((j >> 1) - 1) & 1)) ok = 0;
+        if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
+        if (ok) t5_expect_tx(&k_full[s], T5_TILE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < ppt) {
+        unsigned char* dst = k_smem + s * T5_TILE_BYTES + dst_off;
+        t5_tma_2d(dst, &k_map, 0, row, &k_full[s]);
+        t5_tma_2d(dst + T5_HALF_BYTES, &k_map, 64, row, &k_full[s]);
+      }
+      issued_k = j + 1;
+      // V(j)
+      if (lane == 0) {
+        if (j >= 2 && !t5_wait(&v_empty[s], ((j >> 1) - 1) & 1)) ok = 0;
+        if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
+        if (ok) t5_expect_tx(&v_full[s], T5_TILE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < ppt) {
+        unsigned char* dst = v_smem + s * T5_TILE_BYTES + dst_off;
+        t5_tma_2d(dst, &v_map, 0, row, &v_full[s]);
+        t5_tma_2d(dst + T5_HALF_BYTES, &v_map, 64, row, &v_full[s]);
+      }
+      issued_v = j + 1;
+    }
+    if (lane == 0 && (issued_k < num_tiles || issued_v < num_tiles)) {
+      atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+      atomicExch(abort_flag, 1);
+      // let the copies that were issued land before the block may exit
+      for (int j = max(0, issued_k - 2); j < issued_k; ++j) t5_wait(&k_full[j & 1], (j >> 1) & 1);
+      for (int j = max(0, issued_v - 2); j < issued_v; ++j) t5_wait(&v_full[j & 1], (j >> 1) & 1);
+    }
+  } else if (warp == 5) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      // instruction descriptors: f32 accumulate, bf16 x bf16, M = 128, N = 128
+      const unsigned idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(T5_BN >> 3) << 17) |
+                                  ((unsigned)(T5_BM >> 4) << 24);
+      const unsigned idesc_s = idesc_base;                // A, B both K-major
+      const unsigned idesc_pv = idesc_base | (1u << 16);  // B (= V) MN-major
+      const unsigned q_addr = t5_smem(q_smem), p_addr = t5_smem(p_smem);
+      bool ok = true;
+      auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
+        const unsigned k_addr = t5_smem(k_smem + (j & 1) * T5_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < T5_D / 16; ++kk) {
+          const unsigned off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;
+          t5_mma(tmem_base + (j & 1) * T5_BN, t5_desc(q_addr + off, 16, 1024), t5_desc(k_addr + off, 16, 1024),
+                 idesc_s, kk > 0);
+        }
+        t5_commit(&s_full[j & 1]);
+        t5_commit(&k_empty[j & 1]);
+      };
+      if (!t5_wait(&k_full[0], 0)) ok = false;
+      if (ok) {
+        t5_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        if (j + 1 < num_tiles) {
+          const int n = j + 1;
+          if (!t5_wait(&k_full[n & 1], (n >> 1) & 1)) { ok = false; break; }
+          if (n >= 2 && !t5_wait(&s_free[n & 1], ((n >> 1) - 1) & 1)) { ok = false; break; }
+          t5_fence_after();
+          issue_s(n);
+        }
+        if (!t5_wait(p_ready, j & 1)) { ok = false; break; }
+        if (!t5_wait(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
+        t5_fence_after();
+        const unsigned v_addr = t5_smem(v_smem + (j & 1) * T5_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA
+          const unsigned a_off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;   // P: K-major, keys along K
+          const unsigned b_off = kk * 16 * 128;                                // V: 16 key rows down
+          t5_mma(tmem_o, t5_desc(p_addr + a_off, 16, 1024), t5_desc(v_addr + b_off, T5_HALF_BYTES, 1024),
+                 idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        t5_commit(pv_done);
+        t5_commit(&v_empty[j & 1]);
+      }
+      if (!ok) {
+        atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+        atomicExch(abort_flag, 1);
+      }
+    }
+  } else {
+    // ================= softmax: thread t owns row t =================
+    const int r = threadIdx.x;
+    const int flat = row0 + r;
+    const bool row_valid = flat < rows_total;
+    const int pos = context + (row_valid ? flat / p.G : 0);
+    const int row_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const unsigned lane_addr = ((unsigned)(warp * 32) << 16);
+    float row_max = -INFINITY, row_sum = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < num_tiles; ++j) {
+      const int b = j & 1;
+      if (!t5_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
+      t5_fence_after();
+      float s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) t5_ld32(tmem_base + lane_addr + b * T5_BN + c * 32, s[c]);
+      t5_wait_ld();
+      t5_fence_before();
+      t5_arrive(&s_free[b]);
+      const int key0 = (tile_begin + j) * T5_BN;
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + c * 32 + i;
+          const bool seen = row_valid && key <= pos && key >= row_lo;
+          const float v = seen ? s[c][i] * p.scale_log2 : -INFINITY;
+          s[c][i] = v;
+          tile_max = fmaxf(tile_max, v);
+        }
+      }
+      const float new_max = fmaxf(row_max, tile_max);
+      const float correction = (row_max == -INFINITY) ? (new_max == -INFINITY ? 1.0f : 0.0f) : exp2f(row_max - new_max);
+      row_max = new_max;
+      float tile_sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float pv = (s[c][i] == -INFINITY) ? 0.0f : exp2f(s[c][i] - new_max);
+          s[c][i] = pv;
+          tile_sum += pv;
+        }
+      }
+      row_sum = row_sum * correction + tile_sum;
+      if (j > 0) {  // P buffer free and O quiescent once PV(j-1) has completed
+        if (!t5_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
+        t5_fence_after();
+      }
+      // P row -> shared memory (bf16, swizzled K-major operand layout): 16 chunks of 8 keys
+#pragma unroll
+      for (int c16 = 0; c16 < 16; ++c16) {
+        const float* src = &s[c16 >> 2][(c16 & 3) * 8];
+        uint4 packed;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(src[0], src[1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(src[2], src[3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(src[4], src[5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(src[6], src[7]);
+        packed.x = *reinterpret_cast<unsigned*>(&t0);
+        packed.y = *reinterpret_cast<unsigned*>(&t1);
+        packed.z = *reinterpret_cast<unsigned*>(&t2);
+        packed.w = *reinterpret_cast<unsigned*>(&t3);
+        *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c16)) = packed;
+      }
+      // rescale this row of O when any row of the warp moved its max
+      if (j > 0 && !__all_sync(0xffffffffu, correction == 1.0f)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          t5_ld32(tmem_o + lane_addr + c * 32, o);
+          t5_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= correction;
+          t5_st32(tmem_o + lane_addr + c * 32, o);
+        }
+        t5_wait_st();
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      t5_fence_before();
+      t5_arrive(p_ready);
+    }
+    if (ok && !t5_wait(pv_done, (num_tiles - 1) & 1)) ok = false;
+    if (ok) {
+      t5_fence_after();
+      const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+      bf16* dst = nullptr;
+      if (row_valid)
+        dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float o[32];
+        t5_ld32(tmem_o + lane_addr + c * 32, o);
+        t5_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 packed;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            packed.x = *reinterpret_cast<unsigned*>(&t0);
+            packed.y = *reinterpret_cast<unsigned*>(&t1);
+            packed.z = *reinterpret_cast<unsigned*>(&t2);
+            packed.w = *reinterpret_cast<unsigned*>(&t3);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = packed;
+          }
+        }
+      }
+    } else {
+      atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+      atomicExch(abort_flag, 1);
+    }
+  }
+
+  // ---- everyone meets; the allocating warp frees the tensor memory ----
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    t5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u));
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*T5EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static T5EncodeFn t5_encode_fn() {
+  static T5EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<T5EncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map of one layer's K (or V) cache [pages, KVH, page, 128] bf16 as [rows, 128 columns] with
+// boxes of [page rows, 64 columns] (one 64-column half of a page of a head), 128-byte swizzle.
+extern "C" int kvb_make_kv_half_tensor_map(void* map_out, const void* cache, long long num_pages, int KVH,
+                                           int page_size, int D) {
+  KVB_REQUIRE(D == T5_D, "kv half tensor map: head_dim must be 128");
+  KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
+              "kv half tensor map: page size must be 8, 16, 32 or 64");
+  KVB_REQUIRE(aligned16(cache), "kv half tensor map: the cache must be 16-byte aligned");
+  T5EncodeFn encode = t5_encode_fn();
+  KVB_REQUIRE(encode != nullptr, "kv half tensor map: the driver does not export cuTensorMapEncodeTiled");
+  alignas(64) CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * KVH * page_size};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
+  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
+                             box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  KVB_REQUIRE(rc == CUDA_SUCCESS, "kv half tensor map: cuTensorMapEncodeTiled failed");
+  memcpy(map_out, &map, sizeof(map));
+  return 0;
+}
+
+extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void* q, long long q_stride,
+                                     const void* k_map_host, const void* v_map_host, const int* table,
+                                     int table_stride, const int* query_start, const int* context_lens,
+                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
+                                     int num_pages, float scale, int window, cudaStream_t stream) {
+  if (num_reqs == 0) return 0;
+  KVB_REQUIRE(D == T5_D, "prefill attention (tcgen05): head_dim must be 128");
+  KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
+              "prefill attention (tcgen05): page size must be 8, 16, 32 or 64");
+  KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "prefill attention (tcgen05): H must be a multiple of KVH");
+  KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "prefill attention (tcgen05): batch too large for one launch");
+  KVB_REQUIRE(aligned16(q) && aligned16(out) && (q_stride % 8) == 0 && (out_stride % 8) == 0,
+              "prefill attention (tcgen05): q and out must be 16-byte aligned");
+  KVB_REQUIRE(k_map_host != nullptr && v_map_host != nullptr, "prefill attention (tcgen05): tensor maps are missing");
+  Tc5Params p;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.table = table; p.table_stride = table_stride;
+  p.query_start = query_start; p.context_lens = context_lens;
+  p.num_reqs = num_reqs; p.H = H; p.KVH = KVH; p.G = H / KVH;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = kvb_status_word();
+  KVB_REQUIRE(p.status != nullptr, "prefill attention (tcgen05): no status word");
+  alignas(64) CUtensorMap k_map, v_map;
+  memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
+  memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
+  constexpr size_t SMEM = 1024 + 6 * T5_TILE_BYTES + 16 * 8;
+  static bool configured = false;
+  if (!configured) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    configured = true;
+  }
+  const int max_rows = max_query_len * p.G;
+  dim3 grid((max_rows + T5_BM - 1) / T5_BM, KVH, num_reqs);
+  flash_prefill_tc5_kernel<<<grid, T5_THREADS, SMEM, stream>>>(k_map, v_map, p);
+  KVB_CHECK_LAUNCH();
+  return 0;
+}

@@ -9,6 +9,7 @@ from .api import (
     check_attention_shape,
     decode_splits,
     decode_splits_tma,
+    tc5_prefill_supported,
     tma_decode_supported,
     ensure_built,
     flash_attention_supported,
@@ -33,6 +34,7 @@ __all__ = [
     "check_attention_shape",
     "decode_splits",
     "decode_splits_tma",
+    "tc5_prefill_supported",
     "tma_decode_supported",
     "ensure_built",
     "flash_attention_supported",

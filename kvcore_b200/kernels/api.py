@@ -50,6 +50,9 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                  _int, _int, _int, _float, _int, _int, _vp, _vp],
+        "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
+        "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
+                                  _int, _int, _int, _float, _int, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_gemm_skinny_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
@@ -302,17 +305,25 @@ TMA_DECODE_BLOCKS_PER_SM = 2
 _kv_tensor_maps: dict[tuple, tuple] = {}
 
 
-def _kv_tensor_map_pair(k_cache: torch.Tensor, v_cache: torch.Tensor) -> tuple:
-    """Host-side TMA descriptors of one layer's K and V cache, made once per tensor."""
-    key = (k_cache.data_ptr(), v_cache.data_ptr(), tuple(k_cache.shape))
+def _kv_tensor_map_pair(k_cache: torch.Tensor, v_cache: torch.Tensor, kind: str = "page") -> tuple:
+    """Host-side TMA descriptors of one layer's K and V cache, made once per tensor.  ``kind``:
+    "page" = one contiguous box per page and head (decode), "half" = boxes of one 64-column half
+    of a page (operand tiles of the tcgen05 prefill kernel)."""
+    key = (kind, k_cache.data_ptr(), v_cache.data_ptr(), tuple(k_cache.shape))
     maps = _kv_tensor_maps.get(key)
     if maps is None:
         num_pages, kvh, page_size, d = k_cache.shape
         maps = (ctypes.create_string_buffer(128), ctypes.create_string_buffer(128))
+        maker = "kvb_make_kv_tensor_map" if kind == "page" else "kvb_make_kv_half_tensor_map"
         for buffer, cache in zip(maps, (k_cache, v_cache)):
-            _call("kvb_make_kv_tensor_map", ctypes.addressof(buffer), cache.data_ptr(), num_pages, kvh, page_size, d)
+            _call(maker, ctypes.addressof(buffer), cache.data_ptr(), num_pages, kvh, page_size, d)
         _kv_tensor_maps[key] = maps
     return maps
+
+
+def tc5_prefill_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill kernel takes this cache shape."""
+    return dtype == torch.bfloat16 and head_dim == 128 and page_size in (8, 16, 32, 64)
 
 
 def paged_attention(
@@ -330,6 +341,7 @@ def paged_attention(
     force_general: bool = False,
     num_splits: int | None = None,
     use_tma: bool = True,
+    use_tc5: bool = True,
 ) -> torch.Tensor:
     """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
 
@@ -363,6 +375,15 @@ def paged_attention(
                   ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
                   num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
                   splits, None if scratch is None else scratch.data_ptr(), _stream())
+            return out
+        if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
+                and out.stride(0) % 8 == 0):
+            k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache, "half")
+            _call("kvb_flash_prefill_tc5", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+                  ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
+                  ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+                  num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
+                  _stream())
             return out
         splits = 1
         if split_mode:
@@ -495,6 +516,7 @@ __all__ = [
     "decode_splits",
     "decode_splits_tma",
     "flash_attention_supported",
+    "tc5_prefill_supported",
     "tma_decode_supported",
     "gather_rows",
     "library_is_loaded",

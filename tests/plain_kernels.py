@@ -100,7 +100,7 @@ def rope_kv_write(qkv, positions, req_index, cos_sin, table, k_cache, v_cache,
 
 
 def paged_attention(qkv, k_cache, v_cache, table, ctx, num_heads, num_kv_heads, head_dim, scale, window,
-                    *, force_general=False, num_splits=None, use_tma=True):
+                    *, force_general=False, num_splits=None, use_tma=True, use_tc5=True):
     return paged_attention_plain(qkv, k_cache, v_cache, table, ctx.positions, ctx.req_index,
                                  num_heads, num_kv_heads, head_dim, scale, window)
 

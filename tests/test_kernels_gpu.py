@@ -206,6 +206,12 @@ FLASH_SHAPES = [
     (16, 4, 64, 8, [(777, 1), (64, 2), (0, 1)], None, 3),                    # TMA decode: D=64, pages of 8
     (4, 1, 128, 64, [(500, 3), (63, 1)], None, 2),                           # TMA decode: pages of 64
     (2, 2, 64, 32, [(100, 9)], 17, None),                                    # TMA decode: 9 rows, window
+    (8, 2, 128, 16, [(0, 200), (130, 77), (500, 1), (64, 64)], None, None),  # tcgen05 prefill, mixed with a decode
+    (32, 8, 128, 16, [(0, 300)], None, None),                                # tcgen05 prefill: 3 key tiles, 10 row tiles
+    (4, 1, 128, 64, [(1000, 130)], None, None),                              # tcgen05 prefill: long context, pages of 64
+    (6, 2, 128, 8, [(5, 150), (0, 3)], None, None),                          # tcgen05 prefill: 3 heads a group
+    (8, 2, 128, 32, [(0, 700)], 200, None),                                  # tcgen05 prefill: window
+    (4, 4, 128, 16, [(250, 9), (0, 129)], None, None),                       # tcgen05 prefill: one head a group
 ]
 
 
@@ -234,7 +240,8 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     got = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
                               heads, kv_heads, dim, scale, window, num_splits=splits)
     no_tma = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
-                                 heads, kv_heads, dim, scale, window, num_splits=splits, use_tma=False)
+                                 heads, kv_heads, dim, scale, window, num_splits=splits, use_tma=False,
+                                 use_tc5=False)
     torch.testing.assert_close(got.float(), no_tma.float(), rtol=2e-2, atol=2e-2)
     general = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
                                   heads, kv_heads, dim, scale, window, force_general=True)
