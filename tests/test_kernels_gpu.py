@@ -220,8 +220,11 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     """The tensor-core kernel (tile and split shapes) against the plain statement and the general kernel."""
     dtype = torch.bfloat16
     case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=7)
-    # pages the batch does not own hold NaN: reading one shows up in the output
-    owned = set(case["table"].flatten().tolist())
+    # pages the batch does not own hold NaN: reading one shows up in the output (page 0 is the
+    # null page, which the engine keeps zero: kernels that copy whole pages may read it)
+    owned = set(case["table"].flatten().tolist()) | {0}
+    case["k_cache"][0] = 0
+    case["v_cache"][0] = 0
     for page_id in range(case["k_cache"].shape[0]):
         if page_id not in owned:
             case["k_cache"][page_id] = float("nan")
