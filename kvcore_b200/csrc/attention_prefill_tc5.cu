@@ -321,73 +321,100 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
   } else {
     // ================= softmax: thread t owns row t =================
+    // Two passes over the row of S in TMEM, 32 columns at a time (keeps the code and the live
+    // registers small): pass 1 finds the row maximum, pass 2 forms P = 2^(s*scale - m), sums it
+    // and writes it as bf16 into shared memory.  Masks are applied only on tiles that need them
+    // (the diagonal, a window, rows beyond the batch).  The running maximum m is moved (and O
+    // rescaled) only when some row of the warp would grow by more than 2^8: until then P may
+    // exceed 1, which bf16 and the 32-bit sums hold easily, and O and the row sum stay
+    // consistent because both are taken against the same m.
     const int r = threadIdx.x;
     const int flat = row0 + r;
     const bool row_valid = flat < rows_total;
     const int pos = context + (row_valid ? flat / p.G : 0);
     const int row_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const unsigned lane_addr = ((unsigned)(warp * 32) << 16);
-    float row_max = -INFINITY, row_sum = 0.0f;
+    const bool ragged = row0 + T5_BM > rows_total;        // block holds rows beyond the batch
+    float row_max = -INFINITY, row_sum = 0.0f;            // row_max in the scaled (log2) domain
     bool ok = true;
     for (int j = 0; j < num_tiles; ++j) {
       const int b = j & 1;
       if (!t5_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
       t5_fence_after();
-      float s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) t5_ld32(tmem_base + lane_addr + b * T5_BN + c * 32, s[c]);
-      t5_wait_ld();
-      t5_fence_before();
-      t5_arrive(&s_free[b]);
       const int key0 = (tile_begin + j) * T5_BN;
+      const bool need_mask = ragged || p.window > 0 || key0 + T5_BN - 1 > first_pos;   // block-uniform
+      const unsigned s_addr = tmem_base + lane_addr + b * T5_BN;
+      // ---- pass 1: row maximum of the raw scores ----
       float tile_max = -INFINITY;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
+        float s[32];
+        t5_ld32(s_addr + c * 32, s);
+        t5_wait_ld();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c * 32 + i;
-          const bool seen = row_valid && key <= pos && key >= row_lo;
-          const float v = seen ? s[c][i] * p.scale_log2 : -INFINITY;
-          s[c][i] = v;
-          tile_max = fmaxf(tile_max, v);
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            if (row_valid && key <= pos && key >= row_lo) tile_max = fmaxf(tile_max, s[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, s[i]);
         }
       }
+      tile_max *= p.scale_log2;   // scale > 0; -inf stays -inf
       const float new_max = fmaxf(row_max, tile_max);
-      const float correction = (row_max == -INFINITY) ? (new_max == -INFINITY ? 1.0f : 0.0f) : exp2f(row_max - new_max);
-      row_max = new_max;
-      float tile_sum = 0.0f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = (s[c][i] == -INFINITY) ? 0.0f : exp2f(s[c][i] - new_max);
-          s[c][i] = pv;
-          tile_sum += pv;
-        }
+      const bool grows = new_max > row_max + 8.0f || (row_max == -INFINITY && new_max > -INFINITY);
+      const bool move = __any_sync(0xffffffffu, grows);
+      float correction = 1.0f;
+      if (move) {
+        correction = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - new_max);
+        row_max = new_max;
       }
-      row_sum = row_sum * correction + tile_sum;
+      const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
       if (j > 0) {  // P buffer free and O quiescent once PV(j-1) has completed
         if (!t5_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
         t5_fence_after();
       }
-      // P row -> shared memory (bf16, swizzled K-major operand layout): 16 chunks of 8 keys
+      // ---- pass 2: P = 2^(s*scale - m), row sum, bf16 into the swizzled operand tile ----
+      float tile_sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float s[32];
+        t5_ld32(s_addr + c * 32, s);
+        t5_wait_ld();
 #pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16) {
-        const float* src = &s[c16 >> 2][(c16 & 3) * 8];
-        uint4 packed;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(src[0], src[1]);
-        __nv_bfloat162 t1 = __floats2bfloat162_rn(src[2], src[3]);
-        __nv_bfloat162 t2 = __floats2bfloat162_rn(src[4], src[5]);
-        __nv_bfloat162 t3 = __floats2bfloat162_rn(src[6], src[7]);
-        packed.x = *reinterpret_cast<unsigned*>(&t0);
-        packed.y = *reinterpret_cast<unsigned*>(&t1);
-        packed.z = *reinterpret_cast<unsigned*>(&t2);
-        packed.w = *reinterpret_cast<unsigned*>(&t3);
-        *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c16)) = packed;
+        for (int i = 0; i < 32; ++i) {
+          float x = fmaf(s[i], p.scale_log2, -m_used);
+          if (need_mask) {
+            const int key = key0 + c * 32 + i;
+            if (!(row_valid && key <= pos && key >= row_lo)) x = -INFINITY;
+          }
+          float e;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+          s[i] = e;
+          tile_sum += e;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {   // 4 chunks of 8 keys
+          const float* src = &s[q4 * 8];
+          uint4 packed;
+          __nv_bfloat162 t0 = __floats2bfloat162_rn(src[0], src[1]);
+          __nv_bfloat162 t1 = __floats2bfloat162_rn(src[2], src[3]);
+          __nv_bfloat162 t2 = __floats2bfloat162_rn(src[4], src[5]);
+          __nv_bfloat162 t3 = __floats2bfloat162_rn(src[6], src[7]);
+          packed.x = *reinterpret_cast<unsigned*>(&t0);
+          packed.y = *reinterpret_cast<unsigned*>(&t1);
+          packed.z = *reinterpret_cast<unsigned*>(&t2);
+          packed.w = *reinterpret_cast<unsigned*>(&t3);
+          *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c * 4 + q4)) = packed;
+        }
       }
-      // rescale this row of O when any row of the warp moved its max
-      if (j > 0 && !__all_sync(0xffffffffu, correction == 1.0f)) {
-#pragma unroll
+      t5_fence_before();
+      t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
+      row_sum = row_sum * correction + tile_sum;
+      if (move && j > 0) {       // rescale this warp's rows of O
+#pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float o[32];
           t5_ld32(tmem_o + lane_addr + c * 32, o);
@@ -409,7 +436,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       bf16* dst = nullptr;
       if (row_valid)
         dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         float o[32];
         t5_ld32(tmem_o + lane_addr + c * 32, o);
