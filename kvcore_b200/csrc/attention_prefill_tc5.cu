@@ -62,7 +62,7 @@ __device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity
         "selp.b32 %0, 1, 0, p;\n}\n"
         : "=r"(done) : "r"(t5_smem(bar)), "r"(parity) : "memory");
     if (done) return true;
-    if (spin > 32) __nanosleep(32);
+    if (spin > 4096) __nanosleep(64);   // hand-offs inside the tile loop are short: spin first
   }
   return false;
 }
@@ -321,9 +321,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
   } else {
     // ================= softmax: thread t owns row t =================
-    // Two passes over the row of S in TMEM, 32 columns at a time (keeps the code and the live
-    // registers small): pass 1 finds the row maximum, pass 2 forms P = 2^(s*scale - m), sums it
-    // and writes it as bf16 into shared memory.  Masks are applied only on tiles that need them
+    // The row of S is read from TMEM once (four loads in flight, one wait) and kept in registers:
+    // pass 1 finds the row maximum, pass 2 forms P = 2^(s*scale - m), sums it and writes it as
+    // bf16 into shared memory.  Masks are applied only on tiles that need them
     // (the diagonal, a window, rows beyond the batch).  The running maximum m is moved (and O
     // rescaled) only when some row of the warp would grow by more than 2^8: until then P may
     // exceed 1, which bf16 and the 32-bit sums hold easily, and O and the row sum stay
@@ -344,22 +344,30 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       const int key0 = (tile_begin + j) * T5_BN;
       const bool need_mask = ragged || p.window > 0 || key0 + T5_BN - 1 > first_pos;   // block-uniform
       const unsigned s_addr = tmem_base + lane_addr + b * T5_BN;
+      // the whole row of S: four loads in flight, one wait, then the buffer is free again
+      float s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) t5_ld32(s_addr + c * 32, s[c]);
+      t5_wait_ld();
+      t5_fence_before();
+      t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
       // ---- pass 1: row maximum of the raw scores ----
       float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float s[32];
-        t5_ld32(s_addr + c * 32, s);
-        t5_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
-            if (row_valid && key <= pos && key >= row_lo) tile_max = fmaxf(tile_max, s[i]);
+            if (!(row_valid && key <= pos && key >= row_lo)) s[c][i] = -INFINITY;
+            tile_max = fmaxf(tile_max, s[c][i]);
           }
-        } else {
+        }
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, s[i]);
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, s[c][i]);
         }
       }
       tile_max *= p.scale_log2;   // scale > 0; -inf stays -inf
@@ -378,26 +386,19 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
       // ---- pass 2: P = 2^(s*scale - m), row sum, bf16 into the swizzled operand tile ----
       float tile_sum = 0.0f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        float s[32];
-        t5_ld32(s_addr + c * 32, s);
-        t5_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = fmaf(s[i], p.scale_log2, -m_used);
-          if (need_mask) {
-            const int key = key0 + c * 32 + i;
-            if (!(row_valid && key <= pos && key >= row_lo)) x = -INFINITY;
-          }
+          const float x = fmaf(s[c][i], p.scale_log2, -m_used);   // masked entries are -inf already
           float e;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
-          s[i] = e;
+          s[c][i] = e;
           tile_sum += e;
         }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {   // 4 chunks of 8 keys
-          const float* src = &s[q4 * 8];
+          const float* src = &s[c][q4 * 8];
           uint4 packed;
           __nv_bfloat162 t0 = __floats2bfloat162_rn(src[0], src[1]);
           __nv_bfloat162 t1 = __floats2bfloat162_rn(src[2], src[3]);
@@ -410,8 +411,6 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c * 4 + q4)) = packed;
         }
       }
-      t5_fence_before();
-      t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
       row_sum = row_sum * correction + tile_sum;
       if (move && j > 0) {       // rescale this warp's rows of O
 #pragma unroll 1
