@@ -352,7 +352,10 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       t5_fence_before();
       t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
       // ---- pass 1: row maximum of the raw scores ----
-      float tile_max = -INFINITY;
+      // (eight independent chains: one warp per scheduler has only its own ILP to hide latency)
+      float mx[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mx[a] = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -360,16 +363,18 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
             if (!(row_valid && key <= pos && key >= row_lo)) s[c][i] = -INFINITY;
-            tile_max = fmaxf(tile_max, s[c][i]);
+            mx[i & 7] = fmaxf(mx[i & 7], s[c][i]);
           }
         }
       } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, s[c][i]);
+          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], s[c][i]);
         }
       }
+      float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                             fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       tile_max *= p.scale_log2;   // scale > 0; -inf stays -inf
       const float new_max = fmaxf(row_max, tile_max);
       const bool grows = new_max > row_max + 8.0f || (row_max == -INFINITY && new_max > -INFINITY);
@@ -385,7 +390,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         t5_fence_after();
       }
       // ---- pass 2: P = 2^(s*scale - m), row sum, bf16 into the swizzled operand tile ----
-      float tile_sum = 0.0f;
+      float sm[8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) sm[a] = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -394,7 +401,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           float e;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
           s[c][i] = e;
-          tile_sum += e;
+          sm[i & 7] += e;
         }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {   // 4 chunks of 8 keys
@@ -411,6 +418,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c * 4 + q4)) = packed;
         }
       }
+      const float tile_sum = ((sm[0] + sm[1]) + (sm[2] + sm[3])) + ((sm[4] + sm[5]) + (sm[6] + sm[7]));
       row_sum = row_sum * correction + tile_sum;
       if (move && j > 0) {       // rescale this warp's rows of O
 #pragma unroll 1
