@@ -13,13 +13,14 @@
 //              into two-stage rings.
 //   warp 5     one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
 //              softmax warps work on S(j), then O += P(j).V(j) (V as an MN-major operand).
-// mbarriers: k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S
-// buffers), p_ready (softmax -> MMA), pv_done (MMA -> softmax).  tcgen05.commit arrives on the
+// mbarriers, all in pairs indexed by tile parity so that no waiter can fall two phases behind:
+// k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S buffers),
+// p_ready (softmax -> MMA, two P buffers), pv_done (MMA -> softmax).  tcgen05.commit arrives on the
 // barriers that follow MMAs.  Every wait is bounded: on a time-out the thread sets the
 // WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it returns.
 //
 // Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O [256,384).
-// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB | P 32 KB (all 1024-byte aligned, 128B swizzle).
+// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB | P 2x32 KB (all 1024-byte aligned, 128B swizzle).
 #include <cuda.h>
 #include <string.h>
 
@@ -131,16 +132,16 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned char* k_smem = q_smem + T5_TILE_BYTES;           // 2 stages
   unsigned char* v_smem = k_smem + 2 * T5_TILE_BYTES;       // 2 stages
   unsigned char* p_smem = v_smem + 2 * T5_TILE_BYTES;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_smem + T5_TILE_BYTES);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_smem + 2 * T5_TILE_BYTES);
   unsigned long long* k_full = bars;        // [2]
   unsigned long long* k_empty = bars + 2;   // [2]
   unsigned long long* v_full = bars + 4;    // [2]
   unsigned long long* v_empty = bars + 6;   // [2]
   unsigned long long* s_full = bars + 8;    // [2]
   unsigned long long* s_free = bars + 10;   // [2]
-  unsigned long long* p_ready = bars + 12;
-  unsigned long long* pv_done = bars + 13;
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+  unsigned long long* p_ready = bars + 12;  // [2]
+  unsigned long long* pv_done = bars + 14;  // [2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int req = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
@@ -168,9 +169,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       t5_mbar_init(&v_empty[i], 1);
       t5_mbar_init(&s_full[i], 1);
       t5_mbar_init(&s_free[i], 128);
+      t5_mbar_init(&p_ready[i], 128);
+      t5_mbar_init(&pv_done[i], 1);
     }
-    t5_mbar_init(p_ready, 128);
-    t5_mbar_init(pv_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -274,7 +275,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
                                   ((unsigned)(T5_BM >> 4) << 24);
       const unsigned idesc_s = idesc_base;                // A, B both K-major
       const unsigned idesc_pv = idesc_base | (1u << 16);  // B (= V) MN-major
-      const unsigned q_addr = t5_smem(q_smem), p_addr = t5_smem(p_smem);
+      const unsigned q_addr = t5_smem(q_smem);
       bool ok = true;
       auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
         const unsigned k_addr = t5_smem(k_smem + (j & 1) * T5_TILE_BYTES);
@@ -300,10 +301,11 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           t5_fence_after();
           issue_s(n);
         }
-        if (!t5_wait(p_ready, j & 1)) { ok = false; break; }
+        if (!t5_wait(&p_ready[j & 1], (j >> 1) & 1)) { ok = false; break; }
         if (!t5_wait(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
         t5_fence_after();
         const unsigned v_addr = t5_smem(v_smem + (j & 1) * T5_TILE_BYTES);
+        const unsigned p_addr = t5_smem(p_smem + (j & 1) * T5_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA
           const unsigned a_off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;   // P: K-major, keys along K
@@ -311,7 +313,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           t5_mma(tmem_o, t5_desc(p_addr + a_off, 16, 1024), t5_desc(v_addr + b_off, T5_HALF_BYTES, 1024),
                  idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        t5_commit(pv_done);
+        t5_commit(&pv_done[j & 1]);
         t5_commit(&v_empty[j & 1]);
       }
       if (!ok) {
@@ -385,10 +387,10 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         row_max = new_max;
       }
       const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
-      if (j > 0) {  // P buffer free and O quiescent once PV(j-1) has completed
-        if (!t5_wait(pv_done, (j - 1) & 1)) { ok = false; break; }
-        t5_fence_after();
+      if (j >= 2) {  // P buffer j&1 is free once PV(j-2) has completed
+        if (!t5_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
       }
+      unsigned char* p_tile = p_smem + b * T5_TILE_BYTES;
       // ---- pass 2: P = 2^(s*scale - m), row sum, bf16 into the swizzled operand tile ----
       float sm[8];
 #pragma unroll
@@ -415,12 +417,14 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           packed.y = *reinterpret_cast<unsigned*>(&t1);
           packed.z = *reinterpret_cast<unsigned*>(&t2);
           packed.w = *reinterpret_cast<unsigned*>(&t3);
-          *reinterpret_cast<uint4*>(p_smem + t5_chunk_off(r, c * 4 + q4)) = packed;
+          *reinterpret_cast<uint4*>(p_tile + t5_chunk_off(r, c * 4 + q4)) = packed;
         }
       }
       const float tile_sum = ((sm[0] + sm[1]) + (sm[2] + sm[3])) + ((sm[4] + sm[5]) + (sm[6] + sm[7]));
       row_sum = row_sum * correction + tile_sum;
-      if (move && j > 0) {       // rescale this warp's rows of O
+      if (move && j > 0) {       // rescale this warp's rows of O: PV(j-1) must have landed first
+        if (!t5_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+        t5_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float o[32];
@@ -434,9 +438,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       t5_fence_before();
-      t5_arrive(p_ready);
+      t5_arrive(&p_ready[b]);
     }
-    if (ok && !t5_wait(pv_done, (num_tiles - 1) & 1)) ok = false;
+    if (ok && !t5_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
     if (ok) {
       t5_fence_after();
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
@@ -546,7 +550,7 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   alignas(64) CUtensorMap k_map, v_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
-  constexpr size_t SMEM = 1024 + 6 * T5_TILE_BYTES + 16 * 8;
+  constexpr size_t SMEM = 1024 + 7 * T5_TILE_BYTES + 18 * 8;
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
