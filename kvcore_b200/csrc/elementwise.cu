@@ -291,6 +291,68 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
   }
 }
 
+// Vector form of the kernel above for bf16 rows whose halves are multiples of 8 elements: a
+// thread rotates 8 consecutive pairs (x[j..j+7], x[j+D/2..j+D/2+7]) with 16-byte accesses, and
+// the v heads are copied 16 bytes at a time.  grid (tokens), any block size.
+__global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, long long qkv_stride,
+                                         const int* __restrict__ positions,
+                                         const int* __restrict__ req_index,
+                                         const float2* __restrict__ cos_sin,
+                                         const int* __restrict__ table, int table_stride,
+                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int H,
+                                         int KVH, int D, int page_size, int num_pages, int* status) {
+  const int token = blockIdx.x;
+  const int half = D >> 1;
+  const int groups = half >> 3;                 // 16-byte groups per half
+  const int pos = positions[token];
+  bf16* row = qkv + (size_t)token * qkv_stride;
+  size_t cache_base = 0;
+  bool write = k_cache != nullptr;
+  if (write) {
+    const int page = table[(size_t)req_index[token] * table_stride + pos / page_size];
+    if (page <= 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, KVB_STATUS_BAD_PAGE);
+      write = false;
+    }
+    cache_base = ((size_t)page * KVH * page_size + (pos % page_size)) * D;
+  }
+  const size_t head_stride = (size_t)page_size * D;
+  const int rotate_items = (H + KVH) * groups;
+  const int copy_items = write ? KVH * (D >> 3) : 0;
+  for (int item = threadIdx.x; item < rotate_items + copy_items; item += blockDim.x) {
+    if (item < rotate_items) {
+      const int head = item / groups, g = item % groups;
+      bf16* x = row + (size_t)head * D + g * 8;
+      Vec16<bf16> lo, hi;
+      lo.load(x);
+      hi.load(x + half);
+      if (cos_sin != nullptr) {
+        const float2* cs = cos_sin + (size_t)token * half + g * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 t = cs[i];
+          const float a = lo.get(i), b = hi.get(i);
+          lo.set(i, a * t.x - b * t.y);
+          hi.set(i, b * t.x + a * t.y);
+        }
+        lo.store(x);
+        hi.store(x + half);
+      }
+      if (head >= H && write) {
+        bf16* dst = k_cache + cache_base + (size_t)(head - H) * head_stride + g * 8;
+        lo.store(dst);
+        hi.store(dst + half);
+      }
+    } else {
+      const int i = item - rotate_items;
+      const int vh = i / (D >> 3), g = i % (D >> 3);
+      Vec16<bf16> v;
+      v.load(row + (size_t)(H + KVH) * D + (size_t)vh * D + g * 8);
+      v.store(v_cache + cache_base + (size_t)vh * head_stride + g * 8);
+    }
+  }
+}
+
 extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* positions,
                                  const int* req_index, const float* cos_sin, const int* table,
                                  int table_stride, void* k_cache, void* v_cache, int tokens, int H,
@@ -307,6 +369,17 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "rope_kv_write: no status word");
   const int half = D / 2;
+  if (dtype == KVB_BF16 && D % 16 == 0 && qkv_stride % 8 == 0 && aligned16(qkv) &&
+      (k_cache == nullptr || (aligned16(k_cache) && aligned16(v_cache)))) {
+    const int items = (H + KVH) * (half / 8) + (k_cache ? KVH * (D / 8) : 0);
+    int threads = 32;
+    while (threads < items && threads < 256) threads <<= 1;
+    rope_kv_write_vec_kernel<<<tokens, threads, 0, stream>>>(
+        (bf16*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
+        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status);
+    KVB_CHECK_LAUNCH();
+    return 0;
+  }
   int tx = 1;
   while (tx < half) tx <<= 1;           // threads along j, a power of two >= D/2
   int ty = 128 / tx;
