@@ -45,7 +45,6 @@ struct DecodeParams {
   int num_splits;
   float* partial_o;   // [reqs, KVH, splits, 16, D]
   float* partial_ml;  // [reqs, KVH, splits, 16, 2]
-  int* counters;      // [reqs * KVH], zero between launches: the block that arrives last merges the splits
   int* status;
 };
 
@@ -399,38 +398,6 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
     }
   }
-  if (p.num_splits > 1 && p.counters != nullptr) {
-    // Fused merge of the splits: every block counts itself in after its partials are visible;
-    // the one that arrives last adds all splits in split order (the result does not depend on
-    // which block that is) and leaves the counter at zero for the next launch.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int seen = atomicAdd(&p.counters[req * p.KVH + kvh], 1);
-      abort_flag[1] = (seen == p.num_splits - 1);
-      if (seen == p.num_splits - 1) p.counters[req * p.KVH + kvh] = 0;
-    }
-    __syncthreads();
-    if (abort_flag[1]) {
-      __threadfence();
-      const size_t first = ((size_t)req * p.KVH + kvh) * p.num_splits;
-      for (int i = threadIdx.x; i < rows_total * D; i += TD_THREADS) {
-        const int r = i / D, d = i % D;
-        float m = -INFINITY;
-        for (int s2 = 0; s2 < p.num_splits; ++s2) m = fmaxf(m, __ldcg(p.partial_ml + ((first + s2) * 16 + r) * 2));
-        float total = 0.0f, acc = 0.0f;
-        for (int s2 = 0; s2 < p.num_splits; ++s2) {
-          const float ms = __ldcg(p.partial_ml + ((first + s2) * 16 + r) * 2);
-          const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
-          total += __ldcg(p.partial_ml + ((first + s2) * 16 + r) * 2 + 1) * f;
-          acc += __ldcg(p.partial_o + ((first + s2) * 16 + r) * D + d) * f;
-        }
-        const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-        p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
-            __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
-      }
-    }
-  }
 }
 
 // Same merge of splits as the cp.async kernel's, for this kernel's scratch layout.
@@ -513,7 +480,7 @@ static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map,
   dim3 grid(p.num_splits, p.KVH, p.num_reqs);
   flash_decode_tma_kernel<D><<<grid, TD_THREADS, SMEM, stream>>>(k_map, v_map, p);
   KVB_CHECK_LAUNCH();
-  if (p.num_splits > 1 && p.counters == nullptr) {
+  if (p.num_splits > 1) {
     const int rows = max_rows < 16 ? max_rows : 16;
     dim3 cgrid((rows * D + 127) / 128, p.KVH, p.num_reqs);
     flash_decode_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
@@ -527,7 +494,7 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
                                     int table_stride, const int* query_start, const int* context_lens,
                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
                                     int num_pages, float scale, int window, int num_splits, float* scratch,
-                                    int* counters, cudaStream_t stream) {
+                                    cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == 64 || D == 128, "decode attention (TMA): head_dim must be 64 or 128");
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
@@ -549,7 +516,6 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   KVB_REQUIRE(p.num_splits == 1 || scratch != nullptr, "decode attention (TMA): splits need scratch memory");
   p.partial_o = scratch;
   p.partial_ml = scratch ? scratch + (size_t)num_reqs * KVH * p.num_splits * 16 * D : nullptr;
-  p.counters = counters;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "decode attention (TMA): no status word");
   alignas(64) CUtensorMap k_map, v_map;

@@ -49,7 +49,7 @@ def ensure_built(verbose: bool = False) -> str:
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
-                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp],
+                                 _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
@@ -302,7 +302,6 @@ def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int
 
 
 TMA_DECODE_BLOCKS_PER_SM = 2
-_decode_counters: dict[int, torch.Tensor] = {}   # per device: split counters, zero between launches
 _kv_tensor_maps: dict[tuple, tuple] = {}
 
 
@@ -366,23 +365,16 @@ def paged_attention(
         bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
         if split_mode and use_tma and tma_decode_supported(qkv.dtype, head_dim, page_size):
             splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound)
-            scratch = counters = None
+            scratch = None
             if splits > 1:
                 scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
                                       dtype=torch.float32, device=qkv.device)
-                index = qkv.device.index or 0
-                counters = _decode_counters.get(index)
-                if counters is None or counters.numel() < ctx.num_reqs * num_kv_heads:
-                    counters = torch.zeros(max(65536, ctx.num_reqs * num_kv_heads), dtype=torch.int32,
-                                           device=qkv.device)
-                    _decode_counters[index] = counters
             k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache)
             _call("kvb_flash_decode_tma", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
                   ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
                   ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
                   num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-                  splits, None if scratch is None else scratch.data_ptr(),
-                  None if counters is None else counters.data_ptr(), _stream())
+                  splits, None if scratch is None else scratch.data_ptr(), _stream())
             return out
         if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
                 and out.stride(0) % 8 == 0):
