@@ -39,8 +39,24 @@ TINY_C = dict(
     rope_theta=250000.0, hidden_act="silu", logit_scale=0.5,
     rope_parameters=dict(rope_type="linear", rope_theta=250000.0, factor=2.0),
 )
-TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2}
+# head size 128 (the serving kernels' fast paths: TMA decode, tcgen05 prefill), 2 q heads a kv head
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=384, hidden_size=192,
+    intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=128, max_position_embeddings=1024, tie_word_embeddings=False, rms_norm_eps=1e-5,
+    rope_theta=500000.0, hidden_act="silu",
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=128),
+)
+# head size 64, 3 q heads a kv head
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=200, hidden_size=160,
+    intermediate_size=96, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=2,
+    head_dim=64, max_position_embeddings=1024, tie_word_embeddings=True, rms_norm_eps=1e-6,
+    rope_theta=10000.0, hidden_act="silu",
+)
+TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
 def random_tokens(vocab: int, length: int, seed: int) -> list[int]:

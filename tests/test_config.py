@@ -28,7 +28,7 @@ def test_llama_keys_and_defaults():
     assert cfg.eos_token_ids == ()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_tiny_configs_parse(name):
     raw = rc.TINY_CONFIGS[name]
     cfg = LlamaConfig.from_dict(raw)

@@ -20,16 +20,19 @@ pytestmark = pytest.mark.gpu
 # 0.5% of the largest logit on these models; the bound is four times that.
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2e-2}
 LENGTHS = (45, 70, 33, 101, 64, 17, 128)
+# the two configurations with serving head sizes also get requests that span several key tiles
+LONG_LENGTHS = (45, 300, 33, 161, 64, 17, 520)
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def model_case(request, tmp_path_factory):
     name = request.param
     config = rc.TINY_CONFIGS[name]
     folder = tmp_path_factory.mktemp(f"model_{name}")
     rc.write_model(folder, config, rc.TINY_SEEDS[name], "bfloat16")
     weights = plain_llama.load_weights(folder)
-    requests = {f"r{i}": rc.random_tokens(config["vocab_size"], n, 10 + i) for i, n in enumerate(LENGTHS)}
+    lengths = LONG_LENGTHS if name in ("D", "E") else LENGTHS
+    requests = {f"r{i}": rc.random_tokens(config["vocab_size"], n, 10 + i) for i, n in enumerate(lengths)}
     reference = {rid: plain_llama.forward_logits(config, weights, toks).numpy() for rid, toks in requests.items()}
     return dict(name=name, config=config, folder=folder, requests=requests, reference=reference)
 
