@@ -244,15 +244,15 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
 def reference_arm(args) -> int:
     """The unmodified reference through its own entry point, if it could be installed offline.
 
-    The offline install (pip install --no-index --no-build-isolation --find-links /opt/wheelhouse
-    --target baseline/_ref <reference>) fails on this image: the reference's build backend,
-    hatchling, is neither installed nor in the wheelhouse.  Without an installed copy the arm
-    reports itself unavailable, as the contract asks.
+    The offline install (pip install --no-index --no-build-isolation --find-links <wheelhouse>
+    --target baseline/_ref <reference>) fails where no network is available: the reference's
+    build backend, hatchling, is neither installed nor among the offline wheels.  Without an
+    installed copy the arm reports itself unavailable.
     """
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "kvcore").is_dir():
         reason = ("offline pip install of the reference failed: its build backend hatchling is not installed "
-                  "and not in /opt/wheelhouse, so baseline/_ref is empty")
+                  "and not among the offline wheels, so baseline/_ref is empty")
     else:
         reason = ("baseline/_ref holds the reference, but its entry point needs a tokenizer and a 16 GB "
                   "checkpoint folder that cannot be provided offline")
