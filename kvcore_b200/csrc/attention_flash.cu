@@ -130,7 +130,7 @@ flash_paged_kernel(const FlashParams p) {
   bf16* vs = ks + 2 * FA_KEYS * ROW;
 
   const int req = blockIdx.z, kvh = blockIdx.y;
-  const int tile = SPLIT ? 0 : blockIdx.x;
+  const int tile = SPLIT ? 0 : gridDim.x - 1 - blockIdx.x;   // heaviest (latest) query tiles first
   const int split = SPLIT ? blockIdx.x : 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_begin = p.query_start[req];

@@ -144,7 +144,8 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
-  const int req = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
+  // later query tiles see more keys: hand them out first so the long blocks do not form the tail
+  const int req = blockIdx.z, kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_begin = p.query_start[req];
   const int q_len = p.query_start[req + 1] - q_begin;
