@@ -8,9 +8,10 @@
 //              S = Q.K^T from TMEM (tcgen05.ld), masks, keeps the running max and sum (32-bit),
 //              writes P = exp2(...) as bf16 into shared memory in the swizzled K-major operand
 //              layout, and rescales its row of O in TMEM when the max moved.
-//   warp 4     producer: looks pages up in the block table (batched, a batch ahead) and issues
-//              the tiled TMA copies of K and V (two 64-column boxes per page, 128-byte swizzle)
-//              into two-stage rings.
+//   warps 4, 6 producers of K and of V (separate, so that a wait for a V stage never holds back
+//              the next K tile): each looks pages up in the block table (batched, a batch ahead)
+//              and issues the tiled TMA copies (two 64-column boxes per page, 128-byte swizzle)
+//              into its two-stage ring.
 //   warp 5     one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
 //              softmax warps work on S(j), then O += P(j).V(j) (V as an MN-major operand).
 // mbarriers, all in pairs indexed by tile parity so that no waiter can fall two phases behind:
@@ -29,7 +30,7 @@
 #define T5_BM 128
 #define T5_BN 128
 #define T5_D 128
-#define T5_THREADS 192
+#define T5_THREADS 224
 #define T5_SPIN_LIMIT (1u << 22)
 #define T5_HALF_BYTES (128 * 128)        // one 64-column half of a 128-row operand tile
 #define T5_TILE_BYTES (2 * T5_HALF_BYTES)
@@ -202,8 +203,13 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_o = tmem_base + 256;
 
-  if (warp == 4) {
-    // ================= producer =================
+  if (warp == 4 || warp == 6) {
+    // ================= producers: warp 4 streams K tiles, warp 6 streams V tiles =================
+    const bool is_k = warp == 4;
+    const CUtensorMap* map = is_k ? &k_map : &v_map;
+    unsigned char* ring = is_k ? k_smem : v_smem;
+    unsigned long long* full = is_k ? k_full : v_full;
+    unsigned long long* empty = is_k ? k_empty : v_empty;
     const int* pages = p.table + (size_t)req * p.table_stride;
     const int ppt = T5_BN / p.page_size;          // pages per tile: 2..16
     const int first_entry = tile_begin * ppt;
@@ -220,7 +226,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       return page;
     };
     int cur = fetch(lane), nxt = fetch(32 + lane);
-    int issued_k = 0, issued_v = 0;
+    int issued = 0;
     for (int j = 0; j < num_tiles; ++j) {
       const int s = j & 1;
       const int e0 = j * ppt;
@@ -230,43 +236,28 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
       const int page = __shfl_sync(0xffffffffu, cur, (e0 + lane) & 31);
       const int row = (page * p.KVH + kvh) * p.page_size;
-      const int dst_off = lane * p.page_size * 128;
-      // K(j)
       int ok = 1;
       if (lane == 0) {
-        if (j >= 2 && !t5_wait(&k_empty[s], ((j >> 1) - 1) & 1)) ok = 0;
+        if (j >= 2 && !t5_wait(&empty[s], ((j >> 1) - 1) & 1)) ok = 0;
         if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
-        if (ok) t5_expect_tx(&k_full[s], T5_TILE_BYTES);
+        if (ok) t5_expect_tx(&full[s], T5_TILE_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < ppt) {
-        unsigned char* dst = k_smem + s * T5_TILE_BYTES + dst_off;
-        t5_tma_2d(dst, &k_map, 0, row, &k_full[s]);
-        t5_tma_2d(dst + T5_HALF_BYTES, &k_map, 64, row, &k_full[s]);
+        unsigned char* dst = ring + s * T5_TILE_BYTES + lane * p.page_size * 128;
+        t5_tma_2d(dst, map, 0, row, &full[s]);
+        t5_tma_2d(dst + T5_HALF_BYTES, map, 64, row, &full[s]);
       }
-      issued_k = j + 1;
-      // V(j)
-      if (lane == 0) {
-        if (j >= 2 && !t5_wait(&v_empty[s], ((j >> 1) - 1) & 1)) ok = 0;
-        if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
-        if (ok) t5_expect_tx(&v_full[s], T5_TILE_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      if (lane < ppt) {
-        unsigned char* dst = v_smem + s * T5_TILE_BYTES + dst_off;
-        t5_tma_2d(dst, &v_map, 0, row, &v_full[s]);
-        t5_tma_2d(dst + T5_HALF_BYTES, &v_map, 64, row, &v_full[s]);
-      }
-      issued_v = j + 1;
+      issued = j + 1;
     }
-    if (lane == 0 && (issued_k < num_tiles || issued_v < num_tiles)) {
+    if (lane == 0 && issued < num_tiles) {
       atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
       atomicExch(abort_flag, 1);
+    }
+    if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
       // let the copies that were issued land before the block may exit
-      for (int j = max(0, issued_k - 2); j < issued_k; ++j) t5_wait(&k_full[j & 1], (j >> 1) & 1);
-      for (int j = max(0, issued_v - 2); j < issued_v; ++j) t5_wait(&v_full[j & 1], (j >> 1) & 1);
+      for (int j = max(0, issued - 2); j < issued; ++j) t5_wait(&full[j & 1], (j >> 1) & 1);
     }
   } else if (warp == 5) {
     // ================= MMA issuer =================
