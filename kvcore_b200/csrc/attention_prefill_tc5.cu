@@ -3,20 +3,24 @@
 //
 // A block owns 128 query rows of one (request, kv head); a row is a (token, query head of the
 // group) pair, so the G heads that share a kv head reuse every K/V tile.  It walks the keys in
-// tiles of 128.  Six warps:
-//   warps 0-3  softmax: thread t owns row t = TMEM lane t.  Per tile it reads its row of
-//              S = Q.K^T from TMEM (tcgen05.ld), masks, keeps the running max and sum (32-bit),
-//              writes P = exp2(...) as bf16 into shared memory in the swizzled K-major operand
-//              layout, and rescales its row of O in TMEM when the max moved.
-//   warps 4, 6 producers of K and of V (separate, so that a wait for a V stage never holds back
+// tiles of 128.  Eleven warps:
+//   warps 0-7  softmax, two warpgroups: threads t and t+128 share row t = TMEM lane t and take
+//              columns [0,64) and [64,128) of it.  Per tile each reads its half row of
+//              S = Q.K^T from TMEM (tcgen05.ld), masks, agrees with its partner on the row
+//              maximum (through shared memory and an mbarrier), keeps the running max and a
+//              partial sum (32-bit), writes P = exp2(...) as bf16 into shared memory in the
+//              swizzled K-major operand layout, and rescales its half row of O in TMEM when the
+//              max moved.  (One warpgroup alone is the bottleneck: ~2,300 cycles of exp2 and
+//              conversions per tile against ~1,500 cycles of MMA.)
+//   warps 8, 9 producers of K and of V (separate, so that a wait for a V stage never holds back
 //              the next K tile): each looks pages up in the block table (batched, a batch ahead)
 //              and issues the tiled TMA copies (two 64-column boxes per page, 128-byte swizzle)
 //              into its two-stage ring.
-//   warp 5     one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
+//   warp 10    one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
 //              softmax warps work on S(j), then O += P(j).V(j) (V as an MN-major operand).
 // mbarriers, all in pairs indexed by tile parity so that no waiter can fall two phases behind:
 // k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S buffers),
-// p_ready (softmax -> MMA, two P buffers), pv_done (MMA -> softmax).  tcgen05.commit arrives on the
+// p_ready (softmax -> MMA, two P buffers), pv_done (MMA -> softmax), x_ready (softmax partners).  tcgen05.commit arrives on the
 // barriers that follow MMAs.  Every wait is bounded: on a time-out the thread sets the
 // WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it returns.
 //
@@ -30,7 +34,7 @@
 #define T5_BM 128
 #define T5_BN 128
 #define T5_D 128
-#define T5_THREADS 224
+#define T5_THREADS 352
 #define T5_SPIN_LIMIT (1u << 22)
 #define T5_HALF_BYTES (128 * 128)        // one 64-column half of a 128-row operand tile
 #define T5_TILE_BYTES (2 * T5_HALF_BYTES)
@@ -127,8 +131,8 @@ __device__ __forceinline__ unsigned t5_chunk_off(int r, int chunk16) {
 __global__ void __launch_bounds__(T5_THREADS, 1)
 flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                          const Tc5Params p) {
-  extern __shared__ unsigned char t5_dyn[];
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_dyn) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) unsigned char t5_dyn[];
+  unsigned char* base = t5_dyn;   // the swizzled tiles need 1024-byte alignment (checked below)
   unsigned char* q_smem = base;
   unsigned char* k_smem = q_smem + T5_TILE_BYTES;           // 2 stages
   unsigned char* v_smem = k_smem + 2 * T5_TILE_BYTES;       // 2 stages
@@ -142,8 +146,10 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned long long* s_free = bars + 10;   // [2]
   unsigned long long* p_ready = bars + 12;  // [2]
   unsigned long long* pv_done = bars + 14;  // [2]
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
+  unsigned long long* x_ready = bars + 16;  // [2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 18);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  float* x_buf = reinterpret_cast<float*>(bars + 20);   // [2 parities][2 halves][128 rows]
 
   // later query tiles see more keys: hand them out first so the long blocks do not form the tail
   const int req = blockIdx.z, kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
@@ -154,6 +160,10 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const int rows_total = q_len * p.G;
   const int row0 = tile * T5_BM;
   if (row0 >= rows_total) return;  // whole block, before any barrier or allocation
+  if (t5_smem(base) & 1023u) {     // cannot happen with the alignment asked for; never run misaligned
+    if (threadIdx.x == 0) atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+    return;
+  }
 
   const int last_row = min(row0 + T5_BM, rows_total) - 1;
   const int first_pos = context + row0 / p.G;
@@ -170,15 +180,16 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       t5_mbar_init(&v_full[i], 1);
       t5_mbar_init(&v_empty[i], 1);
       t5_mbar_init(&s_full[i], 1);
-      t5_mbar_init(&s_free[i], 128);
-      t5_mbar_init(&p_ready[i], 128);
+      t5_mbar_init(&s_free[i], 256);
+      t5_mbar_init(&p_ready[i], 256);
       t5_mbar_init(&pv_done[i], 1);
+      t5_mbar_init(&x_ready[i], 256);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  if (warp == 5) {  // tensor memory: 512 columns for this block
+  if (warp == 10) {  // tensor memory: 512 columns for this block
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_smem(tmem_slot)), "r"(512u));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
@@ -203,9 +214,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_o = tmem_base + 256;
 
-  if (warp == 4 || warp == 6) {
-    // ================= producers: warp 4 streams K tiles, warp 6 streams V tiles =================
-    const bool is_k = warp == 4;
+  if (warp == 8 || warp == 9) {
+    // ================= producers: warp 8 streams K tiles, warp 9 streams V tiles =================
+    const bool is_k = warp == 8;
     const CUtensorMap* map = is_k ? &k_map : &v_map;
     unsigned char* ring = is_k ? k_smem : v_smem;
     unsigned long long* full = is_k ? k_full : v_full;
@@ -259,7 +270,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       // let the copies that were issued land before the block may exit
       for (int j = max(0, issued - 2); j < issued; ++j) t5_wait(&full[j & 1], (j >> 1) & 1);
     }
-  } else if (warp == 5) {
+  } else if (warp == 10) {
     // ================= MMA issuer =================
     if (lane == 0) {
       // instruction descriptors: f32 accumulate, bf16 x bf16, M = 128, N = 128
@@ -314,20 +325,21 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
     }
   } else {
-    // ================= softmax: thread t owns row t =================
-    // The row of S is read from TMEM once (four loads in flight, one wait) and kept in registers:
-    // pass 1 finds the row maximum, pass 2 forms P = 2^(s*scale - m), sums it and writes it as
-    // bf16 into shared memory.  Masks are applied only on tiles that need them
-    // (the diagonal, a window, rows beyond the batch).  The running maximum m is moved (and O
-    // rescaled) only when some row of the warp would grow by more than 2^8: until then P may
-    // exceed 1, which bf16 and the 32-bit sums hold easily, and O and the row sum stay
-    // consistent because both are taken against the same m.
-    const int r = threadIdx.x;
+    // ================= softmax: threads t and t+128 own row t, 64 columns each =================
+    // The half row of S is read from TMEM once and kept in registers: pass 1 finds its maximum,
+    // the two partners exchange maxima, pass 2 forms P = 2^(s*scale - m), sums it and writes it
+    // as bf16 into shared memory.  Masks are applied only on tiles that need them (the diagonal,
+    // a window, rows beyond the batch).  The running maximum m is moved (and O rescaled) only
+    // when some row of the warp would grow by more than 2^8: until then P may exceed 1, which
+    // bf16 and the 32-bit sums hold easily, and O and the row sum stay consistent because both
+    // are taken against the same m.
+    const int r = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;                    // which 64 columns of the row
     const int flat = row0 + r;
     const bool row_valid = flat < rows_total;
     const int pos = context + (row_valid ? flat / p.G : 0);
     const int row_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const unsigned lane_addr = ((unsigned)(warp * 32) << 16);
+    const unsigned lane_addr = ((unsigned)((warp & 3) * 32) << 16);
     const bool ragged = row0 + T5_BM > rows_total;        // block holds rows beyond the batch
     float row_max = -INFINITY, row_sum = 0.0f;            // row_max in the scaled (log2) domain
     bool ok = true;
@@ -335,44 +347,44 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       const int b = j & 1;
       if (!t5_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
       t5_fence_after();
-      const int key0 = (tile_begin + j) * T5_BN;
-      const bool need_mask = ragged || p.window > 0 || key0 + T5_BN - 1 > first_pos;   // block-uniform
-      const unsigned s_addr = tmem_base + lane_addr + b * T5_BN;
-      // the whole row of S: four loads in flight, one wait, then the buffer is free again
-      float s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) t5_ld32(s_addr + c * 32, s[c]);
+      const int key0 = (tile_begin + j) * T5_BN + half * 64;
+      const bool need_mask = ragged || p.window > 0 || (tile_begin + j) * T5_BN + T5_BN - 1 > first_pos;
+      const unsigned s_addr = tmem_base + lane_addr + b * T5_BN + half * 64;
+      float s[2][32];
+      t5_ld32(s_addr, s[0]);
+      t5_ld32(s_addr + 32, s[1]);
       t5_wait_ld();
       t5_fence_before();
       t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
-      // ---- pass 1: row maximum of the raw scores ----
-      // (eight independent chains: one warp per scheduler has only its own ILP to hide latency)
-      float mx[8];
-#pragma unroll
-      for (int a = 0; a < 8; ++a) mx[a] = -INFINITY;
+      // ---- pass 1: maximum of the raw scores of this half row ----
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
             if (!(row_valid && key <= pos && key >= row_lo)) s[c][i] = -INFINITY;
-            mx[i & 7] = fmaxf(mx[i & 7], s[c][i]);
+            mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
           }
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], s[c][i]);
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
         }
       }
-      float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                             fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-      tile_max *= p.scale_log2;   // scale > 0; -inf stays -inf
+      const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // ---- partners agree on the row maximum ----
+      float* xb = x_buf + b * 256;
+      xb[half * 128 + r] = my_max;
+      t5_arrive(&x_ready[b]);
+      if (!t5_wait(&x_ready[b], (j >> 1) & 1)) { ok = false; break; }
+      float tile_max = fmaxf(my_max, xb[(half ^ 1) * 128 + r]) * p.scale_log2;   // scale > 0; -inf stays -inf
       const float new_max = fmaxf(row_max, tile_max);
       const bool grows = new_max > row_max + 8.0f || (row_max == -INFINITY && new_max > -INFINITY);
-      const bool move = __any_sync(0xffffffffu, grows);
+      const bool move = __any_sync(0xffffffffu, grows);   // same rows, so the same answer in both partner warps
       float correction = 1.0f;
       if (move) {
         correction = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - new_max);
@@ -383,19 +395,17 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         if (!t5_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
       }
       unsigned char* p_tile = p_smem + b * T5_TILE_BYTES;
-      // ---- pass 2: P = 2^(s*scale - m), row sum, bf16 into the swizzled operand tile ----
-      float sm[8];
+      // ---- pass 2: P = 2^(s*scale - m), partial row sum, bf16 into the swizzled operand tile ----
+      float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int a = 0; a < 8; ++a) sm[a] = 0.0f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float x = fmaf(s[c][i], p.scale_log2, -m_used);   // masked entries are -inf already
           float e;
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
           s[c][i] = e;
-          sm[i & 7] += e;
+          sm[i & 3] += e;
         }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {   // 4 chunks of 8 keys
@@ -409,22 +419,21 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           packed.y = *reinterpret_cast<unsigned*>(&t1);
           packed.z = *reinterpret_cast<unsigned*>(&t2);
           packed.w = *reinterpret_cast<unsigned*>(&t3);
-          *reinterpret_cast<uint4*>(p_tile + t5_chunk_off(r, c * 4 + q4)) = packed;
+          *reinterpret_cast<uint4*>(p_tile + t5_chunk_off(r, half * 8 + c * 4 + q4)) = packed;
         }
       }
-      const float tile_sum = ((sm[0] + sm[1]) + (sm[2] + sm[3])) + ((sm[4] + sm[5]) + (sm[6] + sm[7]));
-      row_sum = row_sum * correction + tile_sum;
-      if (move && j > 0) {       // rescale this warp's rows of O: PV(j-1) must have landed first
+      row_sum = row_sum * correction + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+      if (move && j > 0) {       // rescale this thread's half row of O: PV(j-1) must have landed first
         if (!t5_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
         t5_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           float o[32];
-          t5_ld32(tmem_o + lane_addr + c * 32, o);
+          t5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
           t5_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= correction;
-          t5_st32(tmem_o + lane_addr + c * 32, o);
+          t5_st32(tmem_o + lane_addr + half * 64 + c * 32, o);
         }
         t5_wait_st();
       }
@@ -434,15 +443,25 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
     if (ok && !t5_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
     if (ok) {
+      // partners add their partial row sums (slot of the parity the last tile did not use)
+      const int xb_slot = num_tiles & 1;
+      float* xb = x_buf + xb_slot * 256;
+      xb[half * 128 + r] = row_sum;
+      t5_arrive(&x_ready[xb_slot]);
+      if (!t5_wait(&x_ready[xb_slot], (num_tiles >> 1) & 1)) ok = false;
+      if (ok) row_sum += xb[(half ^ 1) * 128 + r];
+    }
+    if (ok) {
       t5_fence_after();
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
       bf16* dst = nullptr;
       if (row_valid)
-        dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D;
+        dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D +
+              half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float o[32];
-        t5_ld32(tmem_o + lane_addr + c * 32, o);
+        t5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
         t5_wait_ld();
         if (row_valid) {
 #pragma unroll
@@ -469,7 +488,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   // ---- everyone meets; the allocating warp frees the tensor memory ----
   t5_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 10) {
     t5_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u));
   }
@@ -542,7 +561,7 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   alignas(64) CUtensorMap k_map, v_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
-  constexpr size_t SMEM = 1024 + 7 * T5_TILE_BYTES + 18 * 8;
+  constexpr size_t SMEM = 7 * T5_TILE_BYTES + 20 * 8 + 2 * 2 * 128 * sizeof(float);
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
