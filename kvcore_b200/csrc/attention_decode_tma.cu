@@ -116,6 +116,7 @@ template <int D>
 __global__ void __launch_bounds__(TD_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const DecodeParams p) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_DECODE_TMA);
   constexpr int HALVES = D / 64;
   constexpr int KV_BYTES = TD_KEYS * D * 2;        // one of K or V of a stage
   constexpr int STAGE_BYTES = 2 * KV_BYTES;
@@ -403,6 +404,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 // Same merge of splits as the cp.async kernel's, for this kernel's scratch layout.
 template <int D>
 __global__ void flash_decode_combine_kernel(const DecodeParams p) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_DECODE_COMBINE);
   const int req = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.query_start[req];
   const int rows_total = min((p.query_start[req + 1] - q_begin) * p.G, 16);
@@ -478,12 +480,12 @@ static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map,
     configured = true;
   }
   dim3 grid(p.num_splits, p.KVH, p.num_reqs);
-  flash_decode_tma_kernel<D><<<grid, TD_THREADS, SMEM, stream>>>(k_map, v_map, p);
+  KVB_CHECK_CUDA(kvb_launch((flash_decode_tma_kernel<D>), dim3(grid), dim3(TD_THREADS), SMEM, stream, true, k_map, v_map, p));
   KVB_CHECK_LAUNCH();
   if (p.num_splits > 1) {
     const int rows = max_rows < 16 ? max_rows : 16;
     dim3 cgrid((rows * D + 127) / 128, p.KVH, p.num_reqs);
-    flash_decode_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
+    KVB_CHECK_CUDA(kvb_launch((flash_decode_combine_kernel<D>), dim3(cgrid), dim3(128), 0, stream, true, p));
     KVB_CHECK_LAUNCH();
   }
   return 0;
@@ -525,3 +527,5 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   if (D == 64) return launch_decode_tma<64>(k_map, v_map, p, max_rows, stream);
   return launch_decode_tma<128>(k_map, v_map, p, max_rows, stream);
 }
+
+KVB_TRACE_TU(attention_decode_tma)

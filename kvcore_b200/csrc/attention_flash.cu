@@ -115,6 +115,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const FlashPara
 template <int D, bool SPLIT>
 __global__ void __launch_bounds__(FA_THREADS)
 flash_paged_kernel(const FlashParams p) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_FLASH);
   constexpr int ROW = D + FA_PAD;
   constexpr int TILE_M = SPLIT ? 16 : 64;
   constexpr int KSTEPS = D / 16;   // k-steps of Q.K^T
@@ -386,6 +387,7 @@ flash_paged_kernel(const FlashParams p) {
 // One thread per output element; grid.x covers the 16 rows x D elements of a (request, kv head).
 template <int D>
 __global__ void flash_combine_kernel(const FlashParams p) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_FLASH_COMBINE);
   const int req = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = p.query_start[req];
   const int rows_total = (p.query_start[req + 1] - q_begin) * p.G;
@@ -423,12 +425,12 @@ static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cud
       configured_split = true;
     }
     dim3 grid(p.num_splits, p.KVH, p.num_reqs);
-    flash_paged_kernel<D, true><<<grid, FA_THREADS, smem, stream>>>(p);
+    KVB_CHECK_CUDA(kvb_launch((flash_paged_kernel<D, true>), dim3(grid), dim3(FA_THREADS), smem, stream, true, p));
     KVB_CHECK_LAUNCH();
     if (p.num_splits > 1) {
       const int rows = max_rows < 16 ? max_rows : 16;
       dim3 cgrid((rows * D + 127) / 128, p.KVH, p.num_reqs);
-      flash_combine_kernel<D><<<cgrid, 128, 0, stream>>>(p);
+      KVB_CHECK_CUDA(kvb_launch((flash_combine_kernel<D>), dim3(cgrid), dim3(128), 0, stream, true, p));
       KVB_CHECK_LAUNCH();
     }
   } else {
@@ -441,7 +443,7 @@ static int launch_flash(const FlashParams& p, bool split_mode, int max_rows, cud
       configured_tile = true;
     }
     dim3 grid((max_rows + 63) / 64, p.KVH, p.num_reqs);
-    flash_paged_kernel<D, false><<<grid, FA_THREADS, smem, stream>>>(p);
+    KVB_CHECK_CUDA(kvb_launch((flash_paged_kernel<D, false>), dim3(grid), dim3(FA_THREADS), smem, stream, true, p));
     KVB_CHECK_LAUNCH();
   }
   return 0;
@@ -592,3 +594,5 @@ extern "C" int kvb_static_status(int* out) {
   KVB_CHECK_CUDA(cudaMemset(status, 0, sizeof(int)));
   return 0;
 }
+
+KVB_TRACE_TU(attention_flash)

@@ -42,6 +42,7 @@ paged_attention_rows_kernel(T* __restrict__ out, int out_stride, const T* __rest
                             const int* __restrict__ req_index, int num_rows, int H, int KVH, int D,
                             int page_size, int num_pages, float scale, int window, int vec,
                             int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_ATTN_ROWS);
   __shared__ float q_smem[ATT_WARPS][ATT_MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * ATT_WARPS + warp;
@@ -128,15 +129,17 @@ extern "C" int kvb_paged_attention_rows(void* out, int out_stride, const void* q
   KVB_REQUIRE(rows < (1ll << 31), "paged_attention: too many rows");
   const int blocks = (int)((rows + ATT_WARPS - 1) / ATT_WARPS);
   if (dtype == KVB_F32)
-    paged_attention_rows_kernel<float><<<blocks, ATT_WARPS * 32, 0, stream>>>(
+    KVB_CHECK_CUDA(kvb_launch((paged_attention_rows_kernel<float>), dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, true, 
         (float*)out, out_stride, (const float*)q, q_stride, (const float*)k_cache,
         (const float*)v_cache, table, table_stride, positions, req_index, (int)rows, H, KVH, D,
-        page_size, num_pages, scale, window, vec, status);
+        page_size, num_pages, scale, window, vec, status));
   else
-    paged_attention_rows_kernel<bf16><<<blocks, ATT_WARPS * 32, 0, stream>>>(
+    KVB_CHECK_CUDA(kvb_launch((paged_attention_rows_kernel<bf16>), dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, true, 
         (bf16*)out, out_stride, (const bf16*)q, q_stride, (const bf16*)k_cache,
         (const bf16*)v_cache, table, table_stride, positions, req_index, (int)rows, H, KVH, D,
-        page_size, num_pages, scale, window, vec, status);
+        page_size, num_pages, scale, window, vec, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
+
+KVB_TRACE_TU(attention_generic)

@@ -131,6 +131,7 @@ __device__ __forceinline__ unsigned t5_chunk_off(int r, int chunk16) {
 __global__ void __launch_bounds__(T5_THREADS, 1)
 flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                          const Tc5Params p) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_PREFILL_TC5);
   extern __shared__ __align__(1024) unsigned char t5_dyn[];
   unsigned char* base = t5_dyn;   // the swizzled tiles need 1024-byte alignment (checked below)
   unsigned char* q_smem = base;
@@ -569,7 +570,9 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   }
   const int max_rows = max_query_len * p.G;
   dim3 grid((max_rows + T5_BM - 1) / T5_BM, KVH, num_reqs);
-  flash_prefill_tc5_kernel<<<grid, T5_THREADS, SMEM, stream>>>(k_map, v_map, p);
+  KVB_CHECK_CUDA(kvb_launch((flash_prefill_tc5_kernel), dim3(grid), dim3(T5_THREADS), SMEM, stream, true, k_map, v_map, p));
   KVB_CHECK_LAUNCH();
   return 0;
 }
+
+KVB_TRACE_TU(attention_prefill_tc5)

@@ -43,6 +43,111 @@ extern "C" int* kvb_status_word();
 
 typedef __nv_bfloat16 bf16;
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// A kernel launched with the attribute below may start while the kernel before it in the stream
+// is still running: it runs its prologue (barrier set-up, loads of data that no earlier kernel of
+// the step writes: weights, the cached keys of earlier steps), then kvb_grid_wait() returns once
+// the earlier kernel has completed and its writes are visible.  kvb_grid_launch_dependents() tells
+// the scheduler that the next kernel may be brought in.  Both are no-ops in a plain launch.
+// Rule for every kernel that uses them: nothing that an earlier kernel writes is read, and nothing
+// in global memory is written, before kvb_grid_wait().
+__device__ __forceinline__ void kvb_grid_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void kvb_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// ---- kernel timeline trace ----------------------------------------------------------------------
+// When a trace buffer is set, the first and the last block of every kernel of this library append
+// one event {tag, block, time at entry, time after kvb_grid_wait(), time at exit} (nanoseconds of
+// the GPU's global timer).  Word 0 of the buffer counts events, word 1 is the capacity in events.
+// The pointer lives once per translation unit (set through KVB_TRACE_TU's setter); null = off.
+static __device__ unsigned long long* kvb_trace_buffer = nullptr;
+
+__device__ __forceinline__ unsigned long long kvb_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+struct KvbTrace {
+  unsigned long long* buffer;
+  unsigned long long entry, waited;
+  int tag;
+  __device__ __forceinline__ explicit KvbTrace(int kernel_tag) : buffer(nullptr), entry(0), waited(0), tag(kernel_tag) {
+    unsigned long long* b = kvb_trace_buffer;
+    if (b != nullptr && threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+      const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+      const bool last = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1;
+      if (first || last) {
+        buffer = b;
+        entry = kvb_global_ns();
+      }
+    }
+  }
+  __device__ __forceinline__ void after_wait() {
+    if (buffer != nullptr) waited = kvb_global_ns();
+  }
+  __device__ __forceinline__ ~KvbTrace() {
+    if (buffer != nullptr) {
+      const unsigned long long slot = atomicAdd(buffer, 1ull);
+      if (slot < buffer[1]) {
+        unsigned long long* e = buffer + 2 + slot * 4;
+        const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        e[0] = (unsigned long long)tag | (first ? 0ull : 1ull << 32);
+        e[1] = entry;
+        e[2] = waited;
+        e[3] = kvb_global_ns();
+      }
+    }
+  }
+};
+
+// First statements of every kernel: trace scope, wait for the kernel in front, let the next one in.
+#define KVB_KERNEL_PROLOGUE(tag)                                                               \
+  KvbTrace kvb_trace_scope__(tag);                                                             \
+  kvb_grid_wait();               /* ordered after the kernel in front (dependent launch) */    \
+  kvb_trace_scope__.after_wait();                                                              \
+  kvb_grid_launch_dependents()   /* the kernel behind may be brought in; it waits the same way */
+
+// One per .cu file: the setter through which the host hands this file's kernels the trace buffer.
+#define KVB_TRACE_TU(name)                                                                     \
+  extern "C" int kvb_trace_set_##name(unsigned long long* buffer) {                            \
+    return (int)cudaMemcpyToSymbol(kvb_trace_buffer, &buffer, sizeof(buffer));                 \
+  }
+
+// Kernel tags of the trace.
+#define KVB_TAG_GATHER 1
+#define KVB_TAG_RMSNORM 2
+#define KVB_TAG_SILU_MUL 3
+#define KVB_TAG_ROPE_TABLE 4
+#define KVB_TAG_ROPE_KV_WRITE 5
+#define KVB_TAG_ATTN_ROWS 6
+#define KVB_TAG_FLASH 7
+#define KVB_TAG_FLASH_COMBINE 8
+#define KVB_TAG_DECODE_TMA 9
+#define KVB_TAG_DECODE_COMBINE 10
+#define KVB_TAG_PREFILL_TC5 11
+#define KVB_TAG_GEMM_F32 12
+#define KVB_TAG_GEMM_STREAM 13
+#define KVB_TAG_SAMPLE 14
+
+// 1 when launches should carry the programmatic-serialization attribute (set by the host side).
+extern "C" int kvb_pdl_enabled();
+
+template <typename... Params, typename... Args>
+static inline cudaError_t kvb_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, bool overlap, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (overlap && kvb_pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

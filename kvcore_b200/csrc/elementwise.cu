@@ -13,6 +13,7 @@ template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ table,
                                    const int* __restrict__ ids, int width, int rows, int vec_ok,
                                    int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GATHER);
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool valid = id >= 0 && id < rows;
@@ -42,11 +43,11 @@ extern "C" int kvb_gather_rows(void* out, const void* table, const int* ids, int
   const int vec_ok = ((size_t)width * esize) % 16 == 0 && aligned16(out) && aligned16(table);
   const int threads = 128;
   if (dtype == KVB_F32)
-    gather_rows_kernel<float><<<count, threads, 0, stream>>>((float*)out, (const float*)table, ids,
-                                                             width, rows, vec_ok, status);
+    KVB_CHECK_CUDA(kvb_launch((gather_rows_kernel<float>), dim3(count), dim3(threads), 0, stream, true, (float*)out, (const float*)table, ids,
+                                                             width, rows, vec_ok, status));
   else
-    gather_rows_kernel<bf16><<<count, threads, 0, stream>>>((bf16*)out, (const bf16*)table, ids,
-                                                           width, rows, vec_ok, status);
+    KVB_CHECK_CUDA(kvb_launch((gather_rows_kernel<bf16>), dim3(count), dim3(threads), 0, stream, true, (bf16*)out, (const bf16*)table, ids,
+                                                           width, rows, vec_ok, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
@@ -61,6 +62,7 @@ template <typename T, typename W, bool ADD, bool VEC>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restrict__ h,
                const W* __restrict__ weight, int width, float eps) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_RMSNORM);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * width;
   const T* hr = h + base;
@@ -112,14 +114,15 @@ rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restric
 }
 
 template <typename T, typename W>
-static void launch_rmsnorm(void* out, void* residual, const void* h, const void* w, int rows,
-                           int width, float eps, bool add, bool vec, cudaStream_t stream) {
-#define KVB_RMS(ADD_, VEC_)                                                                   \
-  rmsnorm_kernel<T, W, ADD_, VEC_><<<rows, 256, 0, stream>>>((T*)out, (T*)residual, (const T*)h, \
-                                                             (const W*)w, width, eps)
+static int launch_rmsnorm(void* out, void* residual, const void* h, const void* w, int rows,
+                          int width, float eps, bool add, bool vec, cudaStream_t stream) {
+#define KVB_RMS(ADD_, VEC_)                                                                       \
+  KVB_CHECK_CUDA(kvb_launch((rmsnorm_kernel<T, W, ADD_, VEC_>), dim3(rows), dim3(256), 0, stream, true, \
+                            (T*)out, (T*)residual, (const T*)h, (const W*)w, width, eps))
   if (add) { if (vec) KVB_RMS(true, true); else KVB_RMS(true, false); }
   else { if (vec) KVB_RMS(false, true); else KVB_RMS(false, false); }
 #undef KVB_RMS
+  return 0;
 }
 
 // residual == nullptr: plain norm of h.  Otherwise residual is updated in place to h + residual.
@@ -133,36 +136,40 @@ extern "C" int kvb_rmsnorm(void* out, void* residual, const void* h, const void*
                    (!add || aligned16(residual));
   if (dtype == KVB_F32) {
     KVB_REQUIRE(weight_dtype == KVB_F32, "rmsnorm: a 32-bit model needs 32-bit norm weights");
-    launch_rmsnorm<float, float>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+    if (int rc = launch_rmsnorm<float, float>(out, residual, h, weight, rows, width, eps, add, vec, stream)) return rc;
   } else if (weight_dtype == KVB_F32) {
-    launch_rmsnorm<bf16, float>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+    if (int rc = launch_rmsnorm<bf16, float>(out, residual, h, weight, rows, width, eps, add, vec, stream)) return rc;
   } else {
-    launch_rmsnorm<bf16, bf16>(out, residual, h, weight, rows, width, eps, add, vec, stream);
+    if (int rc = launch_rmsnorm<bf16, bf16>(out, residual, h, weight, rows, width, eps, add, vec, stream)) return rc;
   }
   KVB_CHECK_LAUNCH();
   return 0;
 }
 
 // ------------------------------------------------------------------------------------------
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i]
+// out[t, i] = silu(gate(t, i)) * up(t, i).  group == 0: gate(t, i) = gu[t, i], up(t, i) = gu[t, inter + i].
+// group > 0: gate and up alternate in runs of `group` columns (gate 0..g-1, up 0..g-1, gate g..2g-1, ...),
+// the layout a feed-forward keeps when its gate/up matrix is packed for the fused decode kernel.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
 template <typename T, bool VEC>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter,
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int group,
                                 long long total_vecs) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_SILU_MUL);
   constexpr int N = VEC ? Vec16<T>::N : 1;
   const int per_row = inter / N;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vecs;
        v += (long long)gridDim.x * blockDim.x) {
     const long long row = v / per_row;
     const int col = (int)(v % per_row) * N;
-    const T* g = gu + row * 2 * inter + col;
+    const T* g = gu + row * 2 * inter + (group > 0 ? (col / group) * 2 * group + col % group : col);
+    const int up = group > 0 ? group : inter;
     T* o = out + row * inter + col;
     if (VEC) {
       Vec16<T> a, b, r;
       a.load(g);
-      b.load(g + inter);
+      b.load(g + up);
 #pragma unroll
       for (int j = 0; j < Vec16<T>::N; ++j) {
         // the product is formed from the rounded activation, as silu(gate) * up in T would be
@@ -172,28 +179,30 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
       r.store(o);
     } else {
       const float s = to_float(from_float<T>(silu(to_float(g[0]))));
-      o[0] = from_float<T>(s * to_float(g[inter]));
+      o[0] = from_float<T>(s * to_float(g[up]));
     }
   }
 }
 
-extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter, int dtype,
+extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter, int group, int dtype,
                             cudaStream_t stream) {
   if (rows == 0) return 0;
   KVB_REQUIRE(inter > 0, "silu_mul: width must be positive");
+  KVB_REQUIRE(group >= 0 && (group == 0 || inter % group == 0), "silu_mul: the group must divide the width");
   const int esize = dtype == KVB_F32 ? 4 : 2;
-  const bool vec = ((size_t)inter * esize) % 16 == 0 && aligned16(out) && aligned16(gate_up);
+  const bool vec = ((size_t)inter * esize) % 16 == 0 && aligned16(out) && aligned16(gate_up) &&
+                   (group == 0 || ((size_t)group * esize) % 16 == 0);
   const int n = vec ? 16 / esize : 1;
   const long long total = (long long)rows * (inter / n);
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                      : 148 * 16);
   if (dtype == KVB_F32) {
-    if (vec) silu_mul_kernel<float, true><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
-    else silu_mul_kernel<float, false><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+    if (vec) KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<float, true>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out, (const float*)gate_up, inter, group, total));
+    else KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<float, false>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out, (const float*)gate_up, inter, group, total));
   } else {
-    if (vec) silu_mul_kernel<bf16, true><<<blocks, threads, 0, stream>>>((bf16*)out, (const bf16*)gate_up, inter, total);
-    else silu_mul_kernel<bf16, false><<<blocks, threads, 0, stream>>>((bf16*)out, (const bf16*)gate_up, inter, total);
+    if (vec) KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<bf16, true>), dim3(blocks), dim3(threads), 0, stream, true, (bf16*)out, (const bf16*)gate_up, inter, group, total));
+    else KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<bf16, false>), dim3(blocks), dim3(threads), 0, stream, true, (bf16*)out, (const bf16*)gate_up, inter, group, total));
   }
   KVB_CHECK_LAUNCH();
   return 0;
@@ -205,6 +214,7 @@ extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter,
 // ------------------------------------------------------------------------------------------
 __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int tokens, int half) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_ROPE_TABLE);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= tokens * half) return;
   const int t = i / half, j = i % half;
@@ -218,8 +228,8 @@ extern "C" int kvb_rope_table(float* table, const int* positions, const float* i
   if (tokens == 0) return 0;
   KVB_REQUIRE(half > 0, "rope_table: head_dim must be positive");
   const long long total = (long long)tokens * half;
-  rope_table_kernel<<<(int)((total + 255) / 256), 256, 0, stream>>>((float2*)table, positions, inv_freq,
-                                                                    tokens, half);
+  KVB_CHECK_CUDA(kvb_launch((rope_table_kernel), dim3((int)((total + 255) / 256)), dim3(256), 0, stream, true, (float2*)table, positions, inv_freq,
+                                                                    tokens, half));
   KVB_CHECK_LAUNCH();
   return 0;
 }
@@ -243,6 +253,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
                                      const int* __restrict__ table, int table_stride,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int KVH,
                                      int D, int page_size, int num_pages, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_ROPE_KV_WRITE);
   const int token = blockIdx.x;
   const int half = D >> 1;
   const int pos = positions[token];
@@ -301,6 +312,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, long long qkv_s
                                          const int* __restrict__ table, int table_stride,
                                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int H,
                                          int KVH, int D, int page_size, int num_pages, int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_ROPE_KV_WRITE);
   const int token = blockIdx.x;
   const int half = D >> 1;
   const int groups = half >> 3;                 // 16-byte groups per half
@@ -374,9 +386,9 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
     const int items = (H + KVH) * (half / 8) + (k_cache ? KVH * (D / 8) : 0);
     int threads = 32;
     while (threads < items && threads < 256) threads <<= 1;
-    rope_kv_write_vec_kernel<<<tokens, threads, 0, stream>>>(
+    KVB_CHECK_CUDA(kvb_launch((rope_kv_write_vec_kernel), dim3(tokens), dim3(threads), 0, stream, true, 
         (bf16*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
-        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status);
+        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status));
     KVB_CHECK_LAUNCH();
     return 0;
   }
@@ -389,13 +401,15 @@ extern "C" int kvb_rope_kv_write(void* qkv, long long qkv_stride, const int* pos
   dim3 grid(tokens, (H + KVH + ty - 1) / ty);
   KVB_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
   if (dtype == KVB_F32)
-    rope_kv_write_kernel<float><<<grid, block, 0, stream>>>(
+    KVB_CHECK_CUDA(kvb_launch((rope_kv_write_kernel<float>), dim3(grid), dim3(block), 0, stream, true, 
         (float*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
-        (float*)k_cache, (float*)v_cache, H, KVH, D, page_size, num_pages, status);
+        (float*)k_cache, (float*)v_cache, H, KVH, D, page_size, num_pages, status));
   else
-    rope_kv_write_kernel<bf16><<<grid, block, 0, stream>>>(
+    KVB_CHECK_CUDA(kvb_launch((rope_kv_write_kernel<bf16>), dim3(grid), dim3(block), 0, stream, true, 
         (bf16*)qkv, qkv_stride, positions, req_index, (const float2*)cos_sin, table, table_stride,
-        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status);
+        (bf16*)k_cache, (bf16*)v_cache, H, KVH, D, page_size, num_pages, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
+
+KVB_TRACE_TU(elementwise)

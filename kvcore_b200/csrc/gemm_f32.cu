@@ -14,6 +14,7 @@
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                 const float* __restrict__ bias, int M, int N, int K, long long ldx, long long ldo) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GEMM_F32);
   __shared__ float xs[GK][GT + 4];
   __shared__ float ws[GK][GT + 4];
   const int m0 = blockIdx.y * GT, n0 = blockIdx.x * GT;
@@ -68,7 +69,9 @@ extern "C" int kvb_gemm_f32(float* out, const float* x, const float* w, const fl
   KVB_REQUIRE(K > 0, "gemm_f32: K must be positive");
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
   KVB_REQUIRE(grid.y <= 65535, "gemm_f32: too many rows for one launch");
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(out, x, w, bias, M, N, K, ldx, ldo);
+  KVB_CHECK_CUDA(kvb_launch((gemm_f32_kernel), dim3(grid), dim3(256), 0, stream, true, out, x, w, bias, M, N, K, ldx, ldo));
   KVB_CHECK_LAUNCH();
   return 0;
 }
+
+KVB_TRACE_TU(gemm_f32)

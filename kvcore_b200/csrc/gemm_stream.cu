@@ -1,0 +1,439 @@
+// Weight-streaming linear layer for decode: out[M, N] = x[M, K] . W[N, K]^T (+ bias), bf16 in,
+// 32-bit accumulate, M <= 16 tokens, K a multiple of 64 (sm_100a).
+//
+// With so few tokens the layer is one pass over the weight matrix, so the kernel is built around
+// keeping DRAM busy.  What was measured on B200 while building it: the access pattern of the
+// boxes does not matter (rows of 128 bytes 8 KB apart stream as fast as contiguous runs); what
+// matters is the number of bytes in flight per SM (about 180 KB) and the number of 128-byte lines
+// the SM's TMA unit has to move (token rows that travel with every stage are not free; an L2
+// prefetch of each box costs as much as the box and made the kernel slower).
+//
+//  * A stage is 64 weight rows x 256 k-values (32 KB), brought by ONE 3-D TMA box laid out as
+//    [4 slabs of 64 k][64 rows][128 bytes] with the 128-byte swizzle; one more box brings the
+//    token rows of x for the same k-values (rows beyond M and k beyond K arrive as zeros).  The
+//    ring holds five stages.
+//  * One block per SM.  The stages of the layer are numbered tile by tile (k fastest) and dealt to
+//    the blocks as equal contiguous ranges, so every SM streams the same number of bytes whatever
+//    N and K are.  A range that starts inside a tile is a "part": the block adds it up and leaves
+//    it in scratch; the block that holds the tile's first stage (the owner) adds the parts in k
+//    order, adds the bias and stores.  Each block writes at most one part (the first thing it
+//    does) and waits only for blocks that run beside it, with a bounded spin.
+//  * Programmatic dependent launch: weights are written by no kernel of a step, so the whole ring
+//    of weight boxes is asked for before waiting for the kernel in front (whose output x is):
+//    when this kernel follows another in a stream, its blocks fill their rings while the other's
+//    last blocks finish and while small kernels in between run.
+//  * Eight consumer warps: warp w owns weight rows [16 (w mod 4), +16) and one half of the stage's
+//    k-values (ldmatrix the W rows as the A operand and the token rows as the B operand of
+//    mma.sync m16n8k16); the two halves are added in a fixed order when a tile (or the block's
+//    share of it) ends.
+//
+// The result does not depend on timing: halves and parts are added in a fixed order.  All waits
+// are bounded (status bit WAIT_TIMEOUT, then drain and return).
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#define GS_NT 64            // weight rows per tile
+#define GS_KG 4             // slabs of 64 k-values per stage
+#define GS_CONSUMERS 8
+#define GS_THREADS ((GS_CONSUMERS + 1) * 32)
+#define GS_STAGES 5
+#define GS_SPIN_LIMIT (1u << 22)
+
+struct StreamParams {
+  void* out; int out_f32; long long ldo;
+  const bf16* bias;
+  int M, N, K;
+  int n_tiles, kchunks, units;       // kchunks = ceil(K / 256); units = n_tiles * kchunks
+  float* partial;                    // [blocks][MBLK * 4][128]
+  int* flags;                        // [blocks], zero between launches
+  int* status;
+  int silu_pairs;                    // 1: rows n and n+8 of every 16 are a (gate, up) pair: out[m, .] = silu(gate) * up
+};
+
+__device__ __forceinline__ unsigned gs_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gs_mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void gs_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gs_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(gs_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool gs_wait_bounded(unsigned long long* bar, unsigned parity) {
+  for (unsigned spin = 0; spin < GS_SPIN_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(gs_smem(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if (spin > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void gs_tma_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                          unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(gs_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(gs_smem(bar))
+      : "memory");
+}
+__device__ __forceinline__ void gs_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
+               ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void gs_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gs_ldmatrix_x2(unsigned (&r)[2], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ int gs_ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void gs_st_release(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+
+// Byte offset of (row, k) in an operand area made of [rows][128-byte] slabs, one per 64 k-values,
+// 16-byte chunks XOR-swizzled with the row as TMA's 128-byte swizzle lays them out.
+__device__ __forceinline__ unsigned gs_swz(int row, int k, int rows) {
+  const int slab = k >> 6, chunk = (k & 63) >> 3;
+  return (unsigned)(slab * rows * 128 + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// First stage of block b when `units` stages are dealt to `blocks` blocks.
+__device__ __forceinline__ int gs_range_start(int units, int blocks, int b) {
+  return (int)(((long long)units * b) / blocks);
+}
+
+template <int MBLK>   // MB = 8 * MBLK token rows
+__global__ void __launch_bounds__(GS_THREADS, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                   const StreamParams p) {
+  constexpr int MB = 8 * MBLK;
+  constexpr int KB = 64 * GS_KG;
+  constexpr int W_BYTES = GS_NT * KB * 2;
+  constexpr int X_BYTES = MB * KB * 2;
+  constexpr int STAGE_BYTES = W_BYTES + X_BYTES;      // a multiple of 1,024
+  constexpr int STAGES = GS_STAGES;
+
+  extern __shared__ __align__(1024) unsigned char gs_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gs_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(base + STAGES * STAGE_BYTES);
+  unsigned long long* empty_bar = full_bar + STAGES;
+  int* flags = reinterpret_cast<int*>(empty_bar + STAGES);     // [0] abort
+  float* halves = reinterpret_cast<float*>(flags + 4);         // [MBLK * 4][128 threads]
+
+  KvbTrace trace(KVB_TAG_GEMM_STREAM);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blocks = gridDim.x, me = blockIdx.x;
+  const int u_begin = gs_range_start(p.units, blocks, me), u_end = gs_range_start(p.units, blocks, me + 1);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      gs_mbar_init(&full_bar[s], 1);
+      gs_mbar_init(&empty_bar[s], GS_CONSUMERS);
+    }
+    flags[0] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  __syncthreads();
+  kvb_grid_launch_dependents();
+
+  if (warp == GS_CONSUMERS) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int total = u_end - u_begin;
+      const int pre = total < STAGES ? total : STAGES;
+      // before the kernel in front has finished: the whole ring of weight boxes (weights are
+      // written by no kernel of the step)
+      for (int i = 0; i < pre; ++i) {
+        const int u = u_begin + i;
+        gs_expect_tx(&full_bar[i], (unsigned)STAGE_BYTES);
+        gs_tma_3d(base + i * STAGE_BYTES, &w_map, 0, (u / p.kchunks) * GS_NT, (u % p.kchunks) * GS_KG, &full_bar[i]);
+      }
+      kvb_grid_wait();                            // x is the output of the kernel in front
+      int issued = 0;
+      for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        if (it >= STAGES && !gs_wait_bounded(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
+          atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+          atomicExch(&flags[0], 1);
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(&flags[0])) break;
+        const int u = u_begin + it;
+        const int slab = (u % p.kchunks) * GS_KG;
+        unsigned char* wdst = base + stage * STAGE_BYTES;
+        if (it >= pre) {
+          gs_expect_tx(&full_bar[stage], (unsigned)STAGE_BYTES);
+          gs_tma_3d(wdst, &w_map, 0, (u / p.kchunks) * GS_NT, slab, &full_bar[stage]);
+        }
+        gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
+        issued = it + 1;
+      }
+      if (*reinterpret_cast<volatile int*>(&flags[0])) {   // gave up: let the copies in flight land
+        for (int j = max(0, issued - STAGES); j < issued; ++j)
+          gs_wait_bounded(&full_bar[j % STAGES], (j / STAGES) & 1);
+      }
+    }
+  } else {
+    // ---------------- consumers: warp w owns rows [16 (w & 3), +16) and k-half (w >> 2) of every stage ----------------
+    kvb_grid_wait();   // nothing is written to global memory before the kernel in front has finished
+    trace.after_wait();
+    const int rg = warp & 3, kh = warp >> 2;
+    const int tid = rg * 32 + lane;               // 0..127 within the k-half
+    const int a_row = rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), a_k = kh * (KB / 2) + 8 * (lane >> 4);
+    const int b_row = lane & 7, b_k = kh * (KB / 2) + 8 * ((lane >> 3) & 1);
+    int it = 0;
+    int u = u_begin;
+    while (u < u_end) {
+      const int n_tile = u / p.kchunks, kc0 = u % p.kchunks;
+      const int tile_end = (n_tile + 1) * p.kchunks;
+      const int seg_end = tile_end < u_end ? tile_end : u_end;
+      float acc[2][MBLK][4];
+#pragma unroll
+      for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][j][e] = acc[1][j][e] = 0.0f;
+      }
+      for (; u < seg_end; ++u, ++it) {
+        const int stage = it % STAGES;
+        if (!__all_sync(0xffffffffu, gs_wait_bounded(&full_bar[stage], (it / STAGES) & 1))) {
+          atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+          atomicExch(&flags[0], 1);
+          break;
+        }
+        const unsigned wbase = gs_smem(base + stage * STAGE_BYTES);
+        const unsigned xbase = wbase + W_BYTES;
+        // fragments of step kk+1 are fetched while the products of step kk are issued; two
+        // accumulator chains (even and odd steps) halve the dependent-issue latency
+        unsigned a[2][4], b[2][MBLK][2];
+        gs_ldmatrix_x4(a[0], wbase + gs_swz(a_row, a_k, GS_NT));
+#pragma unroll
+        for (int j = 0; j < MBLK; ++j) gs_ldmatrix_x2(b[0][j], xbase + gs_swz(j * 8 + b_row, b_k, MB));
+#pragma unroll
+        for (int kk = 0; kk < KB / 32; ++kk) {
+          const int cur = kk & 1, nxt = cur ^ 1;
+          if (kk + 1 < KB / 32) {
+            gs_ldmatrix_x4(a[nxt], wbase + gs_swz(a_row, a_k + (kk + 1) * 16, GS_NT));
+#pragma unroll
+            for (int j = 0; j < MBLK; ++j)
+              gs_ldmatrix_x2(b[nxt][j], xbase + gs_swz(j * 8 + b_row, b_k + (kk + 1) * 16, MB));
+          }
+#pragma unroll
+          for (int j = 0; j < MBLK; ++j) gs_mma(acc[cur][j], a[cur], b[cur][j][0], b[cur][j][1]);
+        }
+        __syncwarp();
+        if (lane == 0) gs_arrive(&empty_bar[stage]);
+      }
+#pragma unroll
+      for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][j][e] += acc[1][j][e];
+      }
+      // ---- the two k-halves meet: warps 4-7 hand theirs to warps 0-3 ----
+      if (kh == 1) {
+#pragma unroll
+        for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) halves[(j * 4 + e) * 128 + tid] = acc[0][j][e];
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32));
+      if (*reinterpret_cast<volatile int*>(&flags[0])) break;   // somebody gave up waiting
+      if (kh == 0) {
+#pragma unroll
+        for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[0][j][e] += halves[(j * 4 + e) * 128 + tid];
+        }
+        if (kc0 != 0) {
+          // ---- a part: the tile's first stage is another block's; leave the sums in scratch ----
+          float* dst = p.partial + (size_t)me * (MBLK * 4 * 128) + tid;
+#pragma unroll
+          for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) __stcg(dst + (j * 4 + e) * 128, acc[0][j][e]);
+          }
+          __threadfence();
+          asm volatile("bar.sync 2, 128;\n");
+          if (tid == 0) gs_st_release(&p.flags[me], 1);
+        } else {
+          // ---- the owner: add the parts of the blocks behind (in k order), then store ----
+          bool complete = true;
+          if (seg_end < tile_end) {
+            for (int c = me + 1; c < blocks && gs_range_start(p.units, blocks, c) < tile_end; ++c) {
+              if (tid == 0) {
+                int seen = 0;
+                for (unsigned spin = 0; spin < GS_SPIN_LIMIT && !seen; ++spin) {
+                  seen = gs_ld_acquire(&p.flags[c]);
+                  if (!seen && spin > 16) __nanosleep(100);
+                }
+                if (!seen) {
+                  atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+                  atomicExch(&flags[0], 1);
+                }
+              }
+              asm volatile("bar.sync 2, 128;\n");
+              if (*reinterpret_cast<volatile int*>(&flags[0])) { complete = false; break; }
+              __threadfence();
+              const float* src = p.partial + (size_t)c * (MBLK * 4 * 128) + tid;
+#pragma unroll
+              for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[0][j][e] += __ldcg(src + (j * 4 + e) * 128);
+              }
+              asm volatile("bar.sync 2, 128;\n");
+              if (tid == 0) p.flags[c] = 0;   // ready for the next launch
+            }
+          }
+          if (complete && !p.silu_pairs) {
+            const int n_lo = n_tile * GS_NT + rg * 16 + (lane >> 2);
+#pragma unroll
+            for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int n = n_lo + 8 * (e >> 1);
+                const int m = j * 8 + (lane & 3) * 2 + (e & 1);
+                if (n < p.N && m < p.M) {
+                  float v = acc[0][j][e];
+                  if (p.bias) v += __bfloat162float(p.bias[n]);
+                  if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+                  else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                }
+              }
+            }
+          } else if (complete) {
+            // gated pairs: this thread holds gate (row n) and up (row n + 8) of the same output column.
+            // Rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result.
+            const int n = n_tile * GS_NT + rg * 16 + (lane >> 2);          // the gate row
+            const int col = n_tile * (GS_NT / 2) + rg * 8 + (lane >> 2);   // the output column
+#pragma unroll
+            for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int m = j * 8 + (lane & 3) * 2 + e;
+                if (n + 8 < p.N && m < p.M) {
+                  float g = acc[0][j][e], u = acc[0][j][e + 2];
+                  if (p.bias) { g += __bfloat162float(p.bias[n]); u += __bfloat162float(p.bias[n + 8]); }
+                  g = __bfloat162float(__float2bfloat16_rn(g));
+                  u = __bfloat162float(__float2bfloat16_rn(u));
+                  const float act = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+                  reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + col] = __float2bfloat16_rn(act * u);
+                }
+              }
+            }
+          }
+        }
+      }
+      // warps 0-3 have read the halves before they are written again
+      asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32));
+      if (*reinterpret_cast<volatile int*>(&flags[0])) break;
+    }
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*GsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static GsEncodeFn gs_encode_fn() {
+  static GsEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<GsEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// 3-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements),
+// seen as [cols / 64 slabs][rows][64]: boxes of [GS_KG slabs][box_rows][64], 128-byte swizzle, zero
+// fill outside.  cols must be a multiple of 64.
+static int gs_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld,
+                       int box_rows) {
+  GsEncodeFn encode = gs_encode_fn();
+  KVB_REQUIRE(encode != nullptr, "stream gemm: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(bf16), 64 * sizeof(bf16)};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, GS_KG};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
+                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  KVB_REQUIRE(rc == CUDA_SUCCESS, "stream gemm: cuTensorMapEncodeTiled failed");
+  return 0;
+}
+
+// Scratch floats for `blocks` blocks (the largest token block) and flags (ints, zero before the
+// first launch; the kernel leaves them zero).
+extern "C" long long kvb_gemm_stream_scratch_floats(int blocks) { return (long long)blocks * 2 * 4 * 128; }
+
+template <int MBLK>
+static int gs_launch(const void* w, const void* x, long long ldx, StreamParams& p, int sms, cudaStream_t stream) {
+  constexpr int MB = 8 * MBLK;
+  constexpr size_t SMEM = 1024 + (size_t)GS_STAGES * (GS_NT + MB) * GS_KG * 128 + 2 * GS_STAGES * 8 + 16 +
+                          MBLK * 4 * 128 * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<MBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    configured = true;
+  }
+  alignas(64) CUtensorMap w_map, x_map;
+  if (int rc = gs_make_map(&w_map, w, p.N, p.K, p.K, GS_NT)) return rc;
+  if (int rc = gs_make_map(&x_map, x, p.M, p.K, ldx, MB)) return rc;
+  const int blocks = p.units < sms ? p.units : sms;
+  KVB_CHECK_CUDA(kvb_launch(gemm_stream_kernel<MBLK>, dim3(blocks), dim3(GS_THREADS), SMEM, stream, true, w_map,
+                            x_map, p));
+  return 0;
+}
+
+// scratch: kvb_gemm_stream_scratch_floats(sms) floats; flags: sms ints, zero before the first launch.
+// Launches that share scratch and flags must be ordered in one stream.
+// silu_pairs: the rows of w come in runs of 8 gate rows, 8 up rows, ... ; out is [M, N / 2] with
+// out[m, c] = silu(gate_c(m)) * up_c(m) (the feed-forward's activation fused into the epilogue).
+extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const void* x, long long ldx,
+                                    const void* w, const void* bias, int M, int N, int K, int silu_pairs,
+                                    float* scratch, int* flags, int sms, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  KVB_REQUIRE(M > 0 && M <= 16, "stream gemm: takes 1 to 16 rows of x");
+  KVB_REQUIRE(K > 0 && K % 64 == 0 && ldx % 8 == 0, "stream gemm: K must be a multiple of 64 and the row stride of x of 8");
+  KVB_REQUIRE(aligned16(x) && aligned16(w), "stream gemm: x and w must be 16-byte aligned");
+  KVB_REQUIRE(scratch != nullptr && flags != nullptr && sms > 0, "stream gemm: needs scratch and flags");
+  KVB_REQUIRE(!silu_pairs || (N % 16 == 0 && !out_f32), "stream gemm: gated pairs need N a multiple of 16 and a bf16 result");
+  StreamParams p;
+  p.out = out; p.out_f32 = out_f32; p.ldo = ldo;
+  p.bias = (const bf16*)bias;
+  p.M = M; p.N = N; p.K = K;
+  p.silu_pairs = silu_pairs;
+  p.n_tiles = (N + GS_NT - 1) / GS_NT;
+  p.kchunks = (K / 64 + GS_KG - 1) / GS_KG;
+  KVB_REQUIRE((long long)p.n_tiles * p.kchunks < (1ll << 30), "stream gemm: the matrix is too large");
+  p.units = p.n_tiles * p.kchunks;
+  p.partial = scratch;
+  p.flags = flags;
+  p.status = kvb_status_word();
+  KVB_REQUIRE(p.status != nullptr, "stream gemm: no status word");
+  if (M <= 8) return gs_launch<1>(w, x, ldx, p, sms, stream);
+  return gs_launch<2>(w, x, ldx, p, sms, stream);
+}
+
+KVB_TRACE_TU(gemm_stream)

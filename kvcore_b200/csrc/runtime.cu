@@ -37,3 +37,9 @@ extern "C" int kvb_read_status(int reset, int* out) {
 }
 
 extern "C" int kvb_abi_version() { return 1; }
+
+// Whether launches carry the programmatic-serialization attribute (kernels overlap their prologue
+// with the tail of the kernel before them).  Off by default; the host side switches it on.
+static int g_pdl_enabled = 0;
+extern "C" int kvb_pdl_enabled() { return g_pdl_enabled; }
+extern "C" void kvb_set_pdl(int enabled) { g_pdl_enabled = enabled; }

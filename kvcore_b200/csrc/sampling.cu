@@ -78,6 +78,7 @@ __device__ float block_max_f(float v, float* scratch) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const double* __restrict__ params,
               int V, float eps) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_SAMPLE);
   __shared__ float fscratch[32];
   __shared__ ArgMax ascratch[32];
   const int row = blockIdx.x;
@@ -171,7 +172,9 @@ extern "C" int kvb_sample(int* out, const float* logits, const double* params, i
                           float eps, cudaStream_t stream) {
   if (rows == 0) return 0;
   KVB_REQUIRE(V > 0 && V < (1 << 24), "sample: vocabulary must be in [1, 2^24)");
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(out, logits, params, V, eps);
+  KVB_CHECK_CUDA(kvb_launch((sample_kernel), dim3(rows), dim3(SAMPLE_THREADS), 0, stream, true, out, logits, params, V, eps));
   KVB_CHECK_LAUNCH();
   return 0;
 }
+
+KVB_TRACE_TU(sampling)

@@ -9,6 +9,7 @@ linear layers, as the reference uses a library for them (kvcore/model/layer/line
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any
 
 import torch
@@ -39,7 +40,7 @@ def ensure_built(verbose: bool = False) -> str:
     signatures: dict[str, list[Any]] = {
         "kvb_gather_rows": [_vp, _vp, _vp, _int, _int, _int, _int, _vp],
         "kvb_rmsnorm": [_vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _vp],
-        "kvb_silu_mul": [_vp, _vp, _int, _int, _int, _vp],
+        "kvb_silu_mul": [_vp, _vp, _int, _int, _int, _int, _vp],
         "kvb_rope_table": [_vp, _vp, _vp, _int, _int, _vp],
         "kvb_rope_kv_write": [_vp, _ll, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                               _int, _int, _int, _vp],
@@ -54,7 +55,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
-        "kvb_gemm_skinny_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _vp, _int, _vp],
+        "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
     }
@@ -62,6 +63,13 @@ def ensure_built(verbose: bool = False) -> str:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _int
+    lib.kvb_set_pdl.argtypes = [_int]
+    lib.kvb_set_pdl.restype = None
+    # Kernels of this library overlap their start with the end of the kernel in front of them
+    # (programmatic dependent launch); KVCORE_B200_SERIAL_LAUNCH=1 switches that off.
+    lib.kvb_set_pdl(0 if os.environ.get("KVCORE_B200_SERIAL_LAUNCH") == "1" else 1)
+    lib.kvb_gemm_stream_scratch_floats.argtypes = [_int]
+    lib.kvb_gemm_stream_scratch_floats.restype = _ll
     _lib = lib
     return str(path)
 
@@ -180,15 +188,20 @@ def add_rmsnorm(h: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
     return out
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+def silu_mul(gate_up: torch.Tensor, group: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` of a packed ``[T, 2I]`` tensor.
+
+    ``group == 0``: gate is ``gate_up[:, :I]``, up is ``gate_up[:, I:]``.  ``group > 0``: gate and
+    up columns alternate in runs of ``group`` (gate 0..g-1, up 0..g-1, gate g..2g-1, ...)."""
     _check(gate_up, "gate_up")
     rows, two_inter = gate_up.shape
     if two_inter % 2:
         raise KernelError(f"gate_up must have an even width, got {two_inter}")
     inter = two_inter // 2
+    if group < 0 or (group and inter % group):
+        raise KernelError(f"silu_mul: group {group} does not divide the width {inter}")
     out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
-    _call("kvb_silu_mul", out.data_ptr(), gate_up.data_ptr(), rows, inter, _dtype_code(gate_up), _stream())
+    _call("kvb_silu_mul", out.data_ptr(), gate_up.data_ptr(), rows, inter, group, _dtype_code(gate_up), _stream())
     return out
 
 
@@ -406,46 +419,99 @@ def paged_attention(
 
 
 _mm_out_dtype_ok: bool | None = None
-SKINNY_GEMM = True          # bf16 layers of at most SKINNY_MAX_ROWS tokens stream weights through TMA
-SKINNY_MAX_ROWS = 64
-_skinny_counters: dict[int, torch.Tensor] = {}
+# bf16 layers of at most STREAM_MAX_ROWS tokens stream their weights through TMA
+# (KVCORE_B200_LIBRARY_GEMM=1 sends them to the library product instead)
+STREAM_GEMM = os.environ.get("KVCORE_B200_LIBRARY_GEMM") != "1"
+STREAM_MAX_ROWS = 16
+_stream_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
-def skinny_ksplit(n: int, k: int) -> int:
-    """Chunks K is cut into so that a skinny layer has work for every SM (each at least 4 stages)."""
-    n_tiles, kblocks = -(-n // 64), -(-k // 128)
-    return max(1, min(-(-2 * SM_COUNT // n_tiles), kblocks // 4, 16))
+TRACE_TAGS = {1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
+              7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
+              11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample"}
+_TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
+                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream")
+_trace_buffer: torch.Tensor | None = None
 
 
-def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
-                  out_dtype: torch.dtype | None = None, ksplit: int | None = None) -> torch.Tensor:
-    """``x @ weight.T`` for at most 64 rows of bf16 ``x``: the weight-streaming TMA kernel."""
+def _trace_set(pointer: int | None) -> None:
+    for unit in _TRACE_UNITS:
+        fn = getattr(_lib, f"kvb_trace_set_{unit}")
+        fn.argtypes = [_vp]
+        fn.restype = _int
+        if fn(pointer) != 0:
+            raise KernelError(f"kvb_trace_set_{unit} failed")
+
+
+def trace_start(device: torch.device | str = "cuda:0", capacity: int = 1 << 16) -> None:
+    """Start the kernel timeline trace: the first and last block of every kernel of this library
+    record when they entered, when the kernel in front had finished, and when they left."""
+    global _trace_buffer
+    ensure_built()
+    torch.cuda.synchronize(device)
+    buffer = torch.zeros(2 + 4 * capacity, dtype=torch.int64, device=device)
+    buffer[1] = capacity
+    with torch.cuda.device(device):
+        _trace_set(buffer.data_ptr())
+    _trace_buffer = buffer
+
+
+def trace_stop() -> list[dict]:
+    """Stop the trace; events sorted by entry time: kernel, block ("first"/"last"), entry, waited, exit (ns)."""
+    global _trace_buffer
+    if _trace_buffer is None:
+        return []
+    buffer = _trace_buffer
+    torch.cuda.synchronize(buffer.device)
+    with torch.cuda.device(buffer.device):
+        _trace_set(None)
+    host = buffer.cpu().tolist()
+    _trace_buffer = None
+    count = min(host[0], host[1])
+    events = []
+    for i in range(count):
+        tag, entry, waited, leave = host[2 + 4 * i: 6 + 4 * i]
+        events.append({"kernel": TRACE_TAGS.get(tag & 0xFFFFFFFF, str(tag & 0xFFFFFFFF)),
+                       "block": "last" if tag >> 32 else "first", "entry": entry, "waited": waited, "exit": leave})
+    events.sort(key=lambda e: e["entry"])
+    return events
+
+
+def set_overlapped_launch(enabled: bool) -> None:
+    """Switch programmatic dependent launch on or off for this library's kernels."""
+    ensure_built()
+    _lib.kvb_set_pdl(1 if enabled else 0)
+
+
+def linear_stream(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
+                  out_dtype: torch.dtype | None = None, silu_pairs: bool = False) -> torch.Tensor:
+    """``x @ weight.T`` for at most 16 rows of bf16 ``x``, K a multiple of 64: the balanced
+    weight-streaming kernel (one block per SM, every block the same number of bytes).
+
+    ``silu_pairs``: the rows of ``weight`` alternate in runs of 8 gate rows and 8 up rows; the
+    result is ``[M, N/2]``, ``silu(gate) * up``, with the roundings of the unfused path."""
     _check(x, "x", dtype=torch.bfloat16, contiguous=False)
     _check(weight, "weight", dtype=torch.bfloat16)
     m, k = x.shape
     n = weight.shape[0]
-    if not 0 < m <= SKINNY_MAX_ROWS or k % 8 or x.stride(1) != 1 or x.stride(0) % 8:
-        raise KernelError(f"linear_skinny: unsupported shape x {tuple(x.shape)} strides {x.stride()}")
+    if not 0 < m <= STREAM_MAX_ROWS or k % 64 or x.stride(1) != 1 or x.stride(0) % 8:
+        raise KernelError(f"linear_stream: unsupported shape x {tuple(x.shape)} strides {x.stride()}")
     if bias is not None:
         _check(bias, "bias", dtype=torch.bfloat16)
-    out = torch.empty((m, n), dtype=out_dtype or torch.bfloat16, device=x.device)
-    splits = ksplit or skinny_ksplit(n, k)
-    splits = max(1, min(splits, -(-k // 128), 16))
-    scratch = counters = None
-    if splits > 1:
-        mb = 8 if m <= 8 else 16 if m <= 16 else 32 if m <= 32 else 64
-        scratch = torch.empty(splits * mb * (-(-n // 64) * 64), dtype=torch.float32, device=x.device)
-        index = x.device.index or 0
-        counters = _skinny_counters.get(index)
-        if counters is None or counters.numel() < -(-n // 64):
-            counters = torch.zeros(max(4096, -(-n // 64)), dtype=torch.int32, device=x.device)
-            _skinny_counters[index] = counters
-    _call("kvb_gemm_skinny_bf16", out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
+    if silu_pairs and (n % 16 or out_dtype not in (None, torch.bfloat16)):
+        raise KernelError("linear_stream: gated pairs need an output width that is a multiple of 16 and a bf16 result")
+    out = torch.empty((m, n // 2 if silu_pairs else n), dtype=out_dtype or torch.bfloat16, device=x.device)
+    index = x.device.index or 0
+    buffers = _stream_scratch.get(index)
+    if buffers is None:
+        floats = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT))
+        buffers = (torch.empty(floats, dtype=torch.float32, device=x.device),
+                   torch.zeros(SM_COUNT, dtype=torch.int32, device=x.device))
+        _stream_scratch[index] = buffers
+    _call("kvb_gemm_stream_bf16", out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
           x.data_ptr(), x.stride(0), weight.data_ptr(), None if bias is None else bias.data_ptr(),
-          m, n, k, splits, None if scratch is None else scratch.data_ptr(),
-          None if counters is None else counters.data_ptr(), SM_COUNT, _stream())
+          m, n, k, int(silu_pairs), buffers[0].data_ptr(), buffers[1].data_ptr(), SM_COUNT, _stream())
     return out
-
 
 
 def linear(
@@ -475,11 +541,10 @@ def linear(
         _call("kvb_gemm_f32", out.data_ptr(), x.data_ptr(), weight.data_ptr(),
               None if bias is None else bias.data_ptr(), m, n, k, x.stride(0), out.stride(0), _stream())
         return out
-    # Measured on B200: the streaming kernel beats the library product only for very few rows
-    # and narrow outputs (where K can be cut in two); elsewhere the library is as fast or faster.
-    if (SKINNY_GEMM and m <= 4 and n <= 4096 and k % 8 == 0 and x.stride(0) % 8 == 0
-            and weight.is_contiguous() and x.data_ptr() % 16 == 0):
-        return linear_skinny(x, weight, bias, out_dtype=out_dtype, ksplit=2 if k >= 2048 else 1)
+    # Decode-sized batches: the layer is one pass over the weights, which this library's own
+    # streaming kernel does, overlapping its start with the kernels in front of it.
+    if _stream_ok(x, weight):
+        return linear_stream(x, weight, bias, out_dtype=out_dtype)
     if out_dtype == torch.float32:
         if _mm_out_dtype_ok is None:
             try:
@@ -495,6 +560,26 @@ def linear(
             out = out + bias.float()
         return out
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    m, k = x.shape
+    return (STREAM_GEMM and x.dtype == torch.bfloat16 and m <= STREAM_MAX_ROWS and k % 64 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
+                    group: int = 0) -> torch.Tensor:
+    """The first half of a gated feed-forward: ``silu(gate(x)) * up(x)`` for a packed ``[2I, E]``
+    matrix whose gate and up rows are halves (``group == 0``) or alternate in runs of ``group``.
+    Decode-sized bf16 batches with runs of 8 take the streaming kernel with the activation in
+    its epilogue; everything else is the matrix product followed by ``silu_mul``."""
+    _check(x, "x", contiguous=False)
+    _check(weight, "weight", dtype=x.dtype)
+    if group == 8 and x.dim() == 2 and weight.shape[0] % 16 == 0 and _stream_ok(x, weight):
+        return linear_stream(x, weight, bias, silu_pairs=True)
+    return silu_mul(linear(x, weight, bias), group)
 
 
 def sample(logits: torch.Tensor, packed_params: torch.Tensor, eps: float) -> torch.Tensor:
@@ -521,7 +606,11 @@ __all__ = [
     "gather_rows",
     "library_is_loaded",
     "linear",
-    "linear_skinny",
+    "linear_silu_mul",
+    "linear_stream",
+    "set_overlapped_launch",
+    "trace_start",
+    "trace_stop",
     "paged_attention",
     "read_status",
     "require_device",

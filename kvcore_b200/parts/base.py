@@ -33,7 +33,10 @@ class WeightSlot:
     """One tensor of a checkpoint and where it goes.
 
     ``dest`` is the destination storage: a whole parameter, or a row-slice of a packed one
-    (q/k/v rows of one projection matrix).  ``init`` tells the random-weights mode how to
+    (q/k/v rows of one projection matrix), or a strided view that scatters the tensor's rows
+    (gate rows into every other run of 8 rows); in the last case ``file_shape`` is the shape
+    the checkpoint stores and ``dest`` has the same number of elements in the same order.
+    ``init`` tells the random-weights mode how to
     fill it ("normal", "ones", "zeros").  ``keep_f32`` lets a tensor that the file stores in
     32-bit stay 32-bit in a bfloat16 model: the loader then calls ``rebind`` with the
     32-bit tensor instead of casting into ``dest``.
@@ -44,10 +47,12 @@ class WeightSlot:
     init: str = "normal"
     keep_f32: bool = False
     rebind: Callable[[torch.Tensor], None] | None = None
+    file_shape: tuple[int, ...] | None = None
 
     @property
     def shape(self) -> tuple[int, ...]:
-        return tuple(self.dest.shape)
+        """Shape of the tensor in a checkpoint."""
+        return tuple(self.file_shape) if self.file_shape is not None else tuple(self.dest.shape)
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,10 @@
 """Gated feed-forward: ``down(silu(gate(x)) * up(x))`` with gate and up in one matrix.
 
-As the reference (kvcore/model/models/llama3.py:25-45; kvcore/model/layer/activation.py:8-17):
-rows ``[0, I)`` of the packed matrix are the gate projection, rows ``[I, 2I)`` the up projection.
+The arithmetic is the reference's (kvcore/model/models/llama3.py:25-45;
+kvcore/model/layer/activation.py:8-17).  The packing differs: when the intermediate size is a
+multiple of 8, gate and up rows alternate in runs of 8 (gate 0-7, up 0-7, gate 8-15, ...), so that
+the decode kernel, whose threads hold rows n and n+8 of a 16-row tile, can apply the activation
+in its epilogue; otherwise rows ``[0, I)`` are the gate projection and ``[I, 2I)`` the up projection.
 """
 from __future__ import annotations
 
@@ -28,29 +31,40 @@ class SwiGLU(FeedForward):
         self.intermediate_size = int(intermediate_size)
         self.name = name
         inter = self.intermediate_size
+        self.group = 8 if inter % 8 == 0 else 0      # run length of the gate/up interleave (0: halves)
         self.gate_up_weight = torch.empty(2 * inter, self.hidden_size, dtype=dtype, device=device)
         self.down_weight = torch.empty(self.hidden_size, inter, dtype=dtype, device=device)
         self.gate_up_bias = torch.empty(2 * inter, dtype=dtype, device=device) if bias else None
         self.down_bias = torch.empty(self.hidden_size, dtype=dtype, device=device) if bias else None
 
+    def _halves(self, packed: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Where the gate and the up tensor go inside a packed ``[2I, ...]`` tensor."""
+        inter, group = self.intermediate_size, self.group
+        if group == 0:
+            return packed[:inter], packed[inter:]
+        runs = packed.view(inter // group, 2, group, *packed.shape[1:])
+        return runs[:, 0], runs[:, 1]
+
     def weight_slots(self) -> list[WeightSlot]:
-        inter = self.intermediate_size
+        inter, hidden = self.intermediate_size, self.hidden_size
+        gate, up = self._halves(self.gate_up_weight)
         slots = [
-            WeightSlot(f"{self.name}.gate_proj.weight", self.gate_up_weight[:inter]),
-            WeightSlot(f"{self.name}.up_proj.weight", self.gate_up_weight[inter:]),
+            WeightSlot(f"{self.name}.gate_proj.weight", gate, file_shape=(inter, hidden)),
+            WeightSlot(f"{self.name}.up_proj.weight", up, file_shape=(inter, hidden)),
             WeightSlot(f"{self.name}.down_proj.weight", self.down_weight),
         ]
         if self.gate_up_bias is not None:
+            gate_bias, up_bias = self._halves(self.gate_up_bias)
             slots += [
-                WeightSlot(f"{self.name}.gate_proj.bias", self.gate_up_bias[:inter], init="normal"),
-                WeightSlot(f"{self.name}.up_proj.bias", self.gate_up_bias[inter:], init="normal"),
+                WeightSlot(f"{self.name}.gate_proj.bias", gate_bias, init="normal", file_shape=(inter,)),
+                WeightSlot(f"{self.name}.up_proj.bias", up_bias, init="normal", file_shape=(inter,)),
                 WeightSlot(f"{self.name}.down_proj.bias", self.down_bias, init="normal"),
             ]
         return slots
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gate_up = K.linear(x, self.gate_up_weight, self.gate_up_bias)
-        return K.linear(K.silu_mul(gate_up), self.down_weight, self.down_bias)
+        hidden = K.linear_silu_mul(x, self.gate_up_weight, self.gate_up_bias, group=self.group)
+        return K.linear(hidden, self.down_weight, self.down_bias)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

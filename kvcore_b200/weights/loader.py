@@ -47,6 +47,8 @@ class WeightLoadError(ValueError):
 
 def _copy_into(slot: WeightSlot, tensor: torch.Tensor) -> None:
     dest = slot.dest
+    if tuple(tensor.shape) != tuple(dest.shape):   # a scattering view: same elements, same order
+        tensor = tensor.reshape(dest.shape)
     if (
         slot.keep_f32
         and slot.rebind is not None

@@ -46,9 +46,13 @@ def add_rmsnorm(h, residual, weight, eps):
     return rmsnorm(residual, weight, eps)
 
 
-def silu_mul(gate_up):
+def silu_mul(gate_up, group=0):
     inter = gate_up.shape[1] // 2
-    gate, up = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    if group:
+        runs = gate_up.reshape(gate_up.shape[0], inter // group, 2, group)
+        gate, up = runs[:, :, 0].reshape(-1, inter).float(), runs[:, :, 1].reshape(-1, inter).float()
+    else:
+        gate, up = gate_up[:, :inter].float(), gate_up[:, inter:].float()
     act = torch.nn.functional.silu(gate).to(gate_up.dtype).float()
     return (act * up).to(gate_up.dtype)
 
@@ -136,6 +140,10 @@ def linear(x, weight, bias=None, *, out_dtype=None):
     return y.to(out_dtype or x.dtype)
 
 
+def linear_silu_mul(x, weight, bias=None, *, group=0):
+    return silu_mul(linear(x, weight, bias), group)
+
+
 # ---- sampling: the same counter-based noise as the CUDA kernel --------------------------------
 def philox4x32_10(counter, key):
     c = [np.uint64(x) for x in counter]
@@ -191,7 +199,7 @@ def sample(logits, packed_params, eps):
 
 _NAMES = [
     "require_device", "ensure_built", "read_status", "check_attention_shape", "gather_rows", "rmsnorm",
-    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "sample",
+    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "sample",
 ]
 
 

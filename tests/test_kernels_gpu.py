@@ -85,6 +85,18 @@ def test_silu_mul(dtype, rows, inter):
     torch.testing.assert_close(K().silu_mul(gu), P.silu_mul(gu), **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter,group", [(9, 160, 8), (64, 14336, 8), (3, 36, 4), (5, 30, 3)])
+def test_silu_mul_with_alternating_runs(dtype, rows, inter, group):
+    gu = randn(rows, 2 * inter, dtype=dtype, seed=4)
+    got = K().silu_mul(gu, group)
+    torch.testing.assert_close(got, P.silu_mul(gu, group), **tol(dtype))
+    # the same numbers as the halves layout holds them
+    runs = gu.view(rows, inter // group, 2, group)
+    halves = torch.cat((runs[:, :, 0].reshape(rows, inter), runs[:, :, 1].reshape(rows, inter)), dim=1).contiguous()
+    assert torch.equal(got, K().silu_mul(halves))
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 7, 5), (13, 200, 96), (70, 130, 257), (64, 64, 16), (3, 515, 96)])
 @pytest.mark.parametrize("bias", [False, True])
 def test_gemm_f32(m, n, k, bias):
@@ -395,28 +407,55 @@ def test_sample_follows_the_distribution():
 
 
 # ---- weight-streaming linear layer (decode) ---------------------------------------------------
-@pytest.mark.parametrize("m,n,k,ksplit", [
-    (1, 64, 128, 1), (3, 200, 96, 1), (8, 4096, 4096, None), (8, 4096, 4096, 1), (8, 6144, 4096, 5),
-    (9, 515, 1000, 2), (16, 130, 8, 1), (33, 1024, 2048, 4), (64, 96, 14336, 16), (64, 4096, 1024, None),
-    (5, 28672, 1024, None), (2, 70, 520, 3),
+@pytest.mark.parametrize("m,n,k", [
+    (1, 64, 128), (3, 200, 64), (8, 4096, 4096), (8, 6144, 4096), (9, 515, 1024), (16, 130, 64),
+    (13, 1024, 2048), (16, 96, 14336), (4, 4096, 1024), (5, 28672, 1024), (2, 70, 576),
+    (8, 4096, 14336), (11, 4100, 1088), (7, 33, 3136),
 ])
 @pytest.mark.parametrize("bias", [False, True])
-def test_linear_skinny(m, n, k, ksplit, bias):
+def test_linear_stream(m, n, k, bias):
     x = randn(m, k, dtype=torch.bfloat16, seed=20)
     w = randn(n, k, dtype=torch.bfloat16, seed=21, scale=0.05)
     b = randn(n, dtype=torch.bfloat16, seed=22) if bias else None
     want = x.float() @ w.float().T + (b.float() if bias else 0)
-    got = K().linear_skinny(x, w, b, ksplit=ksplit)
+    got = K().linear_stream(x, w, b)
     assert got.dtype == torch.bfloat16
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=2e-2)
-    wide = K().linear_skinny(x, w, b, out_dtype=torch.float32, ksplit=ksplit)
+    wide = K().linear_stream(x, w, b, out_dtype=torch.float32)
     torch.testing.assert_close(wide, want, rtol=1e-3, atol=2e-3)
-    again = K().linear_skinny(x, w, b, out_dtype=torch.float32, ksplit=ksplit)
-    assert torch.equal(wide, again)  # split-K partials are added in a fixed order
+    again = K().linear_stream(x, w, b, out_dtype=torch.float32)
+    assert torch.equal(wide, again)  # halves and parts are added in a fixed order
     assert K().read_status() == 0
 
 
-def test_linear_skinny_takes_row_views():
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 128), (8, 14336, 4096), (5, 200, 576), (16, 1000, 256), (3, 8, 64)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_stream_with_gated_epilogue(m, inter, k, bias):
+    """Rows in runs of 8 gate / 8 up: the activation in the epilogue equals product + silu_mul."""
+    x = randn(m, k, dtype=torch.bfloat16, seed=30)
+    w = randn(2 * inter, k, dtype=torch.bfloat16, seed=31, scale=0.05)
+    b = randn(2 * inter, dtype=torch.bfloat16, seed=32) if bias else None
+    got = K().linear_stream(x, w, b, silu_pairs=True)
+    assert got.shape == (m, inter) and got.dtype == torch.bfloat16
+    products = (x.float() @ w.float().T + (b.float() if bias else 0)).to(torch.bfloat16)
+    want = P.silu_mul(products, 8)
+    torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-2)
+    assert torch.equal(got, K().linear_silu_mul(x, w, b, group=8))
+    assert K().read_status() == 0
+
+
+def test_linear_stream_refuses_what_it_cannot_take():
+    x = randn(17, 128, dtype=torch.bfloat16, seed=20)
+    w = randn(64, 128, dtype=torch.bfloat16, seed=21)
+    with pytest.raises(K().KernelError):
+        K().linear_stream(x, w)            # more than 16 rows
+    with pytest.raises(K().KernelError):
+        K().linear_stream(x[:4, :72], w[:, :72].contiguous())   # K no multiple of 64
+    # the general entry point takes both (library product)
+    torch.testing.assert_close(K().linear(x, w).float(), x.float() @ w.float().T, rtol=1.6e-2, atol=2e-2)
+
+
+def test_linear_stream_takes_row_views():
     """x may be a column slice of a wider buffer (rows 16-byte aligned), as q inside qkv is."""
     full = randn(6, 512 + 256, dtype=torch.bfloat16, seed=23)
     x = full[:, 256:]

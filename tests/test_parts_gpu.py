@@ -21,11 +21,12 @@ def fill(part, seed, std=0.05):
     g = torch.Generator().manual_seed(seed)
     for slot in part.weight_slots():
         if slot.init == "ones":
-            slot.dest.copy_(1.0 + 0.1 * torch.randn(slot.shape, generator=g))
+            slot.dest.copy_((1.0 + 0.1 * torch.randn(slot.shape, generator=g)).reshape(slot.dest.shape))
         else:
-            slot.dest.copy_(torch.randn(slot.shape, generator=g) * std)
+            slot.dest.copy_((torch.randn(slot.shape, generator=g) * std).reshape(slot.dest.shape))
     part.finalize_weights()
-    return {slot.name: slot.dest.detach().float().cpu() for slot in part.weight_slots()}
+    # in the checkpoint's shape (a slot may scatter its rows inside a packed matrix)
+    return {slot.name: slot.dest.detach().float().cpu().reshape(slot.shape) for slot in part.weight_slots()}
 
 
 def randn(*shape, dtype, seed):
@@ -129,12 +130,19 @@ def test_attention_mixer_part(dtype, heads, kv_heads, dim, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_swiglu_part(dtype):
+@pytest.mark.parametrize("hidden,inter,tokens", [
+    (120, 200, 11),    # runs of 8 gate / 8 up rows, the library product (K no multiple of 64)
+    (120, 100, 11),    # an intermediate size that is no multiple of 8: gate and up as halves
+    (128, 208, 5),     # decode-sized: the streaming kernel with the activation in its epilogue
+    (256, 1000, 16),
+])
+def test_swiglu_part(dtype, hidden, inter, tokens):
     from kvcore_b200.parts.mlp import SwiGLU
 
-    part = SwiGLU(hidden_size=120, intermediate_size=200, name="m", bias=True, dtype=dtype, device=DEV)
+    part = SwiGLU(hidden_size=hidden, intermediate_size=inter, name="m", bias=True, dtype=dtype, device=DEV)
+    assert part.group == (8 if inter % 8 == 0 else 0)
     w = {k: v.to(dtype).float() for k, v in fill(part, 8).items()}
-    x = randn(11, 120, dtype=dtype, seed=9)
+    x = randn(tokens, hidden, dtype=dtype, seed=9)
     want = pl.swiglu_mlp(x.float().cpu(), w["m.gate_proj.weight"], w["m.up_proj.weight"], w["m.down_proj.weight"],
                          w["m.gate_proj.bias"], w["m.up_proj.bias"], w["m.down_proj.bias"])
     torch.testing.assert_close(part.forward(x, None).float().cpu(), want, **tol(dtype))

@@ -63,8 +63,14 @@ def test_load_binds_by_name_and_packs(name, tmp_path):
     p = "model.layers.1"
     q, k, v = (theirs[f"{p}.self_attn.{x}_proj.weight"] for x in "qkv")
     assert torch.equal(block.mixer.qkv_weight, torch.cat((q, k, v)))
-    assert torch.equal(block.feed_forward.gate_up_weight,
-                       torch.cat((theirs[f"{p}.mlp.gate_proj.weight"], theirs[f"{p}.mlp.up_proj.weight"])))
+    gate, up = theirs[f"{p}.mlp.gate_proj.weight"], theirs[f"{p}.mlp.up_proj.weight"]
+    group = block.feed_forward.group
+    assert group == (8 if config["intermediate_size"] % 8 == 0 else 0)
+    if group:   # gate and up rows alternate in runs of 8
+        packed = torch.stack((gate.view(-1, group, gate.shape[1]), up.view(-1, group, up.shape[1])), dim=1)
+        assert torch.equal(block.feed_forward.gate_up_weight, packed.reshape(-1, gate.shape[1]))
+    else:
+        assert torch.equal(block.feed_forward.gate_up_weight, torch.cat((gate, up)))
     assert torch.equal(block.feed_forward.down_weight, theirs[f"{p}.mlp.down_proj.weight"])
     assert torch.equal(model.final_norm.weight, theirs["model.norm.weight"])
     if config["tie_word_embeddings"]:
