@@ -71,7 +71,11 @@ rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restric
   float sq = 0.0f;
   if (VEC) {
     constexpr int N = Vec16<T>::N;
-    for (int i = threadIdx.x * N; i < width; i += 256 * N) {
+    constexpr int KEEP = 4;                       // vectors a thread keeps in registers between the passes
+    const bool kept = width <= 256 * N * KEEP;    // rows up to 8,192 bf16 (4,096 float) values wide
+    Vec16<T> mine[KEEP];
+    int slot = 0;
+    for (int i = threadIdx.x * N; i < width; i += 256 * N, ++slot) {
       Vec16<T> a;
       a.load(hr + i);
       if (ADD) {
@@ -83,6 +87,33 @@ rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restric
       }
 #pragma unroll
       for (int j = 0; j < N; ++j) { const float x = a.get(j); sq += x * x; }
+      if (kept) {
+#pragma unroll
+        for (int s = 0; s < KEEP; ++s) if (s == slot) mine[s] = a;
+      }
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    const T* src = ADD ? rr : hr;  // each thread re-reads exactly what it wrote itself
+    slot = 0;
+    for (int i = threadIdx.x * N; i < width; i += 256 * N, ++slot) {
+      Vec16<T> a, o;
+      if (kept) {
+#pragma unroll
+        for (int s = 0; s < KEEP; ++s) if (s == slot) a = mine[s];
+      } else {
+        a.load(src + i);
+      }
+      if (sizeof(W) == sizeof(T)) {
+        Vec16<W> g;
+        g.load(weight + i);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o.set(j, g.get(j) * (a.get(j) * inv));
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) o.set(j, to_float(weight[i + j]) * (a.get(j) * inv));
+      }
+      o.store(orow + i);
     }
   } else {
     for (int i = threadIdx.x; i < width; i += 256) {
@@ -94,20 +125,9 @@ rmsnorm_kernel(T* __restrict__ out, T* __restrict__ residual, const T* __restric
       }
       sq += x * x;
     }
-  }
-  const float total = block_sum(sq, scratch);
-  const float inv = 1.0f / sqrtf(total / (float)width + eps);
-  const T* src = ADD ? rr : hr;  // each thread re-reads exactly what it wrote itself
-  if (VEC) {
-    constexpr int N = Vec16<T>::N;
-    for (int i = threadIdx.x * N; i < width; i += 256 * N) {
-      Vec16<T> a, o;
-      a.load(src + i);
-#pragma unroll
-      for (int j = 0; j < N; ++j) o.set(j, to_float(weight[i + j]) * (a.get(j) * inv));
-      o.store(orow + i);
-    }
-  } else {
+    const float total = block_sum(sq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    const T* src = ADD ? rr : hr;  // each thread re-reads exactly what it wrote itself
     for (int i = threadIdx.x; i < width; i += 256)
       orow[i] = from_float<T>(to_float(weight[i]) * (to_float(src[i]) * inv));
   }

@@ -419,10 +419,12 @@ def paged_attention(
 
 
 _mm_out_dtype_ok: bool | None = None
-# bf16 layers of at most STREAM_MAX_ROWS tokens stream their weights through TMA
-# (KVCORE_B200_LIBRARY_GEMM=1 sends them to the library product instead)
-STREAM_GEMM = os.environ.get("KVCORE_B200_LIBRARY_GEMM") != "1"
+# bf16 layers of at most STREAM_AUTO_ROWS tokens (K a multiple of 64) go to this library's own
+# weight-streaming kernel; above that the library product measured equal or a little faster in a
+# whole decode step (B200, Llama 3.1 8B shapes), so it keeps them.  KVCORE_B200_STREAM_ROWS
+# overrides the bound (0: never, 16: wherever the kernel can).
 STREAM_MAX_ROWS = 16
+STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "4"))
 _stream_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
@@ -564,7 +566,7 @@ def linear(
 
 def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     m, k = x.shape
-    return (STREAM_GEMM and x.dtype == torch.bfloat16 and m <= STREAM_MAX_ROWS and k % 64 == 0
+    return (x.dtype == torch.bfloat16 and m <= min(STREAM_AUTO_ROWS, STREAM_MAX_ROWS) and k % 64 == 0
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 

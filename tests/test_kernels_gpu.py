@@ -440,7 +440,11 @@ def test_linear_stream_with_gated_epilogue(m, inter, k, bias):
     products = (x.float() @ w.float().T + (b.float() if bias else 0)).to(torch.bfloat16)
     want = P.silu_mul(products, 8)
     torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-2)
-    assert torch.equal(got, K().linear_silu_mul(x, w, b, group=8))
+    routed = K().linear_silu_mul(x, w, b, group=8)      # the kernel above for the smallest batches
+    if m <= K().api.STREAM_AUTO_ROWS:
+        assert torch.equal(got, routed)
+    else:
+        torch.testing.assert_close(got.float(), routed.float(), rtol=1.6e-2, atol=2e-2)
     assert K().read_status() == 0
 
 

@@ -133,7 +133,7 @@ def test_attention_mixer_part(dtype, heads, kv_heads, dim, window):
 @pytest.mark.parametrize("hidden,inter,tokens", [
     (120, 200, 11),    # runs of 8 gate / 8 up rows, the library product (K no multiple of 64)
     (120, 100, 11),    # an intermediate size that is no multiple of 8: gate and up as halves
-    (128, 208, 5),     # decode-sized: the streaming kernel with the activation in its epilogue
+    (128, 208, 3),     # decode-sized: the streaming kernel with the activation in its epilogue
     (256, 1000, 16),
 ])
 def test_swiglu_part(dtype, hidden, inter, tokens):
