@@ -395,14 +395,35 @@ __global__ void flash_combine_kernel(const FlashParams p) {
   const int r = i / D, d = i % D;
   if (r >= rows_total || r >= 16) return;
   const size_t base = ((size_t)req * p.KVH + kvh) * p.num_splits;
+  // Loads go out eight splits at a time (the loop would otherwise wait for each in turn); the
+  // splits are still added in their own order.
   float m = -INFINITY;
-  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.partial_ml[((base + s) * 16 + r) * 2]);
+  for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
+    float ms[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      ms[j] = s0 + j < p.num_splits ? p.partial_ml[((base + s0 + j) * 16 + r) * 2] : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
+  }
   float total = 0.0f, acc = 0.0f;
-  for (int s = 0; s < p.num_splits; ++s) {
-    const float ms = p.partial_ml[((base + s) * 16 + r) * 2];
-    const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - m);
-    total += p.partial_ml[((base + s) * 16 + r) * 2 + 1] * f;
-    acc += p.partial_o[((base + s) * 16 + r) * D + d] * f;
+  for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool live = s0 + j < p.num_splits;
+      const float2 ml = live ? *reinterpret_cast<const float2*>(p.partial_ml + ((base + s0 + j) * 16 + r) * 2)
+                             : make_float2(-INFINITY, 0.0f);
+      ms[j] = ml.x;
+      ls[j] = ml.y;
+      os[j] = live ? p.partial_o[((base + s0 + j) * 16 + r) * D + d] : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = (ms[j] == -INFINITY) ? 0.0f : exp2f(ms[j] - m);
+      total += ls[j] * f;
+      acc += os[j] * f;
+    }
   }
   const int token = q_begin + r / p.G;
   const int head = kvh * p.G + r % p.G;
