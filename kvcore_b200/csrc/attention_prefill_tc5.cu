@@ -8,24 +8,26 @@
 //              columns [0,64) and [64,128) of it.  Per tile each reads its half row of
 //              S = Q.K^T from TMEM (tcgen05.ld), masks, agrees with its partner on the row
 //              maximum (through shared memory and an mbarrier), keeps the running max and a
-//              partial sum (32-bit), writes P = exp2(...) as bf16 into shared memory in the
-//              swizzled K-major operand layout, and rescales its half row of O in TMEM when the
-//              max moved.  (One warpgroup alone is the bottleneck: ~2,300 cycles of exp2 and
+//              partial sum (32-bit), writes P = exp2(...) as packed bf16 back into tensor memory
+//              (tcgen05.st: the A operand of the second product is read from there, so P never
+//              touches shared memory), and rescales its half row of O in TMEM when the max moved.  (One warpgroup alone is the bottleneck: ~2,300 cycles of exp2 and
 //              conversions per tile against ~1,500 cycles of MMA.)
 //   warps 8, 9 producers of K and of V (separate, so that a wait for a V stage never holds back
 //              the next K tile): each looks pages up in the block table (batched, a batch ahead)
 //              and issues the tiled TMA copies (two 64-column boxes per page, 128-byte swizzle)
 //              into its two-stage ring.
 //   warp 10    one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
-//              softmax warps work on S(j), then O += P(j).V(j) (V as an MN-major operand).
+//              softmax warps work on S(j), then O += P(j).V(j) (P from tensor memory, V from
+//              shared memory as an MN-major operand).
 // mbarriers, all in pairs indexed by tile parity so that no waiter can fall two phases behind:
 // k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S buffers),
 // p_ready (softmax -> MMA, two P buffers), pv_done (MMA -> softmax), x_ready (softmax partners).  tcgen05.commit arrives on the
 // barriers that follow MMAs.  Every wait is bounded: on a time-out the thread sets the
 // WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it returns.
 //
-// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O [256,384).
-// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB | P 2x32 KB (all 1024-byte aligned, 128B swizzle).
+// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O [256,384) | P0 [384,448) | P1 [448,512)
+// (P: 128 keys as 64 columns of two bf16 each).
+// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB (all 1024-byte aligned, 128B swizzle).
 #include <cuda.h>
 #include <string.h>
 
@@ -92,6 +94,15 @@ __device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// D[tmem] (+)= A[tmem] . B[smem]: A is 128 lanes x 8 columns (16 bf16 a lane, two to a column).
+__device__ __forceinline__ void t5_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
 __device__ __forceinline__ void t5_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_smem(bar)) : "memory");
 }
@@ -137,8 +148,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned char* q_smem = base;
   unsigned char* k_smem = q_smem + T5_TILE_BYTES;           // 2 stages
   unsigned char* v_smem = k_smem + 2 * T5_TILE_BYTES;       // 2 stages
-  unsigned char* p_smem = v_smem + 2 * T5_TILE_BYTES;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_smem + 2 * T5_TILE_BYTES);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_smem + 2 * T5_TILE_BYTES);
   unsigned long long* k_full = bars;        // [2]
   unsigned long long* k_empty = bars + 2;   // [2]
   unsigned long long* v_full = bars + 4;    // [2]
@@ -214,6 +224,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   t5_fence_after();
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_o = tmem_base + 256;
+  const unsigned tmem_p = tmem_base + 384;   // two buffers of 64 columns
 
   if (warp == 8 || warp == 9) {
     // ================= producers: warp 8 streams K tiles, warp 9 streams V tiles =================
@@ -309,13 +320,12 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         if (!t5_wait(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
         t5_fence_after();
         const unsigned v_addr = t5_smem(v_smem + (j & 1) * T5_TILE_BYTES);
-        const unsigned p_addr = t5_smem(p_smem + (j & 1) * T5_TILE_BYTES);
+        const unsigned p_tmem = tmem_p + (j & 1) * (T5_BN / 2);
 #pragma unroll
-        for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA
-          const unsigned a_off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;   // P: K-major, keys along K
-          const unsigned b_off = kk * 16 * 128;                                // V: 16 key rows down
-          t5_mma(tmem_o, t5_desc(p_addr + a_off, 16, 1024), t5_desc(v_addr + b_off, T5_HALF_BYTES, 1024),
-                 idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA: 8 columns of P, 16 key rows of V
+          const unsigned b_off = kk * 16 * 128;
+          t5_mma_ts(tmem_o, p_tmem + kk * 8, t5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv,
+                    (j > 0 || kk > 0) ? 1u : 0u);
         }
         t5_commit(&pv_done[j & 1]);
         t5_commit(&v_empty[j & 1]);
@@ -395,34 +405,26 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       if (j >= 2) {  // P buffer j&1 is free once PV(j-2) has completed
         if (!t5_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
       }
-      unsigned char* p_tile = p_smem + b * T5_TILE_BYTES;
-      // ---- pass 2: P = 2^(s*scale - m), partial row sum, bf16 into the swizzled operand tile ----
+      // ---- pass 2: P = 2^(s*scale - m), partial row sum, packed bf16 into tensor memory ----
       float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      float packed[32];                              // 64 keys of this half row, two bf16 a register
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = fmaf(s[c][i], p.scale_log2, -m_used);   // masked entries are -inf already
-          float e;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
-          s[c][i] = e;
-          sm[i & 3] += e;
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {   // 4 chunks of 8 keys
-          const float* src = &s[c][q4 * 8];
-          uint4 packed;
-          __nv_bfloat162 t0 = __floats2bfloat162_rn(src[0], src[1]);
-          __nv_bfloat162 t1 = __floats2bfloat162_rn(src[2], src[3]);
-          __nv_bfloat162 t2 = __floats2bfloat162_rn(src[4], src[5]);
-          __nv_bfloat162 t3 = __floats2bfloat162_rn(src[6], src[7]);
-          packed.x = *reinterpret_cast<unsigned*>(&t0);
-          packed.y = *reinterpret_cast<unsigned*>(&t1);
-          packed.z = *reinterpret_cast<unsigned*>(&t2);
-          packed.w = *reinterpret_cast<unsigned*>(&t3);
-          *reinterpret_cast<uint4*>(p_tile + t5_chunk_off(r, half * 8 + c * 4 + q4)) = packed;
+        for (int i = 0; i < 32; i += 2) {
+          float e0, e1;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(s[c][i], p.scale_log2, -m_used)));       // masked: -inf
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(s[c][i + 1], p.scale_log2, -m_used)));
+          sm[i & 2] += e0;
+          sm[(i & 2) + 1] += e1;
+          // Two bf16 in a register, the lower key in the lower half.  Rounded by adding half a step
+          // and cutting (integer pipe: the conversion instruction shares the exp2 unit, which is
+          // the busiest unit of this kernel); P >= 0 and finite, so this is round-half-up.
+          packed[c * 16 + i / 2] = __uint_as_float(
+              __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632));
         }
       }
+      t5_st32(tmem_p + lane_addr + b * (T5_BN / 2) + half * 32, packed);
       row_sum = row_sum * correction + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
       if (move && j > 0) {       // rescale this thread's half row of O: PV(j-1) must have landed first
         if (!t5_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
@@ -438,7 +440,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         }
         t5_wait_st();
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      t5_wait_st();
       t5_fence_before();
       t5_arrive(&p_ready[b]);
     }
@@ -562,7 +564,7 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   alignas(64) CUtensorMap k_map, v_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
-  constexpr size_t SMEM = 7 * T5_TILE_BYTES + 20 * 8 + 2 * 2 * 128 * sizeof(float);
+  constexpr size_t SMEM = 5 * T5_TILE_BYTES + 20 * 8 + 2 * 2 * 128 * sizeof(float);
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
