@@ -188,9 +188,40 @@ class OffsetPosition(PositionEncoding):
             k.copy_((k.float() + shift).to(k.dtype))
 
 
+class RoutedFeedForward(FeedForward):
+    """A toy feed-forward with routing: every token goes to the one expert its router scores
+    highest (scores in 32-bit), ``y = p * W_out[e] relu(W_in[e] x)`` with ``p`` the softmax weight of
+    that expert.  Written in torch by the test."""
+
+    def __init__(self, *, hidden_size, inter, experts, name, dtype, device):
+        self.name, self.experts = name, experts
+        self.router = torch.empty(experts, hidden_size, dtype=dtype, device=device)
+        self.w_in = torch.empty(experts, inter, hidden_size, dtype=dtype, device=device)
+        self.w_out = torch.empty(experts, hidden_size, inter, dtype=dtype, device=device)
+
+    def weight_slots(self):
+        slots = [WeightSlot(f"{self.name}.router.weight", self.router)]
+        for e in range(self.experts):
+            slots += [WeightSlot(f"{self.name}.experts.{e}.in.weight", self.w_in[e]),
+                      WeightSlot(f"{self.name}.experts.{e}.out.weight", self.w_out[e])]
+        return slots
+
+    def forward(self, x, ctx):
+        scores = torch.softmax(x.float() @ self.router.float().T, dim=-1)
+        weight, expert = scores.max(dim=-1)
+        out = torch.zeros_like(x)
+        for e in range(self.experts):
+            rows = (expert == e).nonzero().flatten()
+            if rows.numel():
+                hidden = torch.relu(x[rows].float() @ self.w_in[e].float().T)
+                out[rows] = (weight[rows, None] * (hidden @ self.w_out[e].float().T)).to(x.dtype)
+        return out
+
+
 def toy_spec(raw):
-    """Layers: 0 attention (window 9, toy position), 1 running mean, 2 attention (rope).
-    Schedule: 0, 1, 2, 0 again (own cache), then 2 reading the cache of the first run of 2."""
+    """Layers: 0 attention (window 9, toy position), 1 running mean, 2 attention (rope) with a
+    routed feed-forward.  Schedule: 0, 1, 2, 0 again (own cache), then 2 reading the cache of the
+    first run of 2."""
     base = LlamaConfig.from_dict(raw).to_model_spec()
     layers = list(base.layers)
     layers[0] = type(layers[0])(
@@ -201,6 +232,11 @@ def toy_spec(raw):
         prefix=layers[1].prefix, block=layers[1].block,
         mixer=PartSpec("toy_running_mean", dict(hidden_size=raw["hidden_size"], name="model.layers.1.mean")),
         feed_forward=layers[1].feed_forward, norms=layers[1].norms)
+    layers[2] = type(layers[2])(
+        prefix=layers[2].prefix, block=layers[2].block, mixer=layers[2].mixer,
+        feed_forward=PartSpec("toy_routed", dict(hidden_size=raw["hidden_size"], inter=48, experts=3,
+                                                 name="model.layers.2.moe")),
+        norms=layers[2].norms)
     fields = {f: getattr(base, f) for f in base.__dataclass_fields__}
     fields.update(architecture="ToyForCausalLM", layers=tuple(layers),
                   schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(2, cache_of=2)))
@@ -252,7 +288,16 @@ def toy_plain_logits(raw, weights, tokens):
                                              None if borrow is None else kept[borrow])
         residual = a + residual
         x = pl.rms_norm(residual, w[f"{p}.post_attention_layernorm.weight"], eps)
-        h = pl.swiglu_mlp(x, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"])
+        if layer == 2:
+            scores = torch.softmax(x @ w[f"{p}.moe.router.weight"].T, dim=-1)
+            weight, expert = scores.max(dim=-1)
+            h = torch.zeros_like(x)
+            for t in range(n):
+                e = int(expert[t])
+                hidden = torch.relu(w[f"{p}.moe.experts.{e}.in.weight"] @ x[t])
+                h[t] = weight[t] * (w[f"{p}.moe.experts.{e}.out.weight"] @ hidden)
+        else:
+            h = pl.swiglu_mlp(x, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"])
     final = pl.rms_norm(h + residual, w["model.norm.weight"], eps)
     return (final @ w["lm_head.weight"].T).float()
 
@@ -261,10 +306,12 @@ def toy_plain_logits(raw, weights, tokens):
 def toy_parts():
     MIXERS.register("toy_running_mean", RunningMeanMixer)
     POSITION_ENCODINGS.register("toy_offset", OffsetPosition)
+    FEED_FORWARDS.register("toy_routed", RoutedFeedForward)
     register_architecture("ToyForCausalLM", toy_spec)
     yield
     MIXERS.unregister("toy_running_mean")
     POSITION_ENCODINGS.unregister("toy_offset")
+    FEED_FORWARDS.unregister("toy_routed")
     unregister_architecture("ToyForCausalLM")
 
 
@@ -273,6 +320,7 @@ def test_toy_parts_register_build_and_step_without_touching_the_framework(device
     folder = rc.write_model(tmp_path / "m", raw, 4, "float32")
     weights = plain_llama.load_weights(folder)
     assert "model.layers.1.mean.weight" in weights and "model.layers.1.self_attn.q_proj.weight" not in weights
+    assert "model.layers.2.moe.experts.2.out.weight" in weights and "model.layers.2.mlp.down_proj.weight" not in weights
     requests = {f"r{i}": rc.random_tokens(256, n, 30 + i) for i, n in enumerate((40, 75, 23, 58, 31))}
     reference = {rid: toy_plain_logits(raw, weights, toks).numpy() for rid, toks in requests.items()}
     for steps in (rc.trace_whole(requests), rc.trace_chunks(requests), rc.trace_mixed(requests, max_live=3, seed=1)):
