@@ -57,7 +57,8 @@ __device__ __forceinline__ void kvb_grid_launch_dependents() { asm volatile("gri
 // ---- kernel timeline trace ----------------------------------------------------------------------
 // When a trace buffer is set, the first and the last block of every kernel of this library append
 // one event {tag, block, time at entry, time after kvb_grid_wait(), time at exit} (nanoseconds of
-// the GPU's global timer).  Word 0 of the buffer counts events, word 1 is the capacity in events.
+// the GPU's global timer).  Word 0 of the buffer counts events, word 1 is the capacity in events
+// (its top bit set: every block records, not only the first and the last).
 // The pointer lives once per translation unit (set through KVB_TRACE_TU's setter); null = off.
 static __device__ unsigned long long* kvb_trace_buffer = nullptr;
 
@@ -76,7 +77,7 @@ struct KvbTrace {
     if (b != nullptr && threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
       const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
       const bool last = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1;
-      if (first || last) {
+      if (first || last || (b[1] >> 63)) {
         buffer = b;
         entry = kvb_global_ns();
       }
@@ -88,10 +89,11 @@ struct KvbTrace {
   __device__ __forceinline__ ~KvbTrace() {
     if (buffer != nullptr) {
       const unsigned long long slot = atomicAdd(buffer, 1ull);
-      if (slot < buffer[1]) {
+      if (slot < (buffer[1] & ~(1ull << 63))) {
         unsigned long long* e = buffer + 2 + slot * 4;
         const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-        e[0] = (unsigned long long)tag | (first ? 0ull : 1ull << 32);
+        const bool last = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1;
+        e[0] = (unsigned long long)tag | (first ? 0ull : last ? 1ull << 32 : 2ull << 32);
         e[1] = entry;
         e[2] = waited;
         e[3] = kvb_global_ns();

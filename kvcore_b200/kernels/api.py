@@ -445,14 +445,15 @@ def _trace_set(pointer: int | None) -> None:
             raise KernelError(f"kvb_trace_set_{unit} failed")
 
 
-def trace_start(device: torch.device | str = "cuda:0", capacity: int = 1 << 16) -> None:
+def trace_start(device: torch.device | str = "cuda:0", capacity: int = 1 << 16, every_block: bool = False) -> None:
     """Start the kernel timeline trace: the first and last block of every kernel of this library
-    record when they entered, when the kernel in front had finished, and when they left."""
+    (``every_block``: all of them) record when they entered, when the kernel in front had finished,
+    and when they left."""
     global _trace_buffer
     ensure_built()
     torch.cuda.synchronize(device)
     buffer = torch.zeros(2 + 4 * capacity, dtype=torch.int64, device=device)
-    buffer[1] = capacity
+    buffer[1] = capacity | (-(1 << 63) if every_block else 0)
     with torch.cuda.device(device):
         _trace_set(buffer.data_ptr())
     _trace_buffer = buffer
@@ -469,12 +470,13 @@ def trace_stop() -> list[dict]:
         _trace_set(None)
     host = buffer.cpu().tolist()
     _trace_buffer = None
-    count = min(host[0], host[1])
+    count = min(host[0], host[1] & ((1 << 63) - 1))
     events = []
     for i in range(count):
         tag, entry, waited, leave = host[2 + 4 * i: 6 + 4 * i]
         events.append({"kernel": TRACE_TAGS.get(tag & 0xFFFFFFFF, str(tag & 0xFFFFFFFF)),
-                       "block": "last" if tag >> 32 else "first", "entry": entry, "waited": waited, "exit": leave})
+                       "block": ("first", "last", "other")[min(tag >> 32, 2)], "entry": entry, "waited": waited,
+                       "exit": leave})
     events.sort(key=lambda e: e["entry"])
     return events
 
