@@ -13,10 +13,18 @@ finished request's pages in reverse order, so pages are used again.
 
 Tables are persistent numpy rows indexed by the request's state slot and updated
 incrementally; the step function gathers the rows of the requests it runs.
+
+Prefix reuse (off unless asked for; reference: kv_utils.py:31-68, kv_manager.py:135-177,
+single_type_kv_manager.py:148-175): the full pages of a request are registered under a sha256
+chain over their token ids once computed; a new request whose prompt starts with registered
+pages takes them over instead of computing them (at least its last token is always computed).
+Only offered when there is one group that keeps all keys and no mixer has state of its own.
 """
 from __future__ import annotations
 
+import hashlib
 from dataclasses import dataclass, field
+from typing import Sequence
 
 import numpy as np
 
@@ -47,6 +55,7 @@ class _RequestState:
     # leading blocks were already handed back
     num_blocks: list[int] = field(default_factory=list)
     num_released: list[int] = field(default_factory=list)
+    page_keys: list[bytes] = field(default_factory=list)   # chain keys of the full pages registered so far
 
 
 class KVManagerError(RuntimeError):
@@ -62,6 +71,7 @@ class KVManager:
         page_size: int,
         max_num_seqs: int,
         max_model_len: int,
+        enable_prefix_caching: bool = False,
     ) -> None:
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
@@ -79,6 +89,9 @@ class KVManager:
         ]
         self._requests: dict[str, _RequestState] = {}
         self._fresh_slots: list[int] = []
+        # prefix reuse needs one table that keeps every key (a windowed group has given pages back)
+        self.prefix_caching = bool(enable_prefix_caching) and len(self.groups) == 1 and self.groups[0].window is None
+        self.num_prefix_hits = 0          # pages taken over instead of computed
 
     # ---- queries ---------------------------------------------------------------------------
     def has_request(self, request_id: str) -> bool:
@@ -117,26 +130,70 @@ class KVManager:
     def pages_needed(self, request_id: str, num_new_tokens: int) -> list[int]:
         return self._new_pages_needed(self._requests.get(request_id), num_new_tokens)
 
-    def can_fit(self, request_id: str, num_new_tokens: int) -> bool:
+    def can_fit(self, request_id: str, num_new_tokens: int, prefix_pages: Sequence[int] = ()) -> bool:
         """Whether ``num_new_tokens`` more tokens of the request can be given pages (and, for a
         request not yet seen, a state slot) right now.  Admission math as the reference's
-        ``can_fit`` (kv_manager.py:179-201) per group instead of per layer."""
+        ``can_fit`` (kv_manager.py:179-201) per group instead of per layer: new pages, plus the
+        taken-over pages that sit in the free queue now, must not exceed the free pages."""
         state = self._requests.get(request_id)
-        computed = 0 if state is None else state.num_computed
+        computed = len(prefix_pages) * self.page_size if state is None else state.num_computed
         if computed + num_new_tokens > self.max_model_len:
             return False
         if state is None and self.slots.num_free == 0:
             return False
+        if prefix_pages:
+            if state is not None or not self.prefix_caching:
+                return False
+            target = -(-(computed + num_new_tokens) // self.page_size)
+            queued = sum(1 for page in prefix_pages if self.pools[0].is_queued(page))
+            return target - len(prefix_pages) + queued <= self.pools[0].num_free
         needed = self._new_pages_needed(state, num_new_tokens)
         return all(need <= pool.num_free for need, pool in zip(needed, self.pools))
 
+    # ---- prefix reuse ----------------------------------------------------------------------
+    def _chain_key(self, previous: bytes, tokens: Sequence[int]) -> bytes:
+        return hashlib.sha256(previous + np.asarray(tokens, dtype=np.int64).tobytes()).digest()
+
+    def find_prefix(self, token_ids: Sequence[int]) -> list[int]:
+        """Pages whose registered contents are the leading full pages of ``token_ids``; at least
+        the last token is left to compute."""
+        if not self.prefix_caching:
+            return []
+        pages: list[int] = []
+        key = b""
+        for block in range((len(token_ids) - 1) // self.page_size):
+            key = self._chain_key(key, token_ids[block * self.page_size : (block + 1) * self.page_size])
+            page = self.pools[0].lookup(key)
+            if page is None:
+                break
+            pages.append(page)
+        return pages
+
+    def register_full_pages(self, request_id: str, token_ids: Sequence[int]) -> None:
+        """Make the request's computed full pages findable (``token_ids``: all its tokens so far)."""
+        if not self.prefix_caching:
+            return
+        state = self._requests.get(request_id)
+        if state is None:
+            return
+        full = min(state.num_computed, len(token_ids)) // self.page_size
+        row = self.tables[0][state.slot]
+        while len(state.page_keys) < full:
+            block = len(state.page_keys)
+            previous = state.page_keys[-1] if state.page_keys else b""
+            key = self._chain_key(previous, token_ids[block * self.page_size : (block + 1) * self.page_size])
+            state.page_keys.append(key)
+            self.pools[0].register(int(row[block]), key)   # a key already taken stays with its page
+
     # ---- changes ---------------------------------------------------------------------------
-    def allocate_slots(self, request_id: str, num_new_tokens: int) -> bool:
+    def allocate_slots(self, request_id: str, num_new_tokens: int, prefix_pages: Sequence[int] = ()) -> bool:
         """Give the request pages for ``num_new_tokens`` tokens beyond those computed.
-        Returns False (and changes nothing) if they do not fit."""
+        ``prefix_pages`` (a new request only, from ``find_prefix``): pages taken over as its
+        first ones; their tokens count as computed.  Returns False (and changes nothing) if
+        the pages do not fit."""
         if num_new_tokens <= 0:
             raise ValueError(f"num_new_tokens must be positive, got {num_new_tokens}")
-        if not self.can_fit(request_id, num_new_tokens):
+        if not self.can_fit(request_id, num_new_tokens, prefix_pages):
             return False
         state = self._requests.get(request_id)
         if state is None:
@@ -150,6 +207,14 @@ class KVManager:
             self._fresh_slots.append(slot)
             for table in self.tables:
                 table[slot, :] = NULL_PAGE
+            if prefix_pages:
+                for page in prefix_pages:
+                    self.pools[0].share(page)
+                count = len(prefix_pages)
+                self.tables[0][slot, :count] = list(prefix_pages)
+                state.num_blocks[0] = count
+                state.num_computed = count * self.page_size
+                self.num_prefix_hits += count
         needed = self._new_pages_needed(state, num_new_tokens)
         for g, need in enumerate(needed):
             if need:
@@ -207,6 +272,7 @@ class KVManager:
         """No page lost, none held twice, tables and pools agree (used by tests)."""
         for g, pool in enumerate(self.pools):
             seen: dict[int, str] = {}
+            holders: dict[int, int] = {}
             for request_id, state in self._requests.items():
                 row = self.tables[g][state.slot]
                 if np.any(row[state.num_blocks[g] :] != NULL_PAGE):
@@ -215,13 +281,19 @@ class KVManager:
                     page = int(page)
                     if page == NULL_PAGE:
                         continue
-                    if page in seen:
+                    if page in seen and not self.prefix_caching:
                         raise KVManagerError(
                             f"page {page} of group {g} is held by {seen[page]!r} and {request_id!r}"
                         )
                     if not pool.is_held(page):
                         raise KVManagerError(f"page {page} of group {g} is in a table but free")
                     seen[page] = request_id
+                    holders[page] = holders.get(page, 0) + 1
+            for page, count in holders.items():
+                if pool.ref_count(page) != count:
+                    raise KVManagerError(
+                        f"page {page} of group {g} is in {count} table(s) but counts {pool.ref_count(page)} holder(s)"
+                    )
             free = pool.free_pages()
             if len(set(free)) != len(free):
                 raise KVManagerError(f"group {g}: a page is in the free queue twice")

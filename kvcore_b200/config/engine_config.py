@@ -75,12 +75,14 @@ class CacheConfig:
 
     ``block_size`` is the number of tokens a page holds.  ``num_gpu_blocks`` fixes the
     number of pages per cache group; when None the pool is sized from free device memory
-    times ``gpu_memory_utilization``.
+    times ``gpu_memory_utilization``.  ``enable_prefix_caching`` (the reference's
+    ``enable_caching``): requests whose prompts begin with the same full pages share them.
     """
 
     block_size: int = 16
     num_gpu_blocks: int | None = None
     gpu_memory_utilization: float = 0.9
+    enable_prefix_caching: bool = False
 
     def __post_init__(self) -> None:
         if self.block_size <= 0:

@@ -119,6 +119,9 @@ class ModelRunner:
             page_size=self.page_size,
             max_num_seqs=self.max_num_seqs,
             max_model_len=self.max_model_len,
+            # state that a mixer keeps per request cannot be taken over with the pages
+            enable_prefix_caching=config.cache_config.enable_prefix_caching
+            and not any(req.state_spec is not None for req in requirements),
         )
         self.storage = CacheStorage(
             self.model,

@@ -236,6 +236,11 @@ class Scheduler:
             is_prefill = self._is_prefill(request)
             if is_prefill and not self._can_schedule_partial_prefill(request, partial, long_partial):
                 return None
+            # a request that starts (or starts again): pages that already hold its first tokens
+            prefix_pages: list[int] = []
+            if from_waiting and request.num_computed_tokens == 0:
+                prefix_pages = self.kv_manager.find_prefix(request.all_token_ids)
+                request.num_computed_tokens = len(prefix_pages) * self.kv_manager.page_size
             remaining = request.num_tokens - request.num_computed_tokens
             if remaining <= 0:
                 return None
@@ -243,7 +248,9 @@ class Scheduler:
             if 0 < threshold < remaining:
                 remaining = threshold
             num_tokens = min(remaining, token_budget)
-            if not self.kv_manager.allocate_slots(request.request_id, num_tokens):
+            if not self.kv_manager.allocate_slots(request.request_id, num_tokens, prefix_pages):
+                if prefix_pages:
+                    request.num_computed_tokens = 0
                 return None
             context = request.num_computed_tokens
             if from_waiting:
@@ -337,6 +344,7 @@ class Scheduler:
         for request_id, num_tokens in scheduler_output.num_scheduled_tokens.items():
             request = self.requests[request_id]
             request.num_computed_tokens += num_tokens
+            self.kv_manager.register_full_pages(request_id, request.all_token_ids)
             sampled: int | None = None
             finished = False
             reason: FinishReason | None = None

@@ -41,6 +41,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--num-gpu-blocks", type=int, default=None)
     parser.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    parser.add_argument("--enable-prefix-caching", action="store_true",
+                        help="requests whose prompts begin with the same full pages share them")
     parser.add_argument("--max-model-len", type=int, default=None)
     parser.add_argument("--max-num-seqs", type=int, default=1024)
     parser.add_argument("--max-num-scheduled-tokens", type=int, default=1024)
@@ -67,7 +69,8 @@ def build_config(args: argparse.Namespace) -> KVCoreConfig:
                                  max_model_len=args.max_model_len),
         load_config=LoadConfig(random_weights=args.random_weights, seed=args.seed),
         cache_config=CacheConfig(block_size=args.block_size, num_gpu_blocks=args.num_gpu_blocks,
-                                 gpu_memory_utilization=args.gpu_memory_utilization),
+                                 gpu_memory_utilization=args.gpu_memory_utilization,
+                                 enable_prefix_caching=args.enable_prefix_caching),
         scheduler_config=SchedulerConfig(
             max_num_seqs=args.max_num_seqs,
             max_num_scheduled_tokens=args.max_num_scheduled_tokens,

@@ -154,6 +154,134 @@ def test_random_orders_keep_every_page_accounted(seed):
     assert not any(np.any(t) for t in kv.tables)
 
 
+# ---- prefix reuse ----------------------------------------------------------------------------------
+def test_pool_shared_pages_and_registered_contents():
+    pool = PagePool(6)
+    a, b = pool.allocate(2)
+    assert pool.register(a, "ka") and not pool.register(b, "ka") and pool.lookup("ka") == a
+    pool.share(a)
+    assert pool.ref_count(a) == 2
+    pool.free([a])
+    assert pool.is_held(a) and not pool.is_queued(a)
+    pool.free([a])                                   # last holder: to the tail, still findable
+    assert pool.is_queued(a) and pool.lookup("ka") == a and pool.free_pages()[-1] == a
+    pool.share(a)                                    # taken over again, out of the queue
+    assert not pool.is_queued(a) and pool.ref_count(a) == 1
+    pool.free([a])
+    with pytest.raises(PagePoolError, match="twice"):
+        pool.free([a])
+    with pytest.raises(PagePoolError, match="registered"):
+        pool.share(b)
+    taken = pool.allocate(pool.num_free)             # the queue hands the page out again: key dropped
+    assert a in taken and pool.lookup("ka") is None
+
+
+def prefix_manager(**kw):
+    return KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=kw.pop("num_pages", 17), page_size=4,
+                     max_num_seqs=4, max_model_len=64, enable_prefix_caching=True, **kw)
+
+
+def test_prefix_pages_are_taken_over_by_a_later_request():
+    kv = prefix_manager()
+    first = list(range(100, 114))                    # 14 tokens: 3 full pages and a half
+    assert kv.find_prefix(first) == []
+    assert kv.allocate_slots("a", 14)
+    kv.advance("a", 14)
+    kv.register_full_pages("a", first)
+    a_pages = kv.block_ids("a")[0]
+    second = first[:9] + [7, 8, 9]                   # shares two full pages (8 tokens)
+    hit = kv.find_prefix(second)
+    assert hit == list(a_pages[:2])
+    assert kv.allocate_slots("b", len(second) - 8, hit)
+    assert kv.num_computed("b") == 8 and kv.block_ids("b")[0][:2] == a_pages[:2]
+    assert kv.block_ids("b")[0][2] not in a_pages
+    kv.check_invariants()
+    kv.free("a")                                      # shared pages stay with b
+    kv.check_invariants()
+    assert all(kv.pools[0].is_held(p) for p in hit)
+    kv.advance("b", len(second) - 8)
+    kv.register_full_pages("b", second)
+    kv.free("b")
+    kv.check_invariants()
+    assert kv.num_free_pages() == [16]
+    # everything is free, yet still findable: a third request takes pages over out of the queue
+    again = kv.find_prefix(first)
+    assert again == list(a_pages[:3])
+    assert kv.can_fit("c", 2, again) and kv.allocate_slots("c", 2, again)
+    assert kv.num_computed("c") == 12 and kv.num_prefix_hits == 5
+    kv.check_invariants()
+
+
+def test_the_last_token_of_a_prompt_is_always_left_to_compute():
+    kv = prefix_manager()
+    tokens = list(range(8))
+    assert kv.allocate_slots("a", 8)
+    kv.advance("a", 8)
+    kv.register_full_pages("a", tokens)
+    assert len(kv.find_prefix(tokens)) == 1           # 8 tokens = 2 full pages, but only 1 may be taken
+    assert len(kv.find_prefix(tokens + [9])) == 2
+
+
+def test_taken_over_pages_in_the_queue_count_against_the_free_pages():
+    kv = prefix_manager(num_pages=5)                 # 4 usable pages
+    tokens = list(range(12))
+    assert kv.allocate_slots("a", 12)
+    kv.advance("a", 12)
+    kv.register_full_pages("a", tokens)
+    kv.free("a")
+    hit = kv.find_prefix(tokens + [1, 2, 3, 4, 5])   # 3 pages, all in the queue now
+    assert len(hit) == 3
+    assert not kv.can_fit("b", 8, hit)               # 5 pages in all > 4
+    assert kv.can_fit("b", 4, hit) and kv.allocate_slots("b", 4, hit)
+    kv.check_invariants()
+    assert kv.num_free_pages() == [0]
+
+
+def test_prefix_reuse_is_off_without_the_flag_and_with_windows():
+    plain = manager()
+    assert not plain.prefix_caching and plain.find_prefix(list(range(20))) == []
+    windowed = KVManager([CacheGroupSpec(0, (0,), 2, 16, 8)], num_pages=9, page_size=4, max_num_seqs=2,
+                         max_model_len=64, enable_prefix_caching=True)
+    assert not windowed.prefix_caching
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_orders_with_shared_prefixes_keep_every_page_accounted(seed):
+    rng = random.Random(100 + seed)
+    kv = prefix_manager(num_pages=30)
+    stems = [[rng.randint(0, 50) for _ in range(24)] for _ in range(3)]
+    live: dict[str, list[int]] = {}
+    counter = 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.4 and len(live) < 4:
+            counter += 1
+            rid = f"r{counter}"
+            tokens = rng.choice(stems)[: rng.randint(1, 24)] + [rng.randint(60, 90) for _ in range(rng.randint(1, 6))]
+            hit = kv.find_prefix(tokens)
+            n = len(tokens) - 4 * len(hit)
+            if kv.allocate_slots(rid, n, hit):
+                assert kv.num_computed(rid) == 4 * len(hit)
+                kv.advance(rid, n)
+                kv.register_full_pages(rid, tokens)
+                live[rid] = tokens
+        elif action < 0.7 and live:
+            rid = rng.choice(list(live))
+            if kv.allocate_slots(rid, 1):
+                kv.advance(rid, 1)
+                live[rid] = live[rid] + [rng.randint(60, 90)]
+                kv.register_full_pages(rid, live[rid])
+        elif live:
+            rid = rng.choice(list(live))
+            kv.free(rid)
+            del live[rid]
+        kv.check_invariants()
+    for rid in list(live):
+        kv.free(rid)
+    kv.check_invariants()
+    assert kv.num_free_pages() == [29] and kv.num_prefix_hits > 0
+
+
 def test_state_slots():
     pool = StateSlotPool(2)
     a, b = pool.allocate("a"), pool.allocate("b")

@@ -40,7 +40,8 @@ def engine_config(folder, device, dtype="float32", **overrides):
     return KVCoreConfig(
         model_config=ModelConfig(model=str(folder), dtype=dtype, max_model_len=overrides.pop("max_model_len", 128)),
         load_config=LoadConfig(**overrides.pop("load", {})),
-        cache_config=CacheConfig(block_size=overrides.pop("block_size", 16), num_gpu_blocks=overrides.pop("num_gpu_blocks", 40)),
+        cache_config=CacheConfig(block_size=overrides.pop("block_size", 16), num_gpu_blocks=overrides.pop("num_gpu_blocks", 40),
+                                 enable_prefix_caching=overrides.pop("prefix_caching", False)),
         scheduler_config=SchedulerConfig(**sched),
         device_config=DeviceConfig(device=device),
     )
@@ -80,6 +81,33 @@ def test_generation_with_few_pages_and_preemption(device, tmp_path):
         assert list(output.output_token_ids) == plain_llama.greedy_generate(config, weights, prompt, 10)
     assert engine.engine_core.scheduler.num_preemptions > 0
     engine.engine_core.model_runner.kv_manager.check_invariants()
+
+
+def test_generation_with_shared_prefixes_reuses_pages_and_keeps_the_tokens(device, tmp_path):
+    """Prompts that begin alike: with prefix reuse their common pages are computed once (also across
+    generate() calls, after the first owner is gone), and the tokens are the plain ones."""
+    config = rc.TINY_CONFIGS["A"]
+    folder = rc.write_model(tmp_path / "m", config, 0, "float32")
+    weights = plain_llama.load_weights(folder)
+    stem = rc.random_tokens(256, 37, 90)
+    prompts = [stem + rc.random_tokens(256, n, 91 + i) for i, n in enumerate((3, 9, 1))] + [stem[:21]]
+    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=60, prefix_caching=True,
+                                     scheduler=dict(max_num_scheduled_tokens=24, max_num_partial_prefills=2)))
+    kv = engine.engine_core.model_runner.kv_manager
+    assert kv.prefix_caching
+    expected = [plain_llama.greedy_generate(config, weights, p, 6) for p in prompts]
+    for round_ in range(2):
+        requests = [GenerationRequest(f"r{round_}-{i}", SamplingParams(max_tokens=6, temperature=0.0), tuple(p))
+                    for i, p in enumerate(prompts)]
+        outputs = engine.generate(requests)
+        assert [list(o.output_token_ids) for o in outputs] == expected
+        kv.check_invariants()
+        assert not kv.live_requests()
+        if round_ == 0:
+            first_round_hits = kv.num_prefix_hits
+            assert first_round_hits >= 9          # the 36-token stem is 9 pages; later requests take them over
+    # the second round found everything but each prompt's last page
+    assert kv.num_prefix_hits - first_round_hits >= sum((len(p) - 1) // 4 for p in prompts) - 2
 
 
 def test_too_small_a_cache_is_an_error(device, tmp_path):

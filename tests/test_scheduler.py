@@ -11,9 +11,10 @@ from kvcore_b200.engine.scheduler import Scheduler
 from kvcore_b200.sampling import SamplingParams
 
 
-def make(num_pages=33, page_size=4, max_model_len=64, **cfg):
+def make(num_pages=33, page_size=4, max_model_len=64, prefix_caching=False, **cfg):
     kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=num_pages, page_size=page_size,
-                   max_num_seqs=cfg.get("max_num_seqs", 8), max_model_len=max_model_len)
+                   max_num_seqs=cfg.get("max_num_seqs", 8), max_model_len=max_model_len,
+                   enable_prefix_caching=prefix_caching)
     return Scheduler(SchedulerConfig(**cfg), kv), kv
 
 
@@ -185,3 +186,39 @@ def test_no_progress_is_reported_when_preemption_is_off_or_impossible():
     run_step(sched2, kv2)
     out = sched2.schedule()
     assert out.total_num_scheduled_tokens == 0 and sched2.last_no_progress_state.running == ("a",)
+
+
+def test_a_request_with_a_known_prefix_starts_behind_it():
+    sched, kv = make(prefix_caching=True, max_num_scheduled_tokens=64, max_num_partial_prefills=4)
+    sched.add_request(request("a", 14, max_tokens=1))
+    out, upd = run_step(sched, kv)
+    assert out.scheduled_new_reqs[0].num_computed_tokens == 0 and upd.finished_requests
+    # same first 14 tokens, then more: 3 full pages (12 tokens) are taken over, even though "a" is gone
+    sched.add_request(request("b", 20, max_tokens=2))
+    out, _ = run_step(sched, kv)
+    new = out.scheduled_new_reqs[0]
+    assert new.req_id == "b" and new.num_computed_tokens == 12 and out.num_scheduled_tokens == {"b": 8}
+    assert kv.num_prefix_hits == 3
+    kv.check_invariants()
+    # an identical prompt: everything but its last token's page is taken over
+    sched.add_request(request("c", 20, max_tokens=1))
+    out, _ = run_step(sched, kv)
+    assert {r.req_id: r.num_computed_tokens for r in out.scheduled_new_reqs} == {"c": 16}
+    while sched.has_unfinished_requests():
+        run_step(sched, kv)
+    kv.check_invariants()
+    assert kv.num_free_pages() == [32]
+
+
+def test_a_preempted_request_finds_its_own_pages_again():
+    sched, kv = make(num_pages=9, prefix_caching=True, max_num_scheduled_tokens=64, max_num_partial_prefills=4)
+    sched.add_request(request("a", 12, max_tokens=12))
+    sched.add_request(request("b", 12, max_tokens=12))
+    preempted = 0
+    for _ in range(60):
+        if not sched.has_unfinished_requests():
+            break
+        out, _ = run_step(sched, kv)
+        preempted += len(out.preempted_req_ids)
+        kv.check_invariants()
+    assert not sched.has_unfinished_requests() and preempted > 0 and kv.num_prefix_hits > 0
