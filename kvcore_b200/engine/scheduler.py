@@ -238,7 +238,8 @@ class Scheduler:
                 return None
             # a request that starts (or starts again): pages that already hold its first tokens
             prefix_pages: list[int] = []
-            if from_waiting and request.num_computed_tokens == 0:
+            if (from_waiting and request.num_computed_tokens == 0
+                    and not request.sampling_params.skip_reading_prefix_cache):
                 prefix_pages = self.kv_manager.find_prefix(request.all_token_ids)
                 request.num_computed_tokens = len(prefix_pages) * self.kv_manager.page_size
             remaining = request.num_tokens - request.num_computed_tokens

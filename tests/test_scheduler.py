@@ -200,10 +200,11 @@ def test_a_request_with_a_known_prefix_starts_behind_it():
     assert new.req_id == "b" and new.num_computed_tokens == 12 and out.num_scheduled_tokens == {"b": 8}
     assert kv.num_prefix_hits == 3
     kv.check_invariants()
-    # an identical prompt: everything but its last token's page is taken over
+    # an identical prompt: everything but its last token's page is taken over; a request may opt out
     sched.add_request(request("c", 20, max_tokens=1))
+    sched.add_request(request("d", 20, max_tokens=1, skip_reading_prefix_cache=True))
     out, _ = run_step(sched, kv)
-    assert {r.req_id: r.num_computed_tokens for r in out.scheduled_new_reqs} == {"c": 16}
+    assert {r.req_id: r.num_computed_tokens for r in out.scheduled_new_reqs} == {"c": 16, "d": 0}
     while sched.has_unfinished_requests():
         run_step(sched, kv)
     kv.check_invariants()
