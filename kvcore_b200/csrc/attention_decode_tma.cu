@@ -116,7 +116,12 @@ template <int D>
 __global__ void __launch_bounds__(TD_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const DecodeParams p) {
-  KVB_KERNEL_PROLOGUE(KVB_TAG_DECODE_TMA);
+  // No wait at the top: the pages of keys cached by earlier steps, the block table and the lengths
+  // are written by no kernel of this step, so the producer warp starts its ring while the kernel
+  // in front (the rotation and cache write of this step's tokens) still runs.  It waits before
+  // the first tile that reaches this step's tokens; the other warps wait before they read q.
+  KvbTrace kvb_trace_scope__(KVB_TAG_DECODE_TMA);
+  kvb_grid_launch_dependents();
   constexpr int HALVES = D / 64;
   constexpr int KV_BYTES = TD_KEYS * D * 2;        // one of K or V of a stage
   constexpr int STAGE_BYTES = 2 * KV_BYTES;
@@ -162,17 +167,22 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G)
-  for (int i = threadIdx.x; i < 16 * (D / 8); i += TD_THREADS) {
-    const int r = i / (D / 8), chunk = i % (D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows_total) {
-      const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8);
-    }
-    *reinterpret_cast<uint4*>(qs + r * QROW + chunk * 8) = v;
-  }
   __syncthreads();
+  if (warp != TD_CONSUMERS) {
+    kvb_grid_wait();                 // q is the output of the kernels in front
+    kvb_trace_scope__.after_wait();
+    // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G)
+    for (int i = threadIdx.x; i < 16 * (D / 8); i += TD_CONSUMERS * 32) {
+      const int r = i / (D / 8), chunk = i % (D / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_total) {
+        const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+        v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8);
+      }
+      *reinterpret_cast<uint4*>(qs + r * QROW + chunk * 8) = v;
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+  }
 
   float o[DBLOCKS][4];
 #pragma unroll
@@ -201,9 +211,14 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     };
     int cur = fetch(lane), nxt = fetch(32 + lane);
     int issued = 0;
+    bool waited = false;
     for (int it = 0; it < num_tiles; ++it) {
       const int stage = it % TD_STAGES;
       const int e0 = it * ppt;
+      if (!waited && (tile_begin + it + 1) * TD_KEYS > context) {   // this tile holds keys written in this step
+        kvb_grid_wait();
+        waited = true;
+      }
       if (e0 > 0 && (e0 & 31) == 0) {                 // crossed into the next batch of entries
         cur = nxt;
         nxt = fetch(e0 + 32 + lane);
@@ -231,6 +246,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
       issued = it + 1;
     }
+    if (!waited) kvb_grid_wait();   // this warp joins the stores below: nothing is written before the wait
     // on an aborted run, let the copies already issued land before the block may exit
     if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
       for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
