@@ -277,12 +277,18 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           // ---- the owner: add the parts of the blocks behind (in k order), then store ----
           bool complete = true;
           if (seg_end < tile_end) {
-            for (int c = me + 1; c < blocks && gs_range_start(p.units, blocks, c) < tile_end; ++c) {
-              if (tid == 0) {
+            // the blocks behind that hold stages of this tile: all their flags are awaited at once
+            // (one thread each), then all their sums are fetched together and added in k order
+            int parts = 0;
+            while (me + 1 + parts < blocks && gs_range_start(p.units, blocks, me + 1 + parts) < tile_end) ++parts;
+            for (int c0 = 0; c0 < parts && complete; c0 += 4) {
+              const int batch = parts - c0 < 4 ? parts - c0 : 4;
+              if (tid < batch) {
+                const int* flag = &p.flags[me + 1 + c0 + tid];
                 int seen = 0;
                 for (unsigned spin = 0; spin < GS_SPIN_LIMIT && !seen; ++spin) {
-                  seen = gs_ld_acquire(&p.flags[c]);
-                  if (!seen && spin > 16) __nanosleep(100);
+                  seen = gs_ld_acquire(flag);
+                  if (!seen && spin > 4096) __nanosleep(64);   // the blocks finish together: spin first
                 }
                 if (!seen) {
                   atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
@@ -292,14 +298,30 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
               asm volatile("bar.sync 2, 128;\n");
               if (*reinterpret_cast<volatile int*>(&flags[0])) { complete = false; break; }
               __threadfence();
-              const float* src = p.partial + (size_t)c * (MBLK * 4 * 128) + tid;
+              float part[4][MBLK][4];
 #pragma unroll
-              for (int j = 0; j < MBLK; ++j) {
+              for (int c = 0; c < 4; ++c) {
+                if (c < batch) {
+                  const float* src = p.partial + (size_t)(me + 1 + c0 + c) * (MBLK * 4 * 128) + tid;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[0][j][e] += __ldcg(src + (j * 4 + e) * 128);
+                  for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) part[c][j][e] = __ldcg(src + (j * 4 + e) * 128);
+                  }
+                }
+              }
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                if (c < batch) {
+#pragma unroll
+                  for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[0][j][e] += part[c][j][e];
+                  }
+                }
               }
               asm volatile("bar.sync 2, 128;\n");
-              if (tid == 0) p.flags[c] = 0;   // ready for the next launch
+              if (tid < batch) p.flags[me + 1 + c0 + tid] = 0;   // ready for the next launch
             }
           }
           if (complete && !p.silu_pairs) {

@@ -420,11 +420,11 @@ def paged_attention(
 
 _mm_out_dtype_ok: bool | None = None
 # bf16 layers of at most STREAM_AUTO_ROWS tokens (K a multiple of 64) go to this library's own
-# weight-streaming kernel; above that the library product measured equal or a little faster in a
-# whole decode step (B200, Llama 3.1 8B shapes), so it keeps them.  KVCORE_B200_STREAM_ROWS
-# overrides the bound (0: never, 16: wherever the kernel can).
+# weight-streaming kernel (in a whole decode step it measured level with the library product on
+# B200 at Llama 3.1 8B shapes, ahead at batch 1); larger batches go to the library product.
+# KVCORE_B200_STREAM_ROWS overrides the bound (0: never).
 STREAM_MAX_ROWS = 16
-STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "4"))
+STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 _stream_scratch: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
