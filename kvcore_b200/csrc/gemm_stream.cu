@@ -40,6 +40,8 @@
 #define GS_THREADS ((GS_CONSUMERS + 1) * 32)
 #define GS_STAGES 5
 #define GS_SPIN_LIMIT (1u << 22)
+#define GS_NORM_W_BYTES (16 * 1024)   // norm weights a NORMED kernel keeps in shared memory
+#define GS_NORMALISERS 4               // NORMED: warps that normalise the token rows of each stage
 
 struct StreamParams {
   void* out; int out_f32; long long ldo;
@@ -49,6 +51,15 @@ struct StreamParams {
   float* partial;                    // [blocks][MBLK * 4][128]
   int* flags;                        // [blocks], zero between launches
   int* status;
+  // NORMED kernels: the rows of x are sums s that still need their RMS norm.  Every token's sum
+  // of squares arrives in pieces, sumsq_in[m * sumsq_pieces + t] (added in a fixed order); a warp
+  // of its own turns each stage's token rows into bf16(norm_weight[k] * (s * rsqrt(mean + eps)))
+  // before the consumers use them.
+  const float* sumsq_in; int sumsq_pieces; const void* norm_weight; int norm_weight_f32; float eps;
+  // Epilogue with the residual stream (residual != null, [M, N] bf16): s = bf16(bf16(out) + residual)
+  // written over residual (every tile its own columns), and the sum of its squares over the tile's
+  // 64 columns to sumsq_out[m * n_tiles + tile].  out itself is not written.
+  bf16* residual; float* sumsq_out;
   int silu_pairs;                    // 1: rows n and n+8 of every 16 are a (gate, up) pair: out[m, .] = silu(gate) * up
 };
 
@@ -120,8 +131,8 @@ __device__ __forceinline__ int gs_range_start(int units, int blocks, int b) {
   return (int)(((long long)units * b) / blocks);
 }
 
-template <int MBLK>   // MB = 8 * MBLK token rows
-__global__ void __launch_bounds__(GS_THREADS, 1)
+template <int MBLK, bool NORMED>   // MB = 8 * MBLK token rows; NORMED: x is normalised on the way (see StreamParams)
+__global__ void __launch_bounds__(GS_THREADS + GS_NORMALISERS * 32, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                    const StreamParams p) {
   constexpr int MB = 8 * MBLK;
@@ -133,10 +144,16 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 
   extern __shared__ __align__(1024) unsigned char gs_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gs_dyn) + 1023) & ~uintptr_t(1023));
-  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(base + STAGES * STAGE_BYTES);
+  unsigned char* tail = base + STAGES * STAGE_BYTES;
+  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(tail);   // weights (and x, unless NORMED) landed
   unsigned long long* empty_bar = full_bar + STAGES;
-  int* flags = reinterpret_cast<int*>(empty_bar + STAGES);     // [0] abort
-  float* halves = reinterpret_cast<float*>(flags + 4);         // [MBLK * 4][128 threads]
+  unsigned long long* xraw_bar = empty_bar + STAGES;            // NORMED: the raw token rows landed
+  unsigned long long* xready_bar = xraw_bar + STAGES;           // NORMED: the token rows are normalised
+  int* flags = reinterpret_cast<int*>(tail + 512);              // [0] abort
+  float* halves = reinterpret_cast<float*>(tail + 1024);        // [MBLK * 4][128 threads]
+  // the finished tile, [MB tokens][64 rows] in the output's type, so that it leaves in whole lines
+  unsigned char* out_tile = tail + 1024 + MBLK * 4 * 128 * sizeof(float);
+  unsigned char* norm_w = out_tile + MB * GS_NT * sizeof(float);   // NORMED: the norm weights, as stored
 
   KvbTrace trace(KVB_TAG_GEMM_STREAM);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,6 +163,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     for (int s = 0; s < STAGES; ++s) {
       gs_mbar_init(&full_bar[s], 1);
       gs_mbar_init(&empty_bar[s], GS_CONSUMERS);
+      gs_mbar_init(&xraw_bar[s], 1);
+      gs_mbar_init(&xready_bar[s], GS_NORMALISERS);
     }
     flags[0] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -163,7 +182,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       // written by no kernel of the step)
       for (int i = 0; i < pre; ++i) {
         const int u = u_begin + i;
-        gs_expect_tx(&full_bar[i], (unsigned)STAGE_BYTES);
+        gs_expect_tx(&full_bar[i], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
         gs_tma_3d(base + i * STAGE_BYTES, &w_map, 0, (u / p.kchunks) * GS_NT, (u % p.kchunks) * GS_KG, &full_bar[i]);
       }
       kvb_grid_wait();                            // x is the output of the kernel in front
@@ -180,15 +199,90 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         const int slab = (u % p.kchunks) * GS_KG;
         unsigned char* wdst = base + stage * STAGE_BYTES;
         if (it >= pre) {
-          gs_expect_tx(&full_bar[stage], (unsigned)STAGE_BYTES);
+          gs_expect_tx(&full_bar[stage], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
           gs_tma_3d(wdst, &w_map, 0, (u / p.kchunks) * GS_NT, slab, &full_bar[stage]);
         }
-        gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
+        if (NORMED) {
+          gs_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
+          gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &xraw_bar[stage]);
+        } else {
+          gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
+        }
         issued = it + 1;
       }
       if (*reinterpret_cast<volatile int*>(&flags[0])) {   // gave up: let the copies in flight land
-        for (int j = max(0, issued - STAGES); j < issued; ++j)
+        for (int j = max(0, issued - STAGES); j < issued; ++j) {
           gs_wait_bounded(&full_bar[j % STAGES], (j / STAGES) & 1);
+          if (NORMED) gs_wait_bounded(&xraw_bar[j % STAGES], (j / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp > GS_CONSUMERS) {
+    // ---------------- NORMED: the normaliser warps; warp n takes token rows n, n + 4, ... ----------------
+    if (NORMED) {
+      const int nw = warp - GS_CONSUMERS - 1;
+      // the norm weights (written by no kernel of the step) into shared memory, before the wait
+      const int w_bytes = p.K * (p.norm_weight_f32 ? 4 : 2);
+      for (int i = (nw * 32 + lane) * 16; i < w_bytes; i += GS_NORMALISERS * 32 * 16)
+        *reinterpret_cast<uint4*>(norm_w + i) = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.norm_weight) + i);
+      asm volatile("bar.sync 3, %0;\n" ::"n"(GS_NORMALISERS * 32));
+      kvb_grid_wait();
+      // 1 / rms of this warp's token rows from the pieces of their sums of squares: every lane adds
+      // its pieces in order, the lanes are added by a butterfly, so the value depends on the pieces alone
+      constexpr int ROWS = MB / GS_NORMALISERS;
+      float inv[ROWS];
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        const int m = nw + i * GS_NORMALISERS;
+        float part = 0.0f;
+        if (m < p.M)
+          for (int t = lane; t < p.sumsq_pieces; t += 32) part += __ldcg(p.sumsq_in + (size_t)m * p.sumsq_pieces + t);
+        inv[i] = 1.0f / sqrtf(warp_sum(part) / (float)p.K + p.eps);
+      }
+      const int total = u_end - u_begin;
+      for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        int fine = gs_wait_bounded(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
+        fine = __all_sync(0xffffffffu, fine);
+        if (!fine) {
+          if (lane == 0) {
+            atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+            atomicExch(&flags[0], 1);
+          }
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(&flags[0])) break;
+        const int k = ((u_begin + it) % p.kchunks) * KB + lane * 8;   // this lane's 8 k-values of the stage
+        unsigned char* xs = base + stage * STAGE_BYTES + W_BYTES;
+        if (k < p.K) {                                               // beyond K the rows are zeros
+          float g[8];
+          if (p.norm_weight_f32) {
+            const float4 lo = *reinterpret_cast<const float4*>(norm_w + (size_t)k * 4);
+            const float4 hi = *reinterpret_cast<const float4*>(norm_w + (size_t)k * 4 + 16);
+            g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w; g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+          } else {
+            Vec16<bf16> gw;
+            gw.raw = *reinterpret_cast<const uint4*>(norm_w + (size_t)k * 2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = gw.get(j);
+          }
+          uint4 raw[ROWS];
+#pragma unroll
+          for (int i = 0; i < ROWS; ++i)
+            raw[i] = *reinterpret_cast<const uint4*>(xs + gs_swz(nw + i * GS_NORMALISERS, lane * 8, MB));
+#pragma unroll
+          for (int i = 0; i < ROWS; ++i) {
+            Vec16<bf16> v, o;
+            v.raw = raw[i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.set(j, g[j] * (v.get(j) * inv[i]));
+            *reinterpret_cast<uint4*>(xs + gs_swz(nw + i * GS_NORMALISERS, lane * 8, MB)) = o.raw;
+          }
+        }
+        // these writes come before the TMA box that will reuse the stage
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) gs_arrive(&xready_bar[stage]);
       }
     }
   } else {
@@ -213,7 +307,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       }
       for (; u < seg_end; ++u, ++it) {
         const int stage = it % STAGES;
-        if (!__all_sync(0xffffffffu, gs_wait_bounded(&full_bar[stage], (it / STAGES) & 1))) {
+        bool landed = gs_wait_bounded(&full_bar[stage], (it / STAGES) & 1);
+        if (NORMED && landed) landed = gs_wait_bounded(&xready_bar[stage], (it / STAGES) & 1);
+        if (!__all_sync(0xffffffffu, landed)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(&flags[0], 1);
           break;
@@ -324,42 +420,92 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
               if (tid < batch) p.flags[me + 1 + c0 + tid] = 0;   // ready for the next launch
             }
           }
-          if (complete && !p.silu_pairs) {
-            const int n_lo = n_tile * GS_NT + rg * 16 + (lane >> 2);
+          if (complete) {
+            // ---- bias, activation, then through shared memory: the tile leaves as whole 128-byte runs ----
+            const int r_lo = rg * 16 + (lane >> 2);               // row of the tile (and r_lo + 8)
+            const int width = p.silu_pairs ? GS_NT / 2 : GS_NT;   // output columns this tile makes
+            if (!p.silu_pairs) {
 #pragma unroll
-            for (int j = 0; j < MBLK; ++j) {
+              for (int j = 0; j < MBLK; ++j) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int n = n_lo + 8 * (e >> 1);
-                const int m = j * 8 + (lane & 3) * 2 + (e & 1);
-                if (n < p.N && m < p.M) {
+                for (int e = 0; e < 4; ++e) {
+                  const int r = r_lo + 8 * (e >> 1);
+                  const int m = j * 8 + (lane & 3) * 2 + (e & 1);
+                  const int n = n_tile * GS_NT + r;
                   float v = acc[0][j][e];
-                  if (p.bias) v += __bfloat162float(p.bias[n]);
-                  if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-                  else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+                  if (p.bias && n < p.N) v += __bfloat162float(p.bias[n]);
+                  if (p.out_f32) reinterpret_cast<float*>(out_tile)[m * GS_NT + r] = v;
+                  else reinterpret_cast<bf16*>(out_tile)[m * GS_NT + r] = __float2bfloat16_rn(v);
                 }
               }
-            }
-          } else if (complete) {
-            // gated pairs: this thread holds gate (row n) and up (row n + 8) of the same output column.
-            // Rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result.
-            const int n = n_tile * GS_NT + rg * 16 + (lane >> 2);          // the gate row
-            const int col = n_tile * (GS_NT / 2) + rg * 8 + (lane >> 2);   // the output column
+            } else {
+              // gated pairs: this thread holds gate (row r) and up (row r + 8) of the same output column.
+              // Rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result.
+              const int n = n_tile * GS_NT + r_lo;                 // the gate row
+              const int col = rg * 8 + (lane >> 2);                // the output column inside the tile
 #pragma unroll
-            for (int j = 0; j < MBLK; ++j) {
+              for (int j = 0; j < MBLK; ++j) {
 #pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int m = j * 8 + (lane & 3) * 2 + e;
-                if (n + 8 < p.N && m < p.M) {
+                for (int e = 0; e < 2; ++e) {
+                  const int m = j * 8 + (lane & 3) * 2 + e;
                   float g = acc[0][j][e], u = acc[0][j][e + 2];
-                  if (p.bias) { g += __bfloat162float(p.bias[n]); u += __bfloat162float(p.bias[n + 8]); }
+                  if (p.bias && n + 8 < p.N) { g += __bfloat162float(p.bias[n]); u += __bfloat162float(p.bias[n + 8]); }
                   g = __bfloat162float(__float2bfloat16_rn(g));
                   u = __bfloat162float(__float2bfloat16_rn(u));
                   const float act = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
-                  reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + col] = __float2bfloat16_rn(act * u);
+                  reinterpret_cast<bf16*>(out_tile)[m * (GS_NT / 2) + col] = __float2bfloat16_rn(act * u);
                 }
               }
             }
+            asm volatile("bar.sync 2, 128;\n");
+            if (p.residual != nullptr) {
+              // the tile joins the residual stream: thread (m, piece) adds 8 columns and their squares
+              const int m = tid >> 3, piece = tid & 7;
+              float sq = 0.0f;
+              const int col = n_tile * GS_NT + piece * 8;
+              if (m < p.M && col < p.N) {                        // N is a multiple of 8 here
+                bf16* rrow = p.residual + (size_t)m * p.N + col;
+                Vec16<bf16> o, r;
+                o.raw = *reinterpret_cast<const uint4*>(out_tile + ((size_t)m * GS_NT + piece * 8) * 2);
+                r.load(rrow);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  r.set(j, o.get(j) + r.get(j));
+                  const float v = r.get(j);
+                  sq += v * v;
+                }
+                r.store(rrow);
+              }
+              // the eight pieces of a token sit in eight neighbouring lanes
+              sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+              sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+              if (piece == 0 && m < p.M) p.sumsq_out[(size_t)m * p.n_tiles + n_tile] = sq;
+            } else {
+              const int esize = p.out_f32 ? 4 : 2;
+              const int col0 = n_tile * width;                       // first output column of the tile
+              const int n_out = p.silu_pairs ? p.N / 2 : p.N;
+              const int per_row = width * esize / 16;                // 16-byte pieces of a token's run
+              unsigned char* gout = reinterpret_cast<unsigned char*>(p.out);
+              const bool whole = col0 + width <= n_out && ((size_t)p.ldo * esize) % 16 == 0 &&
+                                 (reinterpret_cast<uintptr_t>(gout) + (size_t)col0 * esize) % 16 == 0;
+              if (whole) {
+                for (int i = tid; i < p.M * per_row; i += 128) {
+                  const int m = i / per_row, piece = i % per_row;
+                  *reinterpret_cast<uint4*>(gout + ((size_t)m * p.ldo + col0) * esize + piece * 16) =
+                      *reinterpret_cast<const uint4*>(out_tile + (size_t)m * width * esize + piece * 16);
+                }
+              } else {
+                for (int i = tid; i < p.M * width; i += 128) {
+                  const int m = i / width, c = i % width;
+                  if (col0 + c < n_out) {
+                    if (p.out_f32) reinterpret_cast<float*>(gout)[(size_t)m * p.ldo + col0 + c] = reinterpret_cast<const float*>(out_tile)[i];
+                    else reinterpret_cast<bf16*>(gout)[(size_t)m * p.ldo + col0 + c] = reinterpret_cast<const bf16*>(out_tile)[i];
+                  }
+                }
+              }
+            }
+            asm volatile("bar.sync 2, 128;\n");   // the tile buffer is free again
           }
         }
       }
@@ -409,43 +555,65 @@ static int gs_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
 // first launch; the kernel leaves them zero).
 extern "C" long long kvb_gemm_stream_scratch_floats(int blocks) { return (long long)blocks * 2 * 4 * 128; }
 
-template <int MBLK>
+template <int MBLK, bool NORMED>
 static int gs_launch(const void* w, const void* x, long long ldx, StreamParams& p, int sms, cudaStream_t stream) {
   constexpr int MB = 8 * MBLK;
-  constexpr size_t SMEM = 1024 + (size_t)GS_STAGES * (GS_NT + MB) * GS_KG * 128 + 2 * GS_STAGES * 8 + 16 +
-                          MBLK * 4 * 128 * sizeof(float);
+  constexpr size_t SMEM = 1024 + (size_t)GS_STAGES * (GS_NT + MB) * GS_KG * 128 + 1024 +
+                          MBLK * 4 * 128 * sizeof(float) + MB * GS_NT * sizeof(float) + (NORMED ? GS_NORM_W_BYTES : 0);
   static bool configured = false;
   if (!configured) {
-    KVB_CHECK_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<MBLK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<MBLK, NORMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     configured = true;
   }
   alignas(64) CUtensorMap w_map, x_map;
   if (int rc = gs_make_map(&w_map, w, p.N, p.K, p.K, GS_NT)) return rc;
   if (int rc = gs_make_map(&x_map, x, p.M, p.K, ldx, MB)) return rc;
   const int blocks = p.units < sms ? p.units : sms;
-  KVB_CHECK_CUDA(kvb_launch(gemm_stream_kernel<MBLK>, dim3(blocks), dim3(GS_THREADS), SMEM, stream, true, w_map,
+  const int threads = NORMED ? GS_THREADS + GS_NORMALISERS * 32 : GS_THREADS;    // NORMED: the normaliser warps
+  KVB_CHECK_CUDA(kvb_launch(gemm_stream_kernel<MBLK, NORMED>, dim3(blocks), dim3(threads), SMEM, stream, true, w_map,
                             x_map, p));
   return 0;
 }
 
-// scratch: kvb_gemm_stream_scratch_floats(sms) floats; flags: sms ints, zero before the first launch.
-// Launches that share scratch and flags must be ordered in one stream.
-// silu_pairs: the rows of w come in runs of 8 gate rows, 8 up rows, ... ; out is [M, N / 2] with
-// out[m, c] = silu(gate_c(m)) * up_c(m) (the feed-forward's activation fused into the epilogue).
+// Largest K whose norm weights (taken as 32-bit) a NORMED launch keeps in shared memory.
+extern "C" int kvb_gemm_stream_norm_max_k() { return GS_NORM_W_BYTES / 4; }
+
+// out[M, N] = x[M, K] . w[N, K]^T (+ bias), 1 <= M <= 16, K a multiple of 64.
+//   scratch: kvb_gemm_stream_scratch_floats(sms) floats; flags: sms ints, zero before the first
+//   launch.  Launches that share scratch and flags must be ordered in one stream.
+//   silu_pairs: the rows of w come in runs of 8 gate rows, 8 up rows, ...; out is [M, N / 2] with
+//   out[m, c] = silu(gate_c(m)) * up_c(m) (the feed-forward's activation fused into the epilogue).
+//   norm_weight != null: the rows of x are sums that still need their RMS norm; sumsq_in holds
+//   every token's sum of squares in sumsq_pieces pieces ([M, sumsq_pieces]); the kernel uses
+//   x' = bf16(norm_weight[k] * (x * rsqrt(sum / K + eps))).  K * (4 or 2 bytes) must fit 16 KB.
+//   residual != null ([M, N] bf16, contiguous, N a multiple of 8): the result joins the residual
+//   stream: residual = bf16(bf16(out) + residual) in place, and sumsq_out[m, tile] (M x ceil(N / 64)
+//   floats) gets the squares of the new sums, 64 columns a piece; out is not written.
 extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const void* x, long long ldx,
                                     const void* w, const void* bias, int M, int N, int K, int silu_pairs,
-                                    float* scratch, int* flags, int sms, cudaStream_t stream) {
+                                    const void* norm_weight, int norm_weight_f32, float eps, const float* sumsq_in,
+                                    int sumsq_pieces, void* residual, float* sumsq_out, float* scratch, int* flags,
+                                    int sms, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   KVB_REQUIRE(M > 0 && M <= 16, "stream gemm: takes 1 to 16 rows of x");
   KVB_REQUIRE(K > 0 && K % 64 == 0 && ldx % 8 == 0, "stream gemm: K must be a multiple of 64 and the row stride of x of 8");
   KVB_REQUIRE(aligned16(x) && aligned16(w), "stream gemm: x and w must be 16-byte aligned");
   KVB_REQUIRE(scratch != nullptr && flags != nullptr && sms > 0, "stream gemm: needs scratch and flags");
   KVB_REQUIRE(!silu_pairs || (N % 16 == 0 && !out_f32), "stream gemm: gated pairs need N a multiple of 16 and a bf16 result");
+  KVB_REQUIRE(residual == nullptr || (!silu_pairs && !out_f32 && N % 8 == 0 && sumsq_out != nullptr && aligned16(residual)),
+              "stream gemm: the residual epilogue needs a plain bf16 product, N a multiple of 8 and a place for the squares");
+  KVB_REQUIRE(norm_weight == nullptr || (sumsq_in != nullptr && sumsq_pieces > 0 && aligned16(norm_weight) &&
+                                         (size_t)K * (norm_weight_f32 ? 4 : 2) <= GS_NORM_W_BYTES),
+              "stream gemm: the fused norm needs the sums of squares and K small enough for shared memory");
   StreamParams p;
+  memset(&p, 0, sizeof(p));
   p.out = out; p.out_f32 = out_f32; p.ldo = ldo;
   p.bias = (const bf16*)bias;
   p.M = M; p.N = N; p.K = K;
   p.silu_pairs = silu_pairs;
+  p.norm_weight = norm_weight; p.norm_weight_f32 = norm_weight_f32; p.eps = eps;
+  p.sumsq_in = sumsq_in; p.sumsq_pieces = sumsq_pieces;
+  p.residual = (bf16*)residual; p.sumsq_out = sumsq_out;
   p.n_tiles = (N + GS_NT - 1) / GS_NT;
   p.kchunks = (K / 64 + GS_KG - 1) / GS_KG;
   KVB_REQUIRE((long long)p.n_tiles * p.kchunks < (1ll << 30), "stream gemm: the matrix is too large");
@@ -454,8 +622,12 @@ extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const
   p.flags = flags;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "stream gemm: no status word");
-  if (M <= 8) return gs_launch<1>(w, x, ldx, p, sms, stream);
-  return gs_launch<2>(w, x, ldx, p, sms, stream);
+  if (norm_weight != nullptr) {
+    if (M <= 8) return gs_launch<1, true>(w, x, ldx, p, sms, stream);
+    return gs_launch<2, true>(w, x, ldx, p, sms, stream);
+  }
+  if (M <= 8) return gs_launch<1, false>(w, x, ldx, p, sms, stream);
+  return gs_launch<2, false>(w, x, ldx, p, sms, stream);
 }
 
 KVB_TRACE_TU(gemm_stream)

@@ -55,7 +55,8 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
-        "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _vp, _int, _vp],
+        "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
+                                 _int, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
     }
@@ -70,6 +71,8 @@ def ensure_built(verbose: bool = False) -> str:
     lib.kvb_set_pdl(0 if os.environ.get("KVCORE_B200_SERIAL_LAUNCH") == "1" else 1)
     lib.kvb_gemm_stream_scratch_floats.argtypes = [_int]
     lib.kvb_gemm_stream_scratch_floats.restype = _ll
+    lib.kvb_gemm_stream_norm_max_k.argtypes = []
+    lib.kvb_gemm_stream_norm_max_k.restype = _int
     _lib = lib
     return str(path)
 
@@ -505,16 +508,11 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     if silu_pairs and (n % 16 or out_dtype not in (None, torch.bfloat16)):
         raise KernelError("linear_stream: gated pairs need an output width that is a multiple of 16 and a bf16 result")
     out = torch.empty((m, n // 2 if silu_pairs else n), dtype=out_dtype or torch.bfloat16, device=x.device)
-    index = x.device.index or 0
-    buffers = _stream_scratch.get(index)
-    if buffers is None:
-        floats = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT))
-        buffers = (torch.empty(floats, dtype=torch.float32, device=x.device),
-                   torch.zeros(SM_COUNT, dtype=torch.int32, device=x.device))
-        _stream_scratch[index] = buffers
+    buffers = _stream_buffers(x.device)
     _call("kvb_gemm_stream_bf16", out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
           x.data_ptr(), x.stride(0), weight.data_ptr(), None if bias is None else bias.data_ptr(),
-          m, n, k, int(silu_pairs), buffers[0].data_ptr(), buffers[1].data_ptr(), SM_COUNT, _stream())
+          m, n, k, int(silu_pairs), None, 0, 0.0, None, 0, None, None,
+          buffers[0].data_ptr(), buffers[1].data_ptr(), SM_COUNT, _stream())
     return out
 
 
@@ -566,6 +564,17 @@ def linear(
     return torch.nn.functional.linear(x, weight, bias)
 
 
+def _stream_buffers(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    index = device.index or 0
+    buffers = _stream_scratch.get(index)
+    if buffers is None:
+        floats = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT))
+        buffers = (torch.empty(floats, dtype=torch.float32, device=device),
+                   torch.zeros(SM_COUNT, dtype=torch.int32, device=device))
+        _stream_scratch[index] = buffers
+    return buffers
+
+
 def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     m, k = x.shape
     return (x.dtype == torch.bfloat16 and m <= min(STREAM_AUTO_ROWS, STREAM_MAX_ROWS) and k % 64 == 0
@@ -584,6 +593,75 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
     if group == 8 and x.dim() == 2 and weight.shape[0] % 16 == 0 and _stream_ok(x, weight):
         return linear_stream(x, weight, bias, silu_pairs=True)
     return silu_mul(linear(x, weight, bias), group)
+
+
+def norm_linear(h: torch.Tensor | None, residual: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
+                weight: torch.Tensor, bias: torch.Tensor | None = None, *, silu_group: int | None = None,
+                sumsq: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """A sub-layer's entry: ``x = rmsnorm(h + residual)``, then ``x @ weight.T`` (``silu_group`` None)
+    or the gated ``silu(gate(x)) * up(x)`` (``silu_group`` as in ``linear_silu_mul``).
+
+    Returns ``(out, residual)`` with ``residual`` now holding the sum (``residual`` None: the sum is
+    ``h`` itself).  ``h`` None means the sub-layer in front has already added its output into
+    ``residual`` (see ``linear_add_residual``); if it also left the rows' squares in ``sumsq``, a
+    decode-sized bf16 batch runs as ONE kernel: a warp of the streaming product scales each stage's
+    token rows by ``norm_weight * rsqrt(mean + eps)`` before they are used.  Everything else is
+    the norm kernel followed by the product."""
+    if h is None:
+        if residual is None:
+            raise KernelError("norm_linear: nothing to normalise")
+        _check(residual, "residual", contiguous=False)
+        m, k = residual.shape
+        weight_bytes = 4 if norm_weight.dtype == torch.float32 else 2
+        if (sumsq is not None and _stream_ok(residual, weight)
+                and k * weight_bytes <= 4 * int(_lib.kvb_gemm_stream_norm_max_k())
+                and norm_weight.dtype in (torch.bfloat16, torch.float32) and norm_weight.is_contiguous()
+                and norm_weight.data_ptr() % 16 == 0
+                and sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.shape[0] == m
+                and (silu_group is None or (silu_group == 8 and weight.shape[0] % 16 == 0))):
+            _check(weight, "weight", dtype=torch.bfloat16)
+            if bias is not None:
+                _check(bias, "bias", dtype=torch.bfloat16)
+            n = weight.shape[0]
+            out = torch.empty((m, n // 2 if silu_group else n), dtype=torch.bfloat16, device=residual.device)
+            scratch, flags = _stream_buffers(residual.device)
+            _call("kvb_gemm_stream_bf16", out.data_ptr(), 0, out.stride(0), residual.data_ptr(), residual.stride(0),
+                  weight.data_ptr(), None if bias is None else bias.data_ptr(), m, n, k, int(bool(silu_group)),
+                  norm_weight.data_ptr(), int(norm_weight.dtype == torch.float32), float(eps), sumsq.data_ptr(),
+                  sumsq.shape[1], None, None, scratch.data_ptr(), flags.data_ptr(), SM_COUNT, _stream())
+            return out, residual
+        x = rmsnorm(residual, norm_weight, eps)
+    elif residual is None:
+        x, residual = rmsnorm(h, norm_weight, eps), h
+    else:
+        x = add_rmsnorm(h, residual, norm_weight, eps)
+    out = linear(x, weight, bias) if silu_group is None else linear_silu_mul(x, weight, bias, group=silu_group)
+    return out, residual
+
+
+def linear_add_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                        residual: torch.Tensor | None) -> tuple[torch.Tensor | None, torch.Tensor | None]:
+    """A sub-layer's exit: ``out = x @ weight.T (+ bias)`` on its way into the residual stream.
+
+    Decode-sized bf16 batches: the streaming product adds its (bf16-rounded) result into ``residual``
+    in place and returns ``(None, sumsq)``, ``sumsq [T, ceil(N / 64)]`` being the squares of the new
+    rows of ``residual``, 64 columns a piece, for the norm that follows.  Otherwise returns
+    ``(out, None)``: the sum is left to that norm, as the deferred-residual scheme has it."""
+    if (residual is not None and x.dim() == 2 and _stream_ok(x, weight)
+            and weight.shape[0] % 8 == 0 and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+            and tuple(residual.shape) == (x.shape[0], weight.shape[0]) and residual.data_ptr() % 16 == 0):
+        _check(weight, "weight", dtype=torch.bfloat16)
+        if bias is not None:
+            _check(bias, "bias", dtype=torch.bfloat16)
+        m, k = x.shape
+        n = weight.shape[0]
+        sumsq = torch.empty((m, -(-n // 64)), dtype=torch.float32, device=x.device)
+        scratch, flags = _stream_buffers(x.device)
+        _call("kvb_gemm_stream_bf16", None, 0, n, x.data_ptr(), x.stride(0), weight.data_ptr(),
+              None if bias is None else bias.data_ptr(), m, n, k, 0, None, 0, 0.0, None, 0,
+              residual.data_ptr(), sumsq.data_ptr(), scratch.data_ptr(), flags.data_ptr(), SM_COUNT, _stream())
+        return None, sumsq
+    return linear(x, weight, bias), None
 
 
 def sample(logits: torch.Tensor, packed_params: torch.Tensor, eps: float) -> torch.Tensor:
@@ -610,8 +688,10 @@ __all__ = [
     "gather_rows",
     "library_is_loaded",
     "linear",
+    "linear_add_residual",
     "linear_silu_mul",
     "linear_stream",
+    "norm_linear",
     "set_overlapped_launch",
     "trace_start",
     "trace_stop",

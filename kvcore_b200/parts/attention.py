@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels as K
 from ..config.model_spec import PartSpec
-from .base import MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, WeightSlot
+from .base import MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, Summed, WeightSlot
 from .rope import RotaryEncoding
 
 
@@ -89,7 +89,21 @@ class PagedAttention(Mixer):
         return slots
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        qkv = K.linear(x, self.qkv_weight, self.qkv_bias)
+        out = self._attend(K.linear(x, self.qkv_weight, self.qkv_bias), ctx, cache)
+        return K.linear(out, self.o_weight, self.o_bias)
+
+    def forward_prenorm(self, h, residual, rms_scale, ctx, cache):
+        """The layer's norm folded into the q/k/v product and the residual sum into the output
+        product (decode-sized batches: no kernel of their own for either)."""
+        weight, eps = rms_scale
+        summed = isinstance(h, Summed)
+        qkv, residual = K.norm_linear(None if summed else h, residual, weight, eps, self.qkv_weight, self.qkv_bias,
+                                      sumsq=h.sumsq if summed else None)
+        out = self._attend(qkv, ctx, cache)
+        pending, sumsq = K.linear_add_residual(out, self.o_weight, self.o_bias, residual)
+        return (Summed(sumsq) if pending is None else pending), residual
+
+    def _attend(self, qkv: torch.Tensor, ctx, cache) -> torch.Tensor:
         table = ctx.block_table(cache.group)
         cos_sin = None
         if isinstance(self.position, RotaryEncoding):
@@ -110,7 +124,7 @@ class PagedAttention(Mixer):
             qkv, cache.k, cache.v, table, ctx,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.sliding_window,
         )
-        return K.linear(out, self.o_weight, self.o_bias)
+        return out
 
 
 MIXERS.register("paged_attention", PagedAttention)

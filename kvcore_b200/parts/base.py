@@ -94,6 +94,17 @@ class Part:
         """Called once after all slots are filled (repack, build derived tables)."""
 
 
+class Summed:
+    """Stands where a sub-layer's output would stand in the ``(h, residual)`` pair that runs through
+    the blocks, when that output has already been added into ``residual``.  ``sumsq`` ``[T, pieces]``
+    holds the squares of the rows of ``residual`` (for the norm that follows), or is None."""
+
+    __slots__ = ("sumsq",)
+
+    def __init__(self, sumsq: torch.Tensor | None) -> None:
+        self.sumsq = sumsq
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
@@ -102,6 +113,11 @@ class Norm(Part):
         self, h: torch.Tensor, residual: torch.Tensor
     ) -> tuple[torch.Tensor, torch.Tensor]:
         raise NotImplementedError
+
+    def as_rms_scale(self) -> tuple[torch.Tensor, float] | None:
+        """``(weight, eps)`` if this norm is exactly ``weight * x * rsqrt(mean(x^2) + eps)``, so that
+        the part behind it may fold it into its first matrix product; ``None`` otherwise."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -115,6 +131,12 @@ class Mixer(Part):
 
     def state_spec(self) -> StateSpec | None:
         return None
+
+    # Optional: ``forward_prenorm(h, residual, rms_scale, ctx, cache) -> (out, residual)`` takes the
+    # sub-layer input before its norm (``h`` a tensor or ``Summed``, ``residual`` a tensor or None)
+    # together with the norm's ``as_rms_scale()``; it returns the sub-layer's output (a tensor, or
+    # ``Summed`` if it has added it into the residual already) and the residual.  The block uses it
+    # when both the norm and the part offer it.  (The same holds for a FeedForward, without ``cache``.)
 
     def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
         raise NotImplementedError

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import LayerSpec
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, WeightSlot
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Summed, WeightSlot
 
 
 class PreNormResidualBlock(Block):
@@ -37,14 +37,30 @@ class PreNormResidualBlock(Block):
             part.finalize_weights()
 
     def forward(self, h, residual, ctx, cache):
-        if residual is None:
-            residual = h
-            x = self.mixer_norm.forward(h)
+        # A part that can take its input before the norm (and fold the norm into its first matrix
+        # product, the residual sum into its last) gets it that way; otherwise the norm runs as a
+        # step of its own.  ``h`` may be ``Summed``: the part in front added its output already.
+        scale, prenorm = self.mixer_norm.as_rms_scale(), getattr(self.mixer, "forward_prenorm", None)
+        if scale is not None and prenorm is not None:
+            a, residual = prenorm(h, residual, scale, ctx, cache)
         else:
-            x, residual = self.mixer_norm.forward_residual(h, residual)
-        a = self.mixer.forward(x, ctx, cache)
-        x, residual = self.feed_forward_norm.forward_residual(a, residual)
-        h = self.feed_forward.forward(x, ctx)
+            if isinstance(h, Summed):
+                x = self.mixer_norm.forward(residual)
+            elif residual is None:
+                residual = h
+                x = self.mixer_norm.forward(h)
+            else:
+                x, residual = self.mixer_norm.forward_residual(h, residual)
+            a = self.mixer.forward(x, ctx, cache)
+        scale, prenorm = self.feed_forward_norm.as_rms_scale(), getattr(self.feed_forward, "forward_prenorm", None)
+        if scale is not None and prenorm is not None:
+            h, residual = prenorm(a, residual, scale, ctx)
+        else:
+            if isinstance(a, Summed):
+                x = self.feed_forward_norm.forward(residual)
+            else:
+                x, residual = self.feed_forward_norm.forward_residual(a, residual)
+            h = self.feed_forward.forward(x, ctx)
         return h, residual
 
 

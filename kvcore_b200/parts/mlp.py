@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import FEED_FORWARDS, FeedForward, WeightSlot
+from .base import FEED_FORWARDS, FeedForward, Summed, WeightSlot
 
 
 class SwiGLU(FeedForward):
@@ -65,6 +65,18 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         hidden = K.linear_silu_mul(x, self.gate_up_weight, self.gate_up_bias, group=self.group)
         return K.linear(hidden, self.down_weight, self.down_bias)
+
+
+    def forward_prenorm(self, h, residual, rms_scale, ctx):
+        """The layer's norm folded into the gate/up product and the residual sum into the down
+        product (decode-sized batches: no kernel of their own for either)."""
+        weight, eps = rms_scale
+        summed = isinstance(h, Summed)
+        hidden, residual = K.norm_linear(None if summed else h, residual, weight, eps, self.gate_up_weight,
+                                         self.gate_up_bias, silu_group=self.group,
+                                         sumsq=h.sumsq if summed else None)
+        pending, sumsq = K.linear_add_residual(hidden, self.down_weight, self.down_bias, residual)
+        return (Summed(sumsq) if pending is None else pending), residual
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

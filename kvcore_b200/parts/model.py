@@ -14,7 +14,7 @@ import torch
 from .. import kernels as K
 from ..config.model_spec import ModelSpec
 from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (register the stock parts)
-from .base import BLOCKS, EMBEDDINGS, LM_HEADS, NORMS, CacheSpec, StateSpec, WeightSlot
+from .base import BLOCKS, EMBEDDINGS, LM_HEADS, NORMS, CacheSpec, StateSpec, Summed, WeightSlot
 
 
 @dataclass(frozen=True)
@@ -106,9 +106,11 @@ class DecoderModel:
 
     def compute_logits(self, h: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits ``[len(rows), V]`` of the token rows ``rows`` (int32 indices)."""
-        h_rows = K.gather_rows(h, rows)
         residual_rows = K.gather_rows(residual, rows)
-        normed, _ = self.final_norm.forward_residual(h_rows, residual_rows)
+        if isinstance(h, Summed):      # the last sub-layer has added its output into the residual itself
+            normed = self.final_norm.forward(residual_rows)
+        else:
+            normed, _ = self.final_norm.forward_residual(K.gather_rows(h, rows), residual_rows)
         return self.lm_head.forward(normed)
 
 

@@ -35,6 +35,9 @@ class RMSNorm(Norm):
     def forward_residual(self, h: torch.Tensor, residual: torch.Tensor):
         return K.add_rmsnorm(h, residual, self.weight, self.eps), residual
 
+    def as_rms_scale(self):
+        return self.weight, self.eps
+
 
 NORMS.register("rmsnorm", RMSNorm)
 

@@ -144,6 +144,21 @@ def linear_silu_mul(x, weight, bias=None, *, group=0):
     return silu_mul(linear(x, weight, bias), group)
 
 
+def norm_linear(h, residual, norm_weight, eps, weight, bias=None, *, silu_group=None, sumsq=None):
+    if h is None:
+        x = rmsnorm(residual, norm_weight, eps)
+    elif residual is None:
+        x, residual = rmsnorm(h, norm_weight, eps), h
+    else:
+        x = add_rmsnorm(h, residual, norm_weight, eps)
+    out = linear(x, weight, bias) if silu_group is None else linear_silu_mul(x, weight, bias, group=silu_group)
+    return out, residual
+
+
+def linear_add_residual(x, weight, bias, residual):
+    return linear(x, weight, bias), None
+
+
 # ---- sampling: the same counter-based noise as the CUDA kernel --------------------------------
 def philox4x32_10(counter, key):
     c = [np.uint64(x) for x in counter]
@@ -199,7 +214,7 @@ def sample(logits, packed_params, eps):
 
 _NAMES = [
     "require_device", "ensure_built", "read_status", "check_attention_shape", "gather_rows", "rmsnorm",
-    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "sample",
+    "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
 ]
 
 

@@ -448,6 +448,57 @@ def test_linear_stream_with_gated_epilogue(m, inter, k, bias):
     assert K().read_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 6144, 4096), (5, 200, 576), (16, 4096, 1088), (3, 48, 4096)])
+@pytest.mark.parametrize("weight_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("gated", [False, True])
+def test_residual_stream_kernels(m, n, k, weight_dtype, gated):
+    """A sub-layer's exit (product added into the residual, squares left for the norm) and the next
+    sub-layer's entry (rows normalised inside the product) equal the separate steps."""
+    x = randn(m, 192, dtype=torch.bfloat16, seed=39)
+    w_out = randn(k, 192, dtype=torch.bfloat16, seed=38, scale=0.05)
+    b_out = randn(k, dtype=torch.bfloat16, seed=37)
+    residual = randn(m, k, dtype=torch.bfloat16, seed=41)
+    before = residual.clone()
+    pending, sumsq = K().linear_add_residual(x, w_out, b_out, residual)
+    assert pending is None and sumsq.shape == (m, -(-k // 64))
+    out = (x.float() @ w_out.float().T + b_out.float()).to(torch.bfloat16)
+    want_residual = (out.float() + before.float()).to(torch.bfloat16)
+    # the product differs from the library's by summation order: allow a bf16 step on the sum
+    torch.testing.assert_close(residual.float(), want_residual.float(), rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(sumsq.sum(dim=1), residual.float().pow(2).sum(dim=1), rtol=1e-5, atol=1e-5)
+
+    g = (1.0 + 0.2 * randn(k, dtype=torch.float32, seed=42)).to(weight_dtype)
+    rows = 2 * n if gated else n
+    w = randn(rows, k, dtype=torch.bfloat16, seed=43, scale=0.05)
+    b = randn(rows, dtype=torch.bfloat16, seed=44)
+    got, same = K().norm_linear(None, residual, g, 1e-5, w, b, silu_group=8 if gated else None, sumsq=sumsq)
+    assert same is residual and got.shape == (m, n)
+    normed = P.rmsnorm(residual, g, 1e-5)
+    products = (normed.float() @ w.float().T + b.float()).to(torch.bfloat16)
+    want = P.silu_mul(products, 8) if gated else products
+    torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-2)
+    again, _ = K().norm_linear(None, residual, g, 1e-5, w, b, silu_group=8 if gated else None, sumsq=sumsq)
+    assert torch.equal(got, again)
+    # without the squares the same call takes the separate norm kernel: same numbers up to rounding
+    plain, _ = K().norm_linear(None, residual, g, 1e-5, w, b, silu_group=8 if gated else None)
+    torch.testing.assert_close(got.float(), plain.float(), rtol=1.6e-2, atol=2e-2)
+    assert K().read_status() == 0
+
+
+def test_norm_linear_and_residual_fall_back_for_larger_batches():
+    h = randn(20, 128, dtype=torch.bfloat16, seed=40)
+    residual = randn(20, 128, dtype=torch.bfloat16, seed=41)
+    g = randn(128, dtype=torch.bfloat16, seed=42)
+    w = randn(64, 128, dtype=torch.bfloat16, seed=43, scale=0.05)
+    want_residual = residual.clone()
+    x = P.add_rmsnorm(h, want_residual, g, 1e-6)
+    got, new_residual = K().norm_linear(h, residual, g, 1e-6, w)
+    assert new_residual is residual and torch.equal(residual, want_residual)   # updated in place
+    torch.testing.assert_close(got.float(), x.float() @ w.float().T, rtol=1.6e-2, atol=2e-2)
+    pending, sumsq = K().linear_add_residual(h, w, None, randn(20, 64, dtype=torch.bfloat16, seed=45))
+    assert sumsq is None and pending.shape == (20, 64)
+
+
 def test_linear_stream_refuses_what_it_cannot_take():
     x = randn(17, 128, dtype=torch.bfloat16, seed=20)
     w = randn(64, 128, dtype=torch.bfloat16, seed=21)
