@@ -371,6 +371,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           if (tid == 0) gs_st_release(&p.flags[me], 1);
         } else {
           // ---- the owner: add the parts of the blocks behind (in k order), then store ----
+          // (residual epilogue: this thread's 8 columns of the residual are asked for now, so that
+          // their trip to L2 runs beside the wait for the parts)
+          Vec16<bf16> res_early;
+          const int res_m = tid >> 3, res_col = n_tile * GS_NT + (tid & 7) * 8;
+          const bool res_mine = p.residual != nullptr && res_m < p.M && res_col < p.N;
+          if (res_mine) res_early.load(p.residual + (size_t)res_m * p.N + res_col);
           bool complete = true;
           if (seg_end < tile_end) {
             // the blocks behind that hold stages of this tile: all their flags are awaited at once
@@ -463,11 +469,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
               const int m = tid >> 3, piece = tid & 7;
               float sq = 0.0f;
               const int col = n_tile * GS_NT + piece * 8;
-              if (m < p.M && col < p.N) {                        // N is a multiple of 8 here
+              if (res_mine) {                                    // N is a multiple of 8 here
                 bf16* rrow = p.residual + (size_t)m * p.N + col;
-                Vec16<bf16> o, r;
+                Vec16<bf16> o, r = res_early;
                 o.raw = *reinterpret_cast<const uint4*>(out_tile + ((size_t)m * GS_NT + piece * 8) * 2);
-                r.load(rrow);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                   r.set(j, o.get(j) + r.get(j));
