@@ -46,6 +46,14 @@ struct DecodeParams {
   float* partial_o;   // [reqs, KVH, splits, 16, D]
   float* partial_ml;  // [reqs, KVH, splits, 16, 2]
   int* status;
+  // Rotation and cache write of this step's tokens done here instead of in a kernel in front
+  // cos_sin != null: q rows are rotated on their way into shared memory.  k_cache != null: the
+  // block whose key range holds a new token rotates its key (if cos_sin), writes key and value into
+  // the cache page and lays them over the tile that TMA brought, which holds that slot's old bytes.
+  const float2* cos_sin;      // [tokens, D / 2] (cos, sin)
+  const bf16* k_new;          // this step's keys, row stride q_stride, [tokens][KVH][D] inside the qkv rows
+  const bf16* v_new;
+  bf16* k_cache; bf16* v_cache;   // [pages, KVH, page, D]
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -136,6 +144,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(qs + 16 * QROW);
   unsigned long long* empty_bar = full_bar + TD_STAGES;
   int* abort_flag = reinterpret_cast<int*>(empty_bar + TD_STAGES);
+  bf16* new_kv = reinterpret_cast<bf16*>(abort_flag + 4);   // fused rotation: [16 tokens][K, V][D]
 
   const int req = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -171,15 +180,69 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   if (warp != TD_CONSUMERS) {
     kvb_grid_wait();                 // q is the output of the kernels in front
     kvb_trace_scope__.after_wait();
-    // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G)
-    for (int i = threadIdx.x; i < 16 * (D / 8); i += TD_CONSUMERS * 32) {
-      const int r = i / (D / 8), chunk = i % (D / 8);
-      uint4 v = make_uint4(0, 0, 0, 0);
+    // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G), rotated on
+    // the way when the rotation is done here: an item is the two 16-byte pieces (d, d + D/2)
+    constexpr int PAIRS = D / 16;
+    for (int i = threadIdx.x; i < 16 * PAIRS; i += TD_CONSUMERS * 32) {
+      const int r = i / PAIRS, g = i % PAIRS;
+      Vec16<bf16> lo, hi;
+      lo.raw = make_uint4(0, 0, 0, 0);
+      hi.raw = make_uint4(0, 0, 0, 0);
       if (r < rows_total) {
         const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-        v = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)head * D + chunk * 8);
+        const bf16* x = p.q + (size_t)token * p.q_stride + (size_t)head * D + g * 8;
+        lo.load(x);
+        hi.load(x + D / 2);
+        if (p.cos_sin != nullptr) {
+          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + g * 8;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 t = cs[e];
+            const float a = lo.get(e), b = hi.get(e);
+            lo.set(e, a * t.x - b * t.y);
+            hi.set(e, b * t.x + a * t.y);
+          }
+        }
       }
-      *reinterpret_cast<uint4*>(qs + r * QROW + chunk * 8) = v;
+      *reinterpret_cast<uint4*>(qs + r * QROW + g * 8) = lo.raw;
+      *reinterpret_cast<uint4*>(qs + r * QROW + D / 2 + g * 8) = hi.raw;
+    }
+    // this step's keys and values whose positions fall into this block's key range: rotate the key,
+    // write both into the cache, keep them to lay over the tile that holds their (old) slots
+    if (p.k_cache != nullptr) {
+      const int new_tokens = q_len < 16 ? q_len : 16;
+      for (int i = threadIdx.x; i < new_tokens * 2 * PAIRS; i += TD_CONSUMERS * 32) {
+        const int t = i / (2 * PAIRS), which = (i / PAIRS) & 1, g = i % PAIRS;   // which: 0 key, 1 value
+        const int pos = context + t;
+        if (pos < key_lo || pos >= key_hi) continue;
+        const int token = q_begin + t;
+        const bf16* x = (which ? p.v_new : p.k_new) + (size_t)token * p.q_stride + (size_t)kvh * D + g * 8;
+        Vec16<bf16> lo, hi;
+        lo.load(x);
+        hi.load(x + D / 2);
+        if (!which && p.cos_sin != nullptr) {
+          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + g * 8;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 c = cs[e];
+            const float a = lo.get(e), b = hi.get(e);
+            lo.set(e, a * c.x - b * c.y);
+            hi.set(e, b * c.x + a * c.y);
+          }
+        }
+        bf16* keep = new_kv + ((size_t)t * 2 + which) * D + g * 8;
+        *reinterpret_cast<uint4*>(keep) = lo.raw;
+        *reinterpret_cast<uint4*>(keep + D / 2) = hi.raw;
+        const int page = p.table[(size_t)req * p.table_stride + pos / p.page_size];
+        if (page <= 0 || page >= p.num_pages) {
+          atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+        } else {
+          bf16* dst = (which ? p.v_cache : p.k_cache) +
+                      (((size_t)page * p.KVH + kvh) * p.page_size + pos % p.page_size) * D + g * 8;
+          lo.store(dst);
+          hi.store(dst + D / 2);
+        }
+      }
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
   }
@@ -215,7 +278,9 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     for (int it = 0; it < num_tiles; ++it) {
       const int stage = it % TD_STAGES;
       const int e0 = it * ppt;
-      if (!waited && (tile_begin + it + 1) * TD_KEYS > context) {   // this tile holds keys written in this step
+      // a tile that holds keys written in this step by a kernel in front (with the cache write done
+      // here, the consumers lay those keys over the tile themselves)
+      if (!waited && p.k_cache == nullptr && (tile_begin + it + 1) * TD_KEYS > context) {
         kvb_grid_wait();
         waited = true;
       }
@@ -280,6 +345,24 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
       const unsigned kbase = smem_u32(stages + stage * STAGE_BYTES);
       const unsigned vbase = kbase + KV_BYTES;
+      if (p.k_cache != nullptr) {
+        // a tile that holds slots of this step's tokens: lay the fresh keys and values over them
+        static_assert(TD_GROUPS == 1, "the overlay is written by all consumer warps together");
+        const int tile_lo = (tile_begin + it) * TD_KEYS;
+        const int first_new = max(max(context, key_lo), tile_lo), end_new = min(min(context + q_len, key_hi), tile_lo + TD_KEYS);
+        if (first_new < end_new) {
+          const int count = (end_new - first_new) * 2 * (D / 8);
+          for (int i = threadIdx.x; i < count; i += TD_CONSUMERS * 32) {
+            const int t = i / (2 * (D / 8)), which = (i / (D / 8)) & 1, chunk = i % (D / 8);
+            const int pos = first_new + t;
+            const uint4 v = *reinterpret_cast<const uint4*>(new_kv + ((size_t)(pos - context) * 2 + which) * D + chunk * 8);
+            unsigned char* area = stages + stage * STAGE_BYTES + (which ? KV_BYTES : 0);
+            *reinterpret_cast<uint4*>(area + swz<HALVES>(pos - tile_lo, chunk * 8)) = v;
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // a later copy may reuse the stage
+          asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+        }
+      }
       float s[2][4], s2[2][4];  // two accumulation chains (even and odd k-steps) halve the latency
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
@@ -509,7 +592,8 @@ extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long lon
 template <int D>
 static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
                              int max_rows, cudaStream_t stream) {
-  constexpr size_t SMEM = 1024 + TD_STAGES * 2 * TD_KEYS * D * 2 + 16 * (D + 8) * 2 + 2 * TD_STAGES * 8 + 16;
+  constexpr size_t SMEM = 1024 + TD_STAGES * 2 * TD_KEYS * D * 2 + 16 * (D + 8) * 2 + 2 * TD_STAGES * 8 + 16 +
+                          16 * 2 * D * 2;   // + the new tokens' keys and values (fused rotation)
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -533,9 +617,10 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
                                     int table_stride, const int* query_start, const int* context_lens,
                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
                                     int num_pages, float scale, int window, int num_splits, float* scratch,
-                                    cudaStream_t stream) {
+                                    const float* cos_sin, void* k_cache, void* v_cache, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == 64 || D == 128, "decode attention (TMA): head_dim must be 64 or 128");
+  KVB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "decode attention (TMA): give both caches or none");
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
               "decode attention (TMA): page size must be 8, 16, 32 or 64");
   KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "decode attention (TMA): H must be a multiple of KVH");
@@ -557,6 +642,11 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   p.partial_ml = scratch ? scratch + (size_t)num_reqs * KVH * p.num_splits * 16 * D : nullptr;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "decode attention (TMA): no status word");
+  // q points at the qkv rows [q heads | k heads | v heads]
+  p.cos_sin = (const float2*)cos_sin;
+  p.k_new = (const bf16*)q + (size_t)H * D;
+  p.v_new = (const bf16*)q + (size_t)(H + KVH) * D;
+  p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache;
   alignas(64) CUtensorMap k_map, v_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));

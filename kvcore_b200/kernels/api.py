@@ -50,7 +50,7 @@ def ensure_built(verbose: bool = False) -> str:
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
-                                 _int, _int, _int, _float, _int, _int, _vp, _vp],
+                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp],
         "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
@@ -358,6 +358,8 @@ def paged_attention(
     num_splits: int | None = None,
     use_tma: bool = True,
     use_tc5: bool = True,
+    cos_sin: torch.Tensor | None = None,
+    write_kv: bool | None = None,
 ) -> torch.Tensor:
     """Attention of the step's queries (the first ``H*D`` columns of ``qkv``) over the cache.
 
@@ -365,7 +367,27 @@ def paged_attention(
     tokens, and per request its query start and cached length.  bfloat16 with a head size in
     steps of 16 up to 128 runs on the tensor-core kernel (split over the keys for decode
     batches); everything else, and all of float32, runs on the general kernel.
+
+    ``write_kv=None``: q and k in ``qkv`` are rotated already and the cache holds this step's
+    keys and values.  Otherwise this call also rotates q and k with the ``rope_table`` values
+    ``cos_sin`` (``None``: no rotation) and, if ``write_kv``, writes this step's k and v into
+    their pages: inside the decode kernel where that one runs (``qkv`` is then left as it
+    was), through ``rope_kv_write`` in front of the other kernels.
     """
+    if write_kv is not None:
+        group = num_heads // num_kv_heads
+        fused = (not force_general and use_tma and flash_attention_supported(qkv.dtype, head_dim)
+                 and qkv.stride(0) % 8 == 0 and ctx.max_query_len * group <= 16
+                 and tma_decode_supported(qkv.dtype, head_dim, k_cache.shape[2]))
+        if not fused:
+            rope_kv_write(qkv, ctx.positions, ctx.req_index, cos_sin, table, k_cache, v_cache,
+                          num_heads, num_kv_heads, head_dim, write_kv=write_kv)
+            cos_sin, write_kv = None, None
+        elif cos_sin is not None:
+            _check(cos_sin, "cos_sin", dtype=torch.float32)
+            if tuple(cos_sin.shape) != (qkv.shape[0], head_dim // 2, 2):
+                raise KernelError(f"cos_sin has shape {tuple(cos_sin.shape)} for {qkv.shape[0]} tokens "
+                                  f"of head_dim {head_dim}")
     _check(qkv, "qkv", contiguous=False)
     _check(k_cache, "k_cache", dtype=qkv.dtype)
     _check(v_cache, "v_cache", dtype=qkv.dtype)
@@ -390,7 +412,9 @@ def paged_attention(
                   ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
                   ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
                   num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-                  splits, None if scratch is None else scratch.data_ptr(), _stream())
+                  splits, None if scratch is None else scratch.data_ptr(),
+                  None if cos_sin is None else cos_sin.data_ptr(),
+                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None, _stream())
             return out
         if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
                 and out.stride(0) % 8 == 0):

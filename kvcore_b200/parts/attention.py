@@ -116,15 +116,13 @@ class PagedAttention(Mixer):
                 tokens, self.num_kv_heads, self.head_dim
             )
             self.position.apply(q, k if cache.owner else None, ctx)
-        K.rope_kv_write(
-            qkv, ctx.positions, ctx.req_index, cos_sin, table, cache.k, cache.v,
-            self.num_heads, self.num_kv_heads, self.head_dim, write_kv=cache.owner,
-        )
-        out = K.paged_attention(
+        # rotation and cache write run inside the decode kernel where that one is taken, in a
+        # kernel in front of the attention otherwise
+        return K.paged_attention(
             qkv, cache.k, cache.v, table, ctx,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.sliding_window,
+            cos_sin=cos_sin, write_kv=cache.owner,
         )
-        return out
 
 
 MIXERS.register("paged_attention", PagedAttention)

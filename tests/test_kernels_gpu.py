@@ -268,6 +268,58 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     assert K().read_status() == 0
 
 
+ROTATING_DECODE_SHAPES = [
+    # heads, kv_heads, dim, page, [(context, query), ...], window, forced splits
+    (32, 8, 128, 16, [(1000, 1), (17, 1), (4095, 1), (0, 1)], None, None),
+    (32, 8, 128, 16, [(700, 4), (0, 2), (63, 3), (62, 4)], None, 3),      # new tokens straddle a tile and a split
+    (16, 4, 64, 8, [(777, 1), (64, 2), (0, 1), (127, 1)], None, 3),
+    (4, 1, 128, 64, [(500, 3), (63, 1), (191, 2)], None, 2),
+    (2, 2, 64, 32, [(100, 9), (0, 16)], 17, None),                         # window; sixteen new tokens at once
+    (6, 3, 48, 16, [(17, 2), (0, 1), (100, 2)], None, None),               # not the TMA kernel: kernel in front
+    (8, 2, 128, 16, [(0, 200), (130, 77), (500, 1)], None, None),          # prefill shapes: kernel in front
+]
+
+
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,lens,window,splits", ROTATING_DECODE_SHAPES)
+def test_attention_that_rotates_and_writes_the_cache(heads, kv_heads, dim, page, lens, window, splits, rotate):
+    """Rotation and cache write inside the attention call give the bits of the kernel in front."""
+    dtype = torch.bfloat16
+    case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=11)
+    ctx = _Ctx(case)
+    tokens = case["qkv"].shape[0]
+    cos_sin = None
+    if rotate:
+        angles = randn(tokens, dim // 2, dtype=torch.float32, seed=5) * 3.0
+        cos_sin = torch.stack([angles.cos(), angles.sin()], dim=-1).contiguous()
+    # the slots of this step's tokens hold large stale values before the step
+    for r, (c, q) in enumerate(lens):
+        for pos in range(c, c + q):
+            page_id = int(case["table"][r, pos // page])
+            case["k_cache"][page_id, :, pos % page] = 3.0e4
+            case["v_cache"][page_id, :, pos % page] = -3.0e4
+    scale = dim ** -0.5
+    qkv_a, k_a, v_a = case["qkv"].clone(), case["k_cache"].clone(), case["v_cache"].clone()
+    K().rope_kv_write(qkv_a, case["positions"], case["req_index"], cos_sin, case["table"], k_a, v_a,
+                      heads, kv_heads, dim)
+    want = K().paged_attention(qkv_a, k_a, v_a, case["table"], ctx, heads, kv_heads, dim, scale, window,
+                               num_splits=splits)
+    qkv_b, k_b, v_b = case["qkv"].clone(), case["k_cache"].clone(), case["v_cache"].clone()
+    got = K().paged_attention(qkv_b, k_b, v_b, case["table"], ctx, heads, kv_heads, dim, scale, window,
+                              num_splits=splits, cos_sin=cos_sin, write_kv=True)
+    assert torch.equal(k_a, k_b) and torch.equal(v_a, v_b)
+    assert torch.equal(got, want)
+    assert torch.isfinite(got.float()).all()
+    # a layer that reads another layer's cache: the keys are there already, only q is rotated
+    qkv_c = case["qkv"].clone()
+    k_c, v_c = k_a.clone(), v_a.clone()
+    borrowed = K().paged_attention(qkv_c, k_c, v_c, case["table"], ctx, heads, kv_heads, dim, scale, window,
+                                   num_splits=splits, cos_sin=cos_sin, write_kv=False)
+    assert torch.equal(borrowed, want)
+    assert torch.equal(k_c, k_a) and torch.equal(v_c, v_a)
+    assert K().read_status() == 0
+
+
 def test_flash_split_policy():
     assert K().decode_splits(64, 8, 8192) == 1
     assert K().decode_splits(8, 8, 8192) == 7
