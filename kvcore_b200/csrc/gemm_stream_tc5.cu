@@ -1,0 +1,628 @@
+// Weight-streaming linear layer for decode batches of 17 to 128 tokens on the 5th-generation
+// tensor cores (sm_100a): out[M, N] = x[M, K] . W[N, K]^T (+ bias), bf16 in, 32-bit accumulate in
+// tensor memory, K a multiple of 64.
+//
+// With this few tokens the layer is still one pass over the weight matrix, so the kernel is the
+// streaming kernel of the smallest batches (gemm_stream.cu) with the product moved to tcgen05.mma:
+// the weight tile is the A operand (128 rows of W are the 128 lanes of the accumulator), the token
+// rows are the B operand (MT = 32, 64 or 128 tokens are the accumulator's columns), so the bytes
+// that stream (W) fill the large operand and the tokens ride along.
+//
+//  * A stage is 256 weight rows x 64 k-values (32 KB, ONE 2-D TMA box, 128-byte swizzle) plus the
+//    MT token rows of the same k-values (4 to 16 KB).  Five stages (four at MT = 128): 160 KB of
+//    weights in flight per SM, which is what keeps DRAM busy.
+//  * One block per SM.  Stages are numbered tile by tile (k fastest) and dealt to the blocks as
+//    equal contiguous ranges.  A tile that lies in one block's range is finished from tensor
+//    memory.  A tile shared by P blocks: every block leaves its sums in scratch and raises a flag;
+//    when all P flags are up, block i of the P adds rows [32 * floor(8 i / P), 32 * floor(8 (i+1) / P))
+//    of all P parts in k order and finishes those rows, so the fix-up traffic is spread over the
+//    blocks that share the tile instead of landing on one owner.  The last block through a tile
+//    lowers the flags again.  The result does not depend on timing.
+//  * Warps: 0 producer (TMA), 1 MMA issuer (one thread; owns the tensor memory), 2-5 epilogue
+//    (warp w reads accumulator lanes [32 (w mod 4), +32)), 6-9 (NORMED only) normalise each
+//    stage's token rows in shared memory before the MMA reads them.
+//  * Two accumulator buffers (2 x 2 halves x MT columns): the MMAs of the next tile run while the
+//    epilogue warps finish the last one.
+//  * Programmatic dependent launch: the whole ring of weight boxes is asked for before the wait
+//    for the kernel in front.
+//  * Epilogues as in gemm_stream.cu: plain, gated pairs (rows in runs of 8 gate, 8 up), residual
+//    stream (adds into the residual in place and leaves sums of squares, here 32 columns a piece).
+//
+// Every wait is bounded (status bit WAIT_TIMEOUT; the block drains its copies, frees its tensor
+// memory and returns).
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#define TS_NT 256              // weight rows per tile: two MMA halves of 128
+#define TS_KS 64               // k-values per stage
+#define TS_W_BYTES (TS_NT * TS_KS * 2)
+#define TS_EPI_WARPS 4
+#define TS_NORM_WARPS 4
+#define TS_THREADS ((2 + TS_EPI_WARPS) * 32)
+#define TS_SPIN_LIMIT (1u << 22)
+#define TS_NORM_W_BYTES (16 * 1024)
+#define TS_MAX_TILES 4096      // done counters behind the flags
+
+struct TsParams {
+  void* out; int out_f32; long long ldo;
+  const bf16* bias;
+  int M, N, K;
+  int n_tiles, kchunks, units;       // kchunks = K / 64; units = n_tiles * kchunks
+  float* partial;                    // [blocks][2 slots][2 halves][MT][128]
+  int* flags;                        // [blocks][2 slots] then [TS_MAX_TILES] counters; zero between launches
+  int* status;
+  const float* sumsq_in; int sumsq_pieces; const void* norm_weight; int norm_weight_f32; float eps;
+  bf16* residual; float* sumsq_out;  // sumsq_out [M][ceil(N / 32)]
+  int silu_pairs;
+};
+
+__device__ __forceinline__ unsigned ts_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ts_mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ts_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void ts_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(ts_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ts_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(ts_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool ts_wait(unsigned long long* bar, unsigned parity) {
+  for (unsigned spin = 0; spin < TS_SPIN_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(ts_smem(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if (spin > 1024) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void ts_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(ts_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(ts_smem(bar))
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of 8 rows
+// 1,024 bytes apart, version 1 (sm_100).
+__device__ __forceinline__ unsigned long long ts_desc(unsigned addr) {
+  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(16u >> 4) << 16) |
+         ((unsigned long long)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void ts_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void ts_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(ts_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void ts_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void ts_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void ts_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned* r = reinterpret_cast<unsigned*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void ts_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ int ts_ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ts_st_release(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ts_round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// First stage of block b when `units` stages are dealt to `blocks` blocks, and the block that holds stage u.
+__device__ __forceinline__ int ts_range_start(int units, int blocks, int b) {
+  return (int)(((long long)units * b) / blocks);
+}
+__device__ __forceinline__ int ts_block_of(int units, int blocks, int u) {
+  int b = (int)(((long long)u * blocks) / units);
+  if (b >= blocks) b = blocks - 1;
+  while (b + 1 < blocks && ts_range_start(units, blocks, b + 1) <= u) ++b;
+  while (b > 0 && ts_range_start(units, blocks, b) > u) --b;
+  return b;
+}
+
+// One finished element per lane: the 32 lanes hold rows n0 .. n0+31 (n0 a multiple of 32) of token
+// m (the same for the warp).  Bias, then one of: gated pairs, residual stream, plain store.
+__device__ __forceinline__ void ts_finish(const TsParams& p, int m, int n, int lane, float v) {
+  if (m >= p.M) return;                                  // the whole warp together
+  const bool live = n < p.N;
+  if (p.bias != nullptr && live) v += __bfloat162float(p.bias[n]);
+  if (p.silu_pairs) {
+    // rows in runs of 8 gate, 8 up: lane l holds a gate if (l & 8) == 0, its up sits 8 lanes on.
+    // Rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result.
+    const float mine = ts_round_bf16(v);
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+    if ((lane & 8) == 0 && n + 8 < p.N) {
+      const float act = ts_round_bf16(mine / (1.0f + expf(-mine)));
+      reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + (n >> 4) * 8 + (n & 7)] = __float2bfloat16_rn(act * other);
+    }
+  } else if (p.residual != nullptr) {
+    float s = 0.0f;
+    if (live) {
+      bf16* slot = p.residual + (size_t)m * p.N + n;
+      s = ts_round_bf16(ts_round_bf16(v) + __bfloat162float(*slot));
+      *slot = __float2bfloat16_rn(s);
+    }
+    const float sq = warp_sum(s * s);
+    if (lane == 0 && n < p.N) p.sumsq_out[(size_t)m * ((p.N + 31) / 32) + (n >> 5)] = sq;
+  } else if (live) {
+    if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+    else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+  }
+}
+
+template <int MT, bool NORMED>
+__global__ void __launch_bounds__(TS_THREADS + TS_NORM_WARPS * 32, 1)
+gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                       const TsParams p) {
+  constexpr int X_BYTES = MT * TS_KS * 2;
+  constexpr int STAGE_BYTES = TS_W_BYTES + X_BYTES;            // a multiple of 1,024
+  constexpr int STAGES = MT == 128 ? 4 : 5;
+  constexpr unsigned TMEM_COLS = 4 * MT;                       // 2 buffers x 2 halves x MT columns
+  constexpr int PART_FLOATS = 2 * MT * 128;                    // one slot: [2 halves][MT][128 rows]
+
+  extern __shared__ __align__(1024) unsigned char ts_dyn[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ts_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* tail = base + STAGES * STAGE_BYTES;
+  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(tail);   // [STAGES] weights (and x, unless NORMED) landed
+  unsigned long long* empty_bar = full_bar + STAGES;                            // [STAGES] the MMAs that read the stage are done
+  unsigned long long* xraw_bar = empty_bar + STAGES;                            // [STAGES] NORMED: raw token rows landed
+  unsigned long long* xready_bar = xraw_bar + STAGES;                           // [STAGES] NORMED: token rows normalised
+  unsigned long long* acc_full = xready_bar + STAGES;                           // [2] a segment's sums are complete
+  unsigned long long* acc_free = acc_full + 2;                                  // [2] the epilogue has read them
+  unsigned long long* mma_done = acc_free + 2;                                  // [1] every MMA of the block has retired
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(mma_done + 1);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* epi_abort = abort_flag + 1;   // written by the epilogue warps only, read by them behind their own barrier
+  float* inv_rms = reinterpret_cast<float*>(tail + 512);                        // [MT] NORMED
+  unsigned char* norm_w = tail + 1024;                                          // NORMED: the norm weights, as stored
+
+  KvbTrace trace(KVB_TAG_GEMM_STREAM_TC5);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blocks = gridDim.x, me = blockIdx.x;
+  const int u_begin = ts_range_start(p.units, blocks, me), u_end = ts_range_start(p.units, blocks, me + 1);
+  const int total = u_end - u_begin;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ts_mbar_init(&full_bar[s], 1);
+      ts_mbar_init(&empty_bar[s], 1);
+      ts_mbar_init(&xraw_bar[s], 1);
+      ts_mbar_init(&xready_bar[s], TS_NORM_WARPS);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ts_mbar_init(&acc_full[b], 1);
+      ts_mbar_init(&acc_free[b], TS_EPI_WARPS);
+    }
+    ts_mbar_init(mma_done, 1);
+    *abort_flag = 0;
+    *epi_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(ts_smem(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  ts_fence_before();
+  __syncthreads();
+  ts_fence_after();
+  kvb_grid_launch_dependents();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int pre = total < STAGES ? total : STAGES;
+      // before the kernel in front has finished: the whole ring of weight boxes (weights are
+      // written by no kernel of the step)
+      for (int i = 0; i < pre; ++i) {
+        const int u = u_begin + i;
+        ts_expect_tx(&full_bar[i], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
+        ts_tma_2d(base + i * STAGE_BYTES, &w_map, (u % p.kchunks) * TS_KS, (u / p.kchunks) * TS_NT, &full_bar[i]);
+      }
+      kvb_grid_wait();                            // x is the output of the kernel in front
+      int issued = 0;
+      for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        if (it >= STAGES && !ts_wait(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
+          atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+          atomicExch(abort_flag, 1);
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+        const int u = u_begin + it;
+        const int k0 = (u % p.kchunks) * TS_KS;
+        unsigned char* wdst = base + stage * STAGE_BYTES;
+        if (it >= pre) {
+          ts_expect_tx(&full_bar[stage], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
+          ts_tma_2d(wdst, &w_map, k0, (u / p.kchunks) * TS_NT, &full_bar[stage]);
+        }
+        if (NORMED) {
+          ts_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
+          ts_tma_2d(wdst + TS_W_BYTES, &x_map, k0, 0, &xraw_bar[stage]);
+        } else {
+          ts_tma_2d(wdst + TS_W_BYTES, &x_map, k0, 0, &full_bar[stage]);
+        }
+        issued = it + 1;
+      }
+      if (*reinterpret_cast<volatile int*>(abort_flag)) {   // gave up: let the copies in flight land
+        for (int j = max(0, issued - STAGES); j < issued; ++j) {
+          ts_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
+          if (NORMED) ts_wait(&xraw_bar[j % STAGES], (j / STAGES) & 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M = 128, N = MT
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(MT >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+      bool ok = true;
+      int it = 0, seg = 0, u = u_begin;
+      while (u < u_end && ok) {
+        const int n_tile = u / p.kchunks;
+        const int tile_end = (n_tile + 1) * p.kchunks;
+        const int seg_end = tile_end < u_end ? tile_end : u_end;
+        const int buf = seg & 1;
+        if (seg >= 2 && !ts_wait(&acc_free[buf], ((seg >> 1) - 1) & 1)) { ok = false; break; }
+        bool first = true;
+        for (; u < seg_end; ++u, ++it) {
+          const int stage = it % STAGES;
+          if (!ts_wait(&full_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
+          if (NORMED && !ts_wait(&xready_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
+          if (*reinterpret_cast<volatile int*>(abort_flag)) { ok = false; break; }
+          ts_fence_after();
+          const unsigned wbase = ts_smem(base + stage * STAGE_BYTES);
+          const unsigned xbase = wbase + TS_W_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < TS_KS / 16; ++kk) {
+            const unsigned long long bdesc = ts_desc(xbase + kk * 32);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              ts_mma(tmem_base + (buf * 2 + h) * MT, ts_desc(wbase + h * (128 * 128) + kk * 32), bdesc, idesc,
+                     (first && kk == 0) ? 0u : 1u);
+          }
+          first = false;
+          ts_commit(&empty_bar[stage]);           // the stage may be refilled once these MMAs have read it
+        }
+        if (!ok) break;
+        ts_commit(&acc_full[buf]);
+        ++seg;
+      }
+      if (!ok) {
+        atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+        atomicExch(abort_flag, 1);
+      }
+      // nothing of this block may still be running on the tensor cores when the memory is freed
+      ts_commit(mma_done);
+      ts_wait(mma_done, 0);
+    }
+  } else if (warp < 2 + TS_EPI_WARPS) {
+    // ---------------- epilogue: warp w reads accumulator lanes [32 (w mod 4), +32) ----------------
+    kvb_grid_wait();   // nothing is written to global memory before the kernel in front has finished
+    trace.after_wait();
+    const int q = warp & 3;
+    const int tid = q * 32 + lane;                       // row of a 128-row half
+    const unsigned lane_addr = ((unsigned)(q * 32)) << 16;
+    int shared_tile[2] = {-1, -1};                       // tiles this block shares with others: [slot]
+    bool ok = true;
+    int seg = 0, u = u_begin;
+    while (u < u_end && ok) {
+      const int n_tile = u / p.kchunks, kc0 = u % p.kchunks;
+      const int tile_end = (n_tile + 1) * p.kchunks;
+      const int seg_end = tile_end < u_end ? tile_end : u_end;
+      const int buf = seg & 1;
+      const bool whole = kc0 == 0 && seg_end == tile_end;
+      const int slot = kc0 == 0 ? 1 : 0;
+      // the four warps decide together whether to go on: a wait that ran out in one of them ends all
+      if (!ts_wait(&acc_full[buf], (seg >> 1) & 1)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
+      asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+      if (*reinterpret_cast<volatile int*>(epi_abort)) { ok = false; break; }
+      ts_fence_after();
+      float* part = p.partial + ((size_t)me * 2 + slot) * PART_FLOATS;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < MT; c0 += 32) {
+          float v[32];
+          ts_ld32(tmem_base + lane_addr + (buf * 2 + h) * MT + c0, v);
+          ts_wait_ld();
+          if (whole) {
+            const int n = n_tile * TS_NT + h * 128 + tid;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ts_finish(p, c0 + j, n, lane, v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(part + ((size_t)h * MT + c0 + j) * 128 + tid, v[j]);
+          }
+        }
+      }
+      ts_fence_before();
+      __syncwarp();
+      if (lane == 0) ts_arrive(&acc_free[buf]);
+      if (!whole) {
+        shared_tile[slot] = n_tile;
+        __threadfence();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+        if (tid == 0) ts_st_release(&p.flags[me * 2 + slot], 1);
+      }
+      u = seg_end;
+      ++seg;
+    }
+    if (!ok) {
+      atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+      atomicExch(abort_flag, 1);
+    }
+    // ---- tiles shared with other blocks: when all parts are there, this block finishes its rows ----
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+#pragma unroll 1
+    for (int slot = 0; slot < 2 && ok; ++slot) {
+      const int n_tile = shared_tile[slot];
+      if (n_tile < 0) continue;
+      const int b_first = ts_block_of(p.units, blocks, n_tile * p.kchunks);
+      const int b_last = ts_block_of(p.units, blocks, (n_tile + 1) * p.kchunks - 1);
+      const int parts = b_last - b_first + 1, mine = me - b_first;
+      // part j lies in block b_first + j, slot 1 for the tile's first block, slot 0 for the others
+      bool seen_all = true;
+      for (int j = tid; j < parts; j += TS_EPI_WARPS * 32) {
+        const int* flag = &p.flags[(b_first + j) * 2 + (j == 0 ? 1 : 0)];
+        int seen = 0;
+        for (unsigned spin = 0; spin < TS_SPIN_LIMIT && !seen; ++spin) {
+          seen = ts_ld_acquire(flag);
+          if (!seen && spin > 4096) __nanosleep(64);     // the blocks finish together: spin first
+        }
+        if (!seen) seen_all = false;
+      }
+      if (!seen_all) {
+        atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+        atomicExch(abort_flag, 1);
+        *reinterpret_cast<volatile int*>(epi_abort) = 1;
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+      if (*reinterpret_cast<volatile int*>(epi_abort)) break;
+      __threadfence();
+      // groups of 32 rows [g_lo, g_hi) of the tile's 8 are this block's; warp q takes tokens q, q+4, ...
+      const int g_lo = (8 * mine) / parts, g_hi = (8 * (mine + 1)) / parts;
+      for (int g = g_lo; g < g_hi; ++g) {
+        const int h = g >> 2, row = (g & 3) * 32 + lane;
+        const int n = n_tile * TS_NT + g * 32 + lane;
+        for (int m = q; m < MT && m < p.M; m += TS_EPI_WARPS) {
+          float acc = 0.0f;
+          const size_t within = ((size_t)h * MT + m) * 128 + row;
+          for (int j0 = 0; j0 < parts; j0 += 8) {          // eight loads in flight, added in k order
+            float vals[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int part_index = j0 + j;
+              vals[j] = part_index < parts
+                            ? __ldcg(p.partial + ((size_t)(b_first + part_index) * 2 + (part_index == 0 ? 1 : 0)) * PART_FLOATS + within)
+                            : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j0 + j < parts) acc += vals[j];
+          }
+          ts_finish(p, m, n, lane, acc);
+        }
+      }
+      // the last block through the tile lowers its flags for the next launch
+      asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+      if (tid == 0) {
+        int* counter = &p.flags[blocks * 2 + n_tile];
+        if (atomicAdd(counter, 1) == parts - 1) {
+          *counter = 0;
+          for (int j = 0; j < parts; ++j) p.flags[(b_first + j) * 2 + (j == 0 ? 1 : 0)] = 0;
+        }
+      }
+    }
+  } else {
+    // ---------------- NORMED: the normaliser warps ----------------
+    if (NORMED) {
+      const int nt = (warp - 2 - TS_EPI_WARPS) * 32 + lane;       // 0..127
+      // the norm weights (written by no kernel of the step) into shared memory, before the wait
+      const int w_bytes = p.K * (p.norm_weight_f32 ? 4 : 2);
+      for (int i = nt * 16; i < w_bytes; i += TS_NORM_WARPS * 32 * 16)
+        *reinterpret_cast<uint4*>(norm_w + i) = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.norm_weight) + i);
+      kvb_grid_wait();
+      // 1 / rms of every token row from the pieces of its sum of squares, added in their order
+      for (int m = nt; m < MT; m += TS_NORM_WARPS * 32) {
+        float sum = 0.0f;
+        if (m < p.M) {
+          const float* pieces = p.sumsq_in + (size_t)m * p.sumsq_pieces;
+          for (int t0 = 0; t0 < p.sumsq_pieces; t0 += 8) {
+            float vals[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[j] = t0 + j < p.sumsq_pieces ? __ldcg(pieces + t0 + j) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum += vals[j];
+          }
+        }
+        inv_rms[m] = 1.0f / sqrtf(sum / (float)p.K + p.eps);
+      }
+      asm volatile("bar.sync 2, %0;\n" ::"n"(TS_NORM_WARPS * 32));
+      const int chunk = nt & 7, row0 = nt >> 3;            // 16 bytes of a row; rows row0, row0 + 16, ...
+      for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        int fine = ts_wait(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
+        fine = __all_sync(0xffffffffu, fine);
+        if (!fine) {
+          if (lane == 0) {
+            atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+            atomicExch(abort_flag, 1);
+          }
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+        const int k = ((u_begin + it) % p.kchunks) * TS_KS + chunk * 8;   // this thread's 8 k-values of the stage
+        unsigned char* xs = base + stage * STAGE_BYTES + TS_W_BYTES;
+        float g[8];
+        if (p.norm_weight_f32) {
+          const float4 lo = *reinterpret_cast<const float4*>(norm_w + (size_t)k * 4);
+          const float4 hi = *reinterpret_cast<const float4*>(norm_w + (size_t)k * 4 + 16);
+          g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w; g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+        } else {
+          Vec16<bf16> gw;
+          gw.raw = *reinterpret_cast<const uint4*>(norm_w + (size_t)k * 2);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = gw.get(j);
+        }
+        constexpr int PASSES = MT / 16;
+        uint4 raw[PASSES];
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+          const int r = row0 + i * 16;
+          raw[i] = *reinterpret_cast<const uint4*>(xs + r * 128 + ((chunk ^ (r & 7)) << 4));
+        }
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+          const int r = row0 + i * 16;
+          const float inv = inv_rms[r];
+          Vec16<bf16> v, o;
+          v.raw = raw[i];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o.set(j, g[j] * (v.get(j) * inv));
+          *reinterpret_cast<uint4*>(xs + r * 128 + ((chunk ^ (r & 7)) << 4)) = o.raw;
+        }
+        // these writes come before the MMAs that read the stage and the TMA box that will reuse it
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) ts_arrive(&xready_bar[stage]);
+      }
+    }
+  }
+
+  // ---- everyone meets; the allocating warp frees the tensor memory ----
+  ts_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ts_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+typedef CUresult (*TsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TsEncodeFn ts_encode_fn() {
+  static TsEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TsEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements):
+// boxes of [box_rows][64 columns], 128-byte swizzle, zero fill outside.
+static int ts_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  TsEncodeFn encode = ts_encode_fn();
+  KVB_REQUIRE(encode != nullptr, "stream gemm (tcgen05): the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
+  const cuuint32_t box[2] = {TS_KS, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  KVB_REQUIRE(rc == CUDA_SUCCESS, "stream gemm (tcgen05): cuTensorMapEncodeTiled failed");
+  return 0;
+}
+
+// Scratch floats (for the largest token block) and flag ints (zero before the first launch; the
+// kernel leaves them zero) for `blocks` blocks.
+extern "C" long long kvb_gemm_stream_tc5_scratch_floats(int blocks) { return (long long)blocks * 2 * 2 * 128 * 128; }
+extern "C" long long kvb_gemm_stream_tc5_flag_ints(int blocks) { return (long long)blocks * 2 + TS_MAX_TILES; }
+extern "C" int kvb_gemm_stream_tc5_norm_max_k() { return TS_NORM_W_BYTES / 4; }
+extern "C" int kvb_gemm_stream_tc5_max_rows() { return 128; }
+
+template <int MT, bool NORMED>
+static int ts_launch(const void* w, const void* x, long long ldx, TsParams& p, int sms, cudaStream_t stream) {
+  constexpr int STAGES = MT == 128 ? 4 : 5;
+  constexpr size_t SMEM = 1024 + (size_t)STAGES * (TS_W_BYTES + MT * TS_KS * 2) + 1024 + (NORMED ? TS_NORM_W_BYTES : 0);
+  static bool configured = false;
+  if (!configured) {
+    KVB_CHECK_CUDA(cudaFuncSetAttribute(gemm_stream_tc5_kernel<MT, NORMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+    configured = true;
+  }
+  alignas(64) CUtensorMap w_map, x_map;
+  if (int rc = ts_make_map(&w_map, w, p.N, p.K, p.K, TS_NT)) return rc;
+  if (int rc = ts_make_map(&x_map, x, p.M, p.K, ldx, MT)) return rc;
+  const int blocks = p.units < sms ? p.units : sms;
+  const int threads = NORMED ? TS_THREADS + TS_NORM_WARPS * 32 : TS_THREADS;
+  KVB_CHECK_CUDA(kvb_launch(gemm_stream_tc5_kernel<MT, NORMED>, dim3(blocks), dim3(threads), SMEM, stream, true, w_map,
+                            x_map, p));
+  return 0;
+}
+
+// out[M, N] = x[M, K] . w[N, K]^T (+ bias), 1 <= M <= 128, K a multiple of 64.  Arguments as
+// kvb_gemm_stream_bf16, except: scratch holds kvb_gemm_stream_tc5_scratch_floats(sms) floats, flags
+// kvb_gemm_stream_tc5_flag_ints(sms) ints (zero before the first launch); with the residual epilogue
+// sumsq_out is [M, ceil(N / 32)] (32 columns a piece).  `sms` must not exceed the number of blocks
+// that run at the same time (one per SM): blocks that share a tile wait for one another.
+extern "C" int kvb_gemm_stream_tc5_bf16(void* out, int out_f32, long long ldo, const void* x, long long ldx,
+                                        const void* w, const void* bias, int M, int N, int K, int silu_pairs,
+                                        const void* norm_weight, int norm_weight_f32, float eps,
+                                        const float* sumsq_in, int sumsq_pieces, void* residual, float* sumsq_out,
+                                        float* scratch, int* flags, int sms, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  KVB_REQUIRE(M > 0 && M <= 128, "stream gemm (tcgen05): takes 1 to 128 rows of x");
+  KVB_REQUIRE(K > 0 && K % 64 == 0 && ldx % 8 == 0,
+              "stream gemm (tcgen05): K must be a multiple of 64 and the row stride of x of 8");
+  KVB_REQUIRE(aligned16(x) && aligned16(w), "stream gemm (tcgen05): x and w must be 16-byte aligned");
+  KVB_REQUIRE(scratch != nullptr && flags != nullptr && sms > 0, "stream gemm (tcgen05): needs scratch and flags");
+  KVB_REQUIRE(!silu_pairs || (N % 16 == 0 && !out_f32),
+              "stream gemm (tcgen05): gated pairs need N a multiple of 16 and a bf16 result");
+  KVB_REQUIRE(residual == nullptr || (!silu_pairs && !out_f32 && sumsq_out != nullptr),
+              "stream gemm (tcgen05): the residual epilogue needs a plain bf16 product and a place for the squares");
+  KVB_REQUIRE(norm_weight == nullptr || (sumsq_in != nullptr && sumsq_pieces > 0 && aligned16(norm_weight) &&
+                                         (size_t)K * (norm_weight_f32 ? 4 : 2) <= TS_NORM_W_BYTES),
+              "stream gemm (tcgen05): the fused norm needs the sums of squares and K small enough for shared memory");
+  TsParams p;
+  memset(&p, 0, sizeof(p));
+  p.out = out; p.out_f32 = out_f32; p.ldo = ldo;
+  p.bias = (const bf16*)bias;
+  p.M = M; p.N = N; p.K = K;
+  p.silu_pairs = silu_pairs;
+  p.norm_weight = norm_weight; p.norm_weight_f32 = norm_weight_f32; p.eps = eps;
+  p.sumsq_in = sumsq_in; p.sumsq_pieces = sumsq_pieces;
+  p.residual = (bf16*)residual; p.sumsq_out = sumsq_out;
+  p.n_tiles = (N + TS_NT - 1) / TS_NT;
+  p.kchunks = K / TS_KS;
+  KVB_REQUIRE(p.n_tiles <= TS_MAX_TILES, "stream gemm (tcgen05): N is too large");
+  KVB_REQUIRE((long long)p.n_tiles * p.kchunks < (1ll << 30), "stream gemm (tcgen05): the matrix is too large");
+  p.units = p.n_tiles * p.kchunks;
+  p.partial = scratch;
+  p.flags = flags;
+  p.status = kvb_status_word();
+  KVB_REQUIRE(p.status != nullptr, "stream gemm (tcgen05): no status word");
+  const bool normed = norm_weight != nullptr;
+  if (M <= 32) return normed ? ts_launch<32, true>(w, x, ldx, p, sms, stream) : ts_launch<32, false>(w, x, ldx, p, sms, stream);
+  if (M <= 64) return normed ? ts_launch<64, true>(w, x, ldx, p, sms, stream) : ts_launch<64, false>(w, x, ldx, p, sms, stream);
+  return normed ? ts_launch<128, true>(w, x, ldx, p, sms, stream) : ts_launch<128, false>(w, x, ldx, p, sms, stream);
+}
+
+KVB_TRACE_TU(gemm_stream_tc5)

@@ -104,7 +104,11 @@ def rope_kv_write(qkv, positions, req_index, cos_sin, table, k_cache, v_cache,
 
 
 def paged_attention(qkv, k_cache, v_cache, table, ctx, num_heads, num_kv_heads, head_dim, scale, window,
-                    *, force_general=False, num_splits=None, use_tma=True, use_tc5=True):
+                    *, force_general=False, num_splits=None, use_tma=True, use_tc5=True, cos_sin=None,
+                    write_kv=None):
+    if write_kv is not None:   # the call also rotates q, k and writes this step's k, v
+        rope_kv_write(qkv, ctx.positions, ctx.req_index, cos_sin, table, k_cache, v_cache,
+                      num_heads, num_kv_heads, head_dim, write_kv=write_kv)
     return paged_attention_plain(qkv, k_cache, v_cache, table, ctx.positions, ctx.req_index,
                                  num_heads, num_kv_heads, head_dim, scale, window)
 
