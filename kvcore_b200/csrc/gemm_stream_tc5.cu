@@ -3,26 +3,29 @@
 // tensor memory, K a multiple of 64.
 //
 // With this few tokens the layer is still one pass over the weight matrix, so the kernel is the
-// streaming kernel of the smallest batches (gemm_stream.cu) with the product moved to tcgen05.mma:
-// the weight tile is the A operand (128 rows of W are the 128 lanes of the accumulator), the token
-// rows are the B operand (MT = 32, 64 or 128 tokens are the accumulator's columns), so the bytes
-// that stream (W) fill the large operand and the tokens ride along.
+// streaming kernel of the smallest batches (gemm_stream.cu) with the product moved to tcgen05.mma.
+// The tokens are the A operand: token m is lane m of the accumulator, the 256 weight rows of a
+// tile are its columns.  A thread of the epilogue therefore holds one token's run of output rows,
+// which is how the output, the residual and the gated pairs lie in memory: 16-byte stores, the
+// sum of squares of a piece without a shuffle, gate and up of a pair in the same thread.
 //
-//  * A stage is 256 weight rows x 64 k-values (32 KB, ONE 2-D TMA box, 128-byte swizzle) plus the
-//    MT token rows of the same k-values (4 to 16 KB).  Five stages (four at MT = 128): 160 KB of
-//    weights in flight per SM, which is what keeps DRAM busy.
+//  * A stage is the MT (32, 64 or 128) token rows of 64 k-values (4 to 16 KB) followed by 256 weight
+//    rows of the same k-values (32 KB, ONE 2-D TMA box, 128-byte swizzle).  Five stages (four at
+//    MT = 128): 160 KB of weights in flight per SM, which is what keeps DRAM busy.  The MMA always
+//    reads 128 A rows; beyond MT they are the weight bytes that follow, and no one reads those lanes.
 //  * One block per SM.  Stages are numbered tile by tile (k fastest) and dealt to the blocks as
 //    equal contiguous ranges.  A tile that lies in one block's range is finished from tensor
 //    memory.  A tile shared by P blocks: every block leaves its sums in scratch and raises a flag;
 //    when all P flags are up, block i of the P adds rows [32 * floor(8 i / P), 32 * floor(8 (i+1) / P))
-//    of all P parts in k order and finishes those rows, so the fix-up traffic is spread over the
-//    blocks that share the tile instead of landing on one owner.  The last block through a tile
-//    lowers the flags again.  The result does not depend on timing.
+//    of all P parts in k order (the parts come into the idle stage memory by bulk copies, all in
+//    flight together) and finishes those rows, so the fix-up traffic is spread over the blocks
+//    that share the tile instead of landing on one owner.  The last block through a tile lowers
+//    the flags again.  The result does not depend on timing.
 //  * Warps: 0 producer (TMA), 1 MMA issuer (one thread; owns the tensor memory), 2-5 epilogue
 //    (warp w reads accumulator lanes [32 (w mod 4), +32)), 6-9 (NORMED only) normalise each
 //    stage's token rows in shared memory before the MMA reads them.
-//  * Two accumulator buffers (2 x 2 halves x MT columns): the MMAs of the next tile run while the
-//    epilogue warps finish the last one.
+//  * Two accumulator buffers of 256 columns: the MMAs of the next tile run while the epilogue warps
+//    finish the last one.
 //  * Programmatic dependent launch: the whole ring of weight boxes is asked for before the wait
 //    for the kernel in front.
 //  * Epilogues as in gemm_stream.cu: plain, gated pairs (rows in runs of 8 gate, 8 up), residual
@@ -50,7 +53,7 @@ struct TsParams {
   const bf16* bias;
   int M, N, K;
   int n_tiles, kchunks, units;       // kchunks = K / 64; units = n_tiles * kchunks
-  float* partial;                    // [blocks][2 slots][2 halves][MT][128]
+  float* partial;                    // [blocks][2 slots][8 groups of 32 W rows][MT tokens][32]
   int* flags;                        // [blocks][2 slots] then [TS_MAX_TILES] counters; zero between launches
   int* status;
   const float* sumsq_in; int sumsq_pieces; const void* norm_weight; int norm_weight_f32; float eps;
@@ -140,33 +143,176 @@ __device__ __forceinline__ int ts_block_of(int units, int blocks, int u) {
   return b;
 }
 
-// One finished element per lane: the 32 lanes hold rows n0 .. n0+31 (n0 a multiple of 32) of token
-// m (the same for the warp).  Bias, then one of: gated pairs, residual stream, plain store.
-__device__ __forceinline__ void ts_finish(const TsParams& p, int m, int n, int lane, float v) {
-  if (m >= p.M) return;                                  // the whole warp together
-  const bool live = n < p.N;
-  if (p.bias != nullptr && live) v += __bfloat162float(p.bias[n]);
+// ---- epilogues -----------------------------------------------------------------------------
+// Both take the sums of one token m for a run of output rows (W rows n), with the bias still to
+// be added, and do one of: gated pairs, residual stream, plain store.  `vector_ok` says that the
+// rows of out / residual may be written in 16-byte pieces.
+struct TsOutput {
+  bool vector_ok;     // 16-byte stores are aligned (leading dimensions and bases)
+  int pieces;         // sums of squares per token: ceil(N / 32)
+};
+
+__device__ __forceinline__ unsigned ts_pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+__device__ __forceinline__ float ts_silu_mul(float gate, float up) {
+  // rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result
+  const float g = ts_round_bf16(gate), u = ts_round_bf16(up);
+  const float act = ts_round_bf16(g / (1.0f + expf(-g)));
+  return act * u;
+}
+
+// 32 rows n0 .. n0+31 (n0 a multiple of 32) of token m, all in this thread.
+__device__ __forceinline__ void ts_finish_row32(const TsParams& p, const TsOutput& o, int m, int n0, float (&v)[32]) {
+  const bool full = n0 + 32 <= p.N;
+  if (p.bias != nullptr) {
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        Vec16<bf16> b;
+        b.load(p.bias + n0 + i * 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i * 8 + j] += b.get(j);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) v[j] += __bfloat162float(p.bias[n0 + j]);
+    }
+  }
   if (p.silu_pairs) {
-    // rows in runs of 8 gate, 8 up: lane l holds a gate if (l & 8) == 0, its up sits 8 lanes on.
-    // Rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result.
-    const float mine = ts_round_bf16(v);
-    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-    if ((lane & 8) == 0 && n + 8 < p.N) {
-      const float act = ts_round_bf16(mine / (1.0f + expf(-mine)));
-      reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + (n >> 4) * 8 + (n & 7)] = __float2bfloat16_rn(act * other);
+    // rows in runs of 8 gate, 8 up (N is a multiple of 16): two runs of 8 outputs
+    bf16* out = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.ldo + (n0 >> 1);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (n0 + r * 16 >= p.N) break;
+      float y[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = ts_silu_mul(v[r * 16 + j], v[r * 16 + 8 + j]);
+      if (o.vector_ok) {
+        *reinterpret_cast<uint4*>(out + r * 8) =
+            make_uint4(ts_pack2(y[0], y[1]), ts_pack2(y[2], y[3]), ts_pack2(y[4], y[5]), ts_pack2(y[6], y[7]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) out[r * 8 + j] = __float2bfloat16_rn(y[j]);
+      }
     }
   } else if (p.residual != nullptr) {
-    float s = 0.0f;
-    if (live) {
-      bf16* slot = p.residual + (size_t)m * p.N + n;
-      s = ts_round_bf16(ts_round_bf16(v) + __bfloat162float(*slot));
-      *slot = __float2bfloat16_rn(s);
+    bf16* slot = p.residual + (size_t)m * p.N + n0;
+    float sq = 0.0f;
+    if (full && o.vector_ok) {
+      Vec16<bf16> old[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) old[i].load(slot + i * 8);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        Vec16<bf16> s;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s.set(j, ts_round_bf16(v[i * 8 + j]) + old[i].get(j));
+          const float kept = s.get(j);
+          sq += kept * kept;
+        }
+        s.store(slot + i * 8);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (n0 + j < p.N) {
+          const float kept = ts_round_bf16(ts_round_bf16(v[j]) + __bfloat162float(slot[j]));
+          slot[j] = __float2bfloat16_rn(kept);
+          sq += kept * kept;
+        }
+      }
     }
-    const float sq = warp_sum(s * s);
-    if (lane == 0 && n < p.N) p.sumsq_out[(size_t)m * ((p.N + 31) / 32) + (n >> 5)] = sq;
-  } else if (live) {
-    if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-    else reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+    p.sumsq_out[(size_t)m * o.pieces + (n0 >> 5)] = sq;
+  } else if (p.out_f32) {
+    float* out = reinterpret_cast<float*>(p.out) + (size_t)m * p.ldo + n0;
+    if (full && o.vector_ok) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<float4*>(out + i * 4) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) out[j] = v[j];
+    }
+  } else {
+    bf16* out = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.ldo + n0;
+    if (full && o.vector_ok) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4*>(out + i * 8) =
+            make_uint4(ts_pack2(v[i * 8], v[i * 8 + 1]), ts_pack2(v[i * 8 + 2], v[i * 8 + 3]),
+                       ts_pack2(v[i * 8 + 4], v[i * 8 + 5]), ts_pack2(v[i * 8 + 6], v[i * 8 + 7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) out[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// 4 rows n .. n+3 (n a multiple of 4) of token m in this thread; the 8 threads that hold the 32 rows
+// of a group sit in 8 neighbouring lanes (quad = lane & 7), the whole warp calls together.
+__device__ __forceinline__ void ts_finish_quad(const TsParams& p, const TsOutput& o, int m, int n, int lane, bool token_live,
+                                               float (&v)[4]) {
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (n + j < p.N) v[j] += __bfloat162float(p.bias[n + j]);
+  }
+  if (p.silu_pairs) {
+    // gates are quads 0, 1 of every 4 (rows 0-7 of 16); their ups sit two lanes on
+    float up[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) up[j] = __shfl_down_sync(0xffffffffu, v[j], 2);
+    if (token_live && (lane & 2) == 0 && n < p.N) {
+      bf16* out = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.ldo + (n >> 4) * 8 + (n & 7);
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y[j] = ts_silu_mul(v[j], up[j]);
+      if (o.vector_ok) {
+        *reinterpret_cast<uint2*>(out) = make_uint2(ts_pack2(y[0], y[1]), ts_pack2(y[2], y[3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = __float2bfloat16_rn(y[j]);
+      }
+    }
+  } else if (p.residual != nullptr) {
+    float sq = 0.0f;
+    if (token_live) {
+      bf16* slot = p.residual + (size_t)m * p.N + n;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (n + j < p.N) {
+          const float kept = ts_round_bf16(ts_round_bf16(v[j]) + __bfloat162float(slot[j]));
+          slot[j] = __float2bfloat16_rn(kept);
+          sq += kept * kept;
+        }
+      }
+    }
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+    if (token_live && (lane & 7) == 0 && n < p.N) p.sumsq_out[(size_t)m * o.pieces + (n >> 5)] = sq;
+  } else if (token_live) {
+    if (p.out_f32) {
+      float* out = reinterpret_cast<float*>(p.out) + (size_t)m * p.ldo + n;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n + j < p.N) out[j] = v[j];
+    } else {
+      bf16* out = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.ldo + n;
+      if (o.vector_ok && n + 4 <= p.N) {
+        *reinterpret_cast<uint2*>(out) = make_uint2(ts_pack2(v[0], v[1]), ts_pack2(v[2], v[3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.N) out[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
   }
 }
 
@@ -175,10 +321,10 @@ __global__ void __launch_bounds__(TS_THREADS + TS_NORM_WARPS * 32, 1)
 gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                        const TsParams p) {
   constexpr int X_BYTES = MT * TS_KS * 2;
-  constexpr int STAGE_BYTES = TS_W_BYTES + X_BYTES;            // a multiple of 1,024
+  constexpr int STAGE_BYTES = X_BYTES + TS_W_BYTES;            // token rows first, then the weights; a multiple of 1,024
   constexpr int STAGES = MT == 128 ? 4 : 5;
-  constexpr unsigned TMEM_COLS = 4 * MT;                       // 2 buffers x 2 halves x MT columns
-  constexpr int PART_FLOATS = 2 * MT * 128;                    // one slot: [2 halves][MT][128 rows]
+  constexpr unsigned TMEM_COLS = 512;                          // 2 buffers x 256 columns (W rows)
+  constexpr int PART_FLOATS = 8 * MT * 32;                     // one slot: [8 groups of 32 W rows][MT tokens][32]
 
   extern __shared__ __align__(1024) unsigned char ts_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ts_dyn) + 1023) & ~uintptr_t(1023));
@@ -190,7 +336,8 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
   unsigned long long* acc_full = xready_bar + STAGES;                           // [2] a segment's sums are complete
   unsigned long long* acc_free = acc_full + 2;                                  // [2] the epilogue has read them
   unsigned long long* mma_done = acc_free + 2;                                  // [1] every MMA of the block has retired
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(mma_done + 1);
+  unsigned long long* fix_bar = mma_done + 1;                                   // [1] the parts of shared tiles have arrived in shared memory
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(fix_bar + 1);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* epi_abort = abort_flag + 1;   // written by the epilogue warps only, read by them behind their own barrier
   float* inv_rms = reinterpret_cast<float*>(tail + 512);                        // [MT] NORMED
@@ -213,6 +360,7 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       ts_mbar_init(&acc_free[b], TS_EPI_WARPS);
     }
     ts_mbar_init(mma_done, 1);
+    ts_mbar_init(fix_bar, 1);
     *abort_flag = 0;
     *epi_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -237,9 +385,10 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       for (int i = 0; i < pre; ++i) {
         const int u = u_begin + i;
         ts_expect_tx(&full_bar[i], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
-        ts_tma_2d(base + i * STAGE_BYTES, &w_map, (u % p.kchunks) * TS_KS, (u / p.kchunks) * TS_NT, &full_bar[i]);
+        ts_tma_2d(base + i * STAGE_BYTES + X_BYTES, &w_map, (u % p.kchunks) * TS_KS, (u / p.kchunks) * TS_NT, &full_bar[i]);
       }
       kvb_grid_wait();                            // x is the output of the kernel in front
+      trace.after_wait();
       int issued = 0;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
@@ -251,16 +400,16 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         if (*reinterpret_cast<volatile int*>(abort_flag)) break;
         const int u = u_begin + it;
         const int k0 = (u % p.kchunks) * TS_KS;
-        unsigned char* wdst = base + stage * STAGE_BYTES;
+        unsigned char* xdst = base + stage * STAGE_BYTES;
         if (it >= pre) {
           ts_expect_tx(&full_bar[stage], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
-          ts_tma_2d(wdst, &w_map, k0, (u / p.kchunks) * TS_NT, &full_bar[stage]);
+          ts_tma_2d(xdst + X_BYTES, &w_map, k0, (u / p.kchunks) * TS_NT, &full_bar[stage]);
         }
         if (NORMED) {
           ts_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
-          ts_tma_2d(wdst + TS_W_BYTES, &x_map, k0, 0, &xraw_bar[stage]);
+          ts_tma_2d(xdst, &x_map, k0, 0, &xraw_bar[stage]);
         } else {
-          ts_tma_2d(wdst + TS_W_BYTES, &x_map, k0, 0, &full_bar[stage]);
+          ts_tma_2d(xdst, &x_map, k0, 0, &full_bar[stage]);
         }
         issued = it + 1;
       }
@@ -274,8 +423,8 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M = 128, N = MT
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(MT >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+      // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M = 128 (token lanes), N = 256 (W rows)
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TS_NT >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
       bool ok = true;
       int it = 0, seg = 0, u = u_begin;
       while (u < u_end && ok) {
@@ -291,16 +440,14 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
           if (NORMED && !ts_wait(&xready_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
           if (*reinterpret_cast<volatile int*>(abort_flag)) { ok = false; break; }
           ts_fence_after();
-          const unsigned wbase = ts_smem(base + stage * STAGE_BYTES);
-          const unsigned xbase = wbase + TS_W_BYTES;
+          // A: the MT token rows (the MMA reads 128 rows: lanes beyond MT see the bytes that follow,
+          // which stay inside the stage, and no one reads those lanes); B: the 256 weight rows
+          const unsigned xbase = ts_smem(base + stage * STAGE_BYTES);
+          const unsigned wbase = xbase + X_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < TS_KS / 16; ++kk) {
-            const unsigned long long bdesc = ts_desc(xbase + kk * 32);
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-              ts_mma(tmem_base + (buf * 2 + h) * MT, ts_desc(wbase + h * (128 * 128) + kk * 32), bdesc, idesc,
-                     (first && kk == 0) ? 0u : 1u);
-          }
+          for (int kk = 0; kk < TS_KS / 16; ++kk)
+            ts_mma(tmem_base + buf * TS_NT, ts_desc(xbase + kk * 32), ts_desc(wbase + kk * 32), idesc,
+                   (first && kk == 0) ? 0u : 1u);
           first = false;
           ts_commit(&empty_bar[stage]);           // the stage may be refilled once these MMAs have read it
         }
@@ -317,12 +464,20 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       ts_wait(mma_done, 0);
     }
   } else if (warp < 2 + TS_EPI_WARPS) {
-    // ---------------- epilogue: warp w reads accumulator lanes [32 (w mod 4), +32) ----------------
+    // ---------------- epilogue: thread = token (accumulator lane); warp w reads lanes [32 (w mod 4), +32) ----------------
     kvb_grid_wait();   // nothing is written to global memory before the kernel in front has finished
-    trace.after_wait();
     const int q = warp & 3;
-    const int tid = q * 32 + lane;                       // row of a 128-row half
+    const int tid = q * 32 + lane;                       // token of this thread
     const unsigned lane_addr = ((unsigned)(q * 32)) << 16;
+    const bool warp_live = q * 32 < p.M;                 // some token of the warp exists
+    TsOutput o;
+    o.pieces = (p.N + 31) / 32;
+    {
+      const int esize = p.out_f32 ? 4 : 2;
+      o.vector_ok = p.residual != nullptr
+                        ? (p.N % 8 == 0 && aligned16(p.residual))
+                        : (((size_t)p.ldo * esize) % 16 == 0 && aligned16(p.out));
+    }
     int shared_tile[2] = {-1, -1};                       // tiles this block shares with others: [slot]
     bool ok = true;
     int seg = 0, u = u_begin;
@@ -339,20 +494,21 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       if (*reinterpret_cast<volatile int*>(epi_abort)) { ok = false; break; }
       ts_fence_after();
       float* part = p.partial + ((size_t)me * 2 + slot) * PART_FLOATS;
+      if (warp_live) {
 #pragma unroll 1
-      for (int h = 0; h < 2; ++h) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < MT; c0 += 32) {
+        for (int g = 0; g < 8; ++g) {
+          if (n_tile * TS_NT + g * 32 >= p.N) break;       // rows beyond N: zeros, never read
           float v[32];
-          ts_ld32(tmem_base + lane_addr + (buf * 2 + h) * MT + c0, v);
+          ts_ld32(tmem_base + lane_addr + buf * TS_NT + g * 32, v);
           ts_wait_ld();
-          if (whole) {
-            const int n = n_tile * TS_NT + h * 128 + tid;
+          if (tid < p.M) {
+            if (whole) {
+              ts_finish_row32(p, o, tid, n_tile * TS_NT + g * 32, v);
+            } else if (tid < MT) {
+              float4* dst = reinterpret_cast<float4*>(part + ((size_t)g * MT + tid) * 32);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ts_finish(p, c0 + j, n, lane, v[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) __stcg(part + ((size_t)h * MT + c0 + j) * 128 + tid, v[j]);
+              for (int i = 0; i < 8; ++i) __stcg(dst + i, make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]));
+            }
           }
         }
       }
@@ -373,64 +529,148 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       atomicExch(abort_flag, 1);
     }
     // ---- tiles shared with other blocks: when all parts are there, this block finishes its rows ----
+    // Part j of a tile lies in block b_first + j (slot 1 for the tile's first block, slot 0 for the
+    // others), laid out [8 groups of 32 W rows][MT tokens][32].  Of the 8 groups this block takes
+    // [g_lo, g_hi): that run of every part is one contiguous piece, which a bulk copy brings into the
+    // (now idle) stage memory, all pieces of both tiles in flight together; the sums are then formed
+    // from shared memory in k order.  Pieces that do not fit are read from global memory instead.
     asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
-#pragma unroll 1
-    for (int slot = 0; slot < 2 && ok; ++slot) {
-      const int n_tile = shared_tile[slot];
-      if (n_tile < 0) continue;
-      const int b_first = ts_block_of(p.units, blocks, n_tile * p.kchunks);
-      const int b_last = ts_block_of(p.units, blocks, (n_tile + 1) * p.kchunks - 1);
-      const int parts = b_last - b_first + 1, mine = me - b_first;
-      // part j lies in block b_first + j, slot 1 for the tile's first block, slot 0 for the others
+    constexpr unsigned CAP = STAGES * STAGE_BYTES;
+    constexpr unsigned GROUP_BYTES = MT * 32 * 4;
+    int first_of[2] = {0, 0}, parts_of[2] = {0, 0}, g_lo[2] = {0, 0}, g_hi[2] = {0, 0};
+    unsigned need[2] = {0, 0};
+    if (ok) {
       bool seen_all = true;
-      for (int j = tid; j < parts; j += TS_EPI_WARPS * 32) {
-        const int* flag = &p.flags[(b_first + j) * 2 + (j == 0 ? 1 : 0)];
-        int seen = 0;
-        for (unsigned spin = 0; spin < TS_SPIN_LIMIT && !seen; ++spin) {
-          seen = ts_ld_acquire(flag);
-          if (!seen && spin > 4096) __nanosleep(64);     // the blocks finish together: spin first
+#pragma unroll
+      for (int slot = 0; slot < 2; ++slot) {
+        const int n_tile = shared_tile[slot];
+        if (n_tile < 0) continue;
+        first_of[slot] = ts_block_of(p.units, blocks, n_tile * p.kchunks);
+        parts_of[slot] = ts_block_of(p.units, blocks, (n_tile + 1) * p.kchunks - 1) - first_of[slot] + 1;
+        const int mine = me - first_of[slot];
+        g_lo[slot] = (8 * mine) / parts_of[slot];
+        g_hi[slot] = (8 * (mine + 1)) / parts_of[slot];
+        need[slot] = (unsigned)parts_of[slot] * (unsigned)(g_hi[slot] - g_lo[slot]) * GROUP_BYTES;
+        for (int j = tid; j < parts_of[slot]; j += TS_EPI_WARPS * 32) {
+          const int* flag = &p.flags[(first_of[slot] + j) * 2 + (j == 0 ? 1 : 0)];
+          int seen = 0;
+          for (unsigned spin = 0; spin < TS_SPIN_LIMIT && !seen; ++spin) {
+            seen = ts_ld_acquire(flag);
+            if (!seen && spin > 4096) __nanosleep(64);   // the blocks finish together: spin first
+          }
+          if (!seen) seen_all = false;
         }
-        if (!seen) seen_all = false;
       }
       if (!seen_all) {
         atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
         atomicExch(abort_flag, 1);
         *reinterpret_cast<volatile int*>(epi_abort) = 1;
       }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
-      if (*reinterpret_cast<volatile int*>(epi_abort)) break;
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+    if (*reinterpret_cast<volatile int*>(epi_abort)) ok = false;
+    if (ok && (shared_tile[0] >= 0 || shared_tile[1] >= 0)) {
       __threadfence();
-      // groups of 32 rows [g_lo, g_hi) of the tile's 8 are this block's; warp q takes tokens q, q+4, ...
-      const int g_lo = (8 * mine) / parts, g_hi = (8 * (mine + 1)) / parts;
-      for (int g = g_lo; g < g_hi; ++g) {
-        const int h = g >> 2, row = (g & 3) * 32 + lane;
-        const int n = n_tile * TS_NT + g * 32 + lane;
-        for (int m = q; m < MT && m < p.M; m += TS_EPI_WARPS) {
-          float acc = 0.0f;
-          const size_t within = ((size_t)h * MT + m) * 128 + row;
-          for (int j0 = 0; j0 < parts; j0 += 8) {          // eight loads in flight, added in k order
-            float vals[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int part_index = j0 + j;
-              vals[j] = part_index < parts
-                            ? __ldcg(p.partial + ((size_t)(b_first + part_index) * 2 + (part_index == 0 ? 1 : 0)) * PART_FLOATS + within)
-                            : 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j0 + j < parts) acc += vals[j];
-          }
-          ts_finish(p, m, n, lane, acc);
+      const bool together = need[0] + need[1] <= CAP;
+      unsigned phase = 0;
+#pragma unroll 1
+      for (int round = 0; round < 2 && ok; ++round) {
+        const int s_lo = round == 0 ? 0 : (together ? 2 : 1), s_hi = round == 0 ? (together ? 2 : 1) : 2;
+        unsigned offset[2] = {0, 0}, staged = 0;
+        for (int slot = s_lo; slot < s_hi; ++slot) {
+          offset[slot] = staged;
+          if (need[slot] <= CAP - staged) staged += need[slot];
+          else offset[slot] = 0xffffffffu;               // does not fit: read from global memory
         }
+        if (staged > 0) {
+          if (tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            ts_expect_tx(fix_bar, staged);
+            for (int slot = s_lo; slot < s_hi; ++slot) {
+              if (offset[slot] == 0xffffffffu || need[slot] == 0) continue;
+              const unsigned piece = (unsigned)(g_hi[slot] - g_lo[slot]) * GROUP_BYTES;
+              for (int j = 0; j < parts_of[slot]; ++j) {
+                const float* src = p.partial + ((size_t)(first_of[slot] + j) * 2 + (j == 0 ? 1 : 0)) * PART_FLOATS +
+                                   (size_t)g_lo[slot] * MT * 32;
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                    ::"r"(ts_smem(base + offset[slot] + j * piece)), "l"(src), "r"(piece), "r"(ts_smem(fix_bar))
+                    : "memory");
+              }
+            }
+          }
+          if (!ts_wait(fix_bar, phase)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
+          phase ^= 1;
+          asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
+          if (*reinterpret_cast<volatile int*>(epi_abort)) {
+            if (tid == 0) {
+              atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+              atomicExch(abort_flag, 1);
+            }
+            ok = false;
+            break;
+          }
+        }
+        // thread = (token of a pass of 16, 4 rows of the group's 32): a warp reads 4 tokens x 128 bytes in a row
+        const int quad = tid & 7, sub = tid >> 3;
+        for (int slot = s_lo; slot < s_hi; ++slot) {
+          if (shared_tile[slot] < 0) continue;
+          const int parts = parts_of[slot];
+          const int groups = g_hi[slot] - g_lo[slot];
+          const bool in_smem = offset[slot] != 0xffffffffu;
+          const size_t part_stride = in_smem ? (size_t)groups * MT * 32 : 0;
+#pragma unroll 1
+          for (int item = 0; item < groups * (MT / 16); ++item) {
+            const int g = item / (MT / 16), m = (item % (MT / 16)) * 16 + sub;
+            if ((item % (MT / 16)) * 16 >= p.M) continue;       // the whole pass lies beyond the batch
+            const int n = shared_tile[slot] * TS_NT + (g_lo[slot] + g) * 32 + quad * 4;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (in_smem) {
+              const float4* src = reinterpret_cast<const float4*>(base + offset[slot]) + (((size_t)g * MT + m) * 32 + quad * 4) / 4;
+#pragma unroll 1
+              for (int j0 = 0; j0 < parts; j0 += 4) {      // four parts in flight together, added in k order
+                float4 vals[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  vals[j] = j0 + j < parts ? src[(size_t)(j0 + j) * part_stride / 4] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (j0 + j < parts) { acc[0] += vals[j].x; acc[1] += vals[j].y; acc[2] += vals[j].z; acc[3] += vals[j].w; }
+                }
+              }
+            } else {
+              const size_t within = ((size_t)(g_lo[slot] + g) * MT + m) * 32 + quad * 4;
+#pragma unroll 1
+              for (int j0 = 0; j0 < parts; j0 += 4) {
+                float4 vals[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int part_index = j0 + j;
+                  vals[j] = part_index < parts
+                                ? __ldcg(reinterpret_cast<const float4*>(p.partial + ((size_t)(first_of[slot] + part_index) * 2 + (part_index == 0 ? 1 : 0)) * PART_FLOATS + within))
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (j0 + j < parts) { acc[0] += vals[j].x; acc[1] += vals[j].y; acc[2] += vals[j].z; acc[3] += vals[j].w; }
+                }
+              }
+            }
+            ts_finish_quad(p, o, m, n, lane, m < p.M, acc);
+          }
+        }
+        // the pieces have been read: the memory may be filled again, the flags may go down
+        asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
       }
-      // the last block through the tile lowers its flags for the next launch
-      asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
-      if (tid == 0) {
-        int* counter = &p.flags[blocks * 2 + n_tile];
-        if (atomicAdd(counter, 1) == parts - 1) {
-          *counter = 0;
-          for (int j = 0; j < parts; ++j) p.flags[(b_first + j) * 2 + (j == 0 ? 1 : 0)] = 0;
+      // the last block through a tile lowers its flags for the next launch
+      if (ok && tid == 0) {
+        for (int slot = 0; slot < 2; ++slot) {
+          if (shared_tile[slot] < 0) continue;
+          int* counter = &p.flags[blocks * 2 + shared_tile[slot]];
+          if (atomicAdd(counter, 1) == parts_of[slot] - 1) {
+            *counter = 0;
+            for (int j = 0; j < parts_of[slot]; ++j) p.flags[(first_of[slot] + j) * 2 + (j == 0 ? 1 : 0)] = 0;
+          }
         }
       }
     }
@@ -443,20 +683,25 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       for (int i = nt * 16; i < w_bytes; i += TS_NORM_WARPS * 32 * 16)
         *reinterpret_cast<uint4*>(norm_w + i) = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.norm_weight) + i);
       kvb_grid_wait();
-      // 1 / rms of every token row from the pieces of its sum of squares, added in their order
-      for (int m = nt; m < MT; m += TS_NORM_WARPS * 32) {
-        float sum = 0.0f;
-        if (m < p.M) {
-          const float* pieces = p.sumsq_in + (size_t)m * p.sumsq_pieces;
-          for (int t0 = 0; t0 < p.sumsq_pieces; t0 += 8) {
-            float vals[8];
+      // 1 / rms of this warp's MT / 4 token rows from the pieces of their sums of squares: every lane
+      // adds its pieces in order, the lanes are added by a butterfly, so the value depends on the
+      // pieces alone; the rows' loads go out together
+      {
+        constexpr int TW = MT / TS_NORM_WARPS;
+        const int first = (warp - 2 - TS_EPI_WARPS) * TW;
+        float part[TW];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) vals[j] = t0 + j < p.sumsq_pieces ? __ldcg(pieces + t0 + j) : 0.0f;
+        for (int i = 0; i < TW; ++i) part[i] = 0.0f;
+        for (int t = lane; t < p.sumsq_pieces; t += 32) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sum += vals[j];
-          }
+          for (int i = 0; i < TW; ++i)
+            if (first + i < p.M) part[i] += __ldcg(p.sumsq_in + (size_t)(first + i) * p.sumsq_pieces + t);
         }
-        inv_rms[m] = 1.0f / sqrtf(sum / (float)p.K + p.eps);
+#pragma unroll
+        for (int i = 0; i < TW; ++i) {
+          const float sum = warp_sum(part[i]);
+          if (lane == 0) inv_rms[first + i] = 1.0f / sqrtf(sum / (float)p.K + p.eps);
+        }
       }
       asm volatile("bar.sync 2, %0;\n" ::"n"(TS_NORM_WARPS * 32));
       const int chunk = nt & 7, row0 = nt >> 3;            // 16 bytes of a row; rows row0, row0 + 16, ...
@@ -473,7 +718,7 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         }
         if (*reinterpret_cast<volatile int*>(abort_flag)) break;
         const int k = ((u_begin + it) % p.kchunks) * TS_KS + chunk * 8;   // this thread's 8 k-values of the stage
-        unsigned char* xs = base + stage * STAGE_BYTES + TS_W_BYTES;
+        unsigned char* xs = base + stage * STAGE_BYTES;
         float g[8];
         if (p.norm_weight_f32) {
           const float4 lo = *reinterpret_cast<const float4*>(norm_w + (size_t)k * 4);
@@ -592,7 +837,7 @@ extern "C" int kvb_gemm_stream_tc5_bf16(void* out, int out_f32, long long ldo, c
   KVB_REQUIRE(M > 0 && M <= 128, "stream gemm (tcgen05): takes 1 to 128 rows of x");
   KVB_REQUIRE(K > 0 && K % 64 == 0 && ldx % 8 == 0,
               "stream gemm (tcgen05): K must be a multiple of 64 and the row stride of x of 8");
-  KVB_REQUIRE(aligned16(x) && aligned16(w), "stream gemm (tcgen05): x and w must be 16-byte aligned");
+  KVB_REQUIRE(aligned16(x) && aligned16(w) && aligned16(bias), "stream gemm (tcgen05): x, w and bias must be 16-byte aligned");
   KVB_REQUIRE(scratch != nullptr && flags != nullptr && sms > 0, "stream gemm (tcgen05): needs scratch and flags");
   KVB_REQUIRE(!silu_pairs || (N % 16 == 0 && !out_f32),
               "stream gemm (tcgen05): gated pairs need N a multiple of 16 and a bf16 result");

@@ -104,11 +104,12 @@ def require_device(device: torch.device | str) -> None:
 launch_count = 0  # kernels of this library launched so far (read by the benchmark)
 
 
-def _call(name: str, *args: Any) -> None:
+def _call(name: str, *args: Any, kernels: int = 1) -> None:
+    """Run entry point ``name``, which launches ``kernels`` kernels."""
     global launch_count
     if _lib is None:
         ensure_built()
-    launch_count += 1
+    launch_count += kernels
     code = getattr(_lib, name)(*args)
     if code != 0:
         raise KernelError(f"{name}: {_lib.kvb_last_error().decode()}")
@@ -421,7 +422,8 @@ def paged_attention(
                   num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
                   splits, None if scratch is None else scratch.data_ptr(),
                   None if cos_sin is None else cos_sin.data_ptr(),
-                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None, _stream())
+                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None, _stream(),
+                  kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
             return out
         if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
                 and out.stride(0) % 8 == 0):
@@ -443,7 +445,7 @@ def paged_attention(
               k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
               ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
               num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-              splits, None if scratch is None else scratch.data_ptr(), _stream())
+              splits, None if scratch is None else scratch.data_ptr(), _stream(), kernels=2 if splits > 1 else 1)
         return out
     _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
@@ -459,11 +461,14 @@ _mm_out_dtype_ok: bool | None = None
 # KVCORE_B200_STREAM_ROWS overrides the bound (0: never).
 STREAM_MAX_ROWS = 16
 STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
-# Above that and up to STREAM_TC5_AUTO_ROWS tokens the same layers go to the streaming kernel whose
-# product runs on tcgen05 (tokens as the narrow operand); KVCORE_B200_STREAM_TC5_ROWS overrides
-# the bound (0: never), the kernel itself takes up to STREAM_TC5_MAX_ROWS.
+# A second streaming kernel takes up to STREAM_TC5_MAX_ROWS tokens with its product on tcgen05
+# (tokens as accumulator lanes, the same fused epilogues).  It is correct but not the default:
+# measured on B200 at Llama 3.1 8B shapes and 64 tokens it needs 62 us for the gate/up product
+# against 43 us of the library product (the fix-up of tiles shared between blocks moves 64 KB
+# parts and costs ~15 us a launch), so batches above STREAM_AUTO_ROWS go to the library unless
+# KVCORE_B200_STREAM_TC5_ROWS raises the bound.
 STREAM_TC5_MAX_ROWS = 128
-STREAM_TC5_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_TC5_ROWS", "64"))
+STREAM_TC5_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_TC5_ROWS", "0"))
 _stream_scratch: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor]] = {}
 
 
