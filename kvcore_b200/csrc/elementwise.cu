@@ -171,7 +171,12 @@ extern "C" int kvb_rmsnorm(void* out, void* residual, const void* h, const void*
 // group > 0: gate and up alternate in runs of `group` columns (gate 0..g-1, up 0..g-1, gate g..2g-1, ...),
 // the layout a feed-forward keeps when its gate/up matrix is packed for the fused decode kernel.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+template <typename T>
+__device__ __forceinline__ float silu(float x);
+template <>
+__device__ __forceinline__ float silu<float>(float x) { return x / (1.0f + expf(-x)); }
+template <>
+__device__ __forceinline__ float silu<bf16>(float x) { return kvb_silu_for_bf16(x); }
 
 template <typename T, bool VEC>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int group,
@@ -179,11 +184,21 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   KVB_KERNEL_PROLOGUE(KVB_TAG_SILU_MUL);
   constexpr int N = VEC ? Vec16<T>::N : 1;
   const int per_row = inter / N;
-  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vecs;
-       v += (long long)gridDim.x * blockDim.x) {
-    const long long row = v / per_row;
-    const int col = (int)(v % per_row) * N;
-    const T* g = gu + row * 2 * inter + (group > 0 ? (col / group) * 2 * group + col % group : col);
+  // (row, vector of the row) of this thread's items, stepped without a division per item
+  const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  long long row = first / per_row;
+  int vec = (int)(first % per_row);
+  const long long row_step = step / per_row;
+  const int vec_step = (int)(step % per_row);
+  const bool pow2 = group > 0 && (group & (group - 1)) == 0;   // runs of a power of two: shifts
+  const int shift = pow2 ? __ffs(group) - 1 : 0;
+  for (long long v = first; v < total_vecs; v += step) {
+    const int col = vec * N;
+    const int gate_col = group == 0 ? col
+                         : pow2 ? ((col >> shift) << (shift + 1)) + (col & (group - 1))
+                                : (col / group) * 2 * group + col % group;
+    const T* g = gu + row * 2 * inter + gate_col;
     const int up = group > 0 ? group : inter;
     T* o = out + row * inter + col;
     if (VEC) {
@@ -193,13 +208,19 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
 #pragma unroll
       for (int j = 0; j < Vec16<T>::N; ++j) {
         // the product is formed from the rounded activation, as silu(gate) * up in T would be
-        const float s = to_float(from_float<T>(silu(a.get(j))));
+        const float s = to_float(from_float<T>(silu<T>(a.get(j))));
         r.set(j, s * b.get(j));
       }
       r.store(o);
     } else {
-      const float s = to_float(from_float<T>(silu(to_float(g[0]))));
+      const float s = to_float(from_float<T>(silu<T>(to_float(g[0]))));
       o[0] = from_float<T>(s * to_float(g[up]));
+    }
+    row += row_step;
+    vec += vec_step;
+    if (vec >= per_row) {
+      vec -= per_row;
+      ++row;
     }
   }
 }

@@ -458,7 +458,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                   if (p.bias && n + 8 < p.N) { g += __bfloat162float(p.bias[n]); u += __bfloat162float(p.bias[n + 8]); }
                   g = __bfloat162float(__float2bfloat16_rn(g));
                   u = __bfloat162float(__float2bfloat16_rn(u));
-                  const float act = __bfloat162float(__float2bfloat16_rn(g / (1.0f + expf(-g))));
+                  const float act = __bfloat162float(__float2bfloat16_rn(kvb_silu_for_bf16(g)));
                   reinterpret_cast<bf16*>(out_tile)[m * (GS_NT / 2) + col] = __float2bfloat16_rn(act * u);
                 }
               }

@@ -159,7 +159,7 @@ __device__ __forceinline__ unsigned ts_pack2(float lo, float hi) {
 __device__ __forceinline__ float ts_silu_mul(float gate, float up) {
   // rounded as the unfused path rounds: the products to bf16, the activation to bf16, the result
   const float g = ts_round_bf16(gate), u = ts_round_bf16(up);
-  const float act = ts_round_bf16(g / (1.0f + expf(-g)));
+  const float act = ts_round_bf16(kvb_silu_for_bf16(g));
   return act * u;
 }
 
