@@ -329,6 +329,8 @@ def test_flash_split_policy():
     assert K().decode_splits_tma(64, 8, 8192) == 1
     assert K().decode_splits_tma(1, 8, 8192) == 16
     assert K().decode_splits_tma(4, 8, 100) == 1
+    assert K().decode_splits_tma(1, 8, 1024) == 8     # two tiles a split
+    assert K().decode_splits_tma(8, 8, 1024) == 4
     assert K().tma_decode_supported(torch.bfloat16, 128, 16)
     assert not K().tma_decode_supported(torch.bfloat16, 96, 16)
     assert not K().tma_decode_supported(torch.float32, 128, 16)
