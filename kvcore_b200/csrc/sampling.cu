@@ -93,8 +93,33 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const dou
   const ArgMax none = {-INFINITY, 0x7fffffff};
 
   if (temperature < eps) {
+    // greedy: one pass; 16-byte loads, four of them in flight per thread (the row is read by one
+    // block, so the pass is bound by the latency of its loads)
     ArgMax best = none;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) best = better(best, ArgMax{lg[i], i});
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+      const int quads = V / 4;
+      const float4* lg4 = reinterpret_cast<const float4*>(lg);
+      for (int i0 = tid; i0 < quads; i0 += 4 * SAMPLE_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * SAMPLE_THREADS;
+          v[u] = i < quads ? lg4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (i0 + u * SAMPLE_THREADS >= quads) break;
+          const int i = 4 * (i0 + u * SAMPLE_THREADS);
+          best = better(best, ArgMax{v[u].x, i});
+          best = better(best, ArgMax{v[u].y, i + 1});
+          best = better(best, ArgMax{v[u].z, i + 2});
+          best = better(best, ArgMax{v[u].w, i + 3});
+        }
+      }
+      done = quads * 4;
+    }
+    for (int i = done + tid; i < V; i += SAMPLE_THREADS) best = better(best, ArgMax{lg[i], i});
     best = block_argmax(best, ascratch);
     if (tid == 0) out[row] = best.index;
     return;
