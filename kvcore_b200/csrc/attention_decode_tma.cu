@@ -511,18 +511,10 @@ __global__ void flash_decode_combine_kernel(const DecodeParams p) {
   const int r = i / D, d = i % D;
   if (r >= rows_total) return;
   const size_t base = ((size_t)req * p.KVH + kvh) * p.num_splits;
-  // Loads go out eight splits at a time (the loop would otherwise wait for each in turn); the
-  // splits are still added in their own order.
-  float m = -INFINITY;
-  for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
-    float ms[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      ms[j] = s0 + j < p.num_splits ? p.partial_ml[((base + s0 + j) * 16 + r) * 2] : -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
-  }
-  float total = 0.0f, acc = 0.0f;
+  // One trip to memory per eight splits: their maxima, sums and outputs are asked for together and
+  // merged into the running triple (m, total, acc), rescaled when a later batch raises the maximum.
+  // The splits are still added in their own order.
+  float m = -INFINITY, total = 0.0f, acc = 0.0f;
   for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
     float ms[8], ls[8], os[8];
 #pragma unroll
@@ -533,6 +525,15 @@ __global__ void flash_decode_combine_kernel(const DecodeParams p) {
       ms[j] = ml.x;
       ls[j] = ml.y;
       os[j] = live ? p.partial_o[((base + s0 + j) * 16 + r) * D + d] : 0.0f;
+    }
+    float batch_max = m;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) batch_max = fmaxf(batch_max, ms[j]);
+    if (batch_max > m) {
+      const float keep = (m == -INFINITY) ? 0.0f : exp2f(m - batch_max);
+      total *= keep;
+      acc *= keep;
+      m = batch_max;
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
