@@ -317,14 +317,33 @@ def tma_decode_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> b
 
 
 def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """Splits for the TMA decode kernel, which keeps two blocks per SM: as many as still fit one
-    wave of blocks, at most 16 (the merge grows with them) and at least two 64-key tiles a split
-    (measured inside whole steps on B200: batch 1 at 1,024 tokens gains 3.6 % with 8 splits over 2,
-    loses with 16; at 8,192 tokens 16 beat 24, 32 and 37)."""
+    """Splits for the TMA decode kernel, which keeps two blocks per SM (measured inside whole steps
+    on B200).
+
+    Up to half a wave of (request, kv head) pairs: as many splits as still fit one wave of blocks,
+    at most 16 (the merge grows with them) and at least two 64-key tiles a split (batch 1 at 1,024
+    tokens gains 3.6 % with 8 splits over 2, loses with 16; at 8,192 tokens 16 beat 24, 32 and 37).
+
+    More pairs than that: the kernel is bound by memory as long as the last wave is not sparse
+    (64 requests x 8 heads = 1.73 waves run at 0.97 of the copy bandwidth unsplit, and 4 splits
+    are 1.3 % slower), but a last wave of a few blocks runs no faster than ~0.45 of a full one
+    (48 requests at 8,192 tokens: 3 splits -11 % a step; 40 at 4,096: 4 splits -9 %).  So the
+    cost of 1 to 4 splits is estimated as full waves + max(rest, 0.45), half a percent a split for
+    the merge, and the cheapest is taken."""
     base = max(1, num_reqs * num_kv_heads)
     tiles = max(1, -(-max_seq_len // 64))
     wave = SM_COUNT * TMA_DECODE_BLOCKS_PER_SM
-    return max(1, min(wave // base, tiles // 2, 16))
+    if base * 2 <= wave:
+        return max(1, min(wave // base, tiles // 2, 16))
+    best, best_cost = 1, float("inf")
+    for splits in (1, 2, 3, 4):
+        if splits > 1 and tiles // splits < 4:
+            break
+        full, rest = divmod(base * splits, wave)
+        cost = (full + (max(rest / wave, 0.45) if rest else 0.0)) / splits * (1.0 + 0.005 * (splits - 1))
+        if cost < best_cost - 1e-9:
+            best, best_cost = splits, cost
+    return best
 
 
 TMA_DECODE_BLOCKS_PER_SM = 2

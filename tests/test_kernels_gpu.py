@@ -331,6 +331,9 @@ def test_flash_split_policy():
     assert K().decode_splits_tma(4, 8, 100) == 1
     assert K().decode_splits_tma(1, 8, 1024) == 8     # two tiles a split
     assert K().decode_splits_tma(8, 8, 1024) == 4
+    assert K().decode_splits_tma(48, 8, 8192) == 2    # 1.3 waves unsplit: a sparse last wave
+    assert K().decode_splits_tma(40, 8, 4096) == 4
+    assert K().decode_splits_tma(37, 8, 8192) == 1    # exactly one wave
     assert K().tma_decode_supported(torch.bfloat16, 128, 16)
     assert not K().tma_decode_supported(torch.bfloat16, 96, 16)
     assert not K().tma_decode_supported(torch.float32, 128, 16)
