@@ -182,6 +182,7 @@ class StepFunction:
         self._host_meta = [torch.zeros(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._host_events: list[torch.cuda.Event | None] = [None, None]
         self._turn = 0
+        self._row_numbers = np.arange(self.max_num_seqs, dtype=np.int32)
         self.last_context: StepContext | None = None
         self.num_steps = 0
         # decode-only steps of one shape (requests, wanted rows, table width) replay a CUDA graph
@@ -261,24 +262,41 @@ class StepFunction:
         host[off_slots : off_slots + num_reqs] = slots
         cursor = 0
         logit_rows: list[int] = []
-        for row, (entry, n, context) in enumerate(zip(entries, query_lens, context_lens)):
-            ids = np.asarray(entry.token_ids, dtype=np.int64)
+        if num_tokens == num_reqs:
+            # one token a request (a decode step): the per-token arrays are the per-request ones
+            ids = np.fromiter((entry.token_ids[0] for entry in entries), dtype=np.int64, count=num_reqs)
             if ids.min() < 0 or ids.max() >= self.vocab_size:
-                raise ValueError(
-                    f"request {entry.request_id!r} has a token id outside [0, {self.vocab_size})"
-                )
-            host[off_tokens + cursor : off_tokens + cursor + n] = ids
-            host[off_positions + cursor : off_positions + cursor + n] = np.arange(
-                context, context + n, dtype=np.int32
-            )
-            host[off_req_index + cursor : off_req_index + cursor + n] = row
-            for place in entry.want:
-                if not 0 <= place < n:
+                bad = entries[int(np.argmax((ids < 0) | (ids >= self.vocab_size)))]
+                raise ValueError(f"request {bad.request_id!r} has a token id outside [0, {self.vocab_size})")
+            host[off_tokens : off_tokens + num_reqs] = ids
+            host[off_positions : off_positions + num_reqs] = context_lens
+            host[off_req_index : off_req_index + num_reqs] = self._row_numbers[:num_reqs]
+            for row, entry in enumerate(entries):
+                for place in entry.want:
+                    if place != 0:
+                        raise ValueError(
+                            f"request {entry.request_id!r} wants logits at place {place} of 1 tokens"
+                        )
+                    logit_rows.append(row)
+        else:
+            for row, (entry, n, context) in enumerate(zip(entries, query_lens, context_lens)):
+                ids = np.asarray(entry.token_ids, dtype=np.int64)
+                if ids.min() < 0 or ids.max() >= self.vocab_size:
                     raise ValueError(
-                        f"request {entry.request_id!r} wants logits at place {place} of {n} tokens"
+                        f"request {entry.request_id!r} has a token id outside [0, {self.vocab_size})"
                     )
-                logit_rows.append(cursor + int(place))
-            cursor += n
+                host[off_tokens + cursor : off_tokens + cursor + n] = ids
+                host[off_positions + cursor : off_positions + cursor + n] = np.arange(
+                    context, context + n, dtype=np.int32
+                )
+                host[off_req_index + cursor : off_req_index + cursor + n] = row
+                for place in entry.want:
+                    if not 0 <= place < n:
+                        raise ValueError(
+                            f"request {entry.request_id!r} wants logits at place {place} of {n} tokens"
+                        )
+                    logit_rows.append(cursor + int(place))
+                cursor += n
         if logit_rows:
             host[off_logits : off_logits + num_logits] = logit_rows
         slot_index = np.asarray(slots, dtype=np.int64)

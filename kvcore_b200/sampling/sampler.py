@@ -53,15 +53,20 @@ class Sampler:
             raise ValueError("one SamplingParams, seed and token index per logits row is needed")
         if logits.dtype != torch.float32:
             logits = logits.float()
-        packed = torch.empty((rows, 6), dtype=torch.float64)
-        for row, (p, seed, index) in enumerate(zip(params, seeds, token_indices)):
-            top_k = vocab if p.top_k is None else min(p.top_k, vocab)
-            packed[row, 0] = p.temperature
-            packed[row, 1] = top_k
-            packed[row, 2] = p.top_p
-            packed[row, 3] = float(int(seed) & 0xFFFFFFFF)
-            packed[row, 4] = float((int(seed) >> 32) & 0xFFFFFFFF)
-            packed[row, 5] = index
+        packed = torch.tensor(
+            [
+                (
+                    p.temperature,
+                    vocab if p.top_k is None else min(p.top_k, vocab),
+                    p.top_p,
+                    float(int(seed) & 0xFFFFFFFF),
+                    float((int(seed) >> 32) & 0xFFFFFFFF),
+                    index,
+                )
+                for p, seed, index in zip(params, seeds, token_indices)
+            ],
+            dtype=torch.float64,
+        )
         return K.sample(logits, packed, SAMPLING_EPS)
 
 
