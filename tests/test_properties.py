@@ -1,0 +1,150 @@
+"""Property tests (hypothesis): whatever the order of operations, the cache manager accounts for
+every page and slot; however a request's tokens are cut into steps and mixed with another
+request's, the logits at a position are those of the whole sequence.  The cutting property runs on
+the host with the plain stand-ins of the kernels (``-m "not gpu"``) and on the GPU with the real
+ones (``-m gpu``)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+import plain_kernels
+import plain_llama
+import replay_cases as rc
+from kvcore_b200.cache import CacheGroupSpec, KVManager
+
+
+# ---- cache manager ---------------------------------------------------------------------------
+OPERATIONS = st.lists(
+    st.tuples(st.sampled_from(["start", "grow", "end"]), st.integers(0, 7), st.integers(1, 23)),
+    min_size=1, max_size=120,
+)
+
+
+@settings(max_examples=60, deadline=None)
+@given(ops=OPERATIONS, windows=st.sampled_from([(None,), (None, 7), (5, None, 9)]),
+       num_pages=st.integers(6, 30), page_size=st.sampled_from([2, 4, 8]))
+def test_cache_manager_accounts_for_every_page(ops, windows, num_pages, page_size):
+    groups = [CacheGroupSpec(i, (i,), 2, 16, w) for i, w in enumerate(windows)]
+    kv = KVManager(groups, num_pages=num_pages, page_size=page_size, max_num_seqs=4, max_model_len=64)
+    live: dict[str, int] = {}
+    for action, which, amount in ops:
+        rid = f"r{which}"
+        if action == "start" and rid not in live:
+            before = kv.num_free_pages()
+            if len(live) < 4 and kv.allocate_slots(rid, amount):
+                kv.advance(rid, amount)
+                live[rid] = amount
+            else:
+                assert kv.num_free_pages() == before and not kv.has_request(rid)
+        elif action == "grow" and rid in live:
+            before = kv.num_free_pages()
+            if live[rid] + amount <= 64 and kv.allocate_slots(rid, amount):
+                kv.advance(rid, amount)
+                live[rid] += amount
+            else:
+                assert kv.num_free_pages() == before      # a refused allocation changes nothing
+        elif action == "end" and rid in live:
+            kv.free(rid)
+            del live[rid]
+        kv.check_invariants()
+        assert sorted(kv.live_requests()) == sorted(live)
+        for request, tokens in live.items():
+            assert kv.num_computed(request) == tokens
+            for group, window in enumerate(windows):
+                held = sum(1 for page in kv.block_ids(request)[group] if page)
+                needed = -(-tokens // page_size)
+                assert held <= needed
+                if window is None:
+                    assert held == needed                  # a full group keeps every page
+        slots = [kv.state_slot(request) for request in live]
+        assert len(set(slots)) == len(slots)
+    for request in list(live):
+        kv.free(request)
+    kv.check_invariants()
+    assert kv.num_free_pages() == [num_pages - 1] * len(windows) and kv.slots.num_free == 4
+    assert not any(np.any(table) for table in kv.tables)
+
+
+# ---- cuttings --------------------------------------------------------------------------------
+LENGTHS = {"a": 37, "b": 22}
+
+
+def _model(tmp_path_factory, name):
+    config = rc.TINY_CONFIGS[name]
+    folder = tmp_path_factory.mktemp(f"prop_{name}")
+    rc.write_model(folder, config, rc.TINY_SEEDS[name], "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    requests = {rid: rc.random_tokens(config["vocab_size"], n, 40 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+    reference = {rid: plain_llama.forward_logits(config, weights, tokens).numpy() for rid, tokens in requests.items()}
+    return dict(config=config, folder=folder, requests=requests, reference=reference)
+
+
+@pytest.fixture(scope="module")
+def model_a(tmp_path_factory):
+    return _model(tmp_path_factory, "A")
+
+
+@pytest.fixture(scope="module")
+def model_b(tmp_path_factory):
+    return _model(tmp_path_factory, "B")
+
+
+def _trace(requests, sizes_a, sizes_b, order):
+    """Steps from two lists of portion sizes (cycled until the tokens run out); ``order`` decides
+    step by step whether a, b or both bring their next portion."""
+    portions = {"a": rc.cut(requests["a"], sizes_a), "b": rc.cut(requests["b"], sizes_b)}
+    cursor = {"a": 0, "b": 0}
+    steps, turn = [], 0
+    while any(cursor[r] < len(portions[r]) for r in portions):
+        choice = order[turn % len(order)]
+        turn += 1
+        chosen = [r for r in ("a", "b") if r in choice and cursor[r] < len(portions[r])]
+        if not chosen:
+            chosen = [r for r in ("a", "b") if cursor[r] < len(portions[r])][:1]
+        entries, ended = [], []
+        for rid in chosen:
+            portion = portions[rid][cursor[rid]]
+            cursor[rid] += 1
+            entries.append({"id": rid, "tokens": portion, "want": list(range(len(portion)))})
+            if cursor[rid] == len(portions[rid]):
+                ended.append(rid)
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+def _check_cutting(case, steps, out_dir, dtype, device, tolerance):
+    vocab = case["config"]["vocab_size"]
+    rc.run_inprocess(case["folder"], dtype, steps, out_dir, rc.peak_tokens(steps), device=device)
+    rows = rc.collect(steps, out_dir, vocab)
+    assert len(rows) == sum(LENGTHS.values())
+    for (rid, position), row in rows.items():
+        reference = case["reference"][rid]
+        error = np.abs(row - reference[position]).max() / np.abs(reference).max()
+        assert error <= tolerance, f"{rid}: position {position} is off by {error:.3e}"
+
+
+SIZES = st.lists(st.integers(1, 12), min_size=1, max_size=6)
+ORDER = st.lists(st.sampled_from(["a", "b", "ab"]), min_size=1, max_size=5)
+
+
+@settings(max_examples=12, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(sizes_a=SIZES, sizes_b=SIZES, order=ORDER)
+def test_any_cutting_gives_the_logits_of_the_whole_sequence_on_the_host(model_a, tmp_path_factory, monkeypatch,
+                                                                        sizes_a, sizes_b, order):
+    plain_kernels.install(monkeypatch)
+    steps = _trace(model_a["requests"], sizes_a, sizes_b, order)
+    _check_cutting(model_a, steps, tmp_path_factory.mktemp("cut"), "float32", "cpu", 2e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 2e-5), ("bfloat16", 2e-2)])
+def test_any_cutting_gives_the_logits_of_the_whole_sequence(model_b, tmp_path_factory, dtype, tolerance):
+    @settings(max_examples=10, deadline=None)
+    @given(sizes_a=SIZES, sizes_b=SIZES, order=ORDER)
+    def run(sizes_a, sizes_b, order):
+        steps = _trace(model_b["requests"], sizes_a, sizes_b, order)
+        _check_cutting(model_b, steps, tmp_path_factory.mktemp("cut"), dtype, "cuda:0", tolerance)
+
+    run()
