@@ -148,3 +148,64 @@ def test_any_cutting_gives_the_logits_of_the_whole_sequence(model_b, tmp_path_fa
         _check_cutting(model_b, steps, tmp_path_factory.mktemp("cut"), dtype, "cuda:0", tolerance)
 
     run()
+
+
+# ---- scheduler -------------------------------------------------------------------------------
+@settings(max_examples=60, deadline=None)
+@given(
+    arrivals=st.lists(st.tuples(st.integers(0, 6), st.integers(1, 30), st.integers(1, 9)), min_size=1, max_size=10),
+    num_pages=st.integers(10, 40), budget=st.integers(2, 24), max_seqs=st.integers(1, 5),
+    partial=st.integers(1, 3), prefix=st.booleans(),
+)
+def test_scheduler_finishes_every_request_within_its_limits(arrivals, num_pages, budget, max_seqs, partial, prefix):
+    """Requests of random lengths arriving at random steps, with few pages: every step stays inside
+    the token and request limits, a request's tokens are scheduled in order and once, every request
+    ends with exactly max_tokens outputs (pre-emption on deadlock), and all pages come back."""
+    from kvcore_b200.config import SchedulerConfig
+    from kvcore_b200.engine.request import Request
+    from kvcore_b200.engine.scheduler import Scheduler
+    from kvcore_b200.sampling import SamplingParams
+
+    page_size, max_model_len = 4, 40
+    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=num_pages, page_size=page_size,
+                   max_num_seqs=max_seqs, max_model_len=max_model_len, enable_prefix_caching=prefix)
+    sched = Scheduler(SchedulerConfig(max_num_seqs=max_seqs, max_num_scheduled_tokens=budget,
+                                      max_num_partial_prefills=partial, max_long_partial_prefills=partial), kv)
+    todo = sorted(
+        (when, f"r{i}", n, out) for i, (when, n, out) in enumerate(arrivals)
+        # a request must fit the model length and, alone, the cache
+        if n + out <= max_model_len and -(-(n + out) // page_size) <= num_pages - 1
+    )
+    expected = {rid: out for _, rid, _, out in todo}
+    outputs: dict[str, int] = {}
+    finished: set[str] = set()
+    step = 0
+    while todo or sched.has_unfinished_requests():
+        while todo and todo[0][0] <= step:
+            _, rid, n, out = todo.pop(0)
+            sched.add_request(Request(rid, [1 + (j * 7 + len(rid)) % 5 for j in range(n)],
+                                      SamplingParams(max_tokens=out, temperature=0.0)))
+        plan = sched.schedule()
+        assert plan.total_num_scheduled_tokens <= budget
+        assert len(plan.num_scheduled_tokens) <= max_seqs
+        assert plan.total_num_scheduled_tokens == sum(plan.num_scheduled_tokens.values())
+        sampled = {}
+        for rid, n in plan.num_scheduled_tokens.items():
+            assert n >= 1 and rid not in finished
+            assert not any(kv.pages_needed(rid, n))        # its pages are there before the step
+            kv.advance(rid, n)
+            sampled[rid] = 3
+        update = sched.update_from_outputs(plan, sampled, stop_token_ids=None)
+        for out in update.step_outputs:
+            if out.sampled_token_id is not None:
+                outputs[out.request_id] = outputs.get(out.request_id, 0) + 1
+        for done in update.finished_requests:
+            finished.add(done.request_id)
+            assert len(done.output_token_ids) == expected[done.request_id]
+        kv.check_invariants()
+        step += 1
+        assert step < 2000, "the scheduler makes no progress"
+    assert finished == set(expected)
+    sched.schedule()                                       # reports the last finished ids
+    assert not kv.live_requests()
+    kv.check_invariants()
