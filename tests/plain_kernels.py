@@ -7,7 +7,6 @@ on a machine without a GPU.  The product never imports this file.
 """
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch

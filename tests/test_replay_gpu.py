@@ -8,7 +8,6 @@ from __future__ import annotations
 
 import numpy as np
 import pytest
-import torch
 
 import plain_llama
 import replay_cases as rc
