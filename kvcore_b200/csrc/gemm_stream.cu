@@ -17,7 +17,9 @@
 //    N and K are.  A range that starts inside a tile is a "part": the block adds it up and leaves
 //    it in scratch; the block that holds the tile's first stage (the owner) adds the parts in k
 //    order, adds the bias and stores.  Each block writes at most one part (the first thing it
-//    does) and waits only for blocks that run beside it, with a bounded spin.
+//    does) and waits only for blocks that run beside it, with a bounded spin.  There is no flag:
+//    scratch holds a marker (a NaN that no sum can be) between launches, the owner reads the
+//    values of a part until none is the marker, and puts the marker back.
 //  * Programmatic dependent launch: weights are written by no kernel of a step, so the whole ring
 //    of weight boxes is asked for before waiting for the kernel in front (whose output x is):
 //    when this kernel follows another in a stream, its blocks fill their rings while the other's
@@ -42,14 +44,14 @@
 #define GS_SPIN_LIMIT (1u << 22)
 #define GS_NORM_W_BYTES (16 * 1024)   // norm weights a NORMED kernel keeps in shared memory
 #define GS_NORMALISERS 4               // NORMED: warps that normalise the token rows of each stage
+#define GS_SCRATCH_MARKER 0x7FC0DEADu  // every word of scratch between launches: a NaN no sum can be (sums that are NaN are 0x7FFFFFFF)
 
 struct StreamParams {
   void* out; int out_f32; long long ldo;
   const bf16* bias;
   int M, N, K;
   int n_tiles, kchunks, units;       // kchunks = ceil(K / 256); units = n_tiles * kchunks
-  float* partial;                    // [blocks][MBLK * 4][128]
-  int* flags;                        // [blocks], zero between launches
+  float* partial;                    // [blocks][MBLK * 4][128]; GS_SCRATCH_MARKER everywhere between launches
   int* status;
   // NORMED kernels: the rows of x are sums s that still need their RMS norm.  Every token's sum
   // of squares arrives in pieces, sumsq_in[m * sumsq_pieces + t] (added in a fixed order); a warp
@@ -366,9 +368,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 #pragma unroll
             for (int e = 0; e < 4; ++e) __stcg(dst + (j * 4 + e) * 128, acc[0][j][e]);
           }
-          __threadfence();
-          asm volatile("bar.sync 2, 128;\n");
-          if (tid == 0) gs_st_release(&p.flags[me], 1);
+          // no fence and no flag: between launches every word of scratch holds a marker (a NaN that
+          // no sum can be), and the owner reads each value until it is there
         } else {
           // ---- the owner: add the parts of the blocks behind (in k order), then store ----
           // (residual epilogue: this thread's 8 columns of the residual are asked for now, so that
@@ -379,52 +380,62 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           if (res_mine) res_early.load(p.residual + (size_t)res_m * p.N + res_col);
           bool complete = true;
           if (seg_end < tile_end) {
-            // the blocks behind that hold stages of this tile: all their flags are awaited at once
-            // (one thread each), then all their sums are fetched together and added in k order
+            // the blocks behind that hold stages of this tile: their sums are fetched together, every
+            // thread reading its own values until none is the marker any more (one trip to L2 when the
+            // parts are there, as they are whenever those blocks did them first), then added in k order;
+            // the marker goes back in for the next launch
             int parts = 0;
             while (me + 1 + parts < blocks && gs_range_start(p.units, blocks, me + 1 + parts) < tile_end) ++parts;
-            for (int c0 = 0; c0 < parts && complete; c0 += 4) {
+            for (int c0 = 0; c0 < parts; c0 += 4) {
               const int batch = parts - c0 < 4 ? parts - c0 : 4;
-              if (tid < batch) {
-                const int* flag = &p.flags[me + 1 + c0 + tid];
-                int seen = 0;
-                for (unsigned spin = 0; spin < GS_SPIN_LIMIT && !seen; ++spin) {
-                  seen = gs_ld_acquire(flag);
-                  if (!seen && spin > 4096) __nanosleep(64);   // the blocks finish together: spin first
-                }
-                if (!seen) {
-                  atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
-                  atomicExch(&flags[0], 1);
-                }
-              }
-              asm volatile("bar.sync 2, 128;\n");
-              if (*reinterpret_cast<volatile int*>(&flags[0])) { complete = false; break; }
-              __threadfence();
               float part[4][MBLK][4];
+              bool there = false;
+              for (unsigned spin = 0; spin < GS_SPIN_LIMIT && !there; ++spin) {
+                if (spin > 256) __nanosleep(64);               // the blocks finish together: spin first
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                if (c < batch) {
-                  const float* src = p.partial + (size_t)(me + 1 + c0 + c) * (MBLK * 4 * 128) + tid;
+                for (int c = 0; c < 4; ++c) {
+                  if (c < batch) {
+                    const float* src = p.partial + (size_t)(me + 1 + c0 + c) * (MBLK * 4 * 128) + tid;
 #pragma unroll
-                  for (int j = 0; j < MBLK; ++j) {
+                    for (int j = 0; j < MBLK; ++j) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) part[c][j][e] = __ldcg(src + (j * 4 + e) * 128);
+                      for (int e = 0; e < 4; ++e) part[c][j][e] = __ldcg(src + (j * 4 + e) * 128);
+                    }
                   }
                 }
+                there = true;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  if (c < batch) {
+#pragma unroll
+                    for (int j = 0; j < MBLK; ++j) {
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) there = there && __float_as_uint(part[c][j][e]) != GS_SCRATCH_MARKER;
+                    }
+                  }
+                }
+              }
+              if (!there) {
+                atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+                atomicExch(&flags[0], 1);
               }
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 if (c < batch) {
+                  float* src = p.partial + (size_t)(me + 1 + c0 + c) * (MBLK * 4 * 128) + tid;
 #pragma unroll
                   for (int j = 0; j < MBLK; ++j) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[0][j][e] += part[c][j][e];
+                    for (int e = 0; e < 4; ++e) {
+                      acc[0][j][e] += part[c][j][e];
+                      if (there) __stcg(src + (j * 4 + e) * 128, __uint_as_float(GS_SCRATCH_MARKER));
+                    }
                   }
                 }
               }
-              asm volatile("bar.sync 2, 128;\n");
-              if (tid < batch) p.flags[me + 1 + c0 + tid] = 0;   // ready for the next launch
             }
+            asm volatile("bar.sync 2, 128;\n");
+            if (*reinterpret_cast<volatile int*>(&flags[0])) complete = false;
           }
           if (complete) {
             // ---- bias, activation, then through shared memory: the tile leaves as whole 128-byte runs ----
@@ -556,9 +567,10 @@ static int gs_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
   return 0;
 }
 
-// Scratch floats for `blocks` blocks (the largest token block) and flags (ints, zero before the
-// first launch; the kernel leaves them zero).
+// Scratch words for `blocks` blocks (the largest token block).  Before the first launch every word
+// holds kvb_gemm_stream_scratch_marker(); the kernel leaves them so.
 extern "C" long long kvb_gemm_stream_scratch_floats(int blocks) { return (long long)blocks * 2 * 4 * 128; }
+extern "C" unsigned kvb_gemm_stream_scratch_marker() { return GS_SCRATCH_MARKER; }
 
 template <int MBLK, bool NORMED>
 static int gs_launch(const void* w, const void* x, long long ldx, StreamParams& p, int sms, cudaStream_t stream) {
@@ -584,8 +596,8 @@ static int gs_launch(const void* w, const void* x, long long ldx, StreamParams& 
 extern "C" int kvb_gemm_stream_norm_max_k() { return GS_NORM_W_BYTES / 4; }
 
 // out[M, N] = x[M, K] . w[N, K]^T (+ bias), 1 <= M <= 16, K a multiple of 64.
-//   scratch: kvb_gemm_stream_scratch_floats(sms) floats; flags: sms ints, zero before the first
-//   launch.  Launches that share scratch and flags must be ordered in one stream.
+//   scratch: kvb_gemm_stream_scratch_floats(sms) words, each holding kvb_gemm_stream_scratch_marker()
+//   before the first launch.  Launches that share scratch must be ordered in one stream.
 //   silu_pairs: the rows of w come in runs of 8 gate rows, 8 up rows, ...; out is [M, N / 2] with
 //   out[m, c] = silu(gate_c(m)) * up_c(m) (the feed-forward's activation fused into the epilogue).
 //   norm_weight != null: the rows of x are sums that still need their RMS norm; sumsq_in holds
@@ -597,13 +609,13 @@ extern "C" int kvb_gemm_stream_norm_max_k() { return GS_NORM_W_BYTES / 4; }
 extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const void* x, long long ldx,
                                     const void* w, const void* bias, int M, int N, int K, int silu_pairs,
                                     const void* norm_weight, int norm_weight_f32, float eps, const float* sumsq_in,
-                                    int sumsq_pieces, void* residual, float* sumsq_out, float* scratch, int* flags,
-                                    int sms, cudaStream_t stream) {
+                                    int sumsq_pieces, void* residual, float* sumsq_out, float* scratch, int sms,
+                                    cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   KVB_REQUIRE(M > 0 && M <= 16, "stream gemm: takes 1 to 16 rows of x");
   KVB_REQUIRE(K > 0 && K % 64 == 0 && ldx % 8 == 0, "stream gemm: K must be a multiple of 64 and the row stride of x of 8");
   KVB_REQUIRE(aligned16(x) && aligned16(w), "stream gemm: x and w must be 16-byte aligned");
-  KVB_REQUIRE(scratch != nullptr && flags != nullptr && sms > 0, "stream gemm: needs scratch and flags");
+  KVB_REQUIRE(scratch != nullptr && sms > 0, "stream gemm: needs scratch");
   KVB_REQUIRE(!silu_pairs || (N % 16 == 0 && !out_f32), "stream gemm: gated pairs need N a multiple of 16 and a bf16 result");
   KVB_REQUIRE(residual == nullptr || (!silu_pairs && !out_f32 && N % 8 == 0 && sumsq_out != nullptr && aligned16(residual)),
               "stream gemm: the residual epilogue needs a plain bf16 product, N a multiple of 8 and a place for the squares");
@@ -624,7 +636,6 @@ extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const
   KVB_REQUIRE((long long)p.n_tiles * p.kchunks < (1ll << 30), "stream gemm: the matrix is too large");
   p.units = p.n_tiles * p.kchunks;
   p.partial = scratch;
-  p.flags = flags;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "stream gemm: no status word");
   if (norm_weight != nullptr) {

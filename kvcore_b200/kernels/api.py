@@ -56,7 +56,7 @@ def ensure_built(verbose: bool = False) -> str:
                                   _int, _int, _int, _float, _int, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
-                                 _int, _vp, _vp, _vp, _vp, _int, _vp],
+                                 _int, _vp, _vp, _vp, _int, _vp],
         "kvb_gemm_stream_tc5_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
@@ -75,6 +75,8 @@ def ensure_built(verbose: bool = False) -> str:
     lib.kvb_gemm_stream_scratch_floats.restype = _ll
     lib.kvb_gemm_stream_norm_max_k.argtypes = []
     lib.kvb_gemm_stream_norm_max_k.restype = _int
+    lib.kvb_gemm_stream_scratch_marker.argtypes = []
+    lib.kvb_gemm_stream_scratch_marker.restype = ctypes.c_uint
     for name in ("kvb_gemm_stream_tc5_scratch_floats", "kvb_gemm_stream_tc5_flag_ints"):
         getattr(lib, name).argtypes = [_int]
         getattr(lib, name).restype = _ll
@@ -140,6 +142,14 @@ def read_status(reset: bool = True) -> int:
     """Status bits set by kernels (1 bad token id, 2 bad page id, 4 bounded wait ran out)."""
     out = ctypes.c_int(0)
     _call("kvb_read_status", int(reset), ctypes.byref(out))
+    if out.value & 4:
+        # a kernel gave up a wait: the hand-over areas of the streaming kernels may hold parts that
+        # nobody took; put them back into their state between launches
+        for (kind, _), (scratch, flags) in _stream_scratch.items():
+            if kind == "mma":
+                scratch.view(torch.int32).fill_(int(_lib.kvb_gemm_stream_scratch_marker()))
+            elif flags is not None:
+                flags.zero_()
     return out.value
 
 
@@ -630,19 +640,23 @@ def linear(
     return torch.nn.functional.linear(x, weight, bias)
 
 
-def _stream_buffers(device: torch.device, kind: str = "mma") -> tuple[torch.Tensor, torch.Tensor]:
-    """Scratch and flags (zero between launches) of a streaming kernel; kept for good, since a
-    captured graph holds their addresses."""
+def _stream_buffers(device: torch.device, kind: str = "mma") -> tuple[torch.Tensor, torch.Tensor | None]:
+    """Scratch (and, for the tcgen05 kernel, flags that are zero between launches) of a streaming
+    kernel; kept for good, since a captured graph holds their addresses.  The ``mma.sync`` kernel has
+    no flags: every word of its scratch holds a marker between launches."""
     index = device.index or 0
     buffers = _stream_scratch.get((kind, index))
     if buffers is None:
         if kind == "tc5":
             floats = int(_lib.kvb_gemm_stream_tc5_scratch_floats(SM_COUNT))
             ints = int(_lib.kvb_gemm_stream_tc5_flag_ints(SM_COUNT))
+            buffers = (torch.empty(floats, dtype=torch.float32, device=device),
+                       torch.zeros(ints, dtype=torch.int32, device=device))
         else:
-            floats, ints = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT)), SM_COUNT
-        buffers = (torch.empty(floats, dtype=torch.float32, device=device),
-                   torch.zeros(ints, dtype=torch.int32, device=device))
+            floats = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT))
+            marker = int(_lib.kvb_gemm_stream_scratch_marker())
+            words = torch.full((floats,), marker, dtype=torch.int32, device=device)
+            buffers = (words.view(torch.float32), None)
         _stream_scratch[(kind, index)] = buffers
     return buffers
 
@@ -679,8 +693,10 @@ def _stream_call(kind: str, device: torch.device, *args) -> None:
     """``kvb_gemm_stream(_tc5)_bf16`` with ``args`` up to ``sumsq_out``; scratch, flags, SM count and
     stream are appended."""
     scratch, flags = _stream_buffers(device, kind)
-    _call("kvb_gemm_stream_tc5_bf16" if kind == "tc5" else "kvb_gemm_stream_bf16", *args,
-          scratch.data_ptr(), flags.data_ptr(), SM_COUNT, _stream())
+    if kind == "tc5":
+        _call("kvb_gemm_stream_tc5_bf16", *args, scratch.data_ptr(), flags.data_ptr(), SM_COUNT, _stream())
+    else:
+        _call("kvb_gemm_stream_bf16", *args, scratch.data_ptr(), SM_COUNT, _stream())
 
 
 def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
