@@ -783,8 +783,9 @@ def linear_add_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
 
 
 def sample(logits: torch.Tensor, packed_params: torch.Tensor, eps: float) -> torch.Tensor:
-    """One token per row of ``logits [S, V]`` float32; ``packed_params [S, 6]`` float64 on the host:
-    temperature, top_k, top_p, seed low 32 bits, seed high 32 bits, index of the sampled token."""
+    """One token per row of ``logits [S, V]`` float32; ``packed_params [S, 6]`` float64 (on the
+    device already, or on the host: then copied): temperature, top_k, top_p, seed low 32 bits, seed
+    high 32 bits, index of the sampled token."""
     _check(logits, "logits", dtype=torch.float32)
     rows, vocab = logits.shape
     params = packed_params.to(device=logits.device, dtype=torch.float64, non_blocking=False).contiguous()

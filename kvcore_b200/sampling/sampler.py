@@ -28,6 +28,35 @@ SAMPLING_EPS = 1e-5  # sampler.py:11
 class Sampler:
     def __init__(self, device: torch.device | str) -> None:
         self.device = torch.device(device)
+        # On a CUDA device the rows' parameters travel through two pinned buffers in turn, copied
+        # without waiting, so that a caller who does not read the tokens back (a pipelined loop)
+        # is never held up by the device.
+        self._staging: list[torch.Tensor] = []
+        self._on_device: list[torch.Tensor] = []
+        self._copied: list[torch.cuda.Event | None] = [None, None]
+        self._turn = 0
+
+    def _upload(self, packed: torch.Tensor) -> torch.Tensor:
+        """``packed [rows, 6]`` float64 on the host -> the same on the device, asynchronously."""
+        if self.device.type != "cuda":
+            return packed
+        rows = packed.shape[0]
+        if not self._staging or self._staging[0].shape[0] < rows:
+            capacity = max(64, rows)
+            self._staging = [torch.empty((capacity, 6), dtype=torch.float64, pin_memory=True) for _ in range(2)]
+            self._on_device = [torch.empty((capacity, 6), dtype=torch.float64, device=self.device) for _ in range(2)]
+            self._copied = [None, None]
+        turn = self._turn
+        self._turn ^= 1
+        if self._copied[turn] is not None:
+            self._copied[turn].synchronize()           # the copy that last used this buffer has run
+        self._staging[turn][:rows].copy_(packed)
+        target = self._on_device[turn][:rows]
+        target.copy_(self._staging[turn][:rows], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._copied[turn] = event
+        return target
 
     @staticmethod
     def fresh_seed() -> int:
@@ -67,7 +96,7 @@ class Sampler:
             ],
             dtype=torch.float64,
         )
-        return K.sample(logits, packed, SAMPLING_EPS)
+        return K.sample(logits, self._upload(packed), SAMPLING_EPS)
 
 
 __all__ = ["SAMPLING_EPS", "Sampler"]
