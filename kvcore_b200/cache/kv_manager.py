@@ -87,6 +87,10 @@ class KVManager:
         self.tables = [
             np.zeros((max_num_seqs, self.max_blocks_per_seq), dtype=np.int32) for _ in self.groups
         ]
+        # row_versions[slot] changes whenever a table row of that slot changes (in any group), so
+        # that a copy of a row made earlier can be recognised as still good
+        self.row_versions = [0] * max_num_seqs
+        self._version = 0
         self._requests: dict[str, _RequestState] = {}
         self._fresh_slots: list[int] = []
         # prefix reuse needs one table that keeps every key (a windowed group has given pages back)
@@ -103,6 +107,18 @@ class KVManager:
 
     def state_slot(self, request_id: str) -> int:
         return self._requests[request_id].slot
+
+    def step_place(self, request_id: str, num_new_tokens: int) -> tuple[int, int] | None:
+        """(tokens computed so far, state slot) of a request whose next ``num_new_tokens`` tokens
+        have their pages; ``None`` if the request is unknown or pages are missing."""
+        state = self._requests.get(request_id)
+        if state is None:
+            return None
+        target = -(-(state.num_computed + num_new_tokens) // self.page_size)
+        for blocks in state.num_blocks:
+            if blocks < target:
+                return None
+        return state.num_computed, state.slot
 
     def live_requests(self) -> list[str]:
         return list(self._requests)
@@ -207,6 +223,7 @@ class KVManager:
             self._fresh_slots.append(slot)
             for table in self.tables:
                 table[slot, :] = NULL_PAGE
+            self._touch(slot)
             if prefix_pages:
                 for page in prefix_pages:
                     self.pools[0].share(page)
@@ -222,7 +239,12 @@ class KVManager:
                 begin = state.num_blocks[g]
                 self.tables[g][state.slot, begin : begin + need] = pages
                 state.num_blocks[g] = begin + need
+                self._touch(state.slot)
         return True
+
+    def _touch(self, slot: int) -> None:
+        self._version += 1
+        self.row_versions[slot] = self._version
 
     def advance(self, request_id: str, num_tokens: int) -> None:
         """Record that ``num_tokens`` more tokens are computed; windowed groups hand back the
@@ -247,6 +269,7 @@ class KVManager:
                 self.pools[g].free(pages)
                 row[state.num_released[g] : releasable] = NULL_PAGE
                 state.num_released[g] = releasable
+                self._touch(state.slot)
 
     def free(self, request_id: str) -> None:
         """Return everything the request holds: pages in reverse order, and its slot."""
@@ -258,6 +281,7 @@ class KVManager:
             pages = [int(p) for p in row[: state.num_blocks[g]] if p != NULL_PAGE]
             self.pools[g].free(reversed(pages))
             row[:] = NULL_PAGE
+        self._touch(state.slot)
         self.slots.free(state.slot)
         if state.slot in self._fresh_slots:
             self._fresh_slots.remove(state.slot)

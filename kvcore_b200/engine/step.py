@@ -180,9 +180,12 @@ class StepFunction:
         self._device_meta = torch.zeros(capacity, dtype=torch.int32, device=self.device)
         pin = self.device.type == "cuda"
         self._host_meta = [torch.zeros(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._host_arrays = [buffer.numpy() for buffer in self._host_meta]
         self._host_events: list[torch.cuda.Event | None] = [None, None]
+        self._table_rows: list[list] = [[None, []], [None, []]]   # per buffer: layout stamp, (slot, version) per row
         self._turn = 0
-        self._row_numbers = np.arange(self.max_num_seqs, dtype=np.int32)
+        self._row_numbers = np.arange(self.max_num_seqs + 1, dtype=np.int32)
+        self._views: dict[tuple[int, int, int, int], tuple] = {}
         self.last_context: StepContext | None = None
         self.num_steps = 0
         # decode-only steps of one shape (requests, wanted rows, table width) replay a CUDA graph
@@ -215,13 +218,14 @@ class StepFunction:
             if entry.request_id in seen:
                 raise ValueError(f"request {entry.request_id!r} appears twice in one step")
             seen.add(entry.request_id)
-            if not kv.has_request(entry.request_id) or any(kv.pages_needed(entry.request_id, n)):
+            place = kv.step_place(entry.request_id, n)
+            if place is None:
                 raise RuntimeError(
                     f"request {entry.request_id!r} has no pages for its next {n} tokens: "
                     "allocate_slots must succeed before the step"
                 )
-            context_lens.append(kv.num_computed(entry.request_id))
-            slots.append(kv.state_slot(entry.request_id))
+            context_lens.append(place[0])
+            slots.append(place[1])
         seq_lens = [c + n for c, n in zip(context_lens, query_lens)]
         max_seq_len = max(seq_lens)
         width = -(-max_seq_len // kv.page_size)
@@ -252,11 +256,14 @@ class StepFunction:
         event = self._host_events[turn]
         if event is not None:
             event.synchronize()
-        host = self._host_meta[turn].numpy()
+        host = self._host_arrays[turn]
 
-        starts = np.zeros(num_reqs + 1, dtype=np.int32)
-        np.cumsum(query_lens, out=starts[1:])
-        host[off_query_start : off_query_start + num_reqs + 1] = starts
+        if num_tokens == num_reqs:
+            host[off_query_start : off_query_start + num_reqs + 1] = self._row_numbers[: num_reqs + 1]
+        else:
+            starts = np.zeros(num_reqs + 1, dtype=np.int32)
+            np.cumsum(query_lens, out=starts[1:])
+            host[off_query_start : off_query_start + num_reqs + 1] = starts
         host[off_context : off_context + num_reqs] = context_lens
         host[off_seq : off_seq + num_reqs] = seq_lens
         host[off_slots : off_slots + num_reqs] = slots
@@ -299,35 +306,59 @@ class StepFunction:
                 cursor += n
         if logit_rows:
             host[off_logits : off_logits + num_logits] = logit_rows
-        slot_index = np.asarray(slots, dtype=np.int64)
-        for g in range(len(kv.groups)):
-            begin = off_tables + g * table_len
-            host[begin : begin + num_reqs * width] = kv.tables[g][slot_index, :width].reshape(-1)
+        # block tables: a row of this buffer that still holds the same slot at the same version (the
+        # buffer was last written two steps ago) is left as it is; a steady decode batch rewrites a
+        # row only when its request got a page
+        stamp = (off_tables, width, num_reqs)
+        written = self._table_rows[turn]
+        if written[0] != stamp:
+            written[0] = stamp
+            written[1] = [None] * num_reqs
+        rows = written[1]
+        versions = kv.row_versions
+        for row, slot in enumerate(slots):
+            mark = (slot, versions[slot])
+            if rows[row] != mark:
+                rows[row] = mark
+                for g in range(len(kv.groups)):
+                    begin = off_tables + g * table_len + row * width
+                    host[begin : begin + width] = kv.tables[g][slot, :width]
 
         device_meta = self._device_meta
         device_meta[:used].copy_(self._host_meta[turn][:used], non_blocking=True)
         if self.device.type == "cuda":
-            event = torch.cuda.Event()
+            if event is None:
+                event = self._host_events[turn] = torch.cuda.Event()
             event.record()
-            self._host_events[turn] = event
 
         ctx = StepContext()
         ctx.num_tokens, ctx.num_reqs, ctx.num_logits = num_tokens, num_reqs, num_logits
         ctx.page_size = kv.page_size
-        ctx.query_start = device_meta[off_query_start : off_query_start + num_reqs + 1]
-        ctx.context_lens = device_meta[off_context : off_context + num_reqs]
-        ctx.seq_lens = device_meta[off_seq : off_seq + num_reqs]
-        ctx.state_slots = device_meta[off_slots : off_slots + num_reqs]
-        ctx.token_ids = device_meta[off_tokens : off_tokens + num_tokens]
-        ctx.positions = device_meta[off_positions : off_positions + num_tokens]
-        ctx.req_index = device_meta[off_req_index : off_req_index + num_tokens]
-        ctx.logits_indices = device_meta[off_logits : off_logits + num_logits]
-        ctx.tables = [
-            device_meta[off_tables + g * table_len : off_tables + g * table_len + num_reqs * width].view(
-                num_reqs, width
+        # the views into the metadata buffer depend on the layout only: steps of one shape (every
+        # decode step of a steady batch) share them
+        layout = (num_reqs, num_tokens, num_logits, width)
+        views = self._views.get(layout)
+        if views is None:
+            if len(self._views) >= 256:
+                self._views.clear()
+            views = self._views[layout] = (
+                device_meta[off_query_start : off_query_start + num_reqs + 1],
+                device_meta[off_context : off_context + num_reqs],
+                device_meta[off_seq : off_seq + num_reqs],
+                device_meta[off_slots : off_slots + num_reqs],
+                device_meta[off_tokens : off_tokens + num_tokens],
+                device_meta[off_positions : off_positions + num_tokens],
+                device_meta[off_req_index : off_req_index + num_tokens],
+                device_meta[off_logits : off_logits + num_logits],
+                [
+                    device_meta[off_tables + g * table_len : off_tables + g * table_len + num_reqs * width].view(
+                        num_reqs, width
+                    )
+                    for g in range(len(kv.groups))
+                ],
             )
-            for g in range(len(kv.groups))
-        ]
+        (ctx.query_start, ctx.context_lens, ctx.seq_lens, ctx.state_slots, ctx.token_ids, ctx.positions,
+         ctx.req_index, ctx.logits_indices, ctx.tables) = views
         ctx.table_width = width
         ctx.max_query_len = max(query_lens)
         ctx.max_seq_len = max_seq_len
