@@ -56,8 +56,8 @@ __device__ __forceinline__ void kvb_grid_launch_dependents() { asm volatile("gri
 
 // ---- kernel timeline trace ----------------------------------------------------------------------
 // When a trace buffer is set, the first and the last block of every kernel of this library append
-// one event {tag, block, time at entry, time after kvb_grid_wait(), time at exit} (nanoseconds of
-// the GPU's global timer).  Word 0 of the buffer counts events, word 1 is the capacity in events
+// one event {tag, first/last/other, SM, block index, time at entry, time after kvb_grid_wait(), time
+// at exit} (nanoseconds of the GPU's global timer).  Word 0 of the buffer counts events, word 1 is the capacity in events
 // (its top bit set: every block records, not only the first and the last).
 // The pointer lives once per translation unit (set through KVB_TRACE_TU's setter); null = off.
 static __device__ unsigned long long* kvb_trace_buffer = nullptr;
@@ -93,7 +93,12 @@ struct KvbTrace {
         unsigned long long* e = buffer + 2 + slot * 4;
         const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         const bool last = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1;
-        e[0] = (unsigned long long)tag | (first ? 0ull : last ? 1ull << 32 : 2ull << 32);
+        // word 0: tag (8 bits) | first/last/other (2 bits at 8) | SM (10 bits at 12) | linear block index (at 32)
+        const unsigned long long index = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+        unsigned sm;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+        e[0] = (unsigned long long)(tag & 0xff) | (first ? 0ull : last ? 1ull << 8 : 2ull << 8) |
+               ((unsigned long long)(sm & 0x3ff) << 12) | (index << 32);
         e[1] = entry;
         e[2] = waited;
         e[3] = kvb_global_ns();

@@ -535,7 +535,8 @@ def trace_start(device: torch.device | str = "cuda:0", capacity: int = 1 << 16, 
 
 
 def trace_stop() -> list[dict]:
-    """Stop the trace; events sorted by entry time: kernel, block ("first"/"last"), entry, waited, exit (ns)."""
+    """Stop the trace; events sorted by entry time: kernel, block ("first"/"last"/"other"), sm, index
+    (linear block index), entry, waited, exit (ns)."""
     global _trace_buffer
     if _trace_buffer is None:
         return []
@@ -549,9 +550,9 @@ def trace_stop() -> list[dict]:
     events = []
     for i in range(count):
         tag, entry, waited, leave = host[2 + 4 * i: 6 + 4 * i]
-        events.append({"kernel": TRACE_TAGS.get(tag & 0xFFFFFFFF, str(tag & 0xFFFFFFFF)),
-                       "block": ("first", "last", "other")[min(tag >> 32, 2)], "entry": entry, "waited": waited,
-                       "exit": leave})
+        events.append({"kernel": TRACE_TAGS.get(tag & 0xFF, str(tag & 0xFF)),
+                       "block": ("first", "last", "other")[min((tag >> 8) & 3, 2)], "sm": (tag >> 12) & 0x3FF,
+                       "index": (tag >> 32) & 0xFFFFFFFF, "entry": entry, "waited": waited, "exit": leave})
     events.sort(key=lambda e: e["entry"])
     return events
 
