@@ -625,3 +625,28 @@ def test_linear_stream_takes_row_views():
     x = full[:, 256:]
     w = randn(300, 512, dtype=torch.bfloat16, seed=24, scale=0.05)
     torch.testing.assert_close(K().linear(x, w).float(), x.float() @ w.float().T, rtol=1.6e-2, atol=2e-2)
+
+
+def test_kernel_timeline_trace():
+    """The trace lists the kernels that ran, with times in order and the blocks' places."""
+    x = randn(8, 256, dtype=torch.bfloat16, seed=1)
+    w = randn(640, 256, dtype=torch.bfloat16, seed=2, scale=0.05)
+    g = randn(256, dtype=torch.bfloat16, seed=3)
+    K().linear_stream(x, w)                                   # warm: the library is loaded, buffers exist
+    K().trace_start(DEV, capacity=4096, every_block=True)
+    K().rmsnorm(x, g, 1e-5)
+    K().linear_stream(x, w)
+    events = K().trace_stop()
+    assert K().trace_stop() == []                             # stopped: nothing more to read
+    names = [e["kernel"] for e in events]
+    assert "rmsnorm" in names and "gemm_stream" in names
+    blocks = [e for e in events if e["kernel"] == "gemm_stream"]
+    assert sorted(e["index"] for e in blocks) == list(range(len(blocks)))   # every block once
+    assert {e["block"] for e in blocks} >= {"first", "last"}
+    for e in events:
+        assert e["entry"] <= e["waited"] <= e["exit"] and 0 <= e["sm"] < 1024
+    first_norm = min(e["entry"] for e in events if e["kernel"] == "rmsnorm")
+    assert all(e["exit"] >= first_norm for e in blocks)       # the product was launched behind the norm
+    # with the trace off, kernels record nothing
+    K().rmsnorm(x, g, 1e-5)
+    assert K().read_status() == 0
