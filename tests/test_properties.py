@@ -69,14 +69,15 @@ def test_cache_manager_accounts_for_every_page(ops, windows, num_pages, page_siz
 
 # ---- cuttings --------------------------------------------------------------------------------
 LENGTHS = {"a": 37, "b": 22}
+LONG_LENGTHS = {"a": 230, "b": 141}     # several key tiles and row tiles: the serving kernels' shapes
 
 
-def _model(tmp_path_factory, name):
+def _model(tmp_path_factory, name, lengths=LENGTHS):
     config = rc.TINY_CONFIGS[name]
     folder = tmp_path_factory.mktemp(f"prop_{name}")
     rc.write_model(folder, config, rc.TINY_SEEDS[name], "bfloat16")
     weights = plain_llama.load_weights(folder)
-    requests = {rid: rc.random_tokens(config["vocab_size"], n, 40 + i) for i, (rid, n) in enumerate(LENGTHS.items())}
+    requests = {rid: rc.random_tokens(config["vocab_size"], n, 40 + i) for i, (rid, n) in enumerate(lengths.items())}
     reference = {rid: plain_llama.forward_logits(config, weights, tokens).numpy() for rid, tokens in requests.items()}
     return dict(config=config, folder=folder, requests=requests, reference=reference)
 
@@ -86,9 +87,9 @@ def model_a(tmp_path_factory):
     return _model(tmp_path_factory, "A")
 
 
-@pytest.fixture(scope="module")
-def model_b(tmp_path_factory):
-    return _model(tmp_path_factory, "B")
+@pytest.fixture(scope="module", params=[("B", LENGTHS), ("D", LONG_LENGTHS)], ids=["B", "D-long"])
+def model_gpu(tmp_path_factory, request):
+    return _model(tmp_path_factory, *request.param)
 
 
 def _trace(requests, sizes_a, sizes_b, order):
@@ -118,7 +119,7 @@ def _check_cutting(case, steps, out_dir, dtype, device, tolerance):
     vocab = case["config"]["vocab_size"]
     rc.run_inprocess(case["folder"], dtype, steps, out_dir, rc.peak_tokens(steps), device=device)
     rows = rc.collect(steps, out_dir, vocab)
-    assert len(rows) == sum(LENGTHS.values())
+    assert len(rows) == sum(len(tokens) for tokens in case["requests"].values())
     for (rid, position), row in rows.items():
         reference = case["reference"][rid]
         error = np.abs(row - reference[position]).max() / np.abs(reference).max()
@@ -126,6 +127,7 @@ def _check_cutting(case, steps, out_dir, dtype, device, tolerance):
 
 
 SIZES = st.lists(st.integers(1, 12), min_size=1, max_size=6)
+LONG_SIZES = st.lists(st.one_of(st.integers(1, 12), st.integers(13, 90)), min_size=1, max_size=6)
 ORDER = st.lists(st.sampled_from(["a", "b", "ab"]), min_size=1, max_size=5)
 
 
@@ -140,12 +142,14 @@ def test_any_cutting_gives_the_logits_of_the_whole_sequence_on_the_host(model_a,
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,tolerance", [("float32", 2e-5), ("bfloat16", 2e-2)])
-def test_any_cutting_gives_the_logits_of_the_whole_sequence(model_b, tmp_path_factory, dtype, tolerance):
+def test_any_cutting_gives_the_logits_of_the_whole_sequence(model_gpu, tmp_path_factory, dtype, tolerance):
+    sizes = LONG_SIZES if len(model_gpu["requests"]["a"]) > 100 else SIZES
+
     @settings(max_examples=10, deadline=None)
-    @given(sizes_a=SIZES, sizes_b=SIZES, order=ORDER)
+    @given(sizes_a=sizes, sizes_b=sizes, order=ORDER)
     def run(sizes_a, sizes_b, order):
-        steps = _trace(model_b["requests"], sizes_a, sizes_b, order)
-        _check_cutting(model_b, steps, tmp_path_factory.mktemp("cut"), dtype, "cuda:0", tolerance)
+        steps = _trace(model_gpu["requests"], sizes_a, sizes_b, order)
+        _check_cutting(model_gpu, steps, tmp_path_factory.mktemp("cut"), dtype, "cuda:0", tolerance)
 
     run()
 
