@@ -251,6 +251,9 @@ class ModelRunner:
                 [s.seed for s in states],
                 [s.num_sampled for s in states],
             ).tolist()
+            # the step has finished (its tokens are here): anything its kernels reported is read
+            # from host memory, without another round trip
+            K.raise_on_status()
             for state, token in zip(states, tokens):
                 state.token_ids.append(int(token))
                 state.num_sampled += 1

@@ -73,6 +73,7 @@ def replay_stream(step_function: StepFunction, kv: KVManager, lines, out_dir: Pa
             logits = step_function.step(entries)
             if logits is not None:
                 data = logits.to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False)
+                K.raise_on_status()      # the step has finished: nothing its kernels reported goes unseen
                 data.tofile(out_dir / f"{step_id}.f32")
         for request_id in record.get("end", []):
             kv.free(str(request_id))

@@ -68,6 +68,8 @@ def ensure_built(verbose: bool = False) -> str:
         fn.restype = _int
     lib.kvb_set_pdl.argtypes = [_int]
     lib.kvb_set_pdl.restype = None
+    lib.kvb_peek_status.argtypes = []
+    lib.kvb_peek_status.restype = _int
     # Kernels of this library overlap their start with the end of the kernel in front of them
     # (programmatic dependent launch); KVCORE_B200_SERIAL_LAUNCH=1 switches that off.
     lib.kvb_set_pdl(0 if os.environ.get("KVCORE_B200_SERIAL_LAUNCH") == "1" else 1)
@@ -151,6 +153,26 @@ def read_status(reset: bool = True) -> int:
             elif flags is not None:
                 flags.zero_()
     return out.value
+
+
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a page id outside the cache",
+               4: "a bounded wait inside a kernel ran out"}
+
+
+def peek_status() -> int:
+    """The status bits reported by the kernels that have finished, without waiting for any: free to
+    call after the caller has synchronised on its own (0 when the library is not loaded)."""
+    if _lib is None:
+        return 0
+    return int(_lib.kvb_peek_status())
+
+
+def raise_on_status() -> None:
+    """Raise ``KernelError`` if a finished kernel reported a problem (and clear the report)."""
+    if peek_status():
+        bits = read_status(reset=True)
+        what = "; ".join(text for bit, text in STATUS_BITS.items() if bits & bit) or f"status {bits}"
+        raise KernelError(f"a kernel reported: {what}")
 
 
 # ---- shape policy -------------------------------------------------------------------------------
@@ -817,6 +839,8 @@ __all__ = [
     "trace_stop",
     "paged_attention",
     "read_status",
+    "peek_status",
+    "raise_on_status",
     "require_device",
     "rmsnorm",
     "rope_inplace",

@@ -24,6 +24,14 @@ def read_status(reset: bool = True) -> int:
     return 0
 
 
+def peek_status() -> int:
+    return 0
+
+
+def raise_on_status() -> None:
+    return None
+
+
 def check_attention_shape(num_heads, num_kv_heads, head_dim, dtype) -> None:
     from kvcore_b200.kernels.api import check_attention_shape as real
 
@@ -216,7 +224,7 @@ def sample(logits, packed_params, eps):
 
 
 _NAMES = [
-    "require_device", "ensure_built", "read_status", "check_attention_shape", "gather_rows", "rmsnorm",
+    "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
 ]
 

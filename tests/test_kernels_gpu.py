@@ -650,3 +650,18 @@ def test_kernel_timeline_trace():
     # with the trace off, kernels record nothing
     K().rmsnorm(x, g, 1e-5)
     assert K().read_status() == 0
+
+
+def test_a_reported_status_is_raised_without_a_copy():
+    """Kernels report into host memory that the device sees: the engine's check after a step costs
+    no round trip, and a report becomes an exception."""
+    table = randn(10, 32, dtype=torch.float32, seed=1)
+    assert K().peek_status() == 0
+    K().raise_on_status()                                     # nothing reported: nothing raised
+    ids = torch.tensor([3, 12, 5], dtype=torch.int32, device=DEV)   # 12 is outside the table
+    K().gather_rows(table, ids)
+    torch.cuda.synchronize()
+    assert K().peek_status() & 1
+    with pytest.raises(K().KernelError, match="token id"):
+        K().raise_on_status()
+    assert K().peek_status() == 0 and K().read_status() == 0  # the report was cleared
