@@ -321,6 +321,9 @@ def main() -> int:
         e2e["value"] = round(e2e["value"], 2)
         e2e["ms_per_step"] = round(e2e["ms_per_step"], 3)
     clocks = sampler.stop()
+    status = K.read_status()
+    if status:
+        raise RuntimeError(f"a kernel reported status {status} during the measurement: the numbers are void")
 
     step_bytes = 2.0 * numbers["streamed_params"] + args.batch * args.context * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
