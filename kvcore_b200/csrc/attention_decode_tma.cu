@@ -26,6 +26,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 #define TD_KEYS 64
 #define TD_STAGES 3
@@ -55,42 +56,6 @@ struct DecodeParams {
   const bf16* v_new;
   bf16* k_cache; bf16* v_cache;   // [pages, KVH, page, D]
 };
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
-  unsigned done;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.b32 %0, 1, 0, p;\n}\n"
-      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return done != 0;
-}
-// Waits for the phase of `parity` to complete; gives up after TD_SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
-  for (unsigned spin = 0; spin < TD_SPIN_LIMIT; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 64) __nanosleep(64);
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
-                                            unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
 
 __device__ __forceinline__ void td_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -169,12 +134,11 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TD_STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], TD_GROUP_WARPS);
+      kvb_mbar_init(&full_bar[s], 1);
+      kvb_mbar_init(&empty_bar[s], TD_GROUP_WARPS);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    kvb_mbar_init_fence();
   }
   __syncthreads();
   if (warp != TD_CONSUMERS) {
@@ -290,13 +254,13 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
       int ok = 1;
       if (lane == 0) {
-        if (it >= TD_STAGES && !mbar_wait_bounded(&empty_bar[stage], ((it / TD_STAGES) & 1) ^ 1)) {
+        if (it >= TD_STAGES && !kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&empty_bar[stage], ((it / TD_STAGES) & 1) ^ 1)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(abort_flag, 1);
           ok = 0;
         }
         if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
-        if (ok) mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+        if (ok) kvb_mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
@@ -306,8 +270,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         unsigned char* vdst = kdst + KV_BYTES;
         const int row = (page * p.KVH + kvh) * p.page_size * HALVES;   // in rows of 64 elements
         const int dst_off = lane * p.page_size * HALVES * 128;
-        tma_load_2d(kdst + dst_off, &k_map, 0, row, &full_bar[stage]);     // one contiguous page of a head
-        tma_load_2d(vdst + dst_off, &v_map, 0, row, &full_bar[stage]);
+        kvb_tma_2d(kdst + dst_off, &k_map, 0, row, &full_bar[stage]);     // one contiguous page of a head
+        kvb_tma_2d(vdst + dst_off, &v_map, 0, row, &full_bar[stage]);
       }
       issued = it + 1;
     }
@@ -315,7 +279,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     // on an aborted run, let the copies already issued land before the block may exit
     if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
       for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
-        mbar_wait_bounded(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
+        kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
     }
   } else {
     // ---------------- consumers ----------------
@@ -324,7 +288,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     for (int k = 0; k < KSTEPS; ++k) {
       const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
       const int c = k * 16 + 8 * (lane >> 4);
-      td_ldmatrix_x4(qf[k], smem_u32(qs + r * QROW + c));
+      td_ldmatrix_x4(qf[k], kvb_smem(qs + r * QROW + c));
     }
     int row_pos[2];
     bool row_valid[2];
@@ -338,12 +302,12 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     const int wkey = (warp % TD_GROUP_WARPS) * 16;
     for (int it = group; it < num_tiles; it += TD_GROUPS) {
       const int stage = it % TD_STAGES;
-      if (!mbar_wait_bounded(&full_bar[stage], (it / TD_STAGES) & 1)) {
+      if (!kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[stage], (it / TD_STAGES) & 1)) {
         atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
         atomicExch(abort_flag, 1);
         break;
       }
-      const unsigned kbase = smem_u32(stages + stage * STAGE_BYTES);
+      const unsigned kbase = kvb_smem(stages + stage * STAGE_BYTES);
       const unsigned vbase = kbase + KV_BYTES;
       if (p.k_cache != nullptr) {
         // a tile that holds slots of this step's tokens: lay the fresh keys and values over them
@@ -359,7 +323,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             unsigned char* area = stages + stage * STAGE_BYTES + (which ? KV_BYTES : 0);
             *reinterpret_cast<uint4*>(area + swz<HALVES>(pos - tile_lo, chunk * 8)) = v;
           }
-          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // a later copy may reuse the stage
+          kvb_fence_async_shared();   // a later copy may reuse the stage
           asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
         }
       }
@@ -442,7 +406,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         td_mma(o[j + 1], pa, vb[2], vb[3]);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (lane == 0) kvb_mbar_arrive(&empty_bar[stage]);
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

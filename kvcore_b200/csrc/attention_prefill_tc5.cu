@@ -32,6 +32,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 #define T5_BM 128
 #define T5_BN 128
@@ -50,88 +51,6 @@ struct Tc5Params {
   float scale_log2;
   int* status;
 };
-
-__device__ __forceinline__ unsigned t5_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void t5_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(t5_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void t5_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(t5_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool t5_wait(unsigned long long* bar, unsigned parity) {
-  for (unsigned spin = 0; spin < T5_SPIN_LIMIT; ++spin) {
-    unsigned done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(t5_smem(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if (spin > 4096) __nanosleep(64);   // hand-offs inside the tile loop are short: spin first
-  }
-  return false;
-}
-__device__ __forceinline__ void t5_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(t5_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(t5_smem(bar))
-      : "memory");
-}
-// Shared-memory matrix descriptor: 128-byte swizzle, version 1 (sm_100).
-__device__ __forceinline__ unsigned long long t5_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
-  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(lbo_bytes >> 4) << 16) |
-         ((unsigned long long)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// D[tmem] (+)= A[smem] . B[smem], one elected thread.
-__device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                       unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// D[tmem] (+)= A[tmem] . B[smem]: A is 128 lanes x 8 columns (16 bf16 a lane, two to a column).
-__device__ __forceinline__ void t5_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void t5_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void t5_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned* r = reinterpret_cast<unsigned*>(v);
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void t5_st32(unsigned taddr, const float (&v)[32]) {
-  const unsigned* r = reinterpret_cast<const unsigned*>(v);
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void t5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void t5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // Byte offset of the 16-byte chunk `chunk16` (0..15 across the 128 columns) of row `r` in a
 // [128 rows x 128 columns] bf16 operand tile stored as two swizzled 64-column halves.
@@ -171,7 +90,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const int rows_total = q_len * p.G;
   const int row0 = tile * T5_BM;
   if (row0 >= rows_total) return;  // whole block, before any barrier or allocation
-  if (t5_smem(base) & 1023u) {     // cannot happen with the alignment asked for; never run misaligned
+  if (kvb_smem(base) & 1023u) {     // cannot happen with the alignment asked for; never run misaligned
     if (threadIdx.x == 0) atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
     return;
   }
@@ -186,23 +105,21 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      t5_mbar_init(&k_full[i], 1);
-      t5_mbar_init(&k_empty[i], 1);
-      t5_mbar_init(&v_full[i], 1);
-      t5_mbar_init(&v_empty[i], 1);
-      t5_mbar_init(&s_full[i], 1);
-      t5_mbar_init(&s_free[i], 256);
-      t5_mbar_init(&p_ready[i], 256);
-      t5_mbar_init(&pv_done[i], 1);
-      t5_mbar_init(&x_ready[i], 256);
+      kvb_mbar_init(&k_full[i], 1);
+      kvb_mbar_init(&k_empty[i], 1);
+      kvb_mbar_init(&v_full[i], 1);
+      kvb_mbar_init(&v_empty[i], 1);
+      kvb_mbar_init(&s_full[i], 1);
+      kvb_mbar_init(&s_free[i], 256);
+      kvb_mbar_init(&p_ready[i], 256);
+      kvb_mbar_init(&pv_done[i], 1);
+      kvb_mbar_init(&x_ready[i], 256);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    kvb_mbar_init_fence();
   }
   if (warp == 10) {  // tensor memory: 512 columns for this block
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_smem(tmem_slot)), "r"(512u));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    kvb_tc5_alloc(tmem_slot, 512u);
   }
   // Q rows -> shared memory in the swizzled K-major operand layout (thread t of warps 0-3: row t)
   if (warp < 4) {
@@ -217,11 +134,11 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
       *reinterpret_cast<uint4*>(q_smem + t5_chunk_off(r, c)) = v;
     }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> visible to the MMA's reads
+    kvb_fence_async_shared();  // generic writes -> visible to the MMA's reads
   }
-  t5_fence_before();
+  kvb_tc5_fence_before();
   __syncthreads();
-  t5_fence_after();
+  kvb_tc5_fence_after();
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_o = tmem_base + 256;
   const unsigned tmem_p = tmem_base + 384;   // two buffers of 64 columns
@@ -261,16 +178,16 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       const int row = (page * p.KVH + kvh) * p.page_size;
       int ok = 1;
       if (lane == 0) {
-        if (j >= 2 && !t5_wait(&empty[s], ((j >> 1) - 1) & 1)) ok = 0;
+        if (j >= 2 && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&empty[s], ((j >> 1) - 1) & 1)) ok = 0;
         if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
-        if (ok) t5_expect_tx(&full[s], T5_TILE_BYTES);
+        if (ok) kvb_mbar_expect_tx(&full[s], T5_TILE_BYTES);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (lane < ppt) {
         unsigned char* dst = ring + s * T5_TILE_BYTES + lane * p.page_size * 128;
-        t5_tma_2d(dst, map, 0, row, &full[s]);
-        t5_tma_2d(dst + T5_HALF_BYTES, map, 64, row, &full[s]);
+        kvb_tma_2d(dst, map, 0, row, &full[s]);
+        kvb_tma_2d(dst + T5_HALF_BYTES, map, 64, row, &full[s]);
       }
       issued = j + 1;
     }
@@ -280,55 +197,53 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
     if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
       // let the copies that were issued land before the block may exit
-      for (int j = max(0, issued - 2); j < issued; ++j) t5_wait(&full[j & 1], (j >> 1) & 1);
+      for (int j = max(0, issued - 2); j < issued; ++j) kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&full[j & 1], (j >> 1) & 1);
     }
   } else if (warp == 10) {
     // ================= MMA issuer =================
     if (lane == 0) {
       // instruction descriptors: f32 accumulate, bf16 x bf16, M = 128, N = 128
-      const unsigned idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(T5_BN >> 3) << 17) |
-                                  ((unsigned)(T5_BM >> 4) << 24);
-      const unsigned idesc_s = idesc_base;                // A, B both K-major
-      const unsigned idesc_pv = idesc_base | (1u << 16);  // B (= V) MN-major
-      const unsigned q_addr = t5_smem(q_smem);
+      const unsigned idesc_s = kvb_tc5_idesc(T5_BM, T5_BN, false);   // A, B both K-major
+      const unsigned idesc_pv = kvb_tc5_idesc(T5_BM, T5_BN, true);   // B (= V) MN-major
+      const unsigned q_addr = kvb_smem(q_smem);
       bool ok = true;
       auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
-        const unsigned k_addr = t5_smem(k_smem + (j & 1) * T5_TILE_BYTES);
+        const unsigned k_addr = kvb_smem(k_smem + (j & 1) * T5_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < T5_D / 16; ++kk) {
           const unsigned off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;
-          t5_mma(tmem_base + (j & 1) * T5_BN, t5_desc(q_addr + off, 16, 1024), t5_desc(k_addr + off, 16, 1024),
+          kvb_tc5_mma(tmem_base + (j & 1) * T5_BN, kvb_tc5_desc(q_addr + off, 16, 1024), kvb_tc5_desc(k_addr + off, 16, 1024),
                  idesc_s, kk > 0);
         }
-        t5_commit(&s_full[j & 1]);
-        t5_commit(&k_empty[j & 1]);
+        kvb_tc5_commit(&s_full[j & 1]);
+        kvb_tc5_commit(&k_empty[j & 1]);
       };
-      if (!t5_wait(&k_full[0], 0)) ok = false;
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[0], 0)) ok = false;
       if (ok) {
-        t5_fence_after();
+        kvb_tc5_fence_after();
         issue_s(0);
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
         if (j + 1 < num_tiles) {
           const int n = j + 1;
-          if (!t5_wait(&k_full[n & 1], (n >> 1) & 1)) { ok = false; break; }
-          if (n >= 2 && !t5_wait(&s_free[n & 1], ((n >> 1) - 1) & 1)) { ok = false; break; }
-          t5_fence_after();
+          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[n & 1], (n >> 1) & 1)) { ok = false; break; }
+          if (n >= 2 && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&s_free[n & 1], ((n >> 1) - 1) & 1)) { ok = false; break; }
+          kvb_tc5_fence_after();
           issue_s(n);
         }
-        if (!t5_wait(&p_ready[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        if (!t5_wait(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        t5_fence_after();
-        const unsigned v_addr = t5_smem(v_smem + (j & 1) * T5_TILE_BYTES);
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[j & 1], (j >> 1) & 1)) { ok = false; break; }
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
+        kvb_tc5_fence_after();
+        const unsigned v_addr = kvb_smem(v_smem + (j & 1) * T5_TILE_BYTES);
         const unsigned p_tmem = tmem_p + (j & 1) * (T5_BN / 2);
 #pragma unroll
         for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA: 8 columns of P, 16 key rows of V
           const unsigned b_off = kk * 16 * 128;
-          t5_mma_ts(tmem_o, p_tmem + kk * 8, t5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv,
+          kvb_tc5_mma_ts(tmem_o, p_tmem + kk * 8, kvb_tc5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv,
                     (j > 0 || kk > 0) ? 1u : 0u);
         }
-        t5_commit(&pv_done[j & 1]);
-        t5_commit(&v_empty[j & 1]);
+        kvb_tc5_commit(&pv_done[j & 1]);
+        kvb_tc5_commit(&v_empty[j & 1]);
       }
       if (!ok) {
         atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
@@ -356,17 +271,17 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     bool ok = true;
     for (int j = 0; j < num_tiles; ++j) {
       const int b = j & 1;
-      if (!t5_wait(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
-      t5_fence_after();
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
+      kvb_tc5_fence_after();
       const int key0 = (tile_begin + j) * T5_BN + half * 64;
       const bool need_mask = ragged || p.window > 0 || (tile_begin + j) * T5_BN + T5_BN - 1 > first_pos;
       const unsigned s_addr = tmem_base + lane_addr + b * T5_BN + half * 64;
       float s[2][32];
-      t5_ld32(s_addr, s[0]);
-      t5_ld32(s_addr + 32, s[1]);
-      t5_wait_ld();
-      t5_fence_before();
-      t5_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
+      kvb_tc5_ld32(s_addr, s[0]);
+      kvb_tc5_ld32(s_addr + 32, s[1]);
+      kvb_tc5_wait_ld();
+      kvb_tc5_fence_before();
+      kvb_mbar_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
       // ---- pass 1: maximum of the raw scores of this half row ----
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
@@ -390,8 +305,8 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       // ---- partners agree on the row maximum ----
       float* xb = x_buf + b * 256;
       xb[half * 128 + r] = my_max;
-      t5_arrive(&x_ready[b]);
-      if (!t5_wait(&x_ready[b], (j >> 1) & 1)) { ok = false; break; }
+      kvb_mbar_arrive(&x_ready[b]);
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[b], (j >> 1) & 1)) { ok = false; break; }
       float tile_max = fmaxf(my_max, xb[(half ^ 1) * 128 + r]) * p.scale_log2;   // scale > 0; -inf stays -inf
       const float new_max = fmaxf(row_max, tile_max);
       const bool grows = new_max > row_max + 8.0f || (row_max == -INFINITY && new_max > -INFINITY);
@@ -403,7 +318,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
       const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
       if (j >= 2) {  // P buffer j&1 is free once PV(j-2) has completed
-        if (!t5_wait(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
       }
       // ---- pass 2: P = 2^(s*scale - m), partial row sum, packed bf16 into tensor memory ----
       float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -424,38 +339,38 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
               __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632));
         }
       }
-      t5_st32(tmem_p + lane_addr + b * (T5_BN / 2) + half * 32, packed);
+      kvb_tc5_st32(tmem_p + lane_addr + b * (T5_BN / 2) + half * 32, packed);
       row_sum = row_sum * correction + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
       if (move && j > 0) {       // rescale this thread's half row of O: PV(j-1) must have landed first
-        if (!t5_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
-        t5_fence_after();
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
+        kvb_tc5_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           float o[32];
-          t5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
-          t5_wait_ld();
+          kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
+          kvb_tc5_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= correction;
-          t5_st32(tmem_o + lane_addr + half * 64 + c * 32, o);
+          kvb_tc5_st32(tmem_o + lane_addr + half * 64 + c * 32, o);
         }
-        t5_wait_st();
+        kvb_tc5_wait_st();
       }
-      t5_wait_st();
-      t5_fence_before();
-      t5_arrive(&p_ready[b]);
+      kvb_tc5_wait_st();
+      kvb_tc5_fence_before();
+      kvb_mbar_arrive(&p_ready[b]);
     }
-    if (ok && !t5_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
+    if (ok && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
     if (ok) {
       // partners add their partial row sums (slot of the parity the last tile did not use)
       const int xb_slot = num_tiles & 1;
       float* xb = x_buf + xb_slot * 256;
       xb[half * 128 + r] = row_sum;
-      t5_arrive(&x_ready[xb_slot]);
-      if (!t5_wait(&x_ready[xb_slot], (num_tiles >> 1) & 1)) ok = false;
+      kvb_mbar_arrive(&x_ready[xb_slot]);
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[xb_slot], (num_tiles >> 1) & 1)) ok = false;
       if (ok) row_sum += xb[(half ^ 1) * 128 + r];
     }
     if (ok) {
-      t5_fence_after();
+      kvb_tc5_fence_after();
       const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
       bf16* dst = nullptr;
       if (row_valid)
@@ -464,8 +379,8 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         float o[32];
-        t5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
-        t5_wait_ld();
+        kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
+        kvb_tc5_wait_ld();
         if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -489,11 +404,11 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   }
 
   // ---- everyone meets; the allocating warp frees the tensor memory ----
-  t5_fence_before();
+  kvb_tc5_fence_before();
   __syncthreads();
   if (warp == 10) {
-    t5_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u));
+    kvb_tc5_fence_after();
+    kvb_tc5_dealloc(tmem_base, 512u);
   }
 }
 

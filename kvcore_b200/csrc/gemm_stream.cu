@@ -35,6 +35,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 #define GS_NT 64            // weight rows per tile
 #define GS_KG 4             // slabs of 64 k-values per stage
@@ -65,41 +66,6 @@ struct StreamParams {
   int silu_pairs;                    // 1: rows n and n+8 of every 16 are a (gate, up) pair: out[m, .] = silu(gate) * up
 };
 
-__device__ __forceinline__ unsigned gs_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void gs_mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void gs_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gs_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void gs_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(gs_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool gs_wait_bounded(unsigned long long* bar, unsigned parity) {
-  for (unsigned spin = 0; spin < GS_SPIN_LIMIT; ++spin) {
-    unsigned done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(gs_smem(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if (spin > 64) __nanosleep(64);
-  }
-  return false;
-}
-__device__ __forceinline__ void gs_tma_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2,
-                                          unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
-      ::"r"(gs_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2),
-        "r"(gs_smem(bar))
-      : "memory");
-}
-__device__ __forceinline__ void gs_prefetch_3d(const CUtensorMap* map, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n"
-               ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
 __device__ __forceinline__ void gs_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -112,15 +78,6 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], un
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ int gs_ld_acquire(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void gs_st_release(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-
 // Byte offset of (row, k) in an operand area made of [rows][128-byte] slabs, one per 64 k-values,
 // 16-byte chunks XOR-swizzled with the row as TMA's 128-byte swizzle lays them out.
 __device__ __forceinline__ unsigned gs_swz(int row, int k, int rows) {
@@ -163,14 +120,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   const int u_begin = gs_range_start(p.units, blocks, me), u_end = gs_range_start(p.units, blocks, me + 1);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      gs_mbar_init(&full_bar[s], 1);
-      gs_mbar_init(&empty_bar[s], GS_CONSUMERS);
-      gs_mbar_init(&xraw_bar[s], 1);
-      gs_mbar_init(&xready_bar[s], GS_NORMALISERS);
+      kvb_mbar_init(&full_bar[s], 1);
+      kvb_mbar_init(&empty_bar[s], GS_CONSUMERS);
+      kvb_mbar_init(&xraw_bar[s], 1);
+      kvb_mbar_init(&xready_bar[s], GS_NORMALISERS);
     }
     flags[0] = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    kvb_mbar_init_fence();
   }
   __syncthreads();
   kvb_grid_launch_dependents();
@@ -184,14 +140,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       // written by no kernel of the step)
       for (int i = 0; i < pre; ++i) {
         const int u = u_begin + i;
-        gs_expect_tx(&full_bar[i], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
-        gs_tma_3d(base + i * STAGE_BYTES, &w_map, 0, (u / p.kchunks) * GS_NT, (u % p.kchunks) * GS_KG, &full_bar[i]);
+        kvb_mbar_expect_tx(&full_bar[i], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
+        kvb_tma_3d(base + i * STAGE_BYTES, &w_map, 0, (u / p.kchunks) * GS_NT, (u % p.kchunks) * GS_KG, &full_bar[i]);
       }
       kvb_grid_wait();                            // x is the output of the kernel in front
       int issued = 0;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        if (it >= STAGES && !gs_wait_bounded(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
+        if (it >= STAGES && !kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(&flags[0], 1);
           break;
@@ -201,21 +157,21 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         const int slab = (u % p.kchunks) * GS_KG;
         unsigned char* wdst = base + stage * STAGE_BYTES;
         if (it >= pre) {
-          gs_expect_tx(&full_bar[stage], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
-          gs_tma_3d(wdst, &w_map, 0, (u / p.kchunks) * GS_NT, slab, &full_bar[stage]);
+          kvb_mbar_expect_tx(&full_bar[stage], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
+          kvb_tma_3d(wdst, &w_map, 0, (u / p.kchunks) * GS_NT, slab, &full_bar[stage]);
         }
         if (NORMED) {
-          gs_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
-          gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &xraw_bar[stage]);
+          kvb_mbar_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
+          kvb_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &xraw_bar[stage]);
         } else {
-          gs_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
+          kvb_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
         }
         issued = it + 1;
       }
       if (*reinterpret_cast<volatile int*>(&flags[0])) {   // gave up: let the copies in flight land
         for (int j = max(0, issued - STAGES); j < issued; ++j) {
-          gs_wait_bounded(&full_bar[j % STAGES], (j / STAGES) & 1);
-          if (NORMED) gs_wait_bounded(&xraw_bar[j % STAGES], (j / STAGES) & 1);
+          kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&full_bar[j % STAGES], (j / STAGES) & 1);
+          if (NORMED) kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xraw_bar[j % STAGES], (j / STAGES) & 1);
         }
       }
     }
@@ -244,7 +200,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       const int total = u_end - u_begin;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        int fine = gs_wait_bounded(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
+        int fine = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
         fine = __all_sync(0xffffffffu, fine);
         if (!fine) {
           if (lane == 0) {
@@ -282,9 +238,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           }
         }
         // these writes come before the TMA box that will reuse the stage
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        kvb_fence_async_shared();
         __syncwarp();
-        if (lane == 0) gs_arrive(&xready_bar[stage]);
+        if (lane == 0) kvb_mbar_arrive(&xready_bar[stage]);
       }
     }
   } else {
@@ -309,14 +265,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       }
       for (; u < seg_end; ++u, ++it) {
         const int stage = it % STAGES;
-        bool landed = gs_wait_bounded(&full_bar[stage], (it / STAGES) & 1);
-        if (NORMED && landed) landed = gs_wait_bounded(&xready_bar[stage], (it / STAGES) & 1);
+        bool landed = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&full_bar[stage], (it / STAGES) & 1);
+        if (NORMED && landed) landed = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xready_bar[stage], (it / STAGES) & 1);
         if (!__all_sync(0xffffffffu, landed)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(&flags[0], 1);
           break;
         }
-        const unsigned wbase = gs_smem(base + stage * STAGE_BYTES);
+        const unsigned wbase = kvb_smem(base + stage * STAGE_BYTES);
         const unsigned xbase = wbase + W_BYTES;
         // fragments of step kk+1 are fetched while the products of step kk are issued; two
         // accumulator chains (even and odd steps) halve the dependent-issue latency
@@ -337,7 +293,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           for (int j = 0; j < MBLK; ++j) gs_mma(acc[cur][j], a[cur], b[cur][j][0], b[cur][j][1]);
         }
         __syncwarp();
-        if (lane == 0) gs_arrive(&empty_bar[stage]);
+        if (lane == 0) kvb_mbar_arrive(&empty_bar[stage]);
       }
 #pragma unroll
       for (int j = 0; j < MBLK; ++j) {

@@ -37,6 +37,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 #define TS_NT 256              // weight rows per tile: two MMA halves of 128
 #define TS_KS 64               // k-values per stage
@@ -61,74 +62,6 @@ struct TsParams {
   int silu_pairs;
 };
 
-__device__ __forceinline__ unsigned ts_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void ts_mbar_init(unsigned long long* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(ts_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void ts_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(ts_smem(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void ts_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(ts_smem(bar)) : "memory");
-}
-__device__ __forceinline__ bool ts_wait(unsigned long long* bar, unsigned parity) {
-  for (unsigned spin = 0; spin < TS_SPIN_LIMIT; ++spin) {
-    unsigned done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(ts_smem(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if (spin > 1024) __nanosleep(64);
-  }
-  return false;
-}
-__device__ __forceinline__ void ts_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(ts_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(ts_smem(bar))
-      : "memory");
-}
-// Shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of 8 rows
-// 1,024 bytes apart, version 1 (sm_100).
-__device__ __forceinline__ unsigned long long ts_desc(unsigned addr) {
-  return (unsigned long long)((addr & 0x3FFFFu) >> 4) | ((unsigned long long)(16u >> 4) << 16) |
-         ((unsigned long long)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void ts_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                       unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void ts_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(ts_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void ts_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void ts_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void ts_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned* r = reinterpret_cast<unsigned*>(v);
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void ts_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ int ts_ld_acquire(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void ts_st_release(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ float ts_round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 // First stage of block b when `units` stages are dealt to `blocks` blocks, and the block that holds stage u.
@@ -350,29 +283,27 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
   const int total = u_end - u_begin;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      ts_mbar_init(&full_bar[s], 1);
-      ts_mbar_init(&empty_bar[s], 1);
-      ts_mbar_init(&xraw_bar[s], 1);
-      ts_mbar_init(&xready_bar[s], TS_NORM_WARPS);
+      kvb_mbar_init(&full_bar[s], 1);
+      kvb_mbar_init(&empty_bar[s], 1);
+      kvb_mbar_init(&xraw_bar[s], 1);
+      kvb_mbar_init(&xready_bar[s], TS_NORM_WARPS);
     }
     for (int b = 0; b < 2; ++b) {
-      ts_mbar_init(&acc_full[b], 1);
-      ts_mbar_init(&acc_free[b], TS_EPI_WARPS);
+      kvb_mbar_init(&acc_full[b], 1);
+      kvb_mbar_init(&acc_free[b], TS_EPI_WARPS);
     }
-    ts_mbar_init(mma_done, 1);
-    ts_mbar_init(fix_bar, 1);
+    kvb_mbar_init(mma_done, 1);
+    kvb_mbar_init(fix_bar, 1);
     *abort_flag = 0;
     *epi_abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    kvb_mbar_init_fence();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(ts_smem(tmem_slot)), "r"(TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    kvb_tc5_alloc(tmem_slot, TMEM_COLS);
   }
-  ts_fence_before();
+  kvb_tc5_fence_before();
   __syncthreads();
-  ts_fence_after();
+  kvb_tc5_fence_after();
   kvb_grid_launch_dependents();
   const unsigned tmem_base = *tmem_slot;
 
@@ -384,15 +315,15 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       // written by no kernel of the step)
       for (int i = 0; i < pre; ++i) {
         const int u = u_begin + i;
-        ts_expect_tx(&full_bar[i], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
-        ts_tma_2d(base + i * STAGE_BYTES + X_BYTES, &w_map, (u % p.kchunks) * TS_KS, (u / p.kchunks) * TS_NT, &full_bar[i]);
+        kvb_mbar_expect_tx(&full_bar[i], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
+        kvb_tma_2d(base + i * STAGE_BYTES + X_BYTES, &w_map, (u % p.kchunks) * TS_KS, (u / p.kchunks) * TS_NT, &full_bar[i]);
       }
       kvb_grid_wait();                            // x is the output of the kernel in front
       trace.after_wait();
       int issued = 0;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        if (it >= STAGES && !ts_wait(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
+        if (it >= STAGES && !kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(abort_flag, 1);
           break;
@@ -402,21 +333,21 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         const int k0 = (u % p.kchunks) * TS_KS;
         unsigned char* xdst = base + stage * STAGE_BYTES;
         if (it >= pre) {
-          ts_expect_tx(&full_bar[stage], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
-          ts_tma_2d(xdst + X_BYTES, &w_map, k0, (u / p.kchunks) * TS_NT, &full_bar[stage]);
+          kvb_mbar_expect_tx(&full_bar[stage], (unsigned)(NORMED ? TS_W_BYTES : STAGE_BYTES));
+          kvb_tma_2d(xdst + X_BYTES, &w_map, k0, (u / p.kchunks) * TS_NT, &full_bar[stage]);
         }
         if (NORMED) {
-          ts_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
-          ts_tma_2d(xdst, &x_map, k0, 0, &xraw_bar[stage]);
+          kvb_mbar_expect_tx(&xraw_bar[stage], (unsigned)X_BYTES);
+          kvb_tma_2d(xdst, &x_map, k0, 0, &xraw_bar[stage]);
         } else {
-          ts_tma_2d(xdst, &x_map, k0, 0, &full_bar[stage]);
+          kvb_tma_2d(xdst, &x_map, k0, 0, &full_bar[stage]);
         }
         issued = it + 1;
       }
       if (*reinterpret_cast<volatile int*>(abort_flag)) {   // gave up: let the copies in flight land
         for (int j = max(0, issued - STAGES); j < issued; ++j) {
-          ts_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
-          if (NORMED) ts_wait(&xraw_bar[j % STAGES], (j / STAGES) & 1);
+          kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&full_bar[j % STAGES], (j / STAGES) & 1);
+          if (NORMED) kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&xraw_bar[j % STAGES], (j / STAGES) & 1);
         }
       }
     }
@@ -424,7 +355,7 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, M = 128 (token lanes), N = 256 (W rows)
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TS_NT >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+      const unsigned idesc = kvb_tc5_idesc(128, TS_NT, false);
       bool ok = true;
       int it = 0, seg = 0, u = u_begin;
       while (u < u_end && ok) {
@@ -432,27 +363,27 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         const int tile_end = (n_tile + 1) * p.kchunks;
         const int seg_end = tile_end < u_end ? tile_end : u_end;
         const int buf = seg & 1;
-        if (seg >= 2 && !ts_wait(&acc_free[buf], ((seg >> 1) - 1) & 1)) { ok = false; break; }
+        if (seg >= 2 && !kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&acc_free[buf], ((seg >> 1) - 1) & 1)) { ok = false; break; }
         bool first = true;
         for (; u < seg_end; ++u, ++it) {
           const int stage = it % STAGES;
-          if (!ts_wait(&full_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
-          if (NORMED && !ts_wait(&xready_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
+          if (!kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&full_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
+          if (NORMED && !kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&xready_bar[stage], (it / STAGES) & 1)) { ok = false; break; }
           if (*reinterpret_cast<volatile int*>(abort_flag)) { ok = false; break; }
-          ts_fence_after();
+          kvb_tc5_fence_after();
           // A: the MT token rows (the MMA reads 128 rows: lanes beyond MT see the bytes that follow,
           // which stay inside the stage, and no one reads those lanes); B: the 256 weight rows
-          const unsigned xbase = ts_smem(base + stage * STAGE_BYTES);
+          const unsigned xbase = kvb_smem(base + stage * STAGE_BYTES);
           const unsigned wbase = xbase + X_BYTES;
 #pragma unroll
           for (int kk = 0; kk < TS_KS / 16; ++kk)
-            ts_mma(tmem_base + buf * TS_NT, ts_desc(xbase + kk * 32), ts_desc(wbase + kk * 32), idesc,
+            kvb_tc5_mma(tmem_base + buf * TS_NT, kvb_tc5_desc(xbase + kk * 32, 16, 1024), kvb_tc5_desc(wbase + kk * 32, 16, 1024), idesc,
                    (first && kk == 0) ? 0u : 1u);
           first = false;
-          ts_commit(&empty_bar[stage]);           // the stage may be refilled once these MMAs have read it
+          kvb_tc5_commit(&empty_bar[stage]);           // the stage may be refilled once these MMAs have read it
         }
         if (!ok) break;
-        ts_commit(&acc_full[buf]);
+        kvb_tc5_commit(&acc_full[buf]);
         ++seg;
       }
       if (!ok) {
@@ -460,8 +391,8 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         atomicExch(abort_flag, 1);
       }
       // nothing of this block may still be running on the tensor cores when the memory is freed
-      ts_commit(mma_done);
-      ts_wait(mma_done, 0);
+      kvb_tc5_commit(mma_done);
+      kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(mma_done, 0);
     }
   } else if (warp < 2 + TS_EPI_WARPS) {
     // ---------------- epilogue: thread = token (accumulator lane); warp w reads lanes [32 (w mod 4), +32) ----------------
@@ -489,18 +420,18 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       const bool whole = kc0 == 0 && seg_end == tile_end;
       const int slot = kc0 == 0 ? 1 : 0;
       // the four warps decide together whether to go on: a wait that ran out in one of them ends all
-      if (!ts_wait(&acc_full[buf], (seg >> 1) & 1)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
+      if (!kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&acc_full[buf], (seg >> 1) & 1)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
       asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
       if (*reinterpret_cast<volatile int*>(epi_abort)) { ok = false; break; }
-      ts_fence_after();
+      kvb_tc5_fence_after();
       float* part = p.partial + ((size_t)me * 2 + slot) * PART_FLOATS;
       if (warp_live) {
 #pragma unroll 1
         for (int g = 0; g < 8; ++g) {
           if (n_tile * TS_NT + g * 32 >= p.N) break;       // rows beyond N: zeros, never read
           float v[32];
-          ts_ld32(tmem_base + lane_addr + buf * TS_NT + g * 32, v);
-          ts_wait_ld();
+          kvb_tc5_ld32(tmem_base + lane_addr + buf * TS_NT + g * 32, v);
+          kvb_tc5_wait_ld();
           if (tid < p.M) {
             if (whole) {
               ts_finish_row32(p, o, tid, n_tile * TS_NT + g * 32, v);
@@ -512,14 +443,14 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
           }
         }
       }
-      ts_fence_before();
+      kvb_tc5_fence_before();
       __syncwarp();
-      if (lane == 0) ts_arrive(&acc_free[buf]);
+      if (lane == 0) kvb_mbar_arrive(&acc_free[buf]);
       if (!whole) {
         shared_tile[slot] = n_tile;
         __threadfence();
         asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
-        if (tid == 0) ts_st_release(&p.flags[me * 2 + slot], 1);
+        if (tid == 0) kvb_st_release(&p.flags[me * 2 + slot], 1);
       }
       u = seg_end;
       ++seg;
@@ -555,7 +486,7 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
           const int* flag = &p.flags[(first_of[slot] + j) * 2 + (j == 0 ? 1 : 0)];
           int seen = 0;
           for (unsigned spin = 0; spin < TS_SPIN_LIMIT && !seen; ++spin) {
-            seen = ts_ld_acquire(flag);
+            seen = kvb_ld_acquire(flag);
             if (!seen && spin > 4096) __nanosleep(64);   // the blocks finish together: spin first
           }
           if (!seen) seen_all = false;
@@ -584,22 +515,19 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
         }
         if (staged > 0) {
           if (tid == 0) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            ts_expect_tx(fix_bar, staged);
+            kvb_fence_async_shared();
+            kvb_mbar_expect_tx(fix_bar, staged);
             for (int slot = s_lo; slot < s_hi; ++slot) {
               if (offset[slot] == 0xffffffffu || need[slot] == 0) continue;
               const unsigned piece = (unsigned)(g_hi[slot] - g_lo[slot]) * GROUP_BYTES;
               for (int j = 0; j < parts_of[slot]; ++j) {
                 const float* src = p.partial + ((size_t)(first_of[slot] + j) * 2 + (j == 0 ? 1 : 0)) * PART_FLOATS +
                                    (size_t)g_lo[slot] * MT * 32;
-                asm volatile(
-                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-                    ::"r"(ts_smem(base + offset[slot] + j * piece)), "l"(src), "r"(piece), "r"(ts_smem(fix_bar))
-                    : "memory");
+                kvb_bulk_copy(base + offset[slot] + j * piece, src, piece, fix_bar);
               }
             }
           }
-          if (!ts_wait(fix_bar, phase)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
+          if (!kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(fix_bar, phase)) *reinterpret_cast<volatile int*>(epi_abort) = 1;
           phase ^= 1;
           asm volatile("bar.sync 1, %0;\n" ::"n"(TS_EPI_WARPS * 32));
           if (*reinterpret_cast<volatile int*>(epi_abort)) {
@@ -707,7 +635,7 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
       const int chunk = nt & 7, row0 = nt >> 3;            // 16 bytes of a row; rows row0, row0 + 16, ...
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        int fine = ts_wait(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
+        int fine = kvb_mbar_wait<TS_SPIN_LIMIT, 1024>(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
         fine = __all_sync(0xffffffffu, fine);
         if (!fine) {
           if (lane == 0) {
@@ -748,19 +676,19 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
           *reinterpret_cast<uint4*>(xs + r * 128 + ((chunk ^ (r & 7)) << 4)) = o.raw;
         }
         // these writes come before the MMAs that read the stage and the TMA box that will reuse it
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        kvb_fence_async_shared();
         __syncwarp();
-        if (lane == 0) ts_arrive(&xready_bar[stage]);
+        if (lane == 0) kvb_mbar_arrive(&xready_bar[stage]);
       }
     }
   }
 
   // ---- everyone meets; the allocating warp frees the tensor memory ----
-  ts_fence_before();
+  kvb_tc5_fence_before();
   __syncthreads();
   if (warp == 1) {
-    ts_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+    kvb_tc5_fence_after();
+    kvb_tc5_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
