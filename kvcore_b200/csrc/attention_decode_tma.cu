@@ -512,23 +512,6 @@ __global__ void flash_decode_combine_kernel(const DecodeParams p) {
 }
 
 // ---- host side -----------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 // Writes a 128-byte tensor map describing one layer's K (or V) cache [pages, KVH, page, D] bf16
 // as a 2-D tensor of 64-element rows [pages*KVH*page*(D/64) rows, 64 columns] with boxes of
 // [page*(D/64) rows, 64 columns]: one box is the contiguous block of one page and kv head.
@@ -538,7 +521,7 @@ extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long lon
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
               "kv tensor map: page size must be 8, 16, 32 or 64");
   KVB_REQUIRE(aligned16(cache), "kv tensor map: the cache must be 16-byte aligned");
-  EncodeTiledFn encode = encode_tiled_fn();
+  KvbEncodeTiledFn encode = kvb_encode_tiled_fn();
   KVB_REQUIRE(encode != nullptr, "kv tensor map: the driver does not export cuTensorMapEncodeTiled");
   alignas(64) CUtensorMap map;
   const int halves = D / 64;

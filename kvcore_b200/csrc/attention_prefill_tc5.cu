@@ -413,22 +413,6 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
 }
 
 // ---- host side -----------------------------------------------------------------------------
-typedef CUresult (*T5EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static T5EncodeFn t5_encode_fn() {
-  static T5EncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<T5EncodeFn>(ptr);
-  }
-  return fn;
-}
-
 // Tensor map of one layer's K (or V) cache [pages, KVH, page, 128] bf16 as [rows, 128 columns] with
 // boxes of [page rows, 64 columns] (one 64-column half of a page of a head), 128-byte swizzle.
 extern "C" int kvb_make_kv_half_tensor_map(void* map_out, const void* cache, long long num_pages, int KVH,
@@ -437,7 +421,7 @@ extern "C" int kvb_make_kv_half_tensor_map(void* map_out, const void* cache, lon
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
               "kv half tensor map: page size must be 8, 16, 32 or 64");
   KVB_REQUIRE(aligned16(cache), "kv half tensor map: the cache must be 16-byte aligned");
-  T5EncodeFn encode = t5_encode_fn();
+  KvbEncodeTiledFn encode = kvb_encode_tiled_fn();
   KVB_REQUIRE(encode != nullptr, "kv half tensor map: the driver does not export cuTensorMapEncodeTiled");
   alignas(64) CUtensorMap map;
   const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * KVH * page_size};

@@ -489,28 +489,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 }
 
 // ---- host side -----------------------------------------------------------------------------
-typedef CUresult (*GsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static GsEncodeFn gs_encode_fn() {
-  static GsEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<GsEncodeFn>(ptr);
-  }
-  return fn;
-}
-
 // 3-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements),
 // seen as [cols / 64 slabs][rows][64]: boxes of [GS_KG slabs][box_rows][64], 128-byte swizzle, zero
 // fill outside.  cols must be a multiple of 64.
 static int gs_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld,
                        int box_rows) {
-  GsEncodeFn encode = gs_encode_fn();
+  KvbEncodeTiledFn encode = kvb_encode_tiled_fn();
   KVB_REQUIRE(encode != nullptr, "stream gemm: the driver does not export cuTensorMapEncodeTiled");
   const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
   const cuuint64_t strides[2] = {(cuuint64_t)ld * sizeof(bf16), 64 * sizeof(bf16)};

@@ -693,26 +693,10 @@ gemm_stream_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_c
 }
 
 // ---- host side -----------------------------------------------------------------------------
-typedef CUresult (*TsEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static TsEncodeFn ts_encode_fn() {
-  static TsEncodeFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<TsEncodeFn>(ptr);
-  }
-  return fn;
-}
-
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements):
 // boxes of [box_rows][64 columns], 128-byte swizzle, zero fill outside.
 static int ts_make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
-  TsEncodeFn encode = ts_encode_fn();
+  KvbEncodeTiledFn encode = kvb_encode_tiled_fn();
   KVB_REQUIRE(encode != nullptr, "stream gemm (tcgen05): the driver does not export cuTensorMapEncodeTiled");
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};

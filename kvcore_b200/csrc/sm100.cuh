@@ -146,3 +146,22 @@ __device__ __forceinline__ void kvb_tc5_st32(unsigned taddr, const float (&v)[32
 }
 __device__ __forceinline__ void kvb_tc5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void kvb_tc5_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// ---- host side: tensor maps -------------------------------------------------------------------
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link the
+// driver); null if the driver does not export it.
+typedef CUresult (*KvbEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static inline KvbEncodeTiledFn kvb_encode_tiled_fn() {
+  static KvbEncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<KvbEncodeTiledFn>(ptr);
+  }
+  return fn;
+}
