@@ -66,6 +66,37 @@ def test_greedy_generation_matches_plain(device, tmp_path, name, lengths, steps,
     assert not kv.live_requests() and not engine.engine_core.model_runner.requests
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_bfloat16_generation_on_serving_shapes_picks_tokens_the_plain_logits_allow(tmp_path, name):
+    """Head sizes 128 and 64, prompts of several key tiles, chunked prefill beside decoding, decode
+    steps replayed from graphs: the path that serves (TMA decode attention with its rotation, the
+    streaming products with norm, activation and residual inside, the tcgen05 prompt attention).
+    In bfloat16 a near-tie may fall either way, so every generated token must be one whose plain
+    32-bit logit lies within the rounding bound of the largest."""
+    config = rc.TINY_CONFIGS[name]
+    folder = rc.write_model(tmp_path / "m", config, rc.TINY_SEEDS[name], "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    prompts = [rc.random_tokens(config["vocab_size"], n, 80 + i) for i, n in enumerate((70, 150, 33, 9))]
+    steps = 40
+    engine = LLMEngine(engine_config(folder, "cuda:0", dtype="bfloat16", max_model_len=256, num_gpu_blocks=80,
+                                     scheduler=dict(max_num_scheduled_tokens=48)))
+    outputs = engine.generate([GenerationRequest(f"r{i}", SamplingParams(max_tokens=steps, temperature=0.0), tuple(p))
+                               for i, p in enumerate(prompts)])
+    runner = engine.engine_core.model_runner
+    assert runner.step_function.num_graph_replays > 0
+    for prompt, output in zip(prompts, outputs):
+        tokens = list(output.output_token_ids)
+        assert len(tokens) == steps and output.finish_reason == "length"
+        logits = plain_llama.forward_logits(config, weights, prompt + tokens).numpy()
+        bound = 2 * 2e-2 * np.abs(logits).max()       # both candidates may be off by the bfloat16 tolerance
+        for index, token in enumerate(tokens):
+            row = logits[len(prompt) + index - 1]
+            assert row[token] >= row.max() - bound, f"token {index}: {row[token]} against {row.max()}"
+    runner.kv_manager.check_invariants()
+    assert not runner.kv_manager.live_requests()
+
+
 def test_generation_with_few_pages_and_preemption(device, tmp_path):
     """So few pages that requests wait, are preempted and recomputed: tokens stay the plain ones."""
     config = rc.TINY_CONFIGS["A"]
