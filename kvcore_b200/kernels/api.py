@@ -522,7 +522,7 @@ STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
 # KVCORE_B200_STREAM_TC5_ROWS raises the bound.
 STREAM_TC5_MAX_ROWS = 128
 STREAM_TC5_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_TC5_ROWS", "0"))
-_stream_scratch: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor]] = {}
+_stream_scratch: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor | None]] = {}
 
 
 TRACE_TAGS = {1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
