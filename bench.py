@@ -34,6 +34,22 @@ LLAMA_31_8B = dict(
     rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
 )
+LLAMA_32_3B = dict(
+    LLAMA_31_8B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28, num_attention_heads=24,
+    tie_word_embeddings=True,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+)
+LLAMA_3_70B = dict(
+    LLAMA_31_8B, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80, num_attention_heads=64,
+    max_position_embeddings=8192, rope_scaling=None,
+)
+# name -> (config.json, label, context of the headline decode number, batches of the side points)
+SHAPES = {
+    "llama31_8b": (LLAMA_31_8B, "Llama-3.1-8B shape", 8192, (1, 64)),
+    "llama32_3b": (LLAMA_32_3B, "Llama-3.2-3B shape", 8192, (1, 64)),
+    "llama3_70b": (LLAMA_3_70B, "Llama-3-70B shape", 2048, (1, 32)),
+}
 CONTEXT_LEN = 8192
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
@@ -109,14 +125,14 @@ def model_numbers(config: dict, layers: int) -> dict:
     )
 
 
-def build_runner(layers: int, max_seqs: int, max_len: int, num_pages: int, max_tokens: int):
+def build_runner(shape: dict, layers: int, max_seqs: int, max_len: int, num_pages: int, max_tokens: int):
     import torch
 
     from kvcore_b200 import CacheConfig, DeviceConfig, KVCoreConfig, LoadConfig, ModelConfig, SchedulerConfig
     from kvcore_b200.engine.runner import ModelRunner
 
     folder = Path(tempfile.mkdtemp(prefix="kvcore_bench_"))
-    (folder / "config.json").write_text(json.dumps(dict(LLAMA_31_8B, num_hidden_layers=layers)))
+    (folder / "config.json").write_text(json.dumps({k: v for k, v in dict(shape, num_hidden_layers=layers).items() if v is not None}))
     config = KVCoreConfig(
         model_config=ModelConfig(model=str(folder), dtype="bfloat16", max_model_len=max_len),
         load_config=LoadConfig(random_weights=True, seed=0),
@@ -264,9 +280,11 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=32)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--layers", type=int, default=LLAMA_31_8B["num_hidden_layers"])
+    parser.add_argument("--shape", default="llama31_8b", choices=sorted(SHAPES),
+                        help="layer sizes of the model; the default is the headline configuration")
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--context", type=int, default=CONTEXT_LEN)
+    parser.add_argument("--context", type=int, default=None)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="only the headline decode number")
     parser.add_argument("--only-prefill", action="store_true",
@@ -283,14 +301,17 @@ def main() -> int:
 
     import kvcore_b200.kernels as K
 
+    shape, label, shape_context, side_batches = SHAPES[args.shape]
+    args.layers = args.layers or shape["num_hidden_layers"]
+    args.context = args.context or shape_context
     peaks = measured_peaks()
-    numbers = model_numbers(LLAMA_31_8B, args.layers)
-    max_batch = args.batch if args.skip_points else max(64, args.batch)
+    numbers = model_numbers(shape, args.layers)
+    max_batch = args.batch if args.skip_points else max(max(side_batches), args.batch)
     prefill_steps = -(-max(args.context, PREFILL_TOKENS) // PREFILL_TOKENS)
     margin = args.steps + args.warmup + 8 + args.batch * prefill_steps  # e2e: early requests decode during prefill
     max_len = max(args.context, PREFILL_TOKENS) + margin
     pages = max_batch * (-(-max_len // BLOCK_SIZE)) + 1
-    config, runner = build_runner(args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))
+    config, runner = build_runner(shape, args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))
 
     if args.only_prefill:
         ms_prefill = time_prefill(runner, PREFILL_TOKENS, repeats=max(1, args.steps), warmup=2)
@@ -306,9 +327,9 @@ def main() -> int:
     prefill = None
     e2e = None
     if not args.skip_points:
-        for batch in (1, 64):
+        for batch in side_batches:
             points[f"decode_b{batch}"] = round(batch * 1000.0 / time_decode(runner, batch, args.context, args.steps, args.warmup), 2)
-        for batch in (1, 8, 64):
+        for batch in (side_batches[0], args.batch, side_batches[1]):
             points[f"decode_b{batch}_ctx1024"] = round(batch * 1000.0 / time_decode(runner, batch, 1024, args.steps, args.warmup), 2)
         ms_prefill = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
         t, h, d = PREFILL_TOKENS, numbers["heads"], numbers["head_dim"]
@@ -329,7 +350,7 @@ def main() -> int:
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
     value = args.batch * 1000.0 / ms_step
     line = {
-        "metric": "decode tokens/s, Llama 3.1 8B shape, batch 8, bf16",
+        "metric": f"decode tokens/s, {label.replace('-', ' ')}, batch {args.batch}, bf16",
         "value": round(value, 2),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -343,11 +364,13 @@ def main() -> int:
         "data": "synthetic: random N(0,0.02) weights, seeded uniform-random token ids, random cache contents",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.1-8B shape", "layers": args.layers, "layers_of_config": LLAMA_31_8B["num_hidden_layers"],
-            "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
-            "vocab": 128256, "global_batch": args.batch, "seq_len": args.context, "context_len": args.context,
+            "model": label, "layers": args.layers, "layers_of_config": shape["num_hidden_layers"],
+            "hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
+            "kv_heads": shape["num_key_value_heads"], "head_dim": shape["head_dim"],
+            "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+            "tied_embeddings": shape["tie_word_embeddings"], "global_batch": args.batch, "seq_len": args.context, "context_len": args.context,
             "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
-            "l2": "weights of 15 GB stream every step: inputs larger than L2",
+            "l2": f"weights of {2e-9 * numbers['streamed_params']:.0f} GB stream every step: inputs larger than L2",
         },
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"],

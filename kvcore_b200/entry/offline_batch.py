@@ -95,7 +95,7 @@ def build_requests(args: argparse.Namespace, vocab_size: int) -> list[dict]:
             requests.append(dict(request_id=str(spec.get("request_id", f"offline-{index:03d}")),
                                  prompt_token_ids=spec.get("prompt_token_ids"),
                                  messages=spec.get("messages"),
-                                 sampling_params=SamplingParams(**params)))
+                                 sampling_params=SamplingParams.from_mapping(params)))
         return requests
     count, length = (int(x) for x in (args.random_prompts or "4:32").split(":"))
     import torch

@@ -20,9 +20,9 @@ from typing import Sequence
 import torch
 
 from .. import kernels as K
-from .params import SamplingParams
+from .params import GREEDY_BELOW, SamplingParams
 
-SAMPLING_EPS = 1e-5  # sampler.py:11
+SAMPLING_EPS = GREEDY_BELOW  # one threshold for the host's view and the kernel's
 
 
 class Sampler:
@@ -86,7 +86,7 @@ class Sampler:
             [
                 (
                     p.temperature,
-                    vocab if p.top_k is None else min(p.top_k, vocab),
+                    p.kept_logits(vocab),
                     p.top_p,
                     float(int(seed) & 0xFFFFFFFF),
                     float((int(seed) >> 32) & 0xFFFFFFFF),
