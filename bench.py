@@ -1,6 +1,7 @@
 """Benchmark: decode and prefill throughput of the Llama 3.1 8B shape with random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+                    [--shape llama31_8b|llama32_3b|llama3_70b] [--serve]
 
 Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 with every request
 holding ``context_len`` tokens in the cache (a "step" is one decode step of the whole batch,
@@ -11,6 +12,11 @@ sampled tokens back.  ``prefill`` times one 2,048-token prompt; ``roofline`` rel
 a decode step must read (every weight once, and the cache of the live requests) to its
 time.  ``points`` holds decode at batch 1 and 64, and the same batches at 1,024 tokens of
 context.  Weights are 15 GB, so consecutive steps cannot reuse the L2 cache.
+
+``--shape`` runs the same measurements at the layer sizes of Llama 3.2 3B (tied embeddings, 3 query
+heads a kv head) or Llama 3 70B (8 query heads a kv head, 2,048 tokens of context, batches 1/8/32);
+``--serve`` times continuous batching of 64 requests through ``LLMEngine.generate`` instead and
+prints a line of its own.
 """
 from __future__ import annotations
 
@@ -246,14 +252,57 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
         produced += sum(1 for o in engine.step().request_outputs if o.sampled_token_id is not None)
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - begin
-    assert runner.step_function.num_steps - used_before == steps
+    # with a step kept in flight, one more step than has been read is launched at either end
+    assert abs(runner.step_function.num_steps - used_before - steps) <= 1
     assert produced == steps * batch, f"{produced} tokens from {steps} steps of {batch} requests"
     ctx = runner.step_function.last_context
     h2d = 4 * (4 * (batch + 4) + 4 * batch + batch * ctx.table_width) + batch * 6 * 8
+    if engine.engine_core.num_steps_run_ahead:
+        h2d += 4 * batch   # which row of the sampler output each token id comes from
+    engine.engine_core.drain()
     engine.engine_core.scheduler.shutdown()
     runner.remove_requests(list(runner.requests))
     return {"value": produced / elapsed, "unit": "tokens/s", "ms_per_step": 1000.0 * elapsed / steps,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+            "steps_launched_ahead": engine.engine_core.num_steps_run_ahead}
+
+
+def time_serving(shape: dict, layers: int, requests: int, min_prompt: int, max_prompt: int, chunk: int,
+                 max_tokens: int) -> dict:
+    """Continuous batching through ``LLMEngine.generate``: ``requests`` prompts of seeded random
+    lengths in [min_prompt, max_prompt], at most ``chunk`` tokens a step (portions of prompts beside
+    the decoding requests), ``max_tokens`` greedy tokens each.  Host wall clock, everything included."""
+    import torch
+
+    from kvcore_b200.engine.llm_engine import LLMEngine
+    from kvcore_b200.sampling import SamplingParams
+
+    generator = torch.Generator().manual_seed(4)
+    lengths = torch.randint(min_prompt, max_prompt + 1, (requests,), generator=generator).tolist()
+    max_len = max_prompt + max_tokens
+    pages = sum(-(-(n + max_tokens) // BLOCK_SIZE) for n in lengths) + 1
+    config, runner = build_runner(shape, layers, requests, max_len, pages, chunk)
+    vocab = runner.model.spec.vocab_size
+    batch = [dict(request_id=f"serve-{i}", sampling_params=SamplingParams(max_tokens=max_tokens, temperature=0.0),
+                  prompt_token_ids=torch.randint(0, vocab, (n,), generator=generator).tolist())
+             for i, n in enumerate(lengths)]
+    engine = LLMEngine(config, model_runner=runner)
+    engine.generate(batch[:2])  # warm-up: kernels loaded, first graphs captured
+    for item in batch:
+        item["request_id"] += "-timed"
+    torch.cuda.synchronize()
+    steps_before = runner.step_function.num_steps
+    begin = time.perf_counter()
+    outputs = engine.generate(batch)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - begin
+    generated = sum(len(o.output_token_ids) for o in outputs)
+    assert generated == requests * max_tokens, f"{generated} tokens from {requests} requests"
+    return {"seconds": round(elapsed, 3), "requests": requests, "prompt_tokens": sum(lengths),
+            "generated_tokens": generated, "steps": runner.step_function.num_steps - steps_before,
+            "generated_tokens_per_s": round(generated / elapsed, 1),
+            "total_tokens_per_s": round((generated + sum(lengths)) / elapsed, 1),
+            "chunk": chunk, "prompt_lengths": f"{min_prompt}-{max_prompt}", "max_tokens": max_tokens}
 
 
 def reference_arm(args) -> int:
@@ -289,6 +338,9 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="only the headline decode number")
     parser.add_argument("--only-prefill", action="store_true",
                         help="time the 2,048-token prefill alone and print its line (for profiling)")
+    parser.add_argument("--serve", action="store_true",
+                        help="continuous batching instead: 64 requests of 128-4,096 random prompt tokens, "
+                             "512 tokens a step, 128 generated tokens each, through LLMEngine.generate")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -311,6 +363,16 @@ def main() -> int:
     margin = args.steps + args.warmup + 8 + args.batch * prefill_steps  # e2e: early requests decode during prefill
     max_len = max(args.context, PREFILL_TOKENS) + margin
     pages = max_batch * (-(-max_len // BLOCK_SIZE)) + 1
+    if args.serve:
+        import kvcore_b200.kernels as K
+
+        result = time_serving(shape, args.layers, 64, 128, 4096, 512, 128)
+        status = K.read_status()
+        if status:
+            raise RuntimeError(f"a kernel reported status {status} during the measurement: the numbers are void")
+        print(json.dumps({"metric": f"continuous batching, {label.replace('-', ' ')}, bf16", "impl": "ours",
+                          "layers": args.layers, "layers_of_config": shape["num_hidden_layers"], **result}))
+        return 0
     config, runner = build_runner(shape, args.layers, max_batch, max_len, pages, max(PREFILL_TOKENS, max_batch))
 
     if args.only_prefill:

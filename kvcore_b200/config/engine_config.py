@@ -102,6 +102,8 @@ class SchedulerConfig:
     ``preempt_on_deadlock``: when every running request is blocked on pages and nothing
     can be scheduled, free the youngest running request and queue it for recompute instead
     of reporting no progress (the reference only reports; kvcore/sched/scheduler.py:263-273).
+    ``run_ahead``: keep one step in flight: a batch in steady decoding has its next step planned
+    and launched before the tokens of the current one are read (not in the reference).
     """
 
     max_num_seqs: int = 8
@@ -110,6 +112,7 @@ class SchedulerConfig:
     max_long_partial_prefills: int = 1
     long_prefill_token_threshold: int = 0
     preempt_on_deadlock: bool = True
+    run_ahead: bool = True
 
     def __post_init__(self) -> None:
         for name in (

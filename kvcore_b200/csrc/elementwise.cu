@@ -53,6 +53,39 @@ extern "C" int kvb_gather_rows(void* out, const void* table, const int* ids, int
 }
 
 // ------------------------------------------------------------------------------------------
+// Token feedback: token_ids[t] = sampled[source[t]] where source[t] >= 0.  Lets a decode step be
+// launched before the host has seen the tokens that the step in front sampled: the host packs a
+// placeholder id and names the row of the earlier sampler output that holds the real one.
+// ------------------------------------------------------------------------------------------
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ source,
+                                   const int* __restrict__ sampled, int count, int sampled_rows,
+                                   int* status) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_FEED_TOKENS);
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= count) return;
+  const int row = source[t];
+  if (row < 0) return;
+  if (row >= sampled_rows) {   // never reads outside the sampler's output
+    atomicOr(status, KVB_STATUS_BAD_TOKEN);
+    return;
+  }
+  token_ids[t] = sampled[row];
+}
+
+extern "C" int kvb_feed_tokens(int* token_ids, const int* source, const int* sampled, int count,
+                               int sampled_rows, cudaStream_t stream) {
+  if (count == 0) return 0;
+  KVB_REQUIRE(sampled_rows > 0, "feed_tokens: no sampled tokens to take from");
+  int* status = kvb_status_word();
+  KVB_REQUIRE(status != nullptr, "feed_tokens: no status word");
+  const int threads = 128;
+  KVB_CHECK_CUDA(kvb_launch((feed_tokens_kernel), dim3((count + threads - 1) / threads), dim3(threads), 0,
+                            stream, true, token_ids, source, sampled, count, sampled_rows, status));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
 // RMS norm.  One block of 256 threads per row, whatever the batch: the reduction tree depends
 // on the width only, so a row's result does not depend on what else is in the batch.
 //   ADD: s = h + residual (rounded to T, stored back as the new residual), else s = h

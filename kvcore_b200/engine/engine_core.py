@@ -4,6 +4,14 @@ Same loop as the reference's engine core (kvcore/engine/engine_core.py:38-152, 2
 scheduler owns request state and the cache manager's bookkeeping, the runner owns the model
 and the cache tensors; stop tokens come from config.json's ``eos_token_id`` and from the
 tokenizer when there is one.
+
+Not in the reference: with ``SchedulerConfig.run_ahead`` the core keeps one step in flight.  While
+the device runs step k, the host plans step k+1 where that is possible without k's tokens
+(``Scheduler.schedule_ahead``: a batch in steady decoding), launches it with the token ids fed
+from the sampler's output on the device, and only then waits for k's tokens.  The device no
+longer idles through the host's share of a step; ``step()`` still returns one step's outputs per
+call, in order.  A request that stops on a token is seen one step late: the extra token it
+computed meanwhile is dropped, so outputs are the same as without running ahead.
 """
 from __future__ import annotations
 
@@ -15,8 +23,8 @@ from ..config.engine_config import KVCoreConfig
 from ..sampling.params import SamplingParams
 from ..utils.tokenizer import TokenizerManager
 from .request import FinishReason, Request
-from .runner import ModelRunner
-from .scheduler import RequestStepOutput, Scheduler
+from .runner import ModelRunner, SampleHandle
+from .scheduler import RequestStepOutput, Scheduler, SchedulerOutput
 
 logger = logging.getLogger("kvcore_b200.engine")
 
@@ -42,6 +50,9 @@ class EngineCore:
         self.stop_token_ids.update(self.model_runner.model.spec.eos_token_ids)
         self.scheduler = Scheduler(config.scheduler_config, self.model_runner.kv_manager)
         self.finished_outputs: dict[str, FinishedRequestOutput] = {}
+        self.run_ahead = bool(config.scheduler_config.run_ahead)
+        self._in_flight: tuple[SchedulerOutput, SampleHandle] | None = None
+        self.num_steps_run_ahead = 0
 
     def add_request(
         self,
@@ -64,28 +75,50 @@ class EngineCore:
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished_requests()
 
+    def _launch(self, plan: SchedulerOutput, feed: SampleHandle | None = None) -> tuple[SchedulerOutput, SampleHandle]:
+        self.model_runner.execute_model(plan, feed)
+        return plan, self.model_runner.launch_sampling()
+
     def step(self) -> EngineCoreOutputs:
-        scheduler_output = self.scheduler.schedule()
-        if scheduler_output.total_num_scheduled_tokens == 0:
-            self.model_runner.remove_requests(scheduler_output.finished_req_ids)
-            self.model_runner.remove_requests(scheduler_output.preempted_req_ids)
-            return EngineCoreOutputs()
-        self.model_runner.execute_model(scheduler_output)
-        runner_output = self.model_runner.sample_tokens()
+        if self._in_flight is None:
+            plan = self.scheduler.schedule()
+            if plan.total_num_scheduled_tokens == 0:
+                self.model_runner.remove_requests(plan.finished_req_ids)
+                self.model_runner.remove_requests(plan.preempted_req_ids)
+                return EngineCoreOutputs()
+            self._in_flight = self._launch(plan)
+        plan, handle = self._in_flight
+        ahead = None
+        if self.run_ahead:
+            next_plan = self.scheduler.schedule_ahead(plan)
+            if next_plan is not None:
+                ahead = self._launch(next_plan, feed=handle)
+                self.num_steps_run_ahead += 1
+        runner_output = self.model_runner.collect(handle)
         sampled = {
             req_id: tokens[0]
             for req_id, tokens in zip(runner_output.req_ids, runner_output.sampled_token_ids)
             if tokens
         }
-        update = self.scheduler.update_from_outputs(
-            scheduler_output, sampled, stop_token_ids=self.stop_token_ids
-        )
+        update = self.scheduler.update_from_outputs(plan, sampled, stop_token_ids=self.stop_token_ids)
         for finished in update.finished_requests:
             self.finished_outputs[finished.request_id] = FinishedRequestOutput(
                 finished.request_id, finished.output_token_ids, finished.finish_reason
             )
         self.model_runner.remove_requests([f.request_id for f in update.finished_requests])
+        if ahead is not None and not any(r in self.scheduler.requests for r in ahead[0].num_scheduled_tokens):
+            # every request of the step launched ahead has just ended: its tokens are nobody's
+            self.model_runner.collect(ahead[1])
+            self.model_runner.remove_requests(ahead[0].num_scheduled_tokens)
+            ahead = None
+        self._in_flight = ahead
         return EngineCoreOutputs(update.step_outputs)
+
+    def drain(self) -> None:
+        """Wait for a step that was launched ahead and drop its tokens (after an abort)."""
+        if self._in_flight is not None:
+            self.model_runner.collect(self._in_flight[1])
+            self._in_flight = None
 
     def take_finished_output(self, request_id: str) -> FinishedRequestOutput | None:
         return self.finished_outputs.pop(request_id, None)

@@ -98,6 +98,26 @@ class _PendingSample:
     sampled_req_ids: list[str]
 
 
+@dataclass
+class SampleHandle:
+    """Tokens that the device is sampling (or has sampled) and the host has not read yet.
+
+    ``tokens`` (int32 on the device, one row per sampled request) can feed the next step before
+    anyone has seen it; ``collect`` waits for ``ready`` and reads the pinned copy."""
+
+    req_ids: list[str]
+    states: list[CachedRequestState]
+    tokens: torch.Tensor | None = None
+    host: torch.Tensor | None = None
+    ready: "torch.cuda.Event | None" = None
+
+    def row_of(self, request_id: str) -> int | None:
+        for row, state in enumerate(self.states):
+            if state.request_id == request_id:
+                return row
+        return None
+
+
 class ModelRunner:
     def __init__(self, config: KVCoreConfig, model: DecoderModel | None = None) -> None:
         self.config = config
@@ -145,6 +165,9 @@ class ModelRunner:
         self.requests: dict[str, CachedRequestState] = {}
         self._pending: _PendingSample | None = None
         self.last_stats = StepStats()
+        # sampled tokens come back through pinned buffers in turn; two steps may be unread at once
+        self._token_buffers: list[tuple[torch.Tensor, torch.cuda.Event]] = []
+        self._token_turn = 0
 
     # ---- cache sizing ------------------------------------------------------------------------
     def bytes_per_page(self) -> list[int]:
@@ -189,8 +212,12 @@ class ModelRunner:
         return [int(min(pages, ceiling))] * len(self.groups)
 
     # ---- one step ------------------------------------------------------------------------------
-    def execute_model(self, scheduler_output: SchedulerOutput) -> None:
-        """Run the scheduled tokens; logits are kept for ``sample_tokens``."""
+    def execute_model(self, scheduler_output: SchedulerOutput, feed: SampleHandle | None = None) -> None:
+        """Run the scheduled tokens; logits are kept for ``sample_tokens``.
+
+        ``feed``: the handle of the step in front, when ``scheduler_output`` was planned before that
+        step's tokens were read (its ``pending_token_req_ids``): those requests' tokens are taken
+        from the sampler's output on the device."""
         if self._pending is not None:
             raise RuntimeError("execute_model called twice without sample_tokens")
         started = time.perf_counter()
@@ -226,9 +253,16 @@ class ModelRunner:
             if end >= len(state.token_ids):
                 want = (num_tokens - 1,)
                 sampled_req_ids.append(req_id)
-            entries.append(StepEntry(req_id, state.token_ids[start:end], want))
+            if req_id in scheduler_output.pending_token_req_ids:
+                row = None if feed is None else feed.row_of(req_id)
+                if row is None or num_tokens != 1 or start != len(state.token_ids):
+                    raise RuntimeError(f"request {req_id!r} was planned on a token that no step in flight samples")
+                entries.append(StepEntry(req_id, (0,), want, fed_from=row))
+            else:
+                entries.append(StepEntry(req_id, state.token_ids[start:end], want))
             req_ids.append(req_id)
-        logits = self.step_function.step(entries) if entries else None
+        feedback = feed.tokens if feed is not None and scheduler_output.pending_token_req_ids else None
+        logits = self.step_function.step(entries, feedback) if entries else None
         self._pending = _PendingSample(logits, req_ids, sampled_req_ids)
         self.last_stats = StepStats(
             num_reqs=len(entries),
@@ -237,32 +271,59 @@ class ModelRunner:
             forward_sec=time.perf_counter() - started,
         )
 
-    def sample_tokens(self) -> ModelRunnerOutput:
+    def launch_sampling(self) -> SampleHandle:
+        """Start sampling from the logits of the last ``execute_model`` and start their copy to
+        the host; returns at once."""
         if self._pending is None:
             raise RuntimeError("sample_tokens called without execute_model")
         pending, self._pending = self._pending, None
         started = time.perf_counter()
-        sampled: dict[str, int] = {}
-        if pending.sampled_req_ids:
-            states = [self.requests[r] for r in pending.sampled_req_ids]
-            tokens = self.sampler.sample(
+        states = [self.requests[r] for r in pending.sampled_req_ids]
+        handle = SampleHandle(pending.req_ids, states)
+        if states:
+            handle.tokens = self.sampler.sample(
                 pending.logits,
                 [s.sampling_params for s in states],
                 [s.seed for s in states],
                 [s.num_sampled for s in states],
-            ).tolist()
+            )
+            for state in states:
+                state.num_sampled += 1
+            if handle.tokens.device.type == "cuda":
+                if len(self._token_buffers) < 4:
+                    self._token_buffers.append((torch.empty(self.max_num_seqs, dtype=torch.int32, pin_memory=True),
+                                                torch.cuda.Event()))
+                buffer, event = self._token_buffers[self._token_turn % len(self._token_buffers)]
+                self._token_turn += 1
+                handle.host = buffer[: len(states)]
+                handle.host.copy_(handle.tokens, non_blocking=True)
+                event.record()
+                handle.ready = event
+            else:
+                handle.host = handle.tokens
+        self.last_stats.sample_sec = time.perf_counter() - started
+        return handle
+
+    def collect(self, handle: SampleHandle) -> ModelRunnerOutput:
+        """Wait for the tokens of ``handle`` and record them in the requests' token lists."""
+        sampled: dict[str, int] = {}
+        if handle.states:
+            if handle.ready is not None:
+                handle.ready.synchronize()
+            tokens = handle.host.tolist()
             # the step has finished (its tokens are here): anything its kernels reported is read
             # from host memory, without another round trip
             K.raise_on_status()
-            for state, token in zip(states, tokens):
+            for state, token in zip(handle.states, tokens):
                 state.token_ids.append(int(token))
-                state.num_sampled += 1
                 sampled[state.request_id] = int(token)
-        self.last_stats.sample_sec = time.perf_counter() - started
         return ModelRunnerOutput(
-            req_ids=pending.req_ids,
-            sampled_token_ids=[[sampled[r]] if r in sampled else [] for r in pending.req_ids],
+            req_ids=handle.req_ids,
+            sampled_token_ids=[[sampled[r]] if r in sampled else [] for r in handle.req_ids],
         )
+
+    def sample_tokens(self) -> ModelRunnerOutput:
+        return self.collect(self.launch_sampling())
 
     def remove_requests(self, request_ids) -> None:
         for request_id in request_ids:
@@ -273,6 +334,7 @@ __all__ = [
     "CachedRequestState",
     "ModelRunner",
     "ModelRunnerOutput",
+    "SampleHandle",
     "StepStats",
     "load_model",
     "resolve_dtype",

@@ -63,6 +63,8 @@ class SchedulerOutput:
     finished_req_ids: frozenset[str] = frozenset()
     preempted_req_ids: tuple[str, ...] = ()
     step_id: int = 0
+    # requests whose one scheduled token is the one the step in front samples (plan made ahead)
+    pending_token_req_ids: frozenset[str] = frozenset()
 
     @property
     def is_empty(self) -> bool:
@@ -331,6 +333,63 @@ class Scheduler:
             step_id=self.step_id,
         )
 
+    # ---- planning a step before the one in front has been read -----------------------------------
+    def schedule_ahead(self, in_flight: SchedulerOutput) -> SchedulerOutput | None:
+        """The plan of the step after ``in_flight``, made while ``in_flight`` still runs, or ``None``
+        when that step cannot be known yet.
+
+        It can be known when the batch is in steady decoding: nothing waits to be admitted, and
+        every running request is in ``in_flight`` and samples a token there.  Then each of them
+        decodes that token next, whatever its value, unless it ends by length with it; the one
+        thing not known is a stop token, and a request that turns out to have stopped simply has
+        its extra token dropped by ``update_from_outputs``.  Nothing here preempts or admits; when
+        pages for the next token cannot be had, the answer is ``None`` and the caller plans the
+        ordinary way once the tokens are in."""
+        cfg = self.config
+        if self.waiting or not self.running or in_flight.preempted_req_ids:
+            return None
+        scheduled_now = in_flight.num_scheduled_tokens
+        if len(scheduled_now) != len(self.running) or len(self.running) > cfg.max_num_scheduled_tokens:
+            return None
+        max_model_len = self.kv_manager.max_model_len
+        ids: list[str] = []
+        computed: list[int] = []
+        outputs: list[int] = []
+        for request in self.running:
+            now = scheduled_now.get(request.request_id)
+            if now is None or request.is_finished():
+                return None
+            after = request.num_computed_tokens + now
+            if after < request.num_tokens:
+                return None                       # still inside its prompt: no token is sampled
+            if request.num_output_tokens + 1 >= request.max_tokens or request.num_tokens + 1 >= max_model_len:
+                continue                          # ends by length with the token in flight
+            ids.append(request.request_id)
+            computed.append(after)
+            outputs.append(request.num_output_tokens + 1)
+        if not ids:
+            return None
+        for request_id in ids:
+            # asking again for a page that is already there is harmless, so a refusal half-way
+            # leaves nothing to undo
+            if not self.kv_manager.allocate_slots(request_id, 1):
+                return None
+        finished = frozenset(self.finished_req_ids)
+        self.finished_req_ids.clear()
+        return SchedulerOutput(
+            scheduled_cached_reqs=CachedRequestData(
+                req_ids=tuple(ids),
+                new_token_ids=((),) * len(ids),
+                num_computed_tokens=tuple(computed),
+                num_output_tokens=tuple(outputs),
+            ),
+            num_scheduled_tokens=dict.fromkeys(ids, 1),
+            total_num_scheduled_tokens=len(ids),
+            finished_req_ids=finished,
+            step_id=self.step_id + 1,
+            pending_token_req_ids=frozenset(ids),
+        )
+
     # ---- after the step ----------------------------------------------------------------------------
     def update_from_outputs(
         self,
@@ -343,7 +402,11 @@ class Scheduler:
         finished_requests: list[FinishedRequestState] = []
         max_model_len = self.kv_manager.max_model_len
         for request_id, num_tokens in scheduler_output.num_scheduled_tokens.items():
-            request = self.requests[request_id]
+            request = self.requests.get(request_id)
+            if request is None:
+                if request_id in scheduler_output.pending_token_req_ids:
+                    continue   # planned ahead, then found to have stopped: its extra token is dropped
+                raise KeyError(request_id)
             request.num_computed_tokens += num_tokens
             self.kv_manager.register_full_pages(request_id, request.all_token_ids)
             sampled: int | None = None

@@ -26,11 +26,16 @@ from ..parts.model import DecoderModel
 
 @dataclass
 class StepEntry:
-    """One request's share of a step: its next tokens, and which of them need logits."""
+    """One request's share of a step: its next tokens, and which of them need logits.
+
+    ``fed_from``: the entry's single token is not known to the host yet; it is row ``fed_from``
+    of the sampler output handed to ``StepFunction.step`` as ``feedback`` (``token_ids`` then
+    holds one placeholder)."""
 
     request_id: str
     token_ids: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    fed_from: int | None = None
 
 
 @dataclass
@@ -173,7 +178,7 @@ class StepFunction:
         width = kv_manager.max_blocks_per_seq
         capacity = (
             4 * _round4(self.max_num_seqs + 1)
-            + 4 * _round4(self.max_num_tokens)
+            + 5 * _round4(self.max_num_tokens)
             + len(kv_manager.groups) * _round4(self.max_num_seqs * width)
         )
         self._capacity = capacity
@@ -196,7 +201,7 @@ class StepFunction:
         self.num_graph_replays = 0
 
     # ---- packing -----------------------------------------------------------------------------
-    def _pack(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _pack(self, entries: Sequence[StepEntry], feedback: torch.Tensor | None = None) -> StepContext:
         kv = self.kv
         num_reqs = len(entries)
         if num_reqs == 0:
@@ -245,7 +250,8 @@ class StepFunction:
         off_positions = off_tokens + t4
         off_req_index = off_positions + t4
         off_logits = off_req_index + t4
-        off_tables = off_logits + _round4(max(num_logits, 1))
+        off_feed = off_logits + _round4(max(num_logits, 1))
+        off_tables = off_feed + t4
         table_len = _round4(num_reqs * width)
         used = off_tables + len(kv.groups) * table_len
         if used > self._capacity:
@@ -306,6 +312,20 @@ class StepFunction:
                 cursor += n
         if logit_rows:
             host[off_logits : off_logits + num_logits] = logit_rows
+        fed = any(entry.fed_from is not None for entry in entries)
+        if fed:
+            if feedback is None:
+                raise ValueError("an entry takes its token from the step in front, but no sampler output was given")
+            cursor = 0
+            for entry, n in zip(entries, query_lens):
+                if entry.fed_from is None:
+                    host[off_feed + cursor : off_feed + cursor + n] = -1
+                elif n != 1 or not 0 <= entry.fed_from < feedback.numel():
+                    raise ValueError(f"request {entry.request_id!r}: a fed entry is one token from a row of the "
+                                     f"sampler output, got {n} tokens from row {entry.fed_from}")
+                else:
+                    host[off_feed + cursor] = entry.fed_from
+                cursor += n
         # block tables: a row of this buffer that still holds the same slot at the same version (the
         # buffer was last written two steps ago) is left as it is; a steady decode batch rewrites a
         # row only when its request got a page
@@ -330,6 +350,9 @@ class StepFunction:
             if event is None:
                 event = self._host_events[turn] = torch.cuda.Event()
             event.record()
+        if fed:  # the real ids replace the placeholders on the device, in stream order
+            K.feed_tokens(device_meta[off_tokens : off_tokens + num_tokens],
+                          device_meta[off_feed : off_feed + num_tokens], feedback)
 
         ctx = StepContext()
         ctx.num_tokens, ctx.num_reqs, ctx.num_logits = num_tokens, num_reqs, num_logits
@@ -370,10 +393,11 @@ class StepFunction:
         return ctx
 
     # ---- the step ------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: Sequence[StepEntry], feedback: torch.Tensor | None = None) -> torch.Tensor | None:
         """Run one batch; returns ``[wanted, vocab]`` 32-bit logits on the device (``None`` if
-        nothing is wanted), rows in the order of the entries and of each entry's ``want``."""
-        ctx = self._pack(entries)
+        nothing is wanted), rows in the order of the entries and of each entry's ``want``.
+        ``feedback``: int32 tokens sampled from the step in front, for entries with ``fed_from``."""
+        ctx = self._pack(entries, feedback)
         self.storage.zero_slots(self.kv.take_fresh_slots())
         if self.use_cuda_graphs and ctx.decode_only:
             logits = self._step_with_graph(ctx)

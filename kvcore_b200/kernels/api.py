@@ -60,6 +60,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_gemm_stream_tc5_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
+        "kvb_feed_tokens": [_vp, _vp, _vp, _int, _int, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
     }
     for name, argtypes in signatures.items():
@@ -201,6 +202,18 @@ def gather_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None
     _call("kvb_gather_rows", out.data_ptr(), table.data_ptr(), ids.data_ptr(), count, width, rows,
           _dtype_code(table), _stream())
     return out
+
+
+def feed_tokens(token_ids: torch.Tensor, source: torch.Tensor, sampled: torch.Tensor) -> None:
+    """``token_ids[t] = sampled[source[t]]`` wherever ``source[t] >= 0`` (all int32, in place): the
+    ids of a step that was packed before the step in front had been read back."""
+    _check(token_ids, "token_ids", dtype=torch.int32)
+    _check(source, "source", dtype=torch.int32)
+    _check(sampled, "sampled", dtype=torch.int32)
+    if source.numel() != token_ids.numel():
+        raise KernelError(f"one source per token id is needed, got {source.numel()} for {token_ids.numel()}")
+    _call("kvb_feed_tokens", token_ids.data_ptr(), source.data_ptr(), sampled.data_ptr(), token_ids.numel(),
+          sampled.numel(), _stream())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -527,7 +540,7 @@ _stream_scratch: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor | None]]
 
 TRACE_TAGS = {1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
-              11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 15: "gemm_stream_tc5"}
+              11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 15: "gemm_stream_tc5", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
                 "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "gemm_stream_tc5")
 _trace_buffer: torch.Tensor | None = None
@@ -822,6 +835,7 @@ __all__ = [
     "add_rmsnorm",
     "check_attention_shape",
     "ensure_built",
+    "feed_tokens",
     "decode_splits",
     "decode_splits_tma",
     "flash_attention_supported",

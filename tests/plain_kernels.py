@@ -42,6 +42,11 @@ def gather_rows(table, ids, out=None):
     return table[ids.long()]
 
 
+def feed_tokens(token_ids, source, sampled):
+    take = source >= 0
+    token_ids[take] = sampled[source[take].long()]
+
+
 def rmsnorm(x, weight, eps):
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
@@ -224,7 +229,7 @@ def sample(logits, packed_params, eps):
 
 
 _NAMES = [
-    "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "rmsnorm",
+    "require_device", "ensure_built", "read_status", "peek_status", "raise_on_status", "check_attention_shape", "gather_rows", "feed_tokens", "rmsnorm",
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
 ]
 

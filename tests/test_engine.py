@@ -188,6 +188,52 @@ def test_seeded_sampling_is_reproducible_and_independent_of_the_batch(device, tm
     assert len(unseeded[0].output_token_ids) == 4
 
 
+def test_running_one_step_ahead_changes_no_output(device, tmp_path):
+    """With a step kept in flight the engine returns the tokens it returns without: requests that end
+    by length, requests that stop on a token (seen a step late, the extra token dropped), seeded
+    sampling, requests that arrive while others decode; and every page comes back."""
+    config = rc.TINY_CONFIGS["B"]
+    folder = rc.write_model(tmp_path / "m", config, 1, "float32")
+    weights = plain_llama.load_weights(folder)
+    prompts = [rc.random_tokens(config["vocab_size"], n, 40 + i) for i, n in enumerate((5, 19, 33, 8))]
+    greedy = [plain_llama.greedy_generate(config, weights, p, 14) for p in prompts]
+    stored = json.loads((folder / "config.json").read_text())
+    stored["eos_token_id"] = [greedy[1][6], greedy[3][2]]      # requests 1 and 3 stop early
+    (folder / "config.json").write_text(json.dumps(stored))
+    params = [SamplingParams(max_tokens=14, temperature=0.0), SamplingParams(max_tokens=14, temperature=0.0),
+              SamplingParams(max_tokens=9, temperature=0.7, seed=5, top_k=40),
+              SamplingParams(max_tokens=14, temperature=0.0)]
+
+    def run(run_ahead):
+        engine = LLMEngine(engine_config(folder, device, block_size=8, max_model_len=256, num_gpu_blocks=30,
+                                         scheduler=dict(max_num_scheduled_tokens=24, run_ahead=run_ahead)))
+        for i in range(3):
+            engine.add_request(f"r{i}", params[i], prompt_token_ids=prompts[i])
+        steps, outputs = 0, {}
+        while engine.engine_core.has_unfinished_requests():
+            for out in engine.step().request_outputs:
+                if out.sampled_token_id is not None:
+                    outputs.setdefault(out.request_id, []).append(out.sampled_token_id)
+            steps += 1
+            if steps == 7:    # a late arrival: the batch leaves steady decoding, takes it in, settles again
+                engine.add_request("r3", params[3], prompt_token_ids=prompts[3])
+        core = engine.engine_core
+        finished = {r: core.take_finished_output(r) for r in ("r0", "r1", "r2", "r3")}
+        kv = core.model_runner.kv_manager
+        kv.check_invariants()
+        assert not kv.live_requests() and not core.model_runner.requests and core._in_flight is None
+        assert {r: list(f.output_token_ids) for r, f in finished.items()} == outputs
+        return outputs, {r: f.finish_reason.value for r, f in finished.items()}, core.num_steps_run_ahead
+
+    ahead, ahead_reasons, launched_ahead = run(True)
+    plain, plain_reasons, none_ahead = run(False)
+    assert launched_ahead > 5 and none_ahead == 0
+    assert ahead == plain and ahead_reasons == plain_reasons
+    assert ahead["r0"] == greedy[0]
+    assert ahead["r1"] == greedy[1][: greedy[1].index(greedy[1][6]) + 1] and ahead_reasons["r1"] == "stop"
+    assert ahead_reasons == {"r0": "length", "r1": "stop", "r2": ahead_reasons["r2"], "r3": "stop"}
+
+
 def test_random_weights_mode_needs_no_weight_file(device, tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(rc.TINY_A))
     engine = LLMEngine(engine_config(tmp_path, device, load=dict(random_weights=True, seed=3)))

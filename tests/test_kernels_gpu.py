@@ -41,6 +41,21 @@ def test_gather_rows(dtype, rows, width, count):
     assert K().read_status() == 0
 
 
+def test_feed_tokens():
+    ids = torch.arange(100, 137, dtype=torch.int32, device=DEV)
+    source = torch.full((37,), -1, dtype=torch.int32, device=DEV)
+    source[[0, 5, 36]] = torch.tensor([2, 0, 2], dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([7, 8, 9], dtype=torch.int32, device=DEV)
+    want = ids.clone()
+    P.feed_tokens(want, source, sampled)
+    K().feed_tokens(ids, source, sampled)
+    assert torch.equal(ids, want) and ids[0] == 9 and ids[5] == 7 and ids[36] == 9 and ids[1] == 101
+    assert K().read_status() == 0
+    source[3] = 3                                # a row the sampler output does not have: flagged, not read
+    K().feed_tokens(ids, source, sampled)
+    assert ids[3] == 103 and K().read_status() & 1
+
+
 def test_gather_rows_flags_bad_id():
     table = randn(10, 8, dtype=torch.float32)
     ids = torch.tensor([3, 10, -1], dtype=torch.int32, device=DEV)
@@ -222,6 +237,9 @@ FLASH_SHAPES = [
     (32, 8, 128, 16, [(0, 300)], None, None),                                # tcgen05 prefill: 3 key tiles, 10 row tiles
     (4, 1, 128, 64, [(1000, 130)], None, None),                              # tcgen05 prefill: long context, pages of 64
     (6, 2, 128, 8, [(5, 150), (0, 3)], None, None),                          # tcgen05 prefill: 3 heads a group
+    (64, 8, 128, 16, [(1000, 1), (17, 1), (2047, 2), (0, 1)], None, None),   # TMA decode: 8 heads a group
+    (16, 2, 128, 16, [(0, 200), (100, 50), (333, 1)], None, None),           # tcgen05 prefill: 8 heads a group
+    (24, 8, 128, 16, [(1500, 1), (0, 1), (640, 1)], None, None),             # TMA decode: 3 heads a group
     (8, 2, 128, 32, [(0, 700)], 200, None),                                  # tcgen05 prefill: window
     (4, 4, 128, 16, [(250, 9), (0, 129)], None, None),                       # tcgen05 prefill: one head a group
 ]
@@ -276,6 +294,8 @@ ROTATING_DECODE_SHAPES = [
     (4, 1, 128, 64, [(500, 3), (63, 1), (191, 2)], None, 2),
     (2, 2, 64, 32, [(100, 9), (0, 16)], 17, None),                         # window; sixteen new tokens at once
     (6, 3, 48, 16, [(17, 2), (0, 1), (100, 2)], None, None),               # not the TMA kernel: kernel in front
+    (64, 8, 128, 16, [(1000, 1), (0, 1), (63, 2)], None, None),            # 8 heads a group
+    (24, 8, 128, 16, [(1500, 1), (0, 1), (640, 5)], None, 4),              # 3 heads a group, five new tokens
     (8, 2, 128, 16, [(0, 200), (130, 77), (500, 1)], None, None),          # prefill shapes: kernel in front
 ]
 

@@ -187,3 +187,49 @@ def test_decode_graphs_replay_and_match_eager(dtype, tmp_path):
                 assert np.array_equal(row, results[False][key]), key
             else:
                 assert np.abs(row - results[False][key]).max() < 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tokens_fed_from_the_device_give_the_logits_of_tokens_from_the_host(dtype, tmp_path):
+    """A decode step may take its token ids from a sampler output that the host has not read
+    (``StepEntry.fed_from``): same logits as with the ids packed by the host, eagerly, through the
+    decode graphs, and beside a portion of a prompt."""
+    import torch
+
+    import kvcore_b200.kernels as kernels
+    from kvcore_b200.engine.step import StepEntry
+    from kvcore_b200.engine.trace_replay import build_replay
+
+    config = rc.TINY_CONFIGS["B"]
+    folder = tmp_path / "m"
+    rc.write_model(folder, config, 4, "bfloat16")
+    vocab = config["vocab_size"]
+    prompts = {f"f{i}": rc.random_tokens(vocab, n, 60 + i) for i, n in enumerate((21, 9, 34))}
+    late = rc.random_tokens(vocab, 12, 77)
+    decoded = [rc.random_tokens(vocab, 3, 80 + step) for step in range(8)]
+
+    def run(fed: bool):
+        step_function, kv = build_replay(str(folder), dtype, 512)
+        rows = []
+        for rid, tokens in prompts.items():
+            assert kv.allocate_slots(rid, len(tokens))
+        step_function.step([StepEntry(rid, tokens, ()) for rid, tokens in prompts.items()])
+        for step, tokens in enumerate(decoded):
+            entries = []
+            # rows of the "sampler output" in another order than the entries, with a row nobody takes
+            feedback = torch.tensor([tokens[2], 1, tokens[0], tokens[1]], dtype=torch.int32, device="cuda:0")
+            for (rid, token), row in zip(zip(prompts, tokens), (2, 3, 0)):
+                assert kv.allocate_slots(rid, 1)
+                entries.append(StepEntry(rid, (0,), (0,), fed_from=row) if fed else StepEntry(rid, (token,), (0,)))
+            if step == 5:   # a prompt portion beside the fed tokens
+                assert kv.allocate_slots("late", len(late))
+                entries.insert(1, StepEntry("late", late, (len(late) - 1,)))
+            rows.append(step_function.step(entries, feedback if fed else None).float().cpu())
+        assert kernels.read_status() == 0
+        return rows, step_function.num_graph_replays
+
+    host_rows, _ = run(False)
+    fed_rows, replays = run(True)
+    assert replays >= 4
+    for a, b in zip(host_rows, fed_rows):
+        assert torch.equal(a, b)

@@ -223,3 +223,51 @@ def test_a_preempted_request_finds_its_own_pages_again():
         preempted += len(out.preempted_req_ids)
         kv.check_invariants()
     assert not sched.has_unfinished_requests() and preempted > 0 and kv.num_prefix_hits > 0
+
+
+def test_planning_ahead_of_the_tokens_in_flight():
+    """schedule_ahead: only a batch in steady decoding is planned before its tokens are read; a
+    request that ends by length with the token in flight is left out; one that turns out to have
+    stopped has its extra token dropped; no page is lost on the way."""
+    sched, kv = make(max_num_scheduled_tokens=8, max_num_seqs=4, max_num_partial_prefills=2)
+    sched.add_request(request("a", 10, max_tokens=2))
+    sched.add_request(request("b", 3, max_tokens=5))
+    first = sched.schedule()                                  # a: 8 of 10 prompt tokens, b waits
+    assert first.num_scheduled_tokens == {"a": 8}
+    assert sched.schedule_ahead(first) is None                # a request is waiting
+    kv.advance("a", 8)
+    sched.update_from_outputs(first, {})
+    second = sched.schedule()                                 # a's last 2, b's 3: both sample
+    assert second.num_scheduled_tokens == {"a": 2, "b": 3}
+    for rid, n in second.num_scheduled_tokens.items():
+        kv.advance(rid, n)
+    third = sched.schedule_ahead(second)                      # planned while `second` runs
+    assert third.num_scheduled_tokens == {"a": 1, "b": 1} and third.pending_token_req_ids == {"a", "b"}
+    assert third.scheduled_cached_reqs.num_computed_tokens == (10, 3)
+    assert third.scheduled_cached_reqs.num_output_tokens == (1, 1)
+    assert third.scheduled_cached_reqs.new_token_ids == ((), ())
+    sched.update_from_outputs(second, {"a": 7, "b": 7})
+    for rid in third.num_scheduled_tokens:
+        kv.advance(rid, 1)
+    fourth = sched.schedule_ahead(third)
+    assert fourth.num_scheduled_tokens == {"b": 1}            # a reaches max_tokens=2 with the token in flight
+    kv.advance("b", 1)                                        # `fourth` is launched before `third` is read
+    upd = sched.update_from_outputs(third, {"a": 7, "b": 9}, stop_token_ids={9})   # b stops on 9
+    assert [(o.request_id, o.finished) for o in upd.step_outputs] == [("a", True), ("b", True)]
+    assert [f.output_token_ids for f in upd.finished_requests] == [(7, 7), (7, 9)]
+    upd = sched.update_from_outputs(fourth, {"b": 5})         # b's extra token is nobody's
+    assert upd.step_outputs == () and not sched.requests
+    kv.check_invariants()
+    assert kv.num_free_pages() == [32] and not sched.has_unfinished_requests()
+
+
+def test_planning_ahead_gives_up_where_pages_run_out():
+    sched, kv = make(num_pages=5, page_size=4, max_num_scheduled_tokens=16, max_num_seqs=2, max_num_partial_prefills=2)
+    sched.add_request(request("a", 8, max_tokens=6))
+    sched.add_request(request("b", 8, max_tokens=6))
+    first = sched.schedule()
+    assert first.num_scheduled_tokens == {"a": 8, "b": 8}     # all four pages are taken
+    for rid in first.num_scheduled_tokens:
+        kv.advance(rid, 8)
+    assert sched.schedule_ahead(first) is None                # the ninth token needs a page nobody has
+    kv.check_invariants()
