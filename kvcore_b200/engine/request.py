@@ -1,4 +1,11 @@
-"""Scheduler-side state of one request (reference: kvcore/utils/request.py:13-46, 78-215)."""
+"""Scheduler-side state of one request.
+
+The names the scheduler and its callers use are the reference's (kvcore/utils/request.py:13-46,
+78-215): ``RequestStatus`` with its finished states, ``FinishReason``, and a ``Request`` that counts
+its prompt, output and computed tokens.  A request here keeps one token list (prompt, then every
+sampled token) and derives the rest from it; what the reference carries for streaming, priorities,
+speculative tokens and transfers between engines has no user in this engine and is left out.
+"""
 from __future__ import annotations
 
 import enum
@@ -16,74 +23,78 @@ class FinishReason(enum.StrEnum):
 
 
 class RequestStatus(enum.IntEnum):
-    WAITING = enum.auto()
-    RUNNING = enum.auto()
-    PREEMPTED = enum.auto()
-    FINISHED_STOPPED = enum.auto()
-    FINISHED_LENGTH_CAPPED = enum.auto()
-    FINISHED_ABORTED = enum.auto()
-    FINISHED_ERROR = enum.auto()
+    """Life of a request; every state after ``PREEMPTED`` is final and maps to a ``FinishReason``."""
+
+    WAITING = 1
+    RUNNING = 2
+    PREEMPTED = 3
+    FINISHED_STOPPED = 4
+    FINISHED_LENGTH_CAPPED = 5
+    FINISHED_ABORTED = 6
+    FINISHED_ERROR = 7
 
     @staticmethod
     def is_finished(status: "RequestStatus") -> bool:
-        return status > RequestStatus.PREEMPTED
+        return status >= RequestStatus.FINISHED_STOPPED
 
     @staticmethod
     def finish_reason(status: "RequestStatus") -> FinishReason | None:
-        return _FINISH_REASONS.get(status)
-
-
-_FINISH_REASONS = {
-    RequestStatus.FINISHED_STOPPED: FinishReason.STOP,
-    RequestStatus.FINISHED_LENGTH_CAPPED: FinishReason.LENGTH,
-    RequestStatus.FINISHED_ABORTED: FinishReason.ABORT,
-    RequestStatus.FINISHED_ERROR: FinishReason.ERROR,
-}
+        if not RequestStatus.is_finished(status):
+            return None
+        return (FinishReason.STOP, FinishReason.LENGTH, FinishReason.ABORT,
+                FinishReason.ERROR)[status - RequestStatus.FINISHED_STOPPED]
 
 
 class Request:
-    def __init__(
-        self,
-        request_id: str,
-        prompt_token_ids: Sequence[int],
-        sampling_params: SamplingParams,
-        *,
-        arrival_time: float | None = None,
-    ) -> None:
-        if not prompt_token_ids:
+    """Tokens and progress of one request.
+
+    ``num_computed_tokens`` is how many of ``all_token_ids`` have their keys and values in the cache;
+    the request is in prefill while that is below ``num_prompt_tokens``."""
+
+    def __init__(self, request_id: str, prompt_token_ids: Sequence[int], sampling_params: SamplingParams,
+                 *, arrival_time: float | None = None) -> None:
+        tokens = list(prompt_token_ids)
+        if not tokens:
             raise ValueError("prompt_token_ids must be non-empty")
         self.request_id = request_id
         self.sampling_params = sampling_params
-        self.max_tokens = sampling_params.max_tokens
-        self.arrival_time = time.time() if arrival_time is None else arrival_time
+        self.arrival_time = arrival_time if arrival_time is not None else time.time()
         self.status = RequestStatus.WAITING
-        self.prompt_token_ids = list(prompt_token_ids)
-        self.num_prompt_tokens = len(self.prompt_token_ids)
-        self._output_token_ids: list[int] = []
-        self._all_token_ids: list[int] = list(self.prompt_token_ids)
+        self.num_prompt_tokens = len(tokens)
         self.num_computed_tokens = 0
         self.num_preemptions = 0
+        self._tokens = tokens
 
+    # ---- tokens ------------------------------------------------------------------------------
     @property
-    def output_token_ids(self) -> tuple[int, ...]:
-        return tuple(self._output_token_ids)
+    def max_tokens(self) -> int:
+        return self.sampling_params.max_tokens
 
     @property
     def all_token_ids(self) -> list[int]:
-        return self._all_token_ids
+        """Prompt followed by the sampled tokens (the list itself, not a copy)."""
+        return self._tokens
+
+    @property
+    def prompt_token_ids(self) -> list[int]:
+        return self._tokens[: self.num_prompt_tokens]
+
+    @property
+    def output_token_ids(self) -> tuple[int, ...]:
+        return tuple(self._tokens[self.num_prompt_tokens :])
 
     @property
     def num_tokens(self) -> int:
-        return len(self._all_token_ids)
+        return len(self._tokens)
 
     @property
     def num_output_tokens(self) -> int:
-        return len(self._output_token_ids)
+        return len(self._tokens) - self.num_prompt_tokens
 
     def append_output_token_id(self, token_id: int) -> None:
-        self._output_token_ids.append(token_id)
-        self._all_token_ids.append(token_id)
+        self._tokens.append(token_id)
 
+    # ---- ending ------------------------------------------------------------------------------
     def is_finished(self) -> bool:
         return RequestStatus.is_finished(self.status)
 
