@@ -213,3 +213,72 @@ def test_scheduler_finishes_every_request_within_its_limits(arrivals, num_pages,
     sched.schedule()                                       # reports the last finished ids
     assert not kv.live_requests()
     kv.check_invariants()
+
+
+# ---- one step kept in flight -----------------------------------------------------------------
+@pytest.fixture(scope="module")
+def model_for_engine(tmp_path_factory):
+    folder = tmp_path_factory.mktemp("engine_model")
+    rc.write_model(folder, rc.TINY_CONFIGS["A"], 3, "float32")
+    return folder
+
+
+@settings(max_examples=10, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture])
+@given(
+    arrivals=st.lists(st.tuples(st.integers(0, 12), st.integers(1, 30), st.integers(1, 9)), min_size=1, max_size=7),
+    num_pages=st.integers(12, 40), budget=st.integers(4, 32), max_seqs=st.integers(1, 4),
+    stops=st.lists(st.integers(0, 255), min_size=0, max_size=40),
+)
+def test_keeping_a_step_in_flight_never_changes_what_comes_out(model_for_engine, monkeypatch, arrivals, num_pages,
+                                                                 budget, max_seqs, stops):
+    """Random arrivals, lengths, limits, stop tokens and few pages (waiting, preemption): the engine
+    with a step in flight returns, request by request, the tokens and finish reasons of the engine
+    without, and gives every page back."""
+    import json
+
+    from kvcore_b200 import (CacheConfig, DeviceConfig, KVCoreConfig, LoadConfig, ModelConfig, SamplingParams,
+                             SchedulerConfig)
+    from kvcore_b200.engine.llm_engine import LLMEngine
+
+    plain_kernels.install(monkeypatch)
+    config = json.loads((model_for_engine / "config.json").read_text())
+    config["eos_token_id"] = sorted(set(stops)) or None
+    (model_for_engine / "config.json").write_text(json.dumps({k: v for k, v in config.items() if v is not None}))
+    requests = [(step, f"r{i}", rc.random_tokens(256, length, 200 + i), max_tokens)
+                for i, (step, length, max_tokens) in enumerate(arrivals)]
+
+    def run(run_ahead: bool):
+        engine = LLMEngine(KVCoreConfig(
+            model_config=ModelConfig(model=str(model_for_engine), dtype="float32", max_model_len=48),
+            load_config=LoadConfig(),
+            cache_config=CacheConfig(block_size=4, num_gpu_blocks=num_pages),
+            scheduler_config=SchedulerConfig(max_num_seqs=max_seqs, max_num_scheduled_tokens=budget,
+                                             max_num_partial_prefills=2, max_long_partial_prefills=2,
+                                             run_ahead=run_ahead),
+            device_config=DeviceConfig(device="cpu"),
+        ))
+        core = engine.engine_core
+        seen: dict[str, list[int]] = {}
+        step = 0
+        pending = sorted(requests)
+        while pending or core.has_unfinished_requests():
+            while pending and pending[0][0] <= step:
+                _, rid, prompt, max_tokens = pending.pop(0)
+                engine.add_request(rid, SamplingParams(max_tokens=max_tokens, temperature=0.0), prompt_token_ids=prompt)
+            for out in engine.step().request_outputs:
+                if out.sampled_token_id is not None:
+                    seen.setdefault(out.request_id, []).append(out.sampled_token_id)
+            step += 1
+            assert step < 600, "no progress"
+        finished = {rid: core.take_finished_output(rid) for _, rid, _, _ in requests}
+        kv = core.model_runner.kv_manager
+        kv.check_invariants()
+        assert not kv.live_requests() and core._in_flight is None and not core.model_runner.requests
+        # a preempted request is recomputed, but the tokens it reported stay the tokens it has
+        assert {rid: list(f.output_token_ids) for rid, f in finished.items()} == seen
+        return {rid: (f.output_token_ids, f.finish_reason) for rid, f in finished.items()}, core.num_steps_run_ahead
+
+    with_ahead, launched = run(True)
+    without, none = run(False)
+    assert none == 0
+    assert with_ahead == without
