@@ -336,58 +336,83 @@ class Scheduler:
     # ---- planning a step before the one in front has been read -----------------------------------
     def schedule_ahead(self, in_flight: SchedulerOutput) -> SchedulerOutput | None:
         """The plan of the step after ``in_flight``, made while ``in_flight`` still runs, or ``None``
-        when that step cannot be known yet.
+        when that step is better planned once its tokens are in.
 
-        It can be known when the batch is in steady decoding: nothing waits to be admitted, and
-        every running request is in ``in_flight`` and samples a token there.  Then each of them
-        decodes that token next, whatever its value, unless it ends by length with it; the one
-        thing not known is a stop token, and a request that turns out to have stopped simply has
-        its extra token dropped by ``update_from_outputs``.  Nothing here preempts or admits; when
-        pages for the next token cannot be had, the answer is ``None`` and the caller plans the
-        ordinary way once the tokens are in."""
+        What ``in_flight`` leaves behind is known except for the values of the tokens it samples:
+        every request in it will have its scheduled tokens computed, and one that reaches the end
+        of its tokens there will have one more token.  So the running requests can be served as
+        ``schedule()`` would serve them, in order and under the same limits: the next portion of
+        a prompt, or the one token in flight (its id is taken from the sampler's output on the
+        device), unless the request ends by length with it.  The one thing not known is a stop
+        token; a request that turns out to have stopped has its extra token dropped by
+        ``update_from_outputs``.  Nothing here admits or preempts: with a request waiting that
+        could be admitted, or pages that cannot be had, the answer is ``None``."""
         cfg = self.config
-        if self.waiting or not self.running or in_flight.preempted_req_ids:
+        if not self.running or in_flight.preempted_req_ids:
+            return None
+        if self.waiting and len(self.running) < cfg.max_num_seqs:
             return None
         scheduled_now = in_flight.num_scheduled_tokens
-        if len(scheduled_now) != len(self.running) or len(self.running) > cfg.max_num_scheduled_tokens:
-            return None
         max_model_len = self.kv_manager.max_model_len
+        threshold = cfg.long_prefill_token_threshold
+        token_budget = cfg.max_num_scheduled_tokens
+        partial = long_partial = 0
         ids: list[str] = []
+        tokens: list[tuple[int, ...]] = []
         computed: list[int] = []
         outputs: list[int] = []
+        num_scheduled: dict[str, int] = {}
+        pending: set[str] = set()
         for request in self.running:
-            now = scheduled_now.get(request.request_id)
-            if now is None or request.is_finished():
+            if len(num_scheduled) >= cfg.max_num_seqs or token_budget <= 0:
+                break
+            if request.is_finished():
                 return None
-            after = request.num_computed_tokens + now
-            if after < request.num_tokens:
-                return None                       # still inside its prompt: no token is sampled
-            if request.num_output_tokens + 1 >= request.max_tokens or request.num_tokens + 1 >= max_model_len:
+            done = request.num_computed_tokens + scheduled_now.get(request.request_id, 0)
+            samples = request.request_id in scheduled_now and done >= request.num_tokens
+            if samples and (request.num_output_tokens + 1 >= request.max_tokens
+                            or request.num_tokens + 1 >= max_model_len):
                 continue                          # ends by length with the token in flight
-            ids.append(request.request_id)
-            computed.append(after)
-            outputs.append(request.num_output_tokens + 1)
-        if not ids:
-            return None
-        for request_id in ids:
+            is_prefill = done < request.num_prompt_tokens
+            if is_prefill:
+                if not self._can_schedule_partial_prefill(request, partial, long_partial):
+                    break                         # as in schedule(): the requests behind it wait too
+                partial += 1
+                long_partial += int(self._is_long_prefill(request))
+            remaining = request.num_tokens + int(samples) - done
+            if remaining <= 0 or (samples and remaining != 1):
+                return None
+            if 0 < threshold < remaining:
+                remaining = threshold
+            count = min(remaining, token_budget)
             # asking again for a page that is already there is harmless, so a refusal half-way
             # leaves nothing to undo
-            if not self.kv_manager.allocate_slots(request_id, 1):
+            if not self.kv_manager.allocate_slots(request.request_id, count):
                 return None
+            ids.append(request.request_id)
+            tokens.append(() if samples else tuple(request.all_token_ids[done : done + count]))
+            computed.append(done)
+            outputs.append(request.num_output_tokens + int(samples))
+            num_scheduled[request.request_id] = count
+            if samples:
+                pending.add(request.request_id)
+            token_budget -= count
+        if not num_scheduled:
+            return None
         finished = frozenset(self.finished_req_ids)
         self.finished_req_ids.clear()
         return SchedulerOutput(
             scheduled_cached_reqs=CachedRequestData(
                 req_ids=tuple(ids),
-                new_token_ids=((),) * len(ids),
+                new_token_ids=tuple(tokens),
                 num_computed_tokens=tuple(computed),
                 num_output_tokens=tuple(outputs),
             ),
-            num_scheduled_tokens=dict.fromkeys(ids, 1),
-            total_num_scheduled_tokens=len(ids),
+            num_scheduled_tokens=num_scheduled,
+            total_num_scheduled_tokens=sum(num_scheduled.values()),
             finished_req_ids=finished,
             step_id=self.step_id + 1,
-            pending_token_req_ids=frozenset(ids),
+            pending_token_req_ids=frozenset(pending),
         )
 
     # ---- after the step ----------------------------------------------------------------------------

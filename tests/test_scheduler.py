@@ -271,3 +271,45 @@ def test_planning_ahead_gives_up_where_pages_run_out():
         kv.advance(rid, 8)
     assert sched.schedule_ahead(first) is None                # the ninth token needs a page nobody has
     kv.check_invariants()
+
+
+def test_planning_ahead_continues_prompts_and_respects_the_limits():
+    """A prompt portion in flight is followed by the next portion (known tokens), beside the token in
+    flight of a decoding request; the token budget and the limit on partial prefills hold; a waiting
+    request that could be admitted sends the planner back to schedule()."""
+    sched, kv = make(num_pages=60, max_num_scheduled_tokens=6, max_num_seqs=2, max_num_partial_prefills=1)
+    sched.add_request(request("a", 3, max_tokens=9))
+    out, _ = run_step(sched, kv)                               # a: whole prompt, samples
+    sched.add_request(request("b", 14, max_tokens=2))
+    first = sched.schedule()                                   # a decodes, b: 5 of 14
+    assert first.num_scheduled_tokens == {"a": 1, "b": 5}
+    for rid, n in first.num_scheduled_tokens.items():
+        kv.advance(rid, n)
+    sched.add_request(request("c", 2))
+    ahead = sched.schedule_ahead(first)                        # c waits, but both seats are taken
+    assert ahead.num_scheduled_tokens == {"a": 1, "b": 5} and ahead.pending_token_req_ids == {"a"}
+    cached = ahead.scheduled_cached_reqs
+    assert cached.new_token_ids == ((), (6, 7, 8, 9, 10)) and cached.num_computed_tokens == (4, 5)
+    sched.update_from_outputs(first, {"a": 7})
+    for rid, n in ahead.num_scheduled_tokens.items():
+        kv.advance(rid, n)
+    third = sched.schedule_ahead(ahead)                        # b's last 4 prompt tokens: it will sample
+    assert third.num_scheduled_tokens == {"a": 1, "b": 4}
+    sched.update_from_outputs(ahead, {"a": 7})
+    for rid, n in third.num_scheduled_tokens.items():
+        kv.advance(rid, n)
+    fourth = sched.schedule_ahead(third)
+    assert fourth.num_scheduled_tokens == {"a": 1, "b": 1} and fourth.pending_token_req_ids == {"a", "b"}
+    upd = sched.update_from_outputs(third, {"a": 7, "b": 7})
+    assert [o.sampled_token_id for o in upd.step_outputs] == [7, 7]
+    for rid in fourth.num_scheduled_tokens:
+        kv.advance(rid, 1)
+    assert sched.schedule_ahead(fourth).num_scheduled_tokens == {"a": 1}   # b ends by length with its token in flight
+    kv.check_invariants()
+    # with a free seat and a request waiting, admission comes first
+    roomy, kv2 = make(num_pages=60, max_num_scheduled_tokens=6, max_num_seqs=3)
+    roomy.add_request(request("a", 3, max_tokens=9))
+    out = roomy.schedule()
+    kv2.advance("a", 3)
+    roomy.add_request(request("b", 3))
+    assert roomy.schedule_ahead(out) is None
