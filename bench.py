@@ -302,7 +302,8 @@ def time_serving(shape: dict, layers: int, requests: int, min_prompt: int, max_p
             "generated_tokens": generated, "steps": runner.step_function.num_steps - steps_before,
             "generated_tokens_per_s": round(generated / elapsed, 1),
             "total_tokens_per_s": round((generated + sum(lengths)) / elapsed, 1),
-            "chunk": chunk, "prompt_lengths": f"{min_prompt}-{max_prompt}", "max_tokens": max_tokens}
+            "chunk": chunk, "prompt_lengths": f"{min_prompt}-{max_prompt}", "max_tokens": max_tokens,
+            "steps_launched_ahead": engine.engine_core.num_steps_run_ahead}
 
 
 def reference_arm(args) -> int:
