@@ -132,3 +132,31 @@ def test_engine_config_validation():
         with pytest.raises(ValueError):
             bad()
     assert PartSpec("x", {"a": 1}).with_params(b=2).params == {"a": 1, "b": 2}
+
+
+def test_sampling_options_are_validated_and_named():
+    from kvcore_b200 import SamplingParams
+
+    params = SamplingParams.from_mapping(dict(max_tokens=3, temperature=0.0, top_k=5))
+    assert params.greedy and params.kept_logits(100) == 5 and params.kept_logits(3) == 3
+    assert not SamplingParams(max_tokens=1).greedy and SamplingParams(max_tokens=1).kept_logits(7) == 7
+    for bad, match in ((dict(max_tokens=0), "max_tokens must be positive"),
+                       (dict(max_tokens=1, temperature=-0.1), "temperature must be non-negative"),
+                       (dict(max_tokens=1, top_p=0.0), "top_p must be in"),
+                       (dict(max_tokens=1, top_p=1.5), "top_p must be in"),
+                       (dict(max_tokens=1, top_k=0), "top_k must be positive when set"),
+                       (dict(max_tokens=1, beam_width=4), "unknown sampling option.*beam_width")):
+        with pytest.raises(ValueError, match=match):
+            SamplingParams.from_mapping(bad)
+
+
+def test_generation_requests_are_taken_in_either_form():
+    from kvcore_b200 import GenerationRequest, SamplingParams
+
+    given = GenerationRequest("a", SamplingParams(max_tokens=2), prompt_token_ids=(1, 2))
+    assert GenerationRequest.coerce(given) is given
+    made = GenerationRequest.coerce(dict(request_id=7, sampling_params=dict(max_tokens=2), prompt_token_ids=[3, 4]))
+    assert made.request_id == "7" and made.prompt_token_ids == (3, 4) and made.sampling_params.max_tokens == 2
+    chat = GenerationRequest.coerce(dict(request_id="c", sampling_params=SamplingParams(max_tokens=1),
+                                         messages=[{"role": "user", "content": "hi"}]))
+    assert chat.prompt_token_ids is None and chat.messages[0]["content"] == "hi"
