@@ -1,18 +1,20 @@
 // Split-KV paged attention for decode, fed by TMA (sm_100a).
 //
 // Decode reads every cached key and value once and does little arithmetic on them, so the
-// kernel is built to keep as many bytes in flight as one SM can hold.  One block per SM-sized
-// share of the work: a (request, kv head, split) triple.  A producer warp walks the split's
-// key range in tiles of 64 keys and, for each tile, looks the pages up in the block table and
-// issues one tiled TMA copy per page (cp.async.bulk.tensor.2d, 128-byte swizzle; the block of
-// one page and kv head is contiguous in the cache) for K and for V into a ring of STAGES shared-memory stages; each stage has a
-// "full" mbarrier that the copies complete and an "empty" mbarrier that the consumers
-// release.  Two groups of four consumer warps take alternate tiles (the per-tile chain of
-// score, softmax and accumulate is latency-bound, so two tiles are worked at once); each
-// warp scores 16 keys of its group's tile against the (at most 16) query rows of the request
+// kernel is built to keep as many bytes in flight as one SM can hold.  The work is cut into items,
+// (request, kv head, split) triples; a block (two a SM) takes the item of its index and, when there are
+// more items than blocks that fit the GPU at once, stays and takes further ones from a counter.  A
+// producer warp walks an item's key range in tiles of 64 keys and, for each tile, looks the pages up in
+// the block table and issues one tiled TMA copy per page (cp.async.bulk.tensor.2d, 128-byte swizzle;
+// the block of one page and kv head is contiguous in the cache) for K and for V into a ring of STAGES
+// shared-memory stages; each stage has a "full" mbarrier that the copies complete, an "empty"
+// mbarrier that the consumers release, and a header that says which item and tile it holds.  The
+// ring runs on from one item into the next: the next item's first tiles are on their way while the
+// consumers still merge and store the last one.  Four consumer warps follow the headers; each
+// warp scores 16 keys of a tile against the (at most 16) query rows of the request
 // with mma.sync m16n8k16, keeps a running 32-bit softmax, and accumulates its part of the
-// output; at the end all warps merge through shared memory and the block writes either the
-// final rows (one split) or a partial (max, sum, output) to scratch that a second kernel
+// output; after an item's last tile the warps merge through shared memory (where q lay) and write
+// either the final rows (one split) or a partial (max, sum, output) to scratch that a second kernel
 // merges over the splits.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the thread sets the
@@ -55,6 +57,11 @@ struct DecodeParams {
   const bf16* k_new;          // this step's keys, row stride q_stride, [tokens][KVH][D] inside the qkv rows
   const bf16* v_new;
   bf16* k_cache; bf16* v_cache;   // [pages, KVH, page, D]
+  // Work items are (request, kv head, split) triples, numbered in that order.  work == null: one item
+  // a block.  Else blocks stay and take further items from work[0] (work[1] counts the blocks that
+  // have seen the end; the last one puts both back to zero, where they must be before a launch).
+  int total_items;
+  int* work;
 };
 
 __device__ __forceinline__ void td_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
@@ -85,6 +92,42 @@ __device__ __forceinline__ unsigned swz(int key, int d) {
   return (unsigned)(r * 128 + ((chunk ^ (r & 7)) << 4));
 }
 
+// What the producer tells the consumers about a stage of the ring: the work item it belongs to
+// (a (request, kv head, split) triple; -1: no more items), the tile's index in the item's key range
+// and what the consumers need to set the item up, so that they load nothing but q themselves.
+struct TdStageHeader {
+  int item, it, num_tiles, q_begin, q_len, context, key_lo, key_hi;
+};
+
+// Work item `item` = (request, kv head, split), numbered in that order: its query rows and the
+// range of keys its split covers.
+__device__ __forceinline__ TdStageHeader td_describe_item(const DecodeParams& p, int item) {
+  TdStageHeader h;
+  h.item = item;
+  h.it = 0;
+  const int req = item / (p.KVH * p.num_splits);
+  const int split = item % p.num_splits;
+  h.q_begin = p.query_start[req];
+  h.q_len = p.query_start[req + 1] - h.q_begin;
+  h.context = p.context_lens[req];
+  const int rows_total = min(h.q_len * p.G, 16);
+  const int last_pos = h.context + (rows_total - 1) / p.G;
+  int key_lo = p.window > 0 ? max(0, h.context - p.window + 1) : 0;
+  int key_hi = last_pos + 1;
+  const int first_tile_key = (key_lo / TD_KEYS) * TD_KEYS;
+  const int tiles = (key_hi - first_tile_key + TD_KEYS - 1) / TD_KEYS;
+  const int per = (tiles + p.num_splits - 1) / p.num_splits;
+  const int lo = first_tile_key + split * per * TD_KEYS;
+  key_hi = min(key_hi, lo + per * TD_KEYS);
+  key_lo = max(key_lo, lo);
+  const int tile_begin = key_lo / TD_KEYS;
+  const int tile_end = key_hi > key_lo ? (key_hi + TD_KEYS - 1) / TD_KEYS : tile_begin;
+  h.num_tiles = tile_end - tile_begin;
+  h.key_lo = key_lo;
+  h.key_hi = key_hi;
+  return h;
+}
+
 template <int D>
 __global__ void __launch_bounds__(TD_THREADS, 2)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -95,6 +138,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   // the first tile that reaches this step's tokens; the other warps wait before they read q.
   KvbTrace kvb_trace_scope__(KVB_TAG_DECODE_TMA);
   kvb_grid_launch_dependents();
+  static_assert(TD_GROUPS == 1, "the consumers follow the ring's headers together");
   constexpr int HALVES = D / 64;
   constexpr int KV_BYTES = TD_KEYS * D * 2;        // one of K or V of a stage
   constexpr int STAGE_BYTES = 2 * KV_BYTES;
@@ -106,32 +150,18 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* stages = base;
   bf16* qs = reinterpret_cast<bf16*>(base + TD_STAGES * STAGE_BYTES);
-  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(qs + 16 * QROW);
+  bf16* new_kv = qs + 16 * QROW;                               // fused rotation: [16 tokens][K, V][D]
+  TdStageHeader* headers = reinterpret_cast<TdStageHeader*>(new_kv + 16 * 2 * D);
+  unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(headers + TD_STAGES);
   unsigned long long* empty_bar = full_bar + TD_STAGES;
   int* abort_flag = reinterpret_cast<int*>(empty_bar + TD_STAGES);
-  bf16* new_kv = reinterpret_cast<bf16*>(abort_flag + 4);   // fused rotation: [16 tokens][K, V][D]
+  // q and the new tokens' keys and values are dead once an item's last tile is done: the four consumer
+  // warps merge through that memory, four rows at a time (the stages belong to the next item by then)
+  float* merge_o = reinterpret_cast<float*>(qs);                // [4 warps][4 rows][D]
+  float* merge_ml = merge_o + TD_CONSUMERS * 4 * D;             // [4 warps][4 rows][2]
+  static_assert(16 * QROW * 2 + 16 * 2 * D * 2 >= (TD_CONSUMERS * 4 * D + TD_CONSUMERS * 4 * 2) * 4, "merge area");
 
-  const int req = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_begin = p.query_start[req];
-  const int q_len = p.query_start[req + 1] - q_begin;
-  const int context = p.context_lens[req];
-  const int rows_total = min(q_len * p.G, 16);
-  const int last_pos = context + (rows_total - 1) / p.G;
-  int key_lo = p.window > 0 ? max(0, context - p.window + 1) : 0;
-  int key_hi = last_pos + 1;
-  {
-    const int first_tile_key = (key_lo / TD_KEYS) * TD_KEYS;
-    const int tiles = (key_hi - first_tile_key + TD_KEYS - 1) / TD_KEYS;
-    const int per = (tiles + p.num_splits - 1) / p.num_splits;
-    const int lo = first_tile_key + split * per * TD_KEYS;
-    key_hi = min(key_hi, lo + per * TD_KEYS);
-    key_lo = max(key_lo, lo);
-  }
-  const int tile_begin = key_lo / TD_KEYS;
-  const int tile_end = key_hi > key_lo ? (key_hi + TD_KEYS - 1) / TD_KEYS : tile_begin;
-  const int num_tiles = tile_end - tile_begin;
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < TD_STAGES; ++s) {
       kvb_mbar_init(&full_bar[s], 1);
@@ -141,24 +171,167 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     kvb_mbar_init_fence();
   }
   __syncthreads();
-  if (warp != TD_CONSUMERS) {
-    kvb_grid_wait();                 // q is the output of the kernels in front
-    kvb_trace_scope__.after_wait();
+
+  if (warp == TD_CONSUMERS) {
+    // ---------------- producer ----------------
+    // The whole warp walks the block's work items and, inside an item, its tiles; the ring of stages
+    // runs on from one item into the next, so the first tiles of the next item are on their way while
+    // the consumers still merge and store the last one.  The first item is the block's index; with a
+    // work counter the following ones are taken from it (blocks stay until the work is gone), else
+    // there is one item a block.  Page ids are fetched 32 table entries at a time, one lane each (a
+    // coalesced load), a batch ahead of their use, so no copy waits on a table lookup.  Lane 0 owns
+    // the barriers and writes the headers; lanes 0..pages_per_tile-1 each issue one page's copies.
+    const int ppt = TD_KEYS / p.page_size;            // pages per tile: 1, 2, 4 or 8
+    bool waited = false, reached_end = false;
+    int g = 0;                                        // stages pushed so far
+    int item = blockIdx.x;
+    while (true) {
+      if (item >= p.total_items) item = -1;
+      TdStageHeader h;
+      h.item = -1; h.it = 0; h.num_tiles = 0; h.q_begin = 0; h.q_len = 0; h.context = 0; h.key_lo = 0; h.key_hi = 0;
+      if (item >= 0) h = td_describe_item(p, item);
+      const int req = item >= 0 ? item / (p.KVH * p.num_splits) : 0;
+      const int kvh = item >= 0 ? (item / p.num_splits) % p.KVH : 0;
+      const int tile_begin = h.key_lo / TD_KEYS;
+      const int* pages = p.table + (size_t)req * p.table_stride;
+      const int first_entry = tile_begin * ppt;
+      const int total_entries = h.num_tiles * ppt;
+      const int key_hi = h.key_hi;
+      auto fetch = [&](int entry) -> int {             // table entry `entry` of this item, 0 beyond it
+        if (entry >= total_entries) return 0;
+        const int index = first_entry + entry;
+        if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
+        const int page = pages[index];
+        if (page < 0 || page >= p.num_pages) {
+          atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+          return 0;
+        }
+        return page;
+      };
+      int cur = fetch(lane), nxt = fetch(32 + lane);
+      // an item without keys (an empty split) and the end of the work still get a stage: a header alone
+      const int pushes = h.num_tiles > 0 ? h.num_tiles : 1;
+      int ok = 1;
+      for (int it = 0; it < pushes && ok; ++it, ++g) {
+        const int stage = g % TD_STAGES;
+        const bool data = h.num_tiles > 0;
+        const int e0 = it * ppt;
+        // a tile that holds keys written in this step by a kernel in front (with the cache write done
+        // here, the consumers lay those keys over the tile themselves)
+        if (data && !waited && p.k_cache == nullptr && (tile_begin + it + 1) * TD_KEYS > h.context) {
+          kvb_grid_wait();
+          waited = true;
+        }
+        if (e0 > 0 && (e0 & 31) == 0) {                 // crossed into the next batch of entries
+          cur = nxt;
+          nxt = fetch(e0 + 32 + lane);
+        }
+        if (lane == 0) {
+          if (g >= TD_STAGES && !kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&empty_bar[stage], ((g / TD_STAGES) & 1) ^ 1)) {
+            atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+            atomicExch(abort_flag, 1);
+            ok = 0;
+          }
+          if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
+          if (ok) {
+            h.it = it;
+            headers[stage] = h;                         // released to the consumers by the arrival below
+            if (data) kvb_mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+            else kvb_mbar_arrive(&full_bar[stage]);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (data) {
+          const int page = __shfl_sync(0xffffffffu, cur, (e0 + lane) & 31);
+          if (lane < ppt) {
+            unsigned char* kdst = stages + stage * STAGE_BYTES;
+            unsigned char* vdst = kdst + KV_BYTES;
+            const int row = (page * p.KVH + kvh) * p.page_size * HALVES;   // in rows of 64 elements
+            const int dst_off = lane * p.page_size * HALVES * 128;
+            kvb_tma_2d(kdst + dst_off, &k_map, 0, row, &full_bar[stage]);     // one contiguous page of a head
+            kvb_tma_2d(vdst + dst_off, &v_map, 0, row, &full_bar[stage]);
+          }
+        }
+      }
+      if (!ok) break;
+      if (item < 0) {
+        reached_end = true;
+        break;
+      }
+      if (p.work == nullptr) {
+        item = p.total_items;                           // one item a block: the end comes next
+      } else {
+        // the counter is shared with the launch in front if that is this kernel too: not before it is done
+        if (!waited) {
+          kvb_grid_wait();
+          waited = true;
+        }
+        int next = 0;
+        if (lane == 0) next = gridDim.x + atomicAdd(&p.work[0], 1);
+        item = __shfl_sync(0xffffffffu, next, 0);
+      }
+    }
+    if (!waited) kvb_grid_wait();
+    // the last block to see the end of the work puts the counters back for the next launch
+    if (p.work != nullptr && reached_end && lane == 0) {
+      __threadfence();
+      if (atomicAdd(&p.work[1], 1) == (int)gridDim.x - 1) {
+        p.work[0] = 0;
+        p.work[1] = 0;
+        __threadfence();
+      }
+    }
+    // on an aborted run, let the copies already issued land before the block may exit
+    if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
+      for (int s = max(0, g - TD_STAGES); s < g; ++s)
+        kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[s % TD_STAGES], (s / TD_STAGES) & 1);
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  // They follow the headers of the ring: the first tile of an item sets the item up (q rows into
+  // shared memory, rotated here if asked; this step's keys and values into the cache), every tile is
+  // scored and accumulated, the last one is followed by the merge of the four warps and the store.
+  float o[DBLOCKS][4];
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+  unsigned qf[KSTEPS][4];
+  int row_pos[2] = {0, 0};
+  bool row_valid[2] = {false, false};
+  int req = 0, kvh = 0, split = 0, q_begin = 0, q_len = 0, context = 0, key_lo = 0, key_hi = 0, tile_begin = 0,
+      rows_total = 0;
+  bool waited = false;
+  const int wkey = warp * 16;
+  auto begin_item = [&](const TdStageHeader& h) {
+    // ---- a new item ----
+    req = h.item / (p.KVH * p.num_splits);
+    const int rest = h.item - req * (p.KVH * p.num_splits);
+    kvh = rest / p.num_splits;
+    split = rest - kvh * p.num_splits;
+    q_begin = h.q_begin; q_len = h.q_len; context = h.context; key_lo = h.key_lo; key_hi = h.key_hi;
+    tile_begin = key_lo / TD_KEYS;
+    rows_total = min(q_len * p.G, 16);
+    if (!waited) {
+      kvb_grid_wait();                 // q is the output of the kernels in front
+      kvb_trace_scope__.after_wait();
+      waited = true;
+    }
     // query rows -> padded shared memory (flat row r -> token r / G, head kvh*G + r % G), rotated on
     // the way when the rotation is done here: an item is the two 16-byte pieces (d, d + D/2)
     constexpr int PAIRS = D / 16;
     for (int i = threadIdx.x; i < 16 * PAIRS; i += TD_CONSUMERS * 32) {
-      const int r = i / PAIRS, g = i % PAIRS;
+      const int r = i / PAIRS, gq = i % PAIRS;
       Vec16<bf16> lo, hi;
       lo.raw = make_uint4(0, 0, 0, 0);
       hi.raw = make_uint4(0, 0, 0, 0);
       if (r < rows_total) {
         const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-        const bf16* x = p.q + (size_t)token * p.q_stride + (size_t)head * D + g * 8;
+        const bf16* x = p.q + (size_t)token * p.q_stride + (size_t)head * D + gq * 8;
         lo.load(x);
         hi.load(x + D / 2);
         if (p.cos_sin != nullptr) {
-          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + g * 8;
+          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + gq * 8;
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float2 t = cs[e];
@@ -168,24 +341,24 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
           }
         }
       }
-      *reinterpret_cast<uint4*>(qs + r * QROW + g * 8) = lo.raw;
-      *reinterpret_cast<uint4*>(qs + r * QROW + D / 2 + g * 8) = hi.raw;
+      *reinterpret_cast<uint4*>(qs + r * QROW + gq * 8) = lo.raw;
+      *reinterpret_cast<uint4*>(qs + r * QROW + D / 2 + gq * 8) = hi.raw;
     }
-    // this step's keys and values whose positions fall into this block's key range: rotate the key,
+    // this step's keys and values whose positions fall into this item's key range: rotate the key,
     // write both into the cache, keep them to lay over the tile that holds their (old) slots
     if (p.k_cache != nullptr) {
       const int new_tokens = q_len < 16 ? q_len : 16;
       for (int i = threadIdx.x; i < new_tokens * 2 * PAIRS; i += TD_CONSUMERS * 32) {
-        const int t = i / (2 * PAIRS), which = (i / PAIRS) & 1, g = i % PAIRS;   // which: 0 key, 1 value
+        const int t = i / (2 * PAIRS), which = (i / PAIRS) & 1, gq = i % PAIRS;   // which: 0 key, 1 value
         const int pos = context + t;
         if (pos < key_lo || pos >= key_hi) continue;
         const int token = q_begin + t;
-        const bf16* x = (which ? p.v_new : p.k_new) + (size_t)token * p.q_stride + (size_t)kvh * D + g * 8;
+        const bf16* x = (which ? p.v_new : p.k_new) + (size_t)token * p.q_stride + (size_t)kvh * D + gq * 8;
         Vec16<bf16> lo, hi;
         lo.load(x);
         hi.load(x + D / 2);
         if (!which && p.cos_sin != nullptr) {
-          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + g * 8;
+          const float2* cs = p.cos_sin + (size_t)token * (D / 2) + gq * 8;
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float2 c = cs[e];
@@ -194,7 +367,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             hi.set(e, b * c.x + a * c.y);
           }
         }
-        bf16* keep = new_kv + ((size_t)t * 2 + which) * D + g * 8;
+        bf16* keep = new_kv + ((size_t)t * 2 + which) * D + gq * 8;
         *reinterpret_cast<uint4*>(keep) = lo.raw;
         *reinterpret_cast<uint4*>(keep + D / 2) = hi.raw;
         const int page = p.table[(size_t)req * p.table_stride + pos / p.page_size];
@@ -202,116 +375,50 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
           atomicOr(p.status, KVB_STATUS_BAD_PAGE);
         } else {
           bf16* dst = (which ? p.v_cache : p.k_cache) +
-                      (((size_t)page * p.KVH + kvh) * p.page_size + pos % p.page_size) * D + g * 8;
+                      (((size_t)page * p.KVH + kvh) * p.page_size + pos % p.page_size) * D + gq * 8;
           lo.store(dst);
           hi.store(dst + D / 2);
         }
       }
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
-  }
-
-  float o[DBLOCKS][4];
-#pragma unroll
-  for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
-
-  if (warp == TD_CONSUMERS) {
-    // ---------------- producer ----------------
-    // The whole warp walks the tiles.  Page ids are fetched 32 table entries at a time, one
-    // lane each (a coalesced load), a batch ahead of their use, so no copy waits on a table
-    // lookup.  Lane 0 owns the barriers; lanes 0..pages_per_tile-1 each issue one page's copies.
-    const int* pages = p.table + (size_t)req * p.table_stride;
-    const int ppt = TD_KEYS / p.page_size;            // pages per tile: 1, 2, 4 or 8
-    const int first_entry = tile_begin * ppt;
-    const int total_entries = num_tiles * ppt;
-    auto fetch = [&](int entry) -> int {             // table entry `entry` of this split, 0 beyond it
-      if (entry >= total_entries) return 0;
-      const int index = first_entry + entry;
-      if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
-      const int page = pages[index];
-      if (page < 0 || page >= p.num_pages) {
-        atomicOr(p.status, KVB_STATUS_BAD_PAGE);
-        return 0;
-      }
-      return page;
-    };
-    int cur = fetch(lane), nxt = fetch(32 + lane);
-    int issued = 0;
-    bool waited = false;
-    for (int it = 0; it < num_tiles; ++it) {
-      const int stage = it % TD_STAGES;
-      const int e0 = it * ppt;
-      // a tile that holds keys written in this step by a kernel in front (with the cache write done
-      // here, the consumers lay those keys over the tile themselves)
-      if (!waited && p.k_cache == nullptr && (tile_begin + it + 1) * TD_KEYS > context) {
-        kvb_grid_wait();
-        waited = true;
-      }
-      if (e0 > 0 && (e0 & 31) == 0) {                 // crossed into the next batch of entries
-        cur = nxt;
-        nxt = fetch(e0 + 32 + lane);
-      }
-      int ok = 1;
-      if (lane == 0) {
-        if (it >= TD_STAGES && !kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&empty_bar[stage], ((it / TD_STAGES) & 1) ^ 1)) {
-          atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
-          atomicExch(abort_flag, 1);
-          ok = 0;
-        }
-        if (ok && *reinterpret_cast<volatile int*>(abort_flag)) ok = 0;
-        if (ok) kvb_mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      const int page = __shfl_sync(0xffffffffu, cur, (e0 + lane) & 31);
-      if (lane < ppt) {
-        unsigned char* kdst = stages + stage * STAGE_BYTES;
-        unsigned char* vdst = kdst + KV_BYTES;
-        const int row = (page * p.KVH + kvh) * p.page_size * HALVES;   // in rows of 64 elements
-        const int dst_off = lane * p.page_size * HALVES * 128;
-        kvb_tma_2d(kdst + dst_off, &k_map, 0, row, &full_bar[stage]);     // one contiguous page of a head
-        kvb_tma_2d(vdst + dst_off, &v_map, 0, row, &full_bar[stage]);
-      }
-      issued = it + 1;
-    }
-    if (!waited) kvb_grid_wait();   // this warp joins the stores below: nothing is written before the wait
-    // on an aborted run, let the copies already issued land before the block may exit
-    if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
-      for (int it = max(0, issued - TD_STAGES); it < issued; ++it)
-        kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[it % TD_STAGES], (it / TD_STAGES) & 1);
-    }
-  } else {
-    // ---------------- consumers ----------------
-    unsigned qf[KSTEPS][4];
 #pragma unroll
     for (int k = 0; k < KSTEPS; ++k) {
       const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
       const int c = k * 16 + 8 * (lane >> 4);
       td_ldmatrix_x4(qf[k], kvb_smem(qs + r * QROW + c));
     }
-    int row_pos[2];
-    bool row_valid[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = (lane >> 2) + 8 * h;
-      row_valid[h] = r < rows_total;
-      row_pos[h] = context + (row_valid[h] ? r / p.G : 0);
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = (lane >> 2) + 8 * hh;
+      row_valid[hh] = r < rows_total;
+      row_pos[hh] = context + (row_valid[hh] ? r / p.G : 0);
+      row_max[hh] = -INFINITY;
+      row_sum[hh] = 0.0f;
     }
-    const int group = warp / TD_GROUP_WARPS;
-    const int wkey = (warp % TD_GROUP_WARPS) * 16;
-    for (int it = group; it < num_tiles; it += TD_GROUPS) {
-      const int stage = it % TD_STAGES;
-      if (!kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[stage], (it / TD_STAGES) & 1)) {
-        atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
-        atomicExch(abort_flag, 1);
-        break;
-      }
+#pragma unroll
+    for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+  };
+  // The block's first item is its index: q is loaded (and this step's keys written) while the first
+  // tiles are on their way.  Later items are known from the header of their first stage.
+  begin_item(td_describe_item(p, blockIdx.x));
+  for (int g = 0;; ++g) {
+    const int stage = g % TD_STAGES;
+    if (!kvb_mbar_wait<TD_SPIN_LIMIT, 64>(&full_bar[stage], (g / TD_STAGES) & 1)) {
+      atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
+      atomicExch(abort_flag, 1);
+      break;
+    }
+    const TdStageHeader h = headers[stage];
+    if (h.item < 0) break;                              // the end of the work
+    const int it = h.it;
+    if (it == 0 && g > 0) begin_item(h);
+    if (h.num_tiles > 0) {
+      // ---- one tile of 64 keys ----
       const unsigned kbase = kvb_smem(stages + stage * STAGE_BYTES);
       const unsigned vbase = kbase + KV_BYTES;
       if (p.k_cache != nullptr) {
         // a tile that holds slots of this step's tokens: lay the fresh keys and values over them
-        static_assert(TD_GROUPS == 1, "the overlay is written by all consumer warps together");
         const int tile_lo = (tile_begin + it) * TD_KEYS;
         const int first_new = max(max(context, key_lo), tile_lo), end_new = min(min(context + q_len, key_hi), tile_lo + TD_KEYS);
         if (first_new < end_new) {
@@ -356,25 +463,25 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       for (int j = 0; j < 2; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int h = e >> 1;
+          const int hh = e >> 1;
           const int key = (tile_begin + it) * TD_KEYS + wkey + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool seen = row_valid[h] && key >= key_lo && key < key_hi && key <= row_pos[h] &&
-                            (p.window <= 0 || key > row_pos[h] - p.window);
+          const bool seen = row_valid[hh] && key >= key_lo && key < key_hi && key <= row_pos[hh] &&
+                            (p.window <= 0 || key > row_pos[hh] - p.window);
           const float v = seen ? s[j][e] * p.scale_log2 : -INFINITY;
           s[j][e] = v;
-          tile_max[h] = fmaxf(tile_max[h], v);
+          tile_max[hh] = fmaxf(tile_max[hh], v);
         }
       }
       float correction[2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float m = tile_max[h];
+      for (int hh = 0; hh < 2; ++hh) {
+        float m = tile_max[hh];
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        const float new_max = fmaxf(row_max[h], m);
-        correction[h] = (row_max[h] == -INFINITY) ? 0.0f : exp2f(row_max[h] - new_max);
-        row_max[h] = new_max;
-        row_sum[h] *= correction[h];
+        const float new_max = fmaxf(row_max[hh], m);
+        correction[hh] = (row_max[hh] == -INFINITY) ? 0.0f : exp2f(row_max[hh] - new_max);
+        row_max[hh] = new_max;
+        row_sum[hh] *= correction[hh];
       }
 #pragma unroll
       for (int j = 0; j < DBLOCKS; ++j) {
@@ -385,10 +492,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       for (int j = 0; j < 2; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int h = e >> 1;
-          const float pv = (s[j][e] == -INFINITY) ? 0.0f : exp2f(s[j][e] - row_max[h]);
+          const int hh = e >> 1;
+          const float pv = (s[j][e] == -INFINITY) ? 0.0f : exp2f(s[j][e] - row_max[hh]);
           s[j][e] = pv;
-          row_sum[h] += pv;
+          row_sum[hh] += pv;
         }
       }
       unsigned pa[4];
@@ -405,62 +512,66 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         td_mma(o[j], pa, vb[0], vb[1]);
         td_mma(o[j + 1], pa, vb[2], vb[3]);
       }
-      __syncwarp();
-      if (lane == 0) kvb_mbar_arrive(&empty_bar[stage]);
     }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
-      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
-    }
-  }
+    __syncwarp();
+    if (lane == 0) kvb_mbar_arrive(&empty_bar[stage]);
+    if (it + 1 < h.num_tiles) continue;
 
-  // ---- merge the four consumer warps through the (now idle) stage memory -------------------
-  __syncthreads();
-  float* merge_o = reinterpret_cast<float*>(stages);          // [4][16][D]
-  float* merge_ml = merge_o + TD_CONSUMERS * 16 * D;          // [4][16][2]
-  if (warp < TD_CONSUMERS) {
+    // ---- the item's last tile is done: merge the four warps (four rows at a time) and store ----
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = (lane >> 2) + 8 * h;
+    for (int hh = 0; hh < 2; ++hh) {
+      row_sum[hh] += __shfl_xor_sync(0xffffffffu, row_sum[hh], 1);
+      row_sum[hh] += __shfl_xor_sync(0xffffffffu, row_sum[hh], 2);
+    }
+    const int chunks = (rows_total + 3) / 4;
+    for (int c = 0; c < chunks; ++c) {
+      // all warps are past their last use of q and of the new keys (first chunk) or of the chunk before
+      asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+      const int hh = c >> 1;
+      if (((lane >> 4) & 1) == (c & 1)) {               // lanes that hold rows [4c, 4c + 4)
+        const int r4 = (lane >> 2) & 3;
 #pragma unroll
-      for (int j = 0; j < DBLOCKS; ++j) {
-        float* dst = merge_o + ((size_t)(warp * 16 + r)) * D + j * 8 + (lane & 3) * 2;
-        dst[0] = o[j][2 * h];
-        dst[1] = o[j][2 * h + 1];
+        for (int j = 0; j < DBLOCKS; ++j) {
+          float* dst = merge_o + ((size_t)(warp * 4 + r4)) * D + j * 8 + (lane & 3) * 2;
+          dst[0] = hh ? o[j][2] : o[j][0];
+          dst[1] = hh ? o[j][3] : o[j][1];
+        }
+        if ((lane & 3) == 0) {
+          merge_ml[(warp * 4 + r4) * 2 + 0] = hh ? row_max[1] : row_max[0];
+          merge_ml[(warp * 4 + r4) * 2 + 1] = hh ? row_sum[1] : row_sum[0];
+        }
       }
-      if ((lane & 3) == 0) {
-        merge_ml[(warp * 16 + r) * 2 + 0] = row_max[h];
-        merge_ml[(warp * 16 + r) * 2 + 1] = row_sum[h];
+      asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
+      const int rows_here = min(4, rows_total - 4 * c);
+      for (int i = threadIdx.x; i < rows_here * D; i += TD_CONSUMERS * 32) {
+        const int r4 = i / D, d = i % D, r = 4 * c + r4;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < TD_CONSUMERS; ++w) m = fmaxf(m, merge_ml[(w * 4 + r4) * 2]);
+        float total = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < TD_CONSUMERS; ++w) {
+          const float mw = merge_ml[(w * 4 + r4) * 2];
+          const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
+          total += merge_ml[(w * 4 + r4) * 2 + 1] * f;
+          acc += merge_o[((size_t)(w * 4 + r4)) * D + d] * f;
+        }
+        if (p.num_splits == 1) {
+          const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
+          p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
+              __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+        } else {
+          const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
+          p.partial_o[(slot * 16 + r) * D + d] = acc;
+          if (d == 0) {
+            p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
+            p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
+          }
+        }
       }
     }
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < rows_total * D; i += TD_THREADS) {
-    const int r = i / D, d = i % D;
-    float m = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < TD_CONSUMERS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
-    float total = 0.0f, acc = 0.0f;
-#pragma unroll
-    for (int w = 0; w < TD_CONSUMERS; ++w) {
-      const float mw = merge_ml[(w * 16 + r) * 2];
-      const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
-      total += merge_ml[(w * 16 + r) * 2 + 1] * f;
-      acc += merge_o[((size_t)(w * 16 + r)) * D + d] * f;
-    }
-    if (p.num_splits == 1) {
-      const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-      p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
-          __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
-    } else {
-      const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
-      p.partial_o[(slot * 16 + r) * D + d] = acc;
-      if (d == 0) {
-        p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
-        p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
-      }
-    }
+    // the next item's q goes where the merge just read
+    asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
   }
 }
 
@@ -539,16 +650,17 @@ extern "C" int kvb_make_kv_tensor_map(void* map_out, const void* cache, long lon
 
 template <int D>
 static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeParams& p,
-                             int max_rows, cudaStream_t stream) {
-  constexpr size_t SMEM = 1024 + TD_STAGES * 2 * TD_KEYS * D * 2 + 16 * (D + 8) * 2 + 2 * TD_STAGES * 8 + 16 +
-                          16 * 2 * D * 2;   // + the new tokens' keys and values (fused rotation)
+                             int max_rows, int blocks, cudaStream_t stream) {
+  constexpr size_t SMEM = 1024 + TD_STAGES * 2 * TD_KEYS * D * 2 + 16 * (D + 8) * 2 +
+                          16 * 2 * D * 2 +   // the new tokens' keys and values (fused rotation)
+                          TD_STAGES * sizeof(TdStageHeader) + 2 * TD_STAGES * 8 + 16;
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)SMEM));
     configured = true;
   }
-  dim3 grid(p.num_splits, p.KVH, p.num_reqs);
+  dim3 grid(blocks);
   KVB_CHECK_CUDA(kvb_launch((flash_decode_tma_kernel<D>), dim3(grid), dim3(TD_THREADS), SMEM, stream, true, k_map, v_map, p));
   KVB_CHECK_LAUNCH();
   if (p.num_splits > 1) {
@@ -565,7 +677,8 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
                                     int table_stride, const int* query_start, const int* context_lens,
                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
                                     int num_pages, float scale, int window, int num_splits, float* scratch,
-                                    const float* cos_sin, void* k_cache, void* v_cache, cudaStream_t stream) {
+                                    const float* cos_sin, void* k_cache, void* v_cache, int* work, int max_blocks,
+                                    cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == 64 || D == 128, "decode attention (TMA): head_dim must be 64 or 128");
   KVB_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "decode attention (TMA): give both caches or none");
@@ -573,7 +686,8 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
               "decode attention (TMA): page size must be 8, 16, 32 or 64");
   KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "decode attention (TMA): H must be a multiple of KVH");
   KVB_REQUIRE(max_query_len * (H / KVH) <= 16, "decode attention (TMA): at most 16 rows per request and kv head");
-  KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "decode attention (TMA): batch too large for one launch");
+  KVB_REQUIRE((long long)num_reqs * KVH * (num_splits < 1 ? 1 : num_splits) < (1ll << 30),
+              "decode attention (TMA): batch too large for one launch");
   KVB_REQUIRE(aligned16(q) && (q_stride % 8) == 0, "decode attention (TMA): q must be 16-byte aligned");
   KVB_REQUIRE(k_map_host != nullptr && v_map_host != nullptr, "decode attention (TMA): tensor maps are missing");
   DecodeParams p;
@@ -599,8 +713,14 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
   const int max_rows = max_query_len * p.G;
-  if (D == 64) return launch_decode_tma<64>(k_map, v_map, p, max_rows, stream);
-  return launch_decode_tma<128>(k_map, v_map, p, max_rows, stream);
+  // With a work counter and more items than `max_blocks`, that many blocks stay and share the items;
+  // else one block an item.
+  p.total_items = num_reqs * KVH * p.num_splits;
+  const bool shared = work != nullptr && max_blocks > 0 && p.total_items > max_blocks;
+  p.work = shared ? work : nullptr;
+  const int blocks = shared ? max_blocks : p.total_items;
+  if (D == 64) return launch_decode_tma<64>(k_map, v_map, p, max_rows, blocks, stream);
+  return launch_decode_tma<128>(k_map, v_map, p, max_rows, blocks, stream);
 }
 
 KVB_TRACE_TU(attention_decode_tma)

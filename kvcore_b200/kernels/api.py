@@ -50,7 +50,7 @@ def ensure_built(verbose: bool = False) -> str:
                                       _int, _int, _int, _int, _float, _int, _int, _vp, _vp],
         "kvb_make_kv_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
-                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp],
+                                 _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
         "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
@@ -153,6 +153,8 @@ def read_status(reset: bool = True) -> int:
                 scratch.view(torch.int32).fill_(int(_lib.kvb_gemm_stream_scratch_marker()))
             elif flags is not None:
                 flags.zero_()
+        for counters in _decode_work_counters.values():
+            counters.zero_()
     return out.value
 
 
@@ -392,6 +394,21 @@ def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int
 
 
 TMA_DECODE_BLOCKS_PER_SM = 2
+# more (request, kv head, split) items than blocks fit the GPU at once: blocks stay and share the items
+# (KVCORE_B200_DECODE_SHARED_WORK=0: one block an item, whatever their number)
+TMA_DECODE_SHARED_WORK = os.environ.get("KVCORE_B200_DECODE_SHARED_WORK", "1") != "0"
+_decode_work_counters: dict[torch.device, torch.Tensor] = {}
+
+
+def _decode_work(device: torch.device) -> torch.Tensor:
+    """Two counters through which the blocks of the TMA decode kernel share out their work when there
+    is more of it than blocks that fit the GPU at once (zero between launches: the kernel's last
+    block puts them back)."""
+    counters = _decode_work_counters.get(device)
+    if counters is None:
+        counters = _decode_work_counters[device] = torch.zeros(2, dtype=torch.int32, device=device)
+    return counters
+
 _kv_tensor_maps: dict[tuple, tuple] = {}
 
 
@@ -488,7 +505,9 @@ def paged_attention(
                   num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
                   splits, None if scratch is None else scratch.data_ptr(),
                   None if cos_sin is None else cos_sin.data_ptr(),
-                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None, _stream(),
+                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None,
+                  _decode_work(qkv.device).data_ptr() if TMA_DECODE_SHARED_WORK else None,
+                  SM_COUNT * TMA_DECODE_BLOCKS_PER_SM, _stream(),
                   kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
             return out
         if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)

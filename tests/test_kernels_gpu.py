@@ -240,6 +240,10 @@ FLASH_SHAPES = [
     (64, 8, 128, 16, [(1000, 1), (17, 1), (2047, 2), (0, 1)], None, None),   # TMA decode: 8 heads a group
     (16, 2, 128, 16, [(0, 200), (100, 50), (333, 1)], None, None),           # tcgen05 prefill: 8 heads a group
     (24, 8, 128, 16, [(1500, 1), (0, 1), (640, 1)], None, None),             # TMA decode: 3 heads a group
+    # TMA decode with more (request, kv head, split) items than blocks that fit the GPU: blocks stay and share them
+    (32, 8, 128, 16, [(37 * i % 700 + i % 3, 1) for i in range(50)], None, None),
+    (32, 8, 128, 16, [(1000, 1), (17, 1), (4095, 1), (0, 1), (300, 2)], None, 13),   # with empty splits
+    (16, 4, 64, 8, [(50 * i % 333, 1 + i % 2) for i in range(80)], None, None),
     (8, 2, 128, 32, [(0, 700)], 200, None),                                  # tcgen05 prefill: window
     (4, 4, 128, 16, [(250, 9), (0, 129)], None, None),                       # tcgen05 prefill: one head a group
 ]
@@ -284,6 +288,8 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got.float(), general.float(), rtol=2e-2, atol=2e-2)
     assert K().read_status() == 0
+    # the counters through which blocks share work are back at zero for the next launch
+    assert all(not counters.any() for counters in K().api._decode_work_counters.values())
 
 
 ROTATING_DECODE_SHAPES = [
@@ -296,6 +302,8 @@ ROTATING_DECODE_SHAPES = [
     (6, 3, 48, 16, [(17, 2), (0, 1), (100, 2)], None, None),               # not the TMA kernel: kernel in front
     (64, 8, 128, 16, [(1000, 1), (0, 1), (63, 2)], None, None),            # 8 heads a group
     (24, 8, 128, 16, [(1500, 1), (0, 1), (640, 5)], None, 4),              # 3 heads a group, five new tokens
+    (32, 8, 128, 16, [(29 * i % 500, 1 + i % 3) for i in range(40)], None, None),   # 320 items for 296 blocks
+    (32, 8, 128, 16, [(61 * i % 900, 1) for i in range(14)], None, 3),             # 336 items, splits
     (8, 2, 128, 16, [(0, 200), (130, 77), (500, 1)], None, None),          # prefill shapes: kernel in front
 ]
 
