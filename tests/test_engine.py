@@ -440,3 +440,41 @@ def test_toy_parts_register_build_and_step_without_touching_the_framework(device
         assert [g.kind for g in kv.groups] == ["window", "full"]
         assert [len(g.entries) for g in kv.groups] == [2, 1]
         assert len(step_function.storage.state_tensors) == 1
+
+
+def test_step_entries_fed_from_a_sampler_output(device, tmp_path):
+    """The step function's own view of a token that the host has not seen: a placeholder id and the row
+    of the sampler output that holds the real one give the logits of the id packed by the host; what
+    cannot be right is refused (no output given, more than one token, a row outside the output)."""
+    from kvcore_b200.engine.step import StepEntry
+    from kvcore_b200.engine.trace_replay import build_replay
+
+    config = rc.TINY_CONFIGS["A"]
+    folder = rc.write_model(tmp_path / "m", config, 2, "float32")
+    prompts = {"a": rc.random_tokens(256, 11, 1), "b": rc.random_tokens(256, 6, 2)}
+
+    def run(fed):
+        step_function, kv = build_replay(str(folder), "float32", 256, device=device)
+        for rid, tokens in prompts.items():
+            assert kv.allocate_slots(rid, len(tokens))
+        step_function.step([StepEntry(rid, tokens, ()) for rid, tokens in prompts.items()])
+        sampled = torch.tensor([77, 5, 190], dtype=torch.int32, device=device)
+        for rid in prompts:
+            assert kv.allocate_slots(rid, 1)
+        if fed:
+            entries = [StepEntry("a", (0,), (0,), fed_from=2), StepEntry("b", (0,), (0,), fed_from=0)]
+            return step_function, kv, step_function.step(entries, sampled).float().cpu()
+        entries = [StepEntry("a", (190,), (0,)), StepEntry("b", (77,), (0,))]
+        return step_function, kv, step_function.step(entries).float().cpu()
+
+    _, _, from_host = run(False)
+    step_function, kv, from_device = run(True)
+    assert torch.equal(from_host, from_device)
+    sampled = torch.tensor([1, 2], dtype=torch.int32, device=device)
+    for rid in prompts:
+        assert kv.allocate_slots(rid, 2)
+    for entries, feedback in (([StepEntry("a", (0,), (0,), fed_from=0)], None),
+                              ([StepEntry("a", (0, 0), (1,), fed_from=0)], sampled),
+                              ([StepEntry("a", (0,), (0,), fed_from=2)], sampled)):
+        with pytest.raises(ValueError, match="sampler output"):
+            step_function.step(entries, feedback)
