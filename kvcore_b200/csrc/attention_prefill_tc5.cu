@@ -5,28 +5,35 @@
 // group) pair, so the G heads that share a kv head reuse every K/V tile.  It walks the keys in
 // tiles of 128.  Eleven warps:
 //   warps 0-7  softmax, two warpgroups: threads t and t+128 share row t = TMEM lane t and take
-//              columns [0,64) and [64,128) of it.  Per tile each reads its half row of
-//              S = Q.K^T from TMEM (tcgen05.ld), masks, agrees with its partner on the row
-//              maximum (through shared memory and an mbarrier), keeps the running max and a
-//              partial sum (32-bit), writes P = exp2(...) as packed bf16 back into tensor memory
-//              (tcgen05.st: the A operand of the second product is read from there, so P never
-//              touches shared memory), and rescales its half row of O in TMEM when the max moved.  (One warpgroup alone is the bottleneck: ~2,300 cycles of exp2 and
-//              conversions per tile against ~1,500 cycles of MMA.)
+//              columns [0,64) and [64,128) of it, each for itself: a thread keeps the running max
+//              and sum (32-bit) of its own columns and has an accumulator of its own,
+//              O_h = sum over tiles of P_h(j).V_h(j) (its half of the probabilities times the 64
+//              keys that go with it); the two meet once, at the end, and the row's output is
+//              O_A and O_B put on a common maximum and divided by the common sum.  So the two
+//              warps of a scheduler are not in step, and one's waits on tensor memory are the
+//              other's working time.  Per tile a thread reads its half row of S = Q.K^T from TMEM
+//              (tcgen05.ld), masks, writes P = exp2(...) as packed bf16 over the columns it read
+//              (tcgen05.st: the A operand of the second product is read from tensor memory, so P
+//              never touches shared memory), and rescales its row of O_h when its max moved.
+//              (The softmax is the bottleneck: ~2,300 cycles of exp2 and conversions per tile
+//              against ~1,200 cycles of MMA.)
 //   warps 8, 9 producers of K and of V (separate, so that a wait for a V stage never holds back
 //              the next K tile): each looks pages up in the block table (batched, a batch ahead)
 //              and issues the tiled TMA copies (two 64-column boxes per page, 128-byte swizzle)
 //              into its two-stage ring.
-//   warp 10    one thread issues the MMAs: S(j+1) = Q.K(j+1)^T into the other S buffer while the
-//              softmax warps work on S(j), then O += P(j).V(j) (P from tensor memory, V from
-//              shared memory as an MN-major operand).
-// mbarriers, all in pairs indexed by tile parity so that no waiter can fall two phases behind:
-// k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full/s_free (MMA <-> softmax, two S buffers),
-// p_ready (softmax -> MMA, two P buffers), pv_done (MMA -> softmax), x_ready (softmax partners).  tcgen05.commit arrives on the
-// barriers that follow MMAs.  Every wait is bounded: on a time-out the thread sets the
-// WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it returns.
+//   warp 10    one thread issues the MMAs: S(0) and S(1) at once; then per tile O_A += P_A(j).V_A(j)
+//              and O_B += P_B(j).V_B(j) as the halves of P arrive (P from tensor memory, V from
+//              shared memory as an MN-major operand), and S(j+2) = Q.K(j+2)^T behind them into the
+//              buffer that held S(j) and P(j): the tensor pipe takes its instructions in order.
+// mbarriers, indexed by tile parity so that no waiter can fall two phases behind:
+// k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full (MMA -> softmax, two S buffers), p_ready
+// (softmax -> MMA, per half and buffer), pv_done (MMA -> softmax), x_ready (the partners' one
+// exchange).  tcgen05.commit arrives on the barriers that follow MMAs.  Every wait is bounded: on a
+// time-out the thread sets the WAIT_TIMEOUT status bit and the block drains and frees its tensor
+// memory before it returns.
 //
-// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O [256,384) | P0 [384,448) | P1 [448,512)
-// (P: 128 keys as 64 columns of two bf16 each).
+// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O_A [256,384) | O_B [384,512); P(j) lies
+// over S(j): half h as 32 columns of two bf16 each at column 64 h of the buffer.
 // Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB (all 1024-byte aligned, 128B swizzle).
 #include <cuda.h>
 #include <string.h>
@@ -73,10 +80,9 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned long long* v_full = bars + 4;    // [2]
   unsigned long long* v_empty = bars + 6;   // [2]
   unsigned long long* s_full = bars + 8;    // [2]
-  unsigned long long* s_free = bars + 10;   // [2]
-  unsigned long long* p_ready = bars + 12;  // [2]
+  unsigned long long* p_ready = bars + 10;  // [2 halves][2]: half h of P(j) is in tensor memory
   unsigned long long* pv_done = bars + 14;  // [2]
-  unsigned long long* x_ready = bars + 16;  // [2]
+  unsigned long long* x_ready = bars + 16;  // [1]: the partners' final exchange
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 18);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   float* x_buf = reinterpret_cast<float*>(bars + 20);   // [2 parities][2 halves][128 rows]
@@ -110,8 +116,8 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       kvb_mbar_init(&v_full[i], 1);
       kvb_mbar_init(&v_empty[i], 1);
       kvb_mbar_init(&s_full[i], 1);
-      kvb_mbar_init(&s_free[i], 256);
-      kvb_mbar_init(&p_ready[i], 256);
+      kvb_mbar_init(&p_ready[i], 128);
+      kvb_mbar_init(&p_ready[2 + i], 128);
       kvb_mbar_init(&pv_done[i], 1);
       kvb_mbar_init(&x_ready[i], 256);
     }
@@ -140,8 +146,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   __syncthreads();
   kvb_tc5_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_o = tmem_base + 256;
-  const unsigned tmem_p = tmem_base + 384;   // two buffers of 64 columns
+  const unsigned tmem_o = tmem_base + 256;   // two accumulators of 128 columns: one per half of the keys of a tile
 
   if (warp == 8 || warp == 9) {
     // ================= producers: warp 8 streams K tiles, warp 9 streams V tiles =================
@@ -218,32 +223,39 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         kvb_tc5_commit(&s_full[j & 1]);
         kvb_tc5_commit(&k_empty[j & 1]);
       };
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[0], 0)) ok = false;
-      if (ok) {
+      // S(0) and S(1) at once; then, tile by tile, the two halves of O += P(j).V(j) as their halves of
+      // P arrive, and S(j+2) behind them into the buffer that held S(j) and P(j) (the tensor pipe
+      // takes its instructions in order, so it has read P(j) by then)
+      for (int n = 0; n < 2 && n < num_tiles && ok; ++n) {
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[n], 0)) { ok = false; break; }
         kvb_tc5_fence_after();
-        issue_s(0);
+        issue_s(n);
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
-        if (j + 1 < num_tiles) {
-          const int n = j + 1;
-          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[n & 1], (n >> 1) & 1)) { ok = false; break; }
-          if (n >= 2 && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&s_free[n & 1], ((n >> 1) - 1) & 1)) { ok = false; break; }
+        const int b = j & 1;
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[b], (j >> 1) & 1)) { ok = false; break; }
+        const unsigned v_addr = kvb_smem(v_smem + b * T5_TILE_BYTES);
+        const unsigned p_tmem = tmem_base + b * T5_BN;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[2 * half + b], (j >> 1) & 1)) { ok = false; break; }
+          kvb_tc5_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < T5_BN / 32; ++kk) {   // 16 keys per MMA: 8 columns of P, 16 key rows of V
+            const unsigned b_off = (half * 4 + kk) * 16 * 128;
+            kvb_tc5_mma_ts(tmem_o + half * T5_D, p_tmem + half * 64 + kk * 8,
+                           kvb_tc5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        if (!ok) break;
+        kvb_tc5_commit(&pv_done[b]);
+        kvb_tc5_commit(&v_empty[b]);
+        const int n = j + 2;
+        if (n < num_tiles) {
+          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[b], (n >> 1) & 1)) { ok = false; break; }
           kvb_tc5_fence_after();
           issue_s(n);
         }
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[j & 1], (j >> 1) & 1)) { ok = false; break; }
-        kvb_tc5_fence_after();
-        const unsigned v_addr = kvb_smem(v_smem + (j & 1) * T5_TILE_BYTES);
-        const unsigned p_tmem = tmem_p + (j & 1) * (T5_BN / 2);
-#pragma unroll
-        for (int kk = 0; kk < T5_BN / 16; ++kk) {   // 16 keys per MMA: 8 columns of P, 16 key rows of V
-          const unsigned b_off = kk * 16 * 128;
-          kvb_tc5_mma_ts(tmem_o, p_tmem + kk * 8, kvb_tc5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv,
-                    (j > 0 || kk > 0) ? 1u : 0u);
-        }
-        kvb_tc5_commit(&pv_done[j & 1]);
-        kvb_tc5_commit(&v_empty[j & 1]);
       }
       if (!ok) {
         atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
@@ -252,13 +264,16 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
   } else {
     // ================= softmax: threads t and t+128 own row t, 64 columns each =================
-    // The half row of S is read from TMEM once and kept in registers: pass 1 finds its maximum,
-    // the two partners exchange maxima, pass 2 forms P = 2^(s*scale - m), sums it and writes it
-    // as bf16 into shared memory.  Masks are applied only on tiles that need them (the diagonal,
-    // a window, rows beyond the batch).  The running maximum m is moved (and O rescaled) only
-    // when some row of the warp would grow by more than 2^8: until then P may exceed 1, which
-    // bf16 and the 32-bit sums hold easily, and O and the row sum stay consistent because both
-    // are taken against the same m.
+    // The two partners of a row do not talk to each other until the end: each keeps a running maximum
+    // and sum of its own 64 columns of every tile and its own accumulator O_h = sum over tiles of
+    // P_h(j).V_h(j) (P_h: its half of the probabilities, V_h: the 64 keys that go with it), so the two
+    // warps of a scheduler drift apart and one's waits (tensor-memory loads and stores) are the other's
+    // working time.  The half row of S is read from TMEM once and kept in registers: pass 1 finds
+    // its maximum, pass 2 forms P = 2^(s*scale - m), sums it and writes it as bf16 over the columns it
+    // read S from.  Masks are applied only on tiles that need them (the diagonal, a window, rows beyond
+    // the batch).  The running maximum m is moved (and O_h rescaled) only when some row of the warp
+    // would grow by more than 2^8: until then P may exceed 1, which bf16 and the 32-bit sums hold
+    // easily, and O_h and the row sum stay consistent because both are taken against the same m.
     const int r = threadIdx.x & 127;
     const int half = threadIdx.x >> 7;                    // which 64 columns of the row
     const int flat = row0 + r;
@@ -267,6 +282,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     const int row_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const unsigned lane_addr = ((unsigned)((warp & 3) * 32) << 16);
     const bool ragged = row0 + T5_BM > rows_total;        // block holds rows beyond the batch
+    const unsigned my_o = tmem_o + lane_addr + half * T5_D;
     float row_max = -INFINITY, row_sum = 0.0f;            // row_max in the scaled (log2) domain
     bool ok = true;
     for (int j = 0; j < num_tiles; ++j) {
@@ -280,8 +296,6 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       kvb_tc5_ld32(s_addr, s[0]);
       kvb_tc5_ld32(s_addr + 32, s[1]);
       kvb_tc5_wait_ld();
-      kvb_tc5_fence_before();
-      kvb_mbar_arrive(&s_free[b]);     // this S buffer may be overwritten by S(j+2)
       // ---- pass 1: maximum of the raw scores of this half row ----
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
@@ -301,25 +315,16 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
         }
       }
-      const float my_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      // ---- partners agree on the row maximum ----
-      float* xb = x_buf + b * 256;
-      xb[half * 128 + r] = my_max;
-      kvb_mbar_arrive(&x_ready[b]);
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[b], (j >> 1) & 1)) { ok = false; break; }
-      float tile_max = fmaxf(my_max, xb[(half ^ 1) * 128 + r]) * p.scale_log2;   // scale > 0; -inf stays -inf
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;   // scale > 0; -inf stays -inf
       const float new_max = fmaxf(row_max, tile_max);
       const bool grows = new_max > row_max + 8.0f || (row_max == -INFINITY && new_max > -INFINITY);
-      const bool move = __any_sync(0xffffffffu, grows);   // same rows, so the same answer in both partner warps
+      const bool move = __any_sync(0xffffffffu, grows);
       float correction = 1.0f;
       if (move) {
         correction = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - new_max);
         row_max = new_max;
       }
       const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
-      if (j >= 2) {  // P buffer j&1 is free once PV(j-2) has completed
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[b], ((j >> 1) - 1) & 1)) { ok = false; break; }
-      }
       // ---- pass 2: P = 2^(s*scale - m), partial row sum, packed bf16 into tensor memory ----
       float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       float packed[32];                              // 64 keys of this half row, two bf16 a register
@@ -339,56 +344,69 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
               __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632));
         }
       }
-      kvb_tc5_st32(tmem_p + lane_addr + b * (T5_BN / 2) + half * 32, packed);
+      // P(j) lies over the first half of the columns this thread read S(j) from; S(j+2) is written there
+      // only after the tensor pipe has taken P(j)
+      kvb_tc5_st32(s_addr, packed);
       row_sum = row_sum * correction + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
-      if (move && j > 0) {       // rescale this thread's half row of O: PV(j-1) must have landed first
+      if (move && j > 0) {       // rescale this thread's row of its accumulator: PV(j-1) must have landed first
         if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
         kvb_tc5_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
           float o[32];
-          kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
+          kvb_tc5_ld32(my_o + c * 32, o);
           kvb_tc5_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= correction;
-          kvb_tc5_st32(tmem_o + lane_addr + half * 64 + c * 32, o);
+          kvb_tc5_st32(my_o + c * 32, o);
         }
-        kvb_tc5_wait_st();
       }
       kvb_tc5_wait_st();
       kvb_tc5_fence_before();
-      kvb_mbar_arrive(&p_ready[b]);
+      kvb_mbar_arrive(&p_ready[2 * half + b]);
     }
     if (ok && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
+    float scale_a = 0.0f, scale_b = 0.0f;   // what O_A and O_B of this row are multiplied by
     if (ok) {
-      // partners add their partial row sums (slot of the parity the last tile did not use)
-      const int xb_slot = num_tiles & 1;
-      float* xb = x_buf + xb_slot * 256;
-      xb[half * 128 + r] = row_sum;
-      kvb_mbar_arrive(&x_ready[xb_slot]);
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[xb_slot], (num_tiles >> 1) & 1)) ok = false;
-      if (ok) row_sum += xb[(half ^ 1) * 128 + r];
+      // the partners meet once: maxima and sums of the two halves of the row
+      x_buf[half * 128 + r] = row_max;
+      x_buf[256 + half * 128 + r] = row_sum;
+      kvb_mbar_arrive(&x_ready[0]);
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[0], 0)) ok = false;
+      if (ok) {
+        const float other_max = x_buf[(half ^ 1) * 128 + r], other_sum = x_buf[256 + (half ^ 1) * 128 + r];
+        const float m = fmaxf(row_max, other_max);
+        const float mine = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - m);
+        const float theirs = (other_max == -INFINITY) ? 0.0f : exp2f(other_max - m);
+        const float total = row_sum * mine + other_sum * theirs;
+        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+        scale_a = (half == 0 ? mine : theirs) * inv;
+        scale_b = (half == 0 ? theirs : mine) * inv;
+      }
     }
     if (ok) {
       kvb_tc5_fence_after();
-      const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
       bf16* dst = nullptr;
       if (row_valid)
         dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D +
               half * 64;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float o[32];
-        kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, o);
+      for (int c = 0; c < 2; ++c) {   // this thread stores columns [64 half, +64) of the row: both accumulators' share
+        float oa[32], ob[32];
+        kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, oa);
+        kvb_tc5_ld32(tmem_o + lane_addr + T5_D + half * 64 + c * 32, ob);
         kvb_tc5_wait_ld();
         if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = oa[i + e] * scale_a + ob[i + e] * scale_b;
             uint4 packed;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[4], v[5]);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[6], v[7]);
             packed.x = *reinterpret_cast<unsigned*>(&t0);
             packed.y = *reinterpret_cast<unsigned*>(&t1);
             packed.z = *reinterpret_cast<unsigned*>(&t2);
