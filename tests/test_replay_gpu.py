@@ -233,3 +233,44 @@ def test_tokens_fed_from_the_device_give_the_logits_of_tokens_from_the_host(dtyp
     assert replays >= 4
     for a, b in zip(host_rows, fed_rows):
         assert torch.equal(a, b)
+
+
+def test_decode_step_with_more_work_items_than_block_slots(tmp_path):
+    """160 live requests on a model with two kv heads: 320 (request, kv head) items for the 296 block
+    slots of the decode attention, so its blocks stay and share the items.  The logits of one decode
+    step, eagerly and through a graph, are those of the plain implementation."""
+    import torch
+
+    import kvcore_b200.kernels as kernels
+    from kvcore_b200.engine.step import StepEntry
+    from kvcore_b200.engine.trace_replay import build_replay
+
+    config = rc.TINY_CONFIGS["D"]
+    folder = tmp_path / "m"
+    rc.write_model(folder, config, 3, "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    vocab = config["vocab_size"]
+    lengths = [40 + (37 * i) % 150 for i in range(160)]
+    requests = {f"q{i}": rc.random_tokens(vocab, n + 3, 300 + i) for i, n in enumerate(lengths)}
+    step_function, kv = build_replay(str(folder), "bfloat16", 64 * 160 * 4, max_live=160)
+    assert kernels.decode_splits_tma(160, 2, 256) * 160 * 2 > 296
+    ids = list(requests)
+    for begin in range(0, 160, 16):                      # prompts, sixteen requests a step
+        entries = []
+        for rid, n in zip(ids[begin:begin + 16], lengths[begin:begin + 16]):
+            assert kv.allocate_slots(rid, n)
+            entries.append(StepEntry(rid, requests[rid][:n], ()))
+        step_function.step(entries)
+    sample = ids[::23]
+    reference = {rid: plain_llama.forward_logits(config, weights, requests[rid]).numpy() for rid in sample}
+    for step in range(3):                                # the third step replays the graph captured in the second
+        entries = []
+        for rid, n in zip(ids, lengths):
+            assert kv.allocate_slots(rid, 1)
+            entries.append(StepEntry(rid, (requests[rid][n + step],), (0,)))
+        logits = step_function.step(entries).float().cpu().numpy()
+        assert np.isfinite(logits).all()
+        for rid in sample:
+            row, want = logits[ids.index(rid)], reference[rid][lengths[ids.index(rid)] + step]
+            assert np.abs(row - want).max() <= TOLERANCE["bfloat16"] * np.abs(reference[rid]).max(), (rid, step)
+    assert step_function.num_graph_replays >= 1 and kernels.read_status() == 0
