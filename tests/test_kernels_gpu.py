@@ -387,6 +387,45 @@ def test_paged_attention_finds_a_far_key(dtype):
                                        rtol=2e-2, atol=2e-2)
 
 
+WINDOW_EDGES = [
+    # dtype, dim, page, (context, query), window, what runs
+    (torch.float32, 64, 16, (300, 1), 100, dict(force_general=True)),
+    (torch.bfloat16, 64, 16, (300, 1), 100, dict(force_general=True)),
+    (torch.bfloat16, 128, 16, (300, 1), 100, dict(use_tma=False, use_tc5=False)),     # mma.sync, split shape
+    (torch.bfloat16, 128, 16, (300, 1), 100, dict()),                                  # TMA decode
+    (torch.bfloat16, 64, 8, (300, 1), 45, dict(num_splits=3)),                         # TMA decode: the edge on a tile's edge
+    (torch.bfloat16, 128, 16, (170, 130), 100, dict(use_tma=False, use_tc5=False)),   # mma.sync, tile shape
+    (torch.bfloat16, 128, 16, (170, 130), 100, dict()),                                # tcgen05 prefill
+    (torch.bfloat16, 128, 32, (0, 400), 144, dict()),                                  # tcgen05 prefill: the edge on a tile's edge
+]
+
+
+@pytest.mark.parametrize("dtype,dim,page,lens,window,how", WINDOW_EDGES)
+def test_paged_attention_at_the_windows_edge(dtype, dim, page, lens, window, how):
+    """The last query row sees keys (pos - window, pos].  A key that dominates the row is put just
+    inside that range: the output is its value.  Put just outside, with a huge value, it must leave no
+    trace in the output."""
+    heads = kv_heads = 2
+    context, query = lens
+    pos = context + query - 1
+    for place, inside in ((pos - window + 1, True), (pos - window, False)):
+        case = _cache_case(dtype, heads, kv_heads, dim, page, [lens], seed=13)
+        q = case["qkv"][-1, : heads * dim].view(heads, dim)
+        page_id = int(case["table"][0, place // page])
+        for head in range(heads):
+            case["k_cache"][page_id, head, place % page] = (q[head].float() * 4.0).to(dtype)
+            if not inside:
+                case["v_cache"][page_id, head, place % page] = 3.0e4
+        out = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], _Ctx(case),
+                                  heads, kv_heads, dim, 1.0, window, **how).view(query, heads, dim)[-1].float()
+        assert K().read_status() == 0
+        if inside:
+            want = case["v_cache"][page_id, :, place % page].float()
+            torch.testing.assert_close(out, want, rtol=2e-2, atol=2e-2)
+        else:
+            assert out.abs().max() < 10.0, "a key outside the window reached the output"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,page", [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (32, 8, 128, 16)])
 def test_rope_kv_write(dtype, heads, kv_heads, dim, page):
