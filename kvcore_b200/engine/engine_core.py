@@ -22,7 +22,7 @@ from typing import Any, Mapping, Sequence
 from ..config.engine_config import KVCoreConfig
 from ..sampling.params import SamplingParams
 from ..utils.tokenizer import TokenizerManager
-from .request import FinishReason, Request
+from .request import FinishReason, Request, RequestStatus
 from .runner import ModelRunner, SampleHandle
 from .scheduler import RequestStepOutput, Scheduler, SchedulerOutput
 
@@ -115,10 +115,33 @@ class EngineCore:
         return EngineCoreOutputs(update.step_outputs)
 
     def drain(self) -> None:
-        """Wait for a step that was launched ahead and drop its tokens (after an abort)."""
-        if self._in_flight is not None:
-            self.model_runner.collect(self._in_flight[1])
-            self._in_flight = None
+        """Wait for a step that is still in flight and take its tokens in, so that nothing is pending."""
+        if self._in_flight is None:
+            return
+        plan, handle = self._in_flight
+        self._in_flight = None
+        runner_output = self.model_runner.collect(handle)
+        sampled = {r: t[0] for r, t in zip(runner_output.req_ids, runner_output.sampled_token_ids) if t}
+        update = self.scheduler.update_from_outputs(plan, sampled, stop_token_ids=self.stop_token_ids)
+        for finished in update.finished_requests:
+            self.finished_outputs[finished.request_id] = FinishedRequestOutput(
+                finished.request_id, finished.output_token_ids, finished.finish_reason
+            )
+        self.model_runner.remove_requests([f.request_id for f in update.finished_requests])
+
+    def abort_requests(self, request_ids: Sequence[str] | None = None) -> tuple[FinishedRequestOutput, ...]:
+        """End the given requests (all of them for ``None``) with reason "abort": their pages go back,
+        what they generated so far is kept as their finished output.  A step in flight is taken in
+        first, so a request may turn out to have ended by itself meanwhile."""
+        self.drain()
+        aborted = self.scheduler.finish_requests(
+            None if request_ids is None else list(request_ids), RequestStatus.FINISHED_ABORTED
+        )
+        outputs = tuple(FinishedRequestOutput(f.request_id, f.output_token_ids, f.finish_reason) for f in aborted)
+        for output in outputs:
+            self.finished_outputs[output.request_id] = output
+        self.model_runner.remove_requests([o.request_id for o in outputs])
+        return outputs
 
     def take_finished_output(self, request_id: str) -> FinishedRequestOutput | None:
         return self.finished_outputs.pop(request_id, None)

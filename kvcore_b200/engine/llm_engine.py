@@ -66,6 +66,10 @@ class LLMEngine:
     def step(self) -> EngineCoreOutputs:
         return self.engine_core.step()
 
+    def abort(self, request_ids: Sequence[str] | None = None) -> list[GenerationOutput]:
+        """End the given requests (all of them for ``None``) now; returns what they had generated."""
+        return [self._as_output(finished) for finished in self.engine_core.abort_requests(request_ids)]
+
     def run(self) -> Iterator[EngineCoreOutputs]:
         """Steps until every admitted request has finished, yielding each step's outputs."""
         core = self.engine_core

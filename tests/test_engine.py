@@ -234,6 +234,35 @@ def test_running_one_step_ahead_changes_no_output(device, tmp_path):
     assert ahead_reasons == {"r0": "length", "r1": "stop", "r2": ahead_reasons["r2"], "r3": "stop"}
 
 
+def test_abort_ends_a_request_and_leaves_the_others_alone(device, tmp_path):
+    config = rc.TINY_CONFIGS["A"]
+    folder = rc.write_model(tmp_path / "m", config, 0, "float32")
+    weights = plain_llama.load_weights(folder)
+    prompts = [rc.random_tokens(256, n, 20 + i) for i, n in enumerate((9, 14, 6))]
+    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=40))
+    for i, prompt in enumerate(prompts):
+        engine.add_request(f"r{i}", SamplingParams(max_tokens=12, temperature=0.0), prompt_token_ids=prompt)
+    for _ in range(5):
+        engine.step()
+    aborted = engine.abort(["r1", "unknown"])
+    assert [a.request_id for a in aborted] == ["r1"] and aborted[0].finish_reason == "abort"
+    expected = [plain_llama.greedy_generate(config, weights, p, 12) for p in prompts]
+    assert list(aborted[0].output_token_ids) == expected[1][: len(aborted[0].output_token_ids)]
+    assert 0 < len(aborted[0].output_token_ids) < 12
+    for _ in engine.run():
+        pass
+    core = engine.engine_core
+    assert list(core.take_finished_output("r0").output_token_ids) == expected[0]
+    assert list(core.take_finished_output("r2").output_token_ids) == expected[2]
+    assert core.take_finished_output("r1").finish_reason.value == "abort"
+    kv = core.model_runner.kv_manager
+    kv.check_invariants()
+    assert not kv.live_requests() and not core.model_runner.requests and core._in_flight is None
+    engine.add_request("late", SamplingParams(max_tokens=3, temperature=0.0), prompt_token_ids=prompts[0])
+    engine.step()
+    assert [a.request_id for a in engine.abort()] == ["late"] and not core.has_unfinished_requests()
+
+
 def test_random_weights_mode_needs_no_weight_file(device, tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(rc.TINY_A))
     engine = LLMEngine(engine_config(tmp_path, device, load=dict(random_weights=True, seed=3)))
