@@ -38,13 +38,19 @@ class CacheGroupSpec:
 
     group_id: int
     entries: tuple[int, ...]
-    num_kv_heads: int
-    head_dim: int
+    planes: int                  # tensors a page consists of (keys and values: 2)
+    heads: int                   # a page of a plane is [heads, page_size, width]
+    width: int
     window: int | None = None
 
     @property
     def kind(self) -> str:
         return "full" if self.window is None else "window"
+
+    @property
+    def elements_per_token(self) -> int:
+        """Elements one cached token takes in one entry of the group."""
+        return self.planes * self.heads * self.width
 
 
 @dataclass
@@ -72,6 +78,7 @@ class KVManager:
         max_num_seqs: int,
         max_model_len: int,
         enable_prefix_caching: bool = False,
+        track_released_pages: bool = False,
     ) -> None:
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
@@ -96,6 +103,9 @@ class KVManager:
         # prefix reuse needs one table that keeps every key (a windowed group has given pages back)
         self.prefix_caching = bool(enable_prefix_caching) and len(self.groups) == 1 and self.groups[0].window is None
         self.num_prefix_hits = 0          # pages taken over instead of computed
+        # per group, the pages that nobody holds any more since take_released_pages() was last called
+        # (kept only on request: the debug fill of freed pages reads it)
+        self._released: list[list[int]] | None = [[] for _ in self.groups] if track_released_pages else None
 
     # ---- queries ---------------------------------------------------------------------------
     def has_request(self, request_id: str) -> bool:
@@ -267,6 +277,7 @@ class KVManager:
                 row = self.tables[g][state.slot]
                 pages = [int(p) for p in row[state.num_released[g] : releasable] if p != NULL_PAGE]
                 self.pools[g].free(pages)
+                self._note_released(g, pages)
                 row[state.num_released[g] : releasable] = NULL_PAGE
                 state.num_released[g] = releasable
                 self._touch(state.slot)
@@ -280,11 +291,25 @@ class KVManager:
             row = self.tables[g][state.slot]
             pages = [int(p) for p in row[: state.num_blocks[g]] if p != NULL_PAGE]
             self.pools[g].free(reversed(pages))
+            self._note_released(g, pages)
             row[:] = NULL_PAGE
         self._touch(state.slot)
         self.slots.free(state.slot)
         if state.slot in self._fresh_slots:
             self._fresh_slots.remove(state.slot)
+
+    def _note_released(self, group: int, pages: Sequence[int]) -> None:
+        if self._released is not None:
+            self._released[group].extend(page for page in pages if not self.pools[group].is_held(page))
+
+    def take_released_pages(self) -> list[list[int]]:
+        """Per group, the pages that lost their last holder since the last call (empty lists unless the
+        manager was built with ``track_released_pages``).  A page may have been handed out again since;
+        whoever got it has not written to it yet, because no step has run in between."""
+        if self._released is None:
+            return [[] for _ in self.groups]
+        released, self._released = self._released, [[] for _ in self.groups]
+        return released
 
     def take_fresh_slots(self) -> list[int]:
         """Slots handed to new requests since the last call; their state must start at zero."""
@@ -339,10 +364,10 @@ def group_entries(requirements) -> tuple[list[CacheGroupSpec], dict[int, int]]:
     for req in requirements:
         if req.cache_spec is None or req.cache_of is not None:
             continue
-        key = (req.cache_spec.num_kv_heads, req.cache_spec.head_dim, req.cache_spec.window)
-        by_spec.setdefault(key, []).append(req.entry)
+        spec = req.cache_spec
+        by_spec.setdefault((spec.planes, spec.heads, spec.width, spec.window), []).append(req.entry)
     groups = [
-        CacheGroupSpec(group_id, tuple(entries), key[0], key[1], key[2])
+        CacheGroupSpec(group_id, tuple(entries), *key)
         for group_id, (key, entries) in enumerate(by_spec.items())
     ]
     entry_group: dict[int, int] = {}

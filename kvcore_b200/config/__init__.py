@@ -8,7 +8,8 @@ from .engine_config import (
     SchedulerConfig,
     normalize_dtype_name,
 )
-from .llama import ConfigError, LlamaConfig, RopeScaling, read_config_json
+from .config_json import ConfigError, read_config_json
+from .llama import LlamaConfig, RopeScaling
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule
 from .registry import (
     model_spec_from_config,

@@ -77,12 +77,20 @@ class CacheConfig:
     number of pages per cache group; when None the pool is sized from free device memory
     times ``gpu_memory_utilization``.  ``enable_prefix_caching`` (the reference's
     ``enable_caching``): requests whose prompts begin with the same full pages share them.
+    ``debug_fill_freed_pages`` (a debugging aid, off by default): pages that nobody holds any more
+    are overwritten before the next step runs, with zeros (``"zero"``; the reference zeroes every
+    freshly allocated block, kvcore/model/model_runner.py:646-657) or with a large finite value
+    (``"poison"``), so that a kernel that reads a position its request has not written shows in the
+    logits.  The value is finite because the tensor-core kernels multiply whole value tiles with
+    probabilities that are exactly zero at masked positions, and ``0 * NaN`` is not zero.  Not
+    together with prefix caching, which reads freed pages on purpose.
     """
 
     block_size: int = 16
     num_gpu_blocks: int | None = None
     gpu_memory_utilization: float = 0.9
     enable_prefix_caching: bool = False
+    debug_fill_freed_pages: str | None = None
 
     def __post_init__(self) -> None:
         if self.block_size <= 0:
@@ -93,6 +101,13 @@ class CacheConfig:
             raise ValueError(
                 f"gpu_memory_utilization must be in (0, 1], got {self.gpu_memory_utilization}"
             )
+        if self.debug_fill_freed_pages not in (None, "zero", "poison"):
+            raise ValueError(
+                f"debug_fill_freed_pages must be None, 'zero' or 'poison', got {self.debug_fill_freed_pages!r}"
+            )
+        if self.debug_fill_freed_pages is not None and self.enable_prefix_caching:
+            raise ValueError("debug_fill_freed_pages cannot be combined with enable_prefix_caching: "
+                             "prefix reuse reads pages after their last holder let go of them")
 
 
 @dataclass(frozen=True, slots=True)

@@ -8,11 +8,11 @@ kvcore/model/layer/rotary_embedding.py:38-49; kvcore/engine/engine_core.py:162-1
 """
 from __future__ import annotations
 
-import json
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Mapping
 
+from .config_json import ConfigError, read_config_json
 from .model_spec import LayerSpec, ModelSpec, PartSpec, default_schedule
 
 _REQUIRED_KEYS = (
@@ -22,10 +22,6 @@ _REQUIRED_KEYS = (
     "num_hidden_layers",
     "num_attention_heads",
 )
-
-
-class ConfigError(ValueError):
-    """config.json is missing a key, or holds a value this engine refuses."""
 
 
 @dataclass(frozen=True)
@@ -165,7 +161,12 @@ class LlamaConfig:
             LayerSpec(
                 prefix=f"model.layers.{index}",
                 block=PartSpec("prenorm_residual"),
-                mixer=mixer.with_params(name=f"model.layers.{index}.self_attn"),
+                mixer=mixer.with_params(
+                    name=f"model.layers.{index}.self_attn",
+                    # checkpoints saved from modules that keep the frequency table as a buffer carry
+                    # it under this name; the rotary part names it as ignorable
+                    position=position.with_params(name=f"model.layers.{index}.self_attn.rotary_emb"),
+                ),
                 feed_forward=feed_forward.with_params(name=f"model.layers.{index}.mlp"),
                 norms={
                     "mixer_norm": norm.with_params(name=f"model.layers.{index}.input_layernorm"),
@@ -201,17 +202,6 @@ class LlamaConfig:
             eos_token_ids=self.eos_token_ids,
             stored_dtype=self.stored_dtype,
         )
-
-
-def read_config_json(folder: str | Path) -> dict[str, Any]:
-    path = Path(folder) / "config.json"
-    if not path.is_file():
-        raise FileNotFoundError(f"no config.json in model folder {str(folder)!r}")
-    with path.open("r", encoding="utf-8") as handle:
-        raw = json.load(handle)
-    if not isinstance(raw, dict):
-        raise ConfigError(f"{path} does not hold a JSON object")
-    return raw
 
 
 def _positive_int(raw: Mapping[str, Any], key: str) -> int:

@@ -11,7 +11,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping
 
-from .llama import ConfigError, LlamaConfig, read_config_json
+from .config_json import ConfigError, read_config_json
 from .model_spec import ModelSpec
 
 SpecFactory = Callable[[Mapping[str, Any]], ModelSpec]
@@ -74,11 +74,17 @@ def model_spec_from_folder(folder: str | Path) -> ModelSpec:
     return model_spec_from_config(read_config_json(folder))
 
 
-register_architecture(
-    "LlamaForCausalLM",
-    lambda raw: LlamaConfig.from_dict(raw).to_model_spec(),
-    model_types=("llama",),
-)
+def _register_stock_architectures() -> None:
+    from .llama import LlamaConfig
+
+    register_architecture(
+        "LlamaForCausalLM",
+        lambda raw: LlamaConfig.from_dict(raw).to_model_spec(),
+        model_types=("llama",),
+    )
+
+
+_register_stock_architectures()
 
 __all__ = [
     "ArchitectureEntry",

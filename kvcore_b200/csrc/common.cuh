@@ -21,6 +21,8 @@
 extern "C" int kvb_fail(int code, const char* what, const char* file, int line);
 // Device address of the current device's status word (allocated once per device).
 extern "C" int* kvb_status_word();
+// Multiprocessors of the current device (0 if the driver cannot be asked).
+extern "C" int kvb_sm_count();
 
 #define KVB_REQUIRE(cond, msg)                                   \
   do {                                                           \

@@ -269,8 +269,9 @@ extern "C" int kvb_silu_mul(void* out, const void* gate_up, int rows, int inter,
   const int n = vec ? 16 / esize : 1;
   const long long total = (long long)rows * (inter / n);
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
-                                                                     : 148 * 16);
+  const long long wanted = (total + threads - 1) / threads;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;  // a grid-stride loop beyond that
+  const int blocks = (int)(wanted < resident ? wanted : resident);
   if (dtype == KVB_F32) {
     if (vec) KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<float, true>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out, (const float*)gate_up, inter, group, total));
     else KVB_CHECK_CUDA(kvb_launch((silu_mul_kernel<float, false>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out, (const float*)gate_up, inter, group, total));

@@ -59,6 +59,19 @@ extern "C" int kvb_peek_status() {
 
 extern "C" int kvb_abi_version() { return 1; }
 
+// Multiprocessors of the current device, asked from the driver once per device (0 if that fails).
+extern "C" int kvb_sm_count() {
+  static int counts[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  if (counts[device] == 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    counts[device] = value;
+  }
+  return counts[device];
+}
+
 // Whether launches carry the programmatic-serialization attribute (kernels overlap their prologue
 // with the tail of the kernel before them).  Off by default; the host side switches it on.
 static int g_pdl_enabled = 0;

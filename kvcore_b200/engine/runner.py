@@ -142,6 +142,7 @@ class ModelRunner:
             # state that a mixer keeps per request cannot be taken over with the pages
             enable_prefix_caching=config.cache_config.enable_prefix_caching
             and not any(req.state_spec is not None for req in requirements),
+            track_released_pages=config.cache_config.debug_fill_freed_pages is not None,
         )
         self.storage = CacheStorage(
             self.model,
@@ -160,6 +161,7 @@ class ModelRunner:
             max_num_tokens=self.max_num_tokens,
             max_num_seqs=self.max_num_seqs,
             use_cuda_graphs=not config.model_config.enforce_eager,
+            fill_freed_pages=config.cache_config.debug_fill_freed_pages,
         )
         self.sampler = Sampler(self.device)
         self.requests: dict[str, CachedRequestState] = {}
@@ -171,10 +173,10 @@ class ModelRunner:
 
     # ---- cache sizing ------------------------------------------------------------------------
     def bytes_per_page(self) -> list[int]:
-        """Bytes one page id costs in each group: keys and values of every entry of the group."""
+        """Bytes one page id costs in each group: every plane of every entry of the group."""
         item = torch.empty((), dtype=self.dtype).element_size()
         return [
-            len(group.entries) * 2 * group.num_kv_heads * self.page_size * group.head_dim * item
+            len(group.entries) * group.elements_per_token * self.page_size * item
             for group in self.groups
         ]
 

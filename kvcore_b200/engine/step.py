@@ -40,14 +40,25 @@ class StepEntry:
 
 @dataclass
 class LayerCache:
-    """What one schedule entry's mixer sees of the cache."""
+    """What one schedule entry's mixer sees of the cache: the planes its ``CacheSpec`` declared, each
+    ``[pages, heads, page_size, width]`` (none without a spec), and its state tensor
+    ``[slots, *shape]`` if it declared a ``StateSpec``."""
 
     group: int | None
-    k: torch.Tensor | None
-    v: torch.Tensor | None
+    planes: tuple[torch.Tensor, ...]
     owner: bool
     state: torch.Tensor | None
     page_size: int
+
+    @property
+    def k(self) -> torch.Tensor | None:
+        """The first plane (the keys of a key/value cache)."""
+        return self.planes[0] if self.planes else None
+
+    @property
+    def v(self) -> torch.Tensor | None:
+        """The second plane (the values of a key/value cache)."""
+        return self.planes[1] if len(self.planes) > 1 else None
 
 
 class StepContext:
@@ -93,9 +104,10 @@ class StepContext:
 class CacheStorage:
     """Device tensors behind the cache manager's bookkeeping.
 
-    Per group one tensor ``[entries, 2, pages, kv_heads, page_size, head_dim]`` (keys at
-    index 0, values at 1): every entry of the group stores a page id's tokens in its own
-    slice.  Per schedule entry with a ``StateSpec`` one tensor ``[slots, *shape]``.
+    Per group one tensor ``[entries, planes, pages, heads, page_size, width]`` as the group's
+    ``CacheSpec`` has it (keys at plane 0, values at plane 1 for attention): every entry of the
+    group stores a page id's tokens in its own slice.  Per schedule entry with a ``StateSpec``
+    one tensor ``[slots, *shape]``.
     """
 
     def __init__(
@@ -115,28 +127,40 @@ class CacheStorage:
         for group, pages in zip(groups, num_pages):
             self.group_tensors.append(
                 torch.zeros(
-                    len(group.entries), 2, pages, group.num_kv_heads, page_size, group.head_dim,
+                    len(group.entries), group.planes, pages, group.heads, page_size, group.width,
                     dtype=dtype, device=device,
                 )
             )
         self.layer_caches: list[LayerCache] = []
         self.state_tensors: list[torch.Tensor] = []
         for req in model.entry_requirements():
-            k = v = None
+            planes: tuple[torch.Tensor, ...] = ()
             group_id = entry_group.get(req.entry)
             owner = req.cache_of is None
             if group_id is not None:
                 owner_entry = req.entry if owner else req.cache_of
                 index = groups[group_id].entries.index(owner_entry)
-                k = self.group_tensors[group_id][index, 0]
-                v = self.group_tensors[group_id][index, 1]
+                planes = tuple(self.group_tensors[group_id][index].unbind(0))
             state = None
             if req.state_spec is not None:
                 state = torch.zeros(
                     (num_slots, *req.state_spec.shape), dtype=req.state_spec.dtype, device=device
                 )
                 self.state_tensors.append(state)
-            self.layer_caches.append(LayerCache(group_id, k, v, owner, state, page_size))
+            self.layer_caches.append(LayerCache(group_id, planes, owner, state, page_size))
+
+    # what "poison" writes into freed pages: large enough that a read of a position nobody wrote
+    # changes the logits by orders of magnitude, finite so that a masked probability of exactly
+    # zero still cancels it
+    POISON_VALUE = 3.0e4
+
+    def fill_pages(self, group: int, pages: Sequence[int], value: float) -> None:
+        """Overwrite ``pages`` of ``group`` in every entry and plane (the debug fill of freed pages)."""
+        if not pages:
+            return
+        tensor = self.group_tensors[group]
+        index = torch.as_tensor(sorted(set(int(p) for p in pages)), dtype=torch.long, device=tensor.device)
+        tensor.index_fill_(2, index, value)
 
     def zero_slots(self, slots: Sequence[int]) -> None:
         if not slots or not self.state_tensors:
@@ -147,7 +171,7 @@ class CacheStorage:
 
     def bytes_per_page(self) -> list[int]:
         return [
-            t.shape[0] * 2 * t.shape[3] * t.shape[4] * t.shape[5] * t.element_size()
+            t.shape[0] * t.shape[1] * t.shape[3] * t.shape[4] * t.shape[5] * t.element_size()
             for t in self.group_tensors
         ]
 
@@ -167,6 +191,7 @@ class StepFunction:
         max_num_seqs: int,
         use_cuda_graphs: bool = True,
         max_graphs: int = 24,
+        fill_freed_pages: str | None = None,
     ) -> None:
         self.model = model
         self.kv = kv_manager
@@ -175,6 +200,9 @@ class StepFunction:
         self.max_num_tokens = int(max_num_tokens)
         self.max_num_seqs = int(max_num_seqs)
         self.vocab_size = model.spec.vocab_size
+        if fill_freed_pages not in (None, "zero", "poison"):
+            raise ValueError(f"fill_freed_pages must be None, 'zero' or 'poison', got {fill_freed_pages!r}")
+        self.fill_freed_pages = fill_freed_pages
         width = kv_manager.max_blocks_per_seq
         capacity = (
             4 * _round4(self.max_num_seqs + 1)
@@ -399,6 +427,10 @@ class StepFunction:
         ``feedback``: int32 tokens sampled from the step in front, for entries with ``fed_from``."""
         ctx = self._pack(entries, feedback)
         self.storage.zero_slots(self.kv.take_fresh_slots())
+        if self.fill_freed_pages is not None:
+            value = 0.0 if self.fill_freed_pages == "zero" else self.storage.POISON_VALUE
+            for group, pages in enumerate(self.kv.take_released_pages()):
+                self.storage.fill_pages(group, pages, value)
         if self.use_cuda_graphs and ctx.decode_only:
             logits = self._step_with_graph(ctx)
         else:

@@ -1,8 +1,8 @@
 """Trace replay: feed given token ids through the model step by step and write logits.
 
-It samples nothing and has no forward pass, cache or loader of its own: it builds the same
-model, cache manager, cache storage and step function that generation uses and calls
-``StepFunction.step`` once per input line.  Input (standard input), one JSON object a line:
+It samples nothing and has no forward pass, cache or loader of its own: it asks the model
+runner that generation uses for its model, cache manager, cache storage and step function and
+calls ``StepFunction.step`` once per input line.  Input (standard input), one JSON object a line:
 
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 
@@ -21,33 +21,28 @@ from pathlib import Path
 import torch
 
 from .. import kernels as K
-from ..cache.kv_manager import KVManager, group_entries
+from ..cache.kv_manager import KVManager
 from ..config.engine_config import CacheConfig, DeviceConfig, KVCoreConfig, ModelConfig, SchedulerConfig
-from .runner import load_model
-from .step import CacheStorage, StepEntry, StepFunction
+from .runner import ModelRunner
+from .step import StepEntry, StepFunction
 
 
 def build_replay(model_dir: str, dtype: str, max_tokens: int, *, page_size: int = 16,
-                 max_live: int = 8, device: str = "cuda:0"):
-    """The model with a cache pool for ``max_tokens`` tokens; returns (step function, kv manager)."""
+                 max_live: int = 8, device: str = "cuda:0", fill_freed_pages: str | None = None):
+    """The model with a cache pool for ``max_tokens`` tokens, wired by the model runner as for
+    generation; returns (step function, kv manager)."""
     if max_tokens <= 0:
         raise ValueError(f"--max-tokens must be positive, got {max_tokens}")
+    pages = -(-max_tokens // page_size) + 1  # + the null page
     config = KVCoreConfig(
         model_config=ModelConfig(model=model_dir, dtype=dtype, max_model_len=max_tokens),
-        cache_config=CacheConfig(block_size=page_size),
+        cache_config=CacheConfig(block_size=page_size, num_gpu_blocks=pages,
+                                 debug_fill_freed_pages=fill_freed_pages),
         scheduler_config=SchedulerConfig(max_num_seqs=max_live, max_num_scheduled_tokens=max_tokens),
         device_config=DeviceConfig(device=device),
     )
-    model = load_model(config)
-    groups, entry_group = group_entries(model.entry_requirements())
-    pages = -(-max_tokens // page_size) + 1  # + the null page
-    num_pages = [pages] * len(groups)
-    kv = KVManager(groups, num_pages=num_pages, page_size=page_size, max_num_seqs=max_live,
-                   max_model_len=max_tokens)
-    storage = CacheStorage(model, groups, entry_group, num_pages=num_pages, page_size=page_size,
-                           num_slots=max_live, dtype=model.dtype, device=model.device)
-    step_function = StepFunction(model, kv, storage, max_num_tokens=max_tokens, max_num_seqs=max_live)
-    return step_function, kv
+    runner = ModelRunner(config)
+    return runner.step_function, runner.kv_manager
 
 
 def replay_stream(step_function: StepFunction, kv: KVManager, lines, out_dir: Path, report) -> int:
@@ -90,11 +85,14 @@ def main(argv: list[str] | None = None) -> int:
                         help="tokens the cache pool is made for")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--fill-freed-pages", choices=["zero", "poison"], default=None,
+                        help="debugging aid: overwrite pages that nobody holds any more before the next step")
     args = parser.parse_args(argv)
 
     K.ensure_built(verbose=True)
     step_function, kv = build_replay(
-        args.model, args.dtype, args.max_tokens, page_size=args.block_size, device=args.device
+        args.model, args.dtype, args.max_tokens, page_size=args.block_size, device=args.device,
+        fill_freed_pages=args.fill_freed_pages,
     )
 
     def report(text: str) -> None:

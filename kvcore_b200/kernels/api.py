@@ -341,8 +341,26 @@ def rope_inplace(q: torch.Tensor, k: torch.Tensor | None, positions: torch.Tenso
               _dtype_code(x), _stream())
 
 
-SM_COUNT = 148  # B200
+_sm_counts: dict[int, int] = {}
 _FLASH_CTAS_PER_SM = 3
+
+
+def sm_count(device: torch.device | str | int | None = None) -> int:
+    """Multiprocessors of ``device`` (default: the current CUDA device), asked from the driver once
+    per device.  Grids, split counts and the scratch of the streaming kernels are sized from it."""
+    if device is None:
+        index = torch.cuda.current_device()
+    elif isinstance(device, int):
+        index = device
+    else:
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise KernelError(f"kvcore_b200 runs on CUDA devices only, got device {device}")
+        index = torch.cuda.current_device() if device.index is None else device.index
+    count = _sm_counts.get(index)
+    if count is None:
+        count = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return count
 
 
 def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
@@ -350,10 +368,11 @@ def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
 
 
-def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
-    """How many chunks each request's keys are cut into so that the GPU is filled."""
+def decode_splits(num_reqs: int, num_kv_heads: int, max_seq_len: int, sms: int | None = None) -> int:
+    """How many chunks each request's keys are cut into so that the GPU (``sms`` multiprocessors,
+    default: the current device's) is filled."""
     blocks = max(1, num_reqs * num_kv_heads)
-    wanted = -(-SM_COUNT * _FLASH_CTAS_PER_SM // blocks)
+    wanted = -(-(sms or sm_count()) * _FLASH_CTAS_PER_SM // blocks)
     longest = max(1, -(-max_seq_len // 256))  # a split of fewer than 256 keys is not worth a block
     return max(1, min(wanted, longest, 64))
 
@@ -363,9 +382,9 @@ def tma_decode_supported(dtype: torch.dtype, head_dim: int, page_size: int) -> b
     return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size in (8, 16, 32, 64)
 
 
-def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int:
+def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int, sms: int | None = None) -> int:
     """Splits for the TMA decode kernel, which keeps two blocks per SM (measured inside whole steps
-    on B200).
+    on B200; ``sms``: multiprocessors, default the current device's).
 
     Up to half a wave of (request, kv head) pairs: as many splits as still fit one wave of blocks,
     at most 16 (the merge grows with them) and at least two 64-key tiles a split (batch 1 at 1,024
@@ -379,7 +398,7 @@ def decode_splits_tma(num_reqs: int, num_kv_heads: int, max_seq_len: int) -> int
     the merge, and the cheapest is taken."""
     base = max(1, num_reqs * num_kv_heads)
     tiles = max(1, -(-max_seq_len // 64))
-    wave = SM_COUNT * TMA_DECODE_BLOCKS_PER_SM
+    wave = (sms or sm_count()) * TMA_DECODE_BLOCKS_PER_SM
     if base * 2 <= wave:
         return max(1, min(wave // base, tiles // 2, 16))
     best, best_cost = 1, float("inf")
@@ -493,7 +512,8 @@ def paged_attention(
         split_mode = ctx.max_query_len * group <= 16
         bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
         if split_mode and use_tma and tma_decode_supported(qkv.dtype, head_dim, page_size):
-            splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound)
+            sms = sm_count(qkv.device)
+            splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound, sms)
             scratch = None
             if splits > 1:
                 scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
@@ -507,7 +527,7 @@ def paged_attention(
                   None if cos_sin is None else cos_sin.data_ptr(),
                   k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None,
                   _decode_work(qkv.device).data_ptr() if TMA_DECODE_SHARED_WORK else None,
-                  SM_COUNT * TMA_DECODE_BLOCKS_PER_SM, _stream(),
+                  sms * TMA_DECODE_BLOCKS_PER_SM, _stream(),
                   kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
             return out
         if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
@@ -521,7 +541,7 @@ def paged_attention(
             return out
         splits = 1
         if split_mode:
-            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound)
+            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound, sm_count(qkv.device))
         scratch = None
         if splits > 1:
             scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
@@ -703,12 +723,12 @@ def _stream_buffers(device: torch.device, kind: str = "mma") -> tuple[torch.Tens
     buffers = _stream_scratch.get((kind, index))
     if buffers is None:
         if kind == "tc5":
-            floats = int(_lib.kvb_gemm_stream_tc5_scratch_floats(SM_COUNT))
-            ints = int(_lib.kvb_gemm_stream_tc5_flag_ints(SM_COUNT))
+            floats = int(_lib.kvb_gemm_stream_tc5_scratch_floats(sm_count(device)))
+            ints = int(_lib.kvb_gemm_stream_tc5_flag_ints(sm_count(device)))
             buffers = (torch.empty(floats, dtype=torch.float32, device=device),
                        torch.zeros(ints, dtype=torch.int32, device=device))
         else:
-            floats = int(_lib.kvb_gemm_stream_scratch_floats(SM_COUNT))
+            floats = int(_lib.kvb_gemm_stream_scratch_floats(sm_count(device)))
             marker = int(_lib.kvb_gemm_stream_scratch_marker())
             words = torch.full((floats,), marker, dtype=torch.int32, device=device)
             buffers = (words.view(torch.float32), None)
@@ -749,9 +769,9 @@ def _stream_call(kind: str, device: torch.device, *args) -> None:
     stream are appended."""
     scratch, flags = _stream_buffers(device, kind)
     if kind == "tc5":
-        _call("kvb_gemm_stream_tc5_bf16", *args, scratch.data_ptr(), flags.data_ptr(), SM_COUNT, _stream())
+        _call("kvb_gemm_stream_tc5_bf16", *args, scratch.data_ptr(), flags.data_ptr(), sm_count(device), _stream())
     else:
-        _call("kvb_gemm_stream_bf16", *args, scratch.data_ptr(), SM_COUNT, _stream())
+        _call("kvb_gemm_stream_bf16", *args, scratch.data_ptr(), sm_count(device), _stream())
 
 
 def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
@@ -868,6 +888,7 @@ __all__ = [
     "linear_stream",
     "norm_linear",
     "set_overlapped_launch",
+    "sm_count",
     "trace_start",
     "trace_stop",
     "paged_attention",

@@ -15,7 +15,6 @@ import torch
 from .. import kernels as K
 from ..config.model_spec import PartSpec
 from .base import MIXERS, POSITION_ENCODINGS, CacheSpec, Mixer, Summed, WeightSlot
-from .rope import RotaryEncoding
 
 
 class PagedAttention(Mixer):
@@ -67,7 +66,7 @@ class PagedAttention(Mixer):
         )
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.num_kv_heads, self.head_dim, self.sliding_window)
+        return CacheSpec.keys_and_values(self.num_kv_heads, self.head_dim, self.sliding_window)
 
     def weight_slots(self) -> list[WeightSlot]:
         q, kv = self.q_size, self.kv_size
@@ -88,6 +87,9 @@ class PagedAttention(Mixer):
             slots += self.position.weight_slots()
         return slots
 
+    def ignorable_tensor_names(self) -> list[str]:
+        return [] if self.position is None else self.position.ignorable_tensor_names()
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         out = self._attend(K.linear(x, self.qkv_weight, self.qkv_bias), ctx, cache)
         return K.linear(out, self.o_weight, self.o_bias)
@@ -105,11 +107,9 @@ class PagedAttention(Mixer):
 
     def _attend(self, qkv: torch.Tensor, ctx, cache) -> torch.Tensor:
         table = ctx.block_table(cache.group)
-        cos_sin = None
-        if isinstance(self.position, RotaryEncoding):
-            # rotation fused with the cache write; its cos/sin table is made once per step
-            cos_sin = self.position.cos_sin(ctx)
-        elif self.position is not None:
+        # an encoding that offers its angles as a table gets its rotation fused with the cache write
+        cos_sin = None if self.position is None else self.position.cos_sin(ctx)
+        if cos_sin is None and self.position is not None:
             tokens = qkv.shape[0]
             q = qkv[:, : self.q_size].view(tokens, self.num_heads, self.head_dim)
             k = qkv[:, self.q_size : self.q_size + self.kv_size].view(

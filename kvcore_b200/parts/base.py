@@ -9,7 +9,7 @@ none knows the model it sits in.  What each kind must provide:
 * **PositionEncoding**: ``apply(q, k, ctx)`` rotating/shifting ``q [T,H,D]`` and ``k [T,KVH,D]``
   in place for the tokens of this step (``ctx.positions``).
 * **Mixer**: ``forward(x [T,E], ctx, cache) -> [T,E]``.  It declares what it needs cached
-  through ``cache_spec()`` (paged keys/values; ``None`` if none) and ``state_spec()`` (a
+  through ``cache_spec()`` (what it keeps per cached token, in pages; ``None`` if nothing) and ``state_spec()`` (a
   fixed-size per-request state; ``None`` if none).  ``cache`` is the ``LayerCache`` of the
   schedule entry being run.
 * **FeedForward**: ``forward(x [T,E], ctx) -> [T,E]``.
@@ -57,15 +57,35 @@ class WeightSlot:
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """Paged key/value needs of a mixer: entries with equal specs share a page group.
+    """Paged needs of a mixer: what it keeps per cached token.  Entries with equal specs share a
+    page group (one pool of page ids, one block table).
 
-    ``window`` is ``None`` when every key stays visible, else the number of trailing keys a
-    query sees; pages wholly behind the window are handed back while the request lives.
+    A page of the group holds ``page_size`` tokens in each of ``planes`` tensors of shape
+    ``[heads, page_size, width]``: keys and values of grouped-query attention are two planes of
+    ``kv_heads`` heads of ``head_dim`` (``CacheSpec.keys_and_values``); a mixer that caches one
+    vector per token declares one plane of one head.  ``window`` is ``None`` when every cached
+    token stays visible, else the number of trailing tokens a query sees; pages wholly behind the
+    window are handed back while the request lives.
     """
 
-    num_kv_heads: int
-    head_dim: int
+    planes: int
+    heads: int
+    width: int
     window: int | None = None
+
+    def __post_init__(self) -> None:
+        if self.planes <= 0 or self.heads <= 0 or self.width <= 0:
+            raise ValueError(f"a cache spec needs positive planes, heads and width, got {self}")
+        if self.window is not None and self.window <= 0:
+            raise ValueError(f"window must be positive when set, got {self.window}")
+
+    @classmethod
+    def keys_and_values(cls, num_kv_heads: int, head_dim: int, window: int | None = None) -> "CacheSpec":
+        return cls(2, int(num_kv_heads), int(head_dim), window)
+
+    @property
+    def elements_per_token(self) -> int:
+        return self.planes * self.heads * self.width
 
 
 @dataclass(frozen=True)
@@ -88,6 +108,11 @@ class Part:
     graph_safe = False
 
     def weight_slots(self) -> list[WeightSlot]:
+        return []
+
+    def ignorable_tensor_names(self) -> list[str]:
+        """Names a checkpoint may carry for this part without a slot to load them into (buffers the
+        part derives itself, a tied matrix stored twice).  A part that holds other parts adds theirs."""
         return []
 
     def finalize_weights(self) -> None:
@@ -123,6 +148,13 @@ class Norm(Part):
 class PositionEncoding(Part):
     def apply(self, q: torch.Tensor, k: torch.Tensor | None, ctx: Any) -> None:
         raise NotImplementedError
+
+    def cos_sin(self, ctx: Any) -> torch.Tensor | None:
+        """Capability: an encoding that is a half-rotation of each head by per-token angles may return
+        their ``[T, D/2, 2]`` 32-bit (cos, sin) table for this step's tokens; a mixer then fuses the
+        rotation with its cache write (and, for decode steps, with its attention kernel) instead of
+        calling ``apply``.  ``None`` (the default): the encoding is applied through ``apply``."""
+        return None
 
 
 class Mixer(Part):

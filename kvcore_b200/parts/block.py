@@ -32,6 +32,12 @@ class PreNormResidualBlock(Block):
             slots += part.weight_slots()
         return slots
 
+    def ignorable_tensor_names(self) -> list[str]:
+        names: list[str] = []
+        for part in self.parts():
+            names += part.ignorable_tensor_names()
+        return names
+
     def finalize_weights(self) -> None:
         for part in self.parts():
             part.finalize_weights()

@@ -65,9 +65,7 @@ class DecoderModel:
     def ignorable_tensor_names(self) -> list[str]:
         names: list[str] = []
         for part in self._parts():
-            extra = getattr(part, "ignorable_tensor_names", None)
-            if extra is not None:
-                names += extra()
+            names += part.ignorable_tensor_names()
         return names
 
     def finalize_weights(self) -> None:

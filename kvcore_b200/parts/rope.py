@@ -67,9 +67,11 @@ class RotaryEncoding(PositionEncoding):
         low_freq_factor: float = 1.0,
         high_freq_factor: float = 4.0,
         original_max_position_embeddings: int = 8192,
+        name: str | None = None,
         dtype: torch.dtype,
         device: torch.device,
     ) -> None:
+        self.name = name
         if head_dim % 2:
             raise ValueError(f"rotary encoding needs an even head_dim, got {head_dim}")
         self.head_dim = int(head_dim)
@@ -81,6 +83,11 @@ class RotaryEncoding(PositionEncoding):
             original_max_position_embeddings,
         )
         self.inv_freq = table if torch.device(device).type == "meta" else table.to(device)
+
+    def ignorable_tensor_names(self) -> list[str]:
+        # checkpoints written from modules that register the frequency table as a buffer carry it;
+        # the table is derived from the configuration here
+        return [] if self.name is None else [f"{self.name}.inv_freq"]
 
     def cos_sin(self, ctx) -> torch.Tensor:
         """``[T, D/2, 2]`` (cos, sin) of this step's positions; one table per step and frequency table."""

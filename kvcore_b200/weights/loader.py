@@ -73,8 +73,8 @@ def load_named_tensors(
 ) -> set[str]:
     """Copy ``tensors`` into ``slots`` by name; return the names loaded.
 
-    ``ignorable`` names may be present in the checkpoint without a slot (a tied output
-    matrix, rotary frequency buffers).  With ``strict`` any mismatch raises after all
+    ``ignorable`` names may be present in the checkpoint without a slot; the parts name them
+    (a tied output matrix, a frequency table that a part derives itself).  With ``strict`` any mismatch raises after all
     tensors were looked at, so the message is complete.
     """
     by_name: dict[str, WeightSlot] = {}
@@ -89,7 +89,7 @@ def load_named_tensors(
     for name, tensor in tensors:
         slot = by_name.get(name)
         if slot is None:
-            if name not in ignorable and not name.endswith("rotary_emb.inv_freq"):
+            if name not in ignorable:
                 unexpected.append(name)
             continue
         if tuple(tensor.shape) != slot.shape:

@@ -177,10 +177,11 @@ def collect(steps: list[dict], out_dir: Path, vocab: int) -> dict[tuple[str, int
 
 
 def run_inprocess(model_dir, dtype: str, steps: list[dict], out_dir: Path, max_tokens: int,
-                  device: str = "cuda:0", page_size: int = 16):
+                  device: str = "cuda:0", page_size: int = 16, fill_freed_pages: str | None = None):
     from kvcore_b200.engine.trace_replay import build_replay, replay_stream
 
-    step_function, kv = build_replay(str(model_dir), dtype, max_tokens, page_size=page_size, device=device)
+    step_function, kv = build_replay(str(model_dir), dtype, max_tokens, page_size=page_size, device=device,
+                                     fill_freed_pages=fill_freed_pages)
     lines = [json.dumps(step) for step in steps]
     done: list[str] = []
     replay_stream(step_function, kv, lines, Path(out_dir), done.append)

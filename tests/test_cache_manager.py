@@ -13,7 +13,7 @@ from kvcore_b200.cache import (
 
 
 def manager(num_pages=9, page_size=4, windows=(None,), max_num_seqs=4, max_model_len=64):
-    groups = [CacheGroupSpec(i, (i,), 2, 16, w) for i, w in enumerate(windows)]
+    groups = [CacheGroupSpec(i, (i,), 2, 2, 16, w) for i, w in enumerate(windows)]
     return KVManager(groups, num_pages=num_pages, page_size=page_size, max_num_seqs=max_num_seqs,
                      max_model_len=max_model_len)
 
@@ -177,7 +177,7 @@ def test_pool_shared_pages_and_registered_contents():
 
 
 def prefix_manager(**kw):
-    return KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=kw.pop("num_pages", 17), page_size=4,
+    return KVManager([CacheGroupSpec(0, (0, 1), 2, 2, 16, None)], num_pages=kw.pop("num_pages", 17), page_size=4,
                      max_num_seqs=4, max_model_len=64, enable_prefix_caching=True, **kw)
 
 
@@ -240,7 +240,7 @@ def test_taken_over_pages_in_the_queue_count_against_the_free_pages():
 def test_prefix_reuse_is_off_without_the_flag_and_with_windows():
     plain = manager()
     assert not plain.prefix_caching and plain.find_prefix(list(range(20))) == []
-    windowed = KVManager([CacheGroupSpec(0, (0,), 2, 16, 8)], num_pages=9, page_size=4, max_num_seqs=2,
+    windowed = KVManager([CacheGroupSpec(0, (0,), 2, 2, 16, 8)], num_pages=9, page_size=4, max_num_seqs=2,
                          max_model_len=64, enable_prefix_caching=True)
     assert not windowed.prefix_caching
 
@@ -292,3 +292,25 @@ def test_state_slots():
     with pytest.raises(StateSlotError):
         pool.free(a)
     assert pool.allocate("c") == 0
+
+
+def test_released_pages_are_reported_once_when_tracking_is_on():
+    """The debug fill of freed pages reads this list: every page that lost its last holder (a finished
+    request's pages, pages behind a window) appears once, and nothing is kept without the switch."""
+    kv = KVManager([CacheGroupSpec(0, (0,), 2, 2, 16, None), CacheGroupSpec(1, (1,), 2, 2, 16, 8)], num_pages=[9, 9],
+                   page_size=4, max_num_seqs=2, max_model_len=32, track_released_pages=True)
+    assert kv.allocate_slots("a", 16)
+    held = kv.block_ids("a")
+    kv.advance("a", 16)                       # the windowed group hands back pages behind the window
+    released = kv.take_released_pages()
+    assert released[0] == [] and released[1] == list(held[1][:2])
+    assert kv.take_released_pages() == [[], []]
+    kv.free("a")
+    released = kv.take_released_pages()
+    assert sorted(released[0]) == sorted(held[0]) and sorted(released[1]) == sorted(held[1][2:])
+    kv.check_invariants()
+    silent = KVManager([CacheGroupSpec(0, (0,), 2, 2, 16, None)], num_pages=9, page_size=4, max_num_seqs=2,
+                       max_model_len=32)
+    assert silent.allocate_slots("a", 8)
+    silent.free("a")
+    assert silent.take_released_pages() == [[]]

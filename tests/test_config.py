@@ -53,7 +53,8 @@ def test_rope_parameters_and_legacy_scaling_agree():
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_rope_table_matches_plain_formula(name):
     raw = rc.TINY_CONFIGS[name]
-    params = LlamaConfig.from_dict(raw).to_model_spec().layers[0].mixer.params["position"].params
+    params = dict(LlamaConfig.from_dict(raw).to_model_spec().layers[0].mixer.params["position"].params)
+    assert params.pop("name") == "model.layers.0.self_attn.rotary_emb"   # where a checkpoint may keep the table
     table = rope_inverse_frequencies(**params)
     want = plain_llama.rope_inv_freq(raw).to(torch.float32)
     assert table.dtype == torch.float32 and torch.allclose(table, want, rtol=1e-6, atol=0)
@@ -160,3 +161,13 @@ def test_generation_requests_are_taken_in_either_form():
     chat = GenerationRequest.coerce(dict(request_id="c", sampling_params=SamplingParams(max_tokens=1),
                                          messages=[{"role": "user", "content": "hi"}]))
     assert chat.prompt_token_ids is None and chat.messages[0]["content"] == "hi"
+
+
+def test_debug_fill_of_freed_pages_is_validated():
+    from kvcore_b200 import CacheConfig
+
+    assert CacheConfig(debug_fill_freed_pages="poison").debug_fill_freed_pages == "poison"
+    with pytest.raises(ValueError, match="debug_fill_freed_pages"):
+        CacheConfig(debug_fill_freed_pages="nan")
+    with pytest.raises(ValueError, match="prefix"):
+        CacheConfig(debug_fill_freed_pages="zero", enable_prefix_caching=True)

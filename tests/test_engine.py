@@ -22,7 +22,8 @@ from kvcore_b200 import (
 from kvcore_b200.config import LlamaConfig, register_architecture, unregister_architecture
 from kvcore_b200.config.model_spec import ModelSpec, PartSpec, ScheduleEntry
 from kvcore_b200.engine.llm_engine import GenerationRequest, LLMEngine
-from kvcore_b200.parts import MIXERS, POSITION_ENCODINGS, FEED_FORWARDS, Mixer, PositionEncoding, FeedForward, StateSpec, WeightSlot
+from kvcore_b200.parts import (MIXERS, POSITION_ENCODINGS, FEED_FORWARDS, CacheSpec, Mixer, PositionEncoding, FeedForward,
+                               StateSpec, WeightSlot)
 
 BACKENDS = [pytest.param("cpu", id="host"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
 
@@ -41,7 +42,8 @@ def engine_config(folder, device, dtype="float32", **overrides):
         model_config=ModelConfig(model=str(folder), dtype=dtype, max_model_len=overrides.pop("max_model_len", 128)),
         load_config=LoadConfig(**overrides.pop("load", {})),
         cache_config=CacheConfig(block_size=overrides.pop("block_size", 16), num_gpu_blocks=overrides.pop("num_gpu_blocks", 40),
-                                 enable_prefix_caching=overrides.pop("prefix_caching", False)),
+                                 enable_prefix_caching=overrides.pop("prefix_caching", False),
+                                 debug_fill_freed_pages=overrides.pop("fill_freed_pages", None)),
         scheduler_config=SchedulerConfig(**sched),
         device_config=DeviceConfig(device=device),
     )
@@ -97,13 +99,15 @@ def test_bfloat16_generation_on_serving_shapes_picks_tokens_the_plain_logits_all
     assert not runner.kv_manager.live_requests()
 
 
-def test_generation_with_few_pages_and_preemption(device, tmp_path):
-    """So few pages that requests wait, are preempted and recomputed: tokens stay the plain ones."""
+@pytest.mark.parametrize("fill", [None, "zero", "poison"])
+def test_generation_with_few_pages_and_preemption(device, tmp_path, fill):
+    """So few pages that requests wait, are preempted and recomputed: tokens stay the plain ones, also
+    when every page that lost its holder is overwritten (zeros, or a large value) before the next step."""
     config = rc.TINY_CONFIGS["A"]
     folder = rc.write_model(tmp_path / "m", config, 0, "bfloat16")
     weights = plain_llama.load_weights(folder)
     prompts = [rc.random_tokens(256, n, 70 + i) for i, n in enumerate((9, 14, 6, 11))]
-    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=14,
+    engine = LLMEngine(engine_config(folder, device, block_size=4, num_gpu_blocks=14, fill_freed_pages=fill,
                                      scheduler=dict(max_num_scheduled_tokens=16)))
     outputs = engine.generate([dict(request_id=f"r{i}", prompt_token_ids=p,
                                     sampling_params=dict(max_tokens=10, temperature=0.0))
@@ -111,7 +115,14 @@ def test_generation_with_few_pages_and_preemption(device, tmp_path):
     for prompt, output in zip(prompts, outputs):
         assert list(output.output_token_ids) == plain_llama.greedy_generate(config, weights, prompt, 10)
     assert engine.engine_core.scheduler.num_preemptions > 0
-    engine.engine_core.model_runner.kv_manager.check_invariants()
+    runner = engine.engine_core.model_runner
+    runner.kv_manager.check_invariants()
+    if fill is not None:    # every page has been freed at least once by now and was overwritten at the next step
+        storage = runner.storage.group_tensors[0]
+        written = 0.0 if fill == "zero" else runner.storage.POISON_VALUE
+        for group, pages in enumerate(runner.kv_manager.take_released_pages()):
+            runner.storage.fill_pages(group, pages, written)
+        assert bool((storage[:, :, 1:] == written).all())
 
 
 def test_generation_with_shared_prefixes_reuses_pages_and_keeps_the_tokens(device, tmp_path):
@@ -309,6 +320,46 @@ class RunningMeanMixer(Mixer):
         return out
 
 
+class LatentMixer(Mixer):
+    """A toy mixer whose pages hold ONE plane: a latent vector ``c_t = W_c x_t`` per cached token
+    (no keys and values).  ``y_t = W_o sum_s softmax_s(q_t . c_s / sqrt(L)) c_s`` over ``s <= t`` with
+    ``q_t = W_q x_t``.  Written in torch by the test, reading and writing its pages through the step's
+    block table."""
+
+    def __init__(self, *, hidden_size, latent, name, dtype, device):
+        self.latent, self.name = latent, name
+        self.w_c = torch.empty(latent, hidden_size, dtype=dtype, device=device)
+        self.w_q = torch.empty(latent, hidden_size, dtype=dtype, device=device)
+        self.w_o = torch.empty(hidden_size, latent, dtype=dtype, device=device)
+
+    def cache_spec(self):
+        return CacheSpec(planes=1, heads=1, width=self.latent)
+
+    def weight_slots(self):
+        return [WeightSlot(f"{self.name}.c.weight", self.w_c), WeightSlot(f"{self.name}.q.weight", self.w_q),
+                WeightSlot(f"{self.name}.o.weight", self.w_o)]
+
+    def forward(self, x, ctx, cache):
+        assert len(cache.planes) == 1 and cache.v is None
+        plane, page = cache.planes[0], cache.page_size        # [pages, 1, page, L]
+        table = ctx.block_table(cache.group).long()
+        latents = x.float() @ self.w_c.float().T
+        queries = x.float() @ self.w_q.float().T
+        out = torch.empty_like(x)
+        start = 0
+        for row, (n, context) in enumerate(zip(ctx.host_query_lens, ctx.host_context_lens)):
+            positions = torch.arange(context, context + n, device=x.device)
+            plane[table[row, positions // page], 0, positions % page] = latents[start:start + n].to(plane.dtype)
+            total = context + n
+            cached = plane[table[row, : -(-total // page)], 0].reshape(-1, self.latent)[:total].float()
+            scores = queries[start:start + n] @ cached.T / self.latent ** 0.5
+            visible = torch.arange(total, device=x.device)[None, :] <= positions[:, None]
+            weights = torch.softmax(scores.masked_fill(~visible, float("-inf")), dim=-1)
+            out[start:start + n] = ((weights @ cached) @ self.w_o.float().T).to(x.dtype)
+            start += n
+        return out
+
+
 class OffsetPosition(PositionEncoding):
     """A toy position encoding: adds ``amplitude * sin(position * rate)`` to every q and k entry."""
 
@@ -354,8 +405,8 @@ class RoutedFeedForward(FeedForward):
 
 def toy_spec(raw):
     """Layers: 0 attention (window 9, toy position), 1 running mean, 2 attention (rope) with a
-    routed feed-forward.  Schedule: 0, 1, 2, 0 again (own cache), then 2 reading the cache of the
-    first run of 2."""
+    routed feed-forward, 3 a mixer that caches one latent vector per token.  Schedule: 0, 1, 2, 0 again
+    (own cache), then 2 reading the cache of the first run of 2, then 3."""
     base = LlamaConfig.from_dict(raw).to_model_spec()
     layers = list(base.layers)
     layers[0] = type(layers[0])(
@@ -371,9 +422,14 @@ def toy_spec(raw):
         feed_forward=PartSpec("toy_routed", dict(hidden_size=raw["hidden_size"], inter=48, experts=3,
                                                  name="model.layers.2.moe")),
         norms=layers[2].norms)
+    layers[3] = type(layers[3])(
+        prefix=layers[3].prefix, block=layers[3].block,
+        mixer=PartSpec("toy_latent", dict(hidden_size=raw["hidden_size"], latent=24, name="model.layers.3.latent")),
+        feed_forward=layers[3].feed_forward, norms=layers[3].norms)
     fields = {f: getattr(base, f) for f in base.__dataclass_fields__}
     fields.update(architecture="ToyForCausalLM", layers=tuple(layers),
-                  schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(2, cache_of=2)))
+                  schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0),
+                            ScheduleEntry(2, cache_of=2), ScheduleEntry(3)))
     return ModelSpec(**fields)
 
 
@@ -408,15 +464,23 @@ def toy_plain_logits(raw, weights, tokens):
         running = torch.cumsum(x.float(), dim=0).double() / torch.arange(1, n + 1).double()[:, None]
         return pl.linear(running, w["model.layers.1.mean.weight"]), None
 
+    def latent_layer(x, p):
+        c, q = pl.linear(x, w[f"{p}.latent.c.weight"]), pl.linear(x, w[f"{p}.latent.q.weight"])
+        scores = (q @ c.T) / c.shape[1] ** 0.5
+        scores = scores.masked_fill(positions[None, :] > positions[:, None], float("-inf"))
+        return pl.linear(torch.softmax(scores, dim=-1) @ c, w[f"{p}.latent.o.weight"]), None
+
     h = pl.embed(ids, w["model.embed_tokens.weight"])
     residual = None
     kept = {}
-    for entry, (layer, borrow) in enumerate([(0, None), (1, None), (2, None), (0, None), (2, 2)]):
+    for entry, (layer, borrow) in enumerate([(0, None), (1, None), (2, None), (0, None), (2, 2), (3, None)]):
         p = f"model.layers.{layer}"
         residual = h if residual is None else h + residual
         x = pl.rms_norm(residual, w[f"{p}.input_layernorm.weight"], eps)
         if layer == 1:
             a, _ = mean_layer(x, p)
+        elif layer == 3:
+            a, _ = latent_layer(x, p)
         else:
             a, kept[entry] = attention_layer(x, p, "toy" if layer == 0 else "rope",
                                              None if borrow is None else kept[borrow])
@@ -439,22 +503,25 @@ def toy_plain_logits(raw, weights, tokens):
 @pytest.fixture
 def toy_parts():
     MIXERS.register("toy_running_mean", RunningMeanMixer)
+    MIXERS.register("toy_latent", LatentMixer)
     POSITION_ENCODINGS.register("toy_offset", OffsetPosition)
     FEED_FORWARDS.register("toy_routed", RoutedFeedForward)
     register_architecture("ToyForCausalLM", toy_spec)
     yield
     MIXERS.unregister("toy_running_mean")
+    MIXERS.unregister("toy_latent")
     POSITION_ENCODINGS.unregister("toy_offset")
     FEED_FORWARDS.unregister("toy_routed")
     unregister_architecture("ToyForCausalLM")
 
 
 def test_toy_parts_register_build_and_step_without_touching_the_framework(device, toy_parts, tmp_path):
-    raw = dict(rc.TINY_A, architectures=["ToyForCausalLM"], num_hidden_layers=3, max_position_embeddings=256)
+    raw = dict(rc.TINY_A, architectures=["ToyForCausalLM"], num_hidden_layers=4, max_position_embeddings=256)
     folder = rc.write_model(tmp_path / "m", raw, 4, "float32")
     weights = plain_llama.load_weights(folder)
     assert "model.layers.1.mean.weight" in weights and "model.layers.1.self_attn.q_proj.weight" not in weights
     assert "model.layers.2.moe.experts.2.out.weight" in weights and "model.layers.2.mlp.down_proj.weight" not in weights
+    assert "model.layers.3.latent.c.weight" in weights and "model.layers.3.self_attn.k_proj.weight" not in weights
     requests = {f"r{i}": rc.random_tokens(256, n, 30 + i) for i, n in enumerate((40, 75, 23, 58, 31))}
     reference = {rid: toy_plain_logits(raw, weights, toks).numpy() for rid, toks in requests.items()}
     for steps in (rc.trace_whole(requests), rc.trace_chunks(requests), rc.trace_mixed(requests, max_live=3, seed=1)):
@@ -465,9 +532,12 @@ def test_toy_parts_register_build_and_step_without_touching_the_framework(device
         for (rid, pos), row in rows.items():
             err = np.abs(row - reference[rid][pos]).max() / np.abs(reference[rid]).max()
             assert err < 3e-5, (rid, pos, err)
-        # two groups of pages: windowed (both runs of layer 0) and full (layer 2 and its borrower)
-        assert [g.kind for g in kv.groups] == ["window", "full"]
-        assert [len(g.entries) for g in kv.groups] == [2, 1]
+        # three groups of pages: windowed keys and values (both runs of layer 0), keys and values that
+        # stay (layer 2 and its borrower), and the latent mixer's single plane of one vector a token
+        assert [g.kind for g in kv.groups] == ["window", "full", "full"]
+        assert [len(g.entries) for g in kv.groups] == [2, 1, 1]
+        assert [(g.planes, g.heads, g.width) for g in kv.groups] == [(2, 2, 16), (2, 2, 16), (1, 1, 24)]
+        assert tuple(step_function.storage.group_tensors[2].shape[:2]) == (1, 1)
         assert len(step_function.storage.state_tensors) == 1
 
 

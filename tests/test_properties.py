@@ -26,7 +26,7 @@ OPERATIONS = st.lists(
 @given(ops=OPERATIONS, windows=st.sampled_from([(None,), (None, 7), (5, None, 9)]),
        num_pages=st.integers(6, 30), page_size=st.sampled_from([2, 4, 8]))
 def test_cache_manager_accounts_for_every_page(ops, windows, num_pages, page_size):
-    groups = [CacheGroupSpec(i, (i,), 2, 16, w) for i, w in enumerate(windows)]
+    groups = [CacheGroupSpec(i, (i,), 2, 2, 16, w) for i, w in enumerate(windows)]
     kv = KVManager(groups, num_pages=num_pages, page_size=page_size, max_num_seqs=4, max_model_len=64)
     live: dict[str, int] = {}
     for action, which, amount in ops:
@@ -171,7 +171,7 @@ def test_scheduler_finishes_every_request_within_its_limits(arrivals, num_pages,
     from kvcore_b200.sampling import SamplingParams
 
     page_size, max_model_len = 4, 40
-    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=num_pages, page_size=page_size,
+    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 2, 16, None)], num_pages=num_pages, page_size=page_size,
                    max_num_seqs=max_seqs, max_model_len=max_model_len, enable_prefix_caching=prefix)
     sched = Scheduler(SchedulerConfig(max_num_seqs=max_seqs, max_num_scheduled_tokens=budget,
                                       max_num_partial_prefills=partial, max_long_partial_prefills=partial), kv)

@@ -12,7 +12,7 @@ from kvcore_b200.sampling import SamplingParams
 
 
 def make(num_pages=33, page_size=4, max_model_len=64, prefix_caching=False, **cfg):
-    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 16, None)], num_pages=num_pages, page_size=page_size,
+    kv = KVManager([CacheGroupSpec(0, (0, 1), 2, 2, 16, None)], num_pages=num_pages, page_size=page_size,
                    max_num_seqs=cfg.get("max_num_seqs", 8), max_model_len=max_model_len,
                    enable_prefix_caching=prefix_caching)
     return Scheduler(SchedulerConfig(**cfg), kv), kv
