@@ -222,6 +222,82 @@ def time_prefill(runner, tokens: int, repeats: int, warmup: int) -> float:
     return total / repeats
 
 
+def check_logits(runner, shape: dict, layers: int, batch: int = 8) -> dict:
+    """Before anything is timed: the model that is about to be timed, with its own weights, against the
+    plain implementation (tests/plain_llama.py, evaluated in 32-bit on the GPU with elementary torch
+    operations on the weights read back from the model).  Two requests of 333 and 700 tokens go
+    through the step function in portions of 256 beside each other, six short ones beside them, then
+    three decode steps of the whole batch (run eagerly, captured, replayed); the logits at the end of
+    both prompts and at every decode step must lie within 2e-2 of the request's largest |logit|."""
+    import torch
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    import plain_llama
+
+    from kvcore_b200.engine.step import StepEntry
+    import kvcore_b200.kernels as K
+
+    kv, step_function = runner.kv_manager, runner.step_function
+    for rid in kv.live_requests():
+        kv.free(rid)
+    vocab = shape["vocab_size"]
+    generator = torch.Generator().manual_seed(5)
+    lengths = [333, 700] + [50 + 7 * i for i in range(batch - 2)]
+    tokens = [torch.randint(0, vocab, (n + 3,), generator=generator).tolist() for n in lengths]
+    ids = [f"check-{i}" for i in range(len(lengths))]
+    got: dict[tuple[int, int], torch.Tensor] = {}
+    done = [0] * len(lengths)
+    while any(d < n for d, n in zip(done, lengths)):
+        entries, rows = [], []
+        for index, (rid, n) in enumerate(zip(ids, lengths)):
+            if done[index] >= n:
+                continue
+            size = min(256, n - done[index])
+            assert kv.allocate_slots(rid, size)
+            last = done[index] + size == n
+            entries.append(StepEntry(rid, tokens[index][done[index]:done[index] + size], (size - 1,) if last else ()))
+            if last:
+                rows.append((index, n - 1))
+            done[index] += size
+        logits = step_function.step(entries)
+        for row, key in enumerate(rows):
+            got[key] = logits[row].float().cpu()
+    for _ in range(3):
+        entries = []
+        for index, rid in enumerate(ids):
+            assert kv.allocate_slots(rid, 1)
+            entries.append(StepEntry(rid, (tokens[index][done[index]],), (0,)))
+        logits = step_function.step(entries).float().cpu()
+        for index in range(len(ids)):
+            got[(index, done[index])] = logits[index]
+            done[index] += 1
+    for rid in ids:
+        kv.free(rid)
+    status = K.read_status()
+    if status:
+        raise RuntimeError(f"a kernel reported status {status} during the logits check")
+    config = {k: v for k, v in dict(shape, num_hidden_layers=layers).items() if v is not None}
+    weights = runner.model.state_dict()
+    worst, checked = 0.0, 0
+    with torch.no_grad():
+        for index in (0, 1, batch - 1):
+            rows = sorted(pos for i, pos in got if i == index)
+            want = plain_llama.forward_logits(config, weights, tokens[index][:done[index]], compute=torch.float32,
+                                              rows=rows, device="cuda:0").float().cpu()
+            scale = float(want.abs().max())
+            for row, pos in enumerate(rows):
+                worst = max(worst, float((got[(index, pos)] - want[row]).abs().max()) / scale)
+                checked += 1
+    del weights
+    torch.cuda.empty_cache()
+    tolerance = 2e-2
+    if not worst <= tolerance:
+        raise RuntimeError(f"logits of the benchmark model differ from the plain implementation: "
+                           f"{worst:.3e} of the largest logit (allowed {tolerance})")
+    return {"logits_checked": True, "logits_max_err": round(worst, 5), "logits_tolerance": tolerance,
+            "logits_rows_checked": checked}
+
+
 def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) -> dict:
     """Decode steps through ``LLMEngine.step``: host token ids in, sampled token ids out."""
     import torch
@@ -307,22 +383,189 @@ def time_serving(shape: dict, layers: int, requests: int, min_prompt: int, max_p
 
 
 def reference_arm(args) -> int:
-    """The unmodified reference through its own entry point, if it could be installed offline.
+    """The unmodified reference, run through its own step loop at the headline's shape.
 
-    The offline install (pip install --no-index --no-build-isolation --find-links <wheelhouse>
-    --target baseline/_ref <reference>) fails where no network is available: the reference's
-    build backend, hatchling, is neither installed nor among the offline wheels.  Without an
-    installed copy the arm reports itself unavailable.
-    """
+    ``baseline/_ref/kvcore`` is a plain copy of the reference's pure-Python package (its offline pip
+    install fails: the build backend, hatchling, is neither installed nor among the offline wheels).
+    Nothing of this repository's engine is on the path: the reference's own ``Llama3ForCausalLM`` is
+    built from an in-memory ``LlamaConfig`` (transformers serves as the configuration container the
+    reference asks for) with N(0, 0.02) bfloat16 weights on the GPU, and driven by the reference's own
+    ``EngineCore.step`` (kvcore/engine/engine_core.py:103-149: ``Scheduler.schedule`` ->
+    ``ModelRunner.execute_model`` -> ``sample_tokens`` -> ``update_from_outputs``) with its stock CUDA
+    attention backend ``triton_paged``.  Only ``EngineCore.__init__`` is bypassed, because it loads a
+    tokenizer and a checkpoint folder that do not exist offline; requests are given as token ids.
+    Same batch, same context reached by its own chunked prefill (untimed), same steps and warm-up;
+    ``value`` from CUDA events, ``e2e`` from the wall clock (the reference reads its tokens back every
+    step, so the two nearly coincide).  Anything that goes wrong is reported as ``unavailable`` with
+    the error's own text."""
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "kvcore").is_dir():
-        reason = ("offline pip install of the reference failed: its build backend hatchling is not installed "
-                  "and not among the offline wheels, so baseline/_ref is empty")
-    else:
-        reason = ("baseline/_ref holds the reference, but its entry point needs a tokenizer and a 16 GB "
-                  "checkpoint folder that cannot be provided offline")
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref/kvcore is missing (the offline pip install of the reference fails for want "
+                          "of its build backend hatchling; a plain copy of its kvcore/ package goes there instead)"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference runs on one GPU only"}))
+        return 0
+    try:
+        line = _run_reference(args, ref)
+    except BaseException as error:  # the arm must print its line whatever happens
+        if isinstance(error, KeyboardInterrupt):
+            raise
+        text = " ".join(f"{type(error).__name__}: {error}".split())[:400]
+        line = {"impl": "reference", "unavailable": f"the reference failed while running: {text}"}
+    print(json.dumps(line))
     return 0
+
+
+def _run_reference(args, ref: Path) -> dict:
+    sys.path.insert(0, str(ref))
+    sys.dont_write_bytecode = True
+    import torch
+    from transformers.models.llama.configuration_llama import LlamaConfig  # configuration container only
+
+    from kvcore.config import CacheConfig, DeviceConfig, KVCoreConfig, ModelConfig, SchedulerConfig
+    from kvcore.engine.engine_core import EngineCore
+    from kvcore.model.model_runner import ModelRunner
+    from kvcore.model.models.llama3 import Llama3ForCausalLM
+    from kvcore.sched.scheduler import Scheduler
+    from kvcore.utils.request import Request
+    from kvcore.utils.sampling_params import SamplingParams
+
+    shape, label, shape_context, _ = SHAPES[args.shape]
+    layers = args.layers or shape["num_hidden_layers"]
+    context = args.context or shape_context
+    batch, steps, warmup = args.batch, args.steps, max(args.warmup, 3)
+    keys = ("vocab_size", "hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
+            "head_dim", "max_position_embeddings", "tie_word_embeddings", "rms_norm_eps")
+    # the reference's rotary layer reads the base only (kvcore/model/layer/rotary_embedding.py:38-49): it has no
+    # llama3 frequency scaling, which changes a table of 64 numbers and no cost
+    hf = LlamaConfig(**{k: shape[k] for k in keys}, num_hidden_layers=layers,
+                     rope_parameters={"rope_type": "default", "rope_theta": shape["rope_theta"]})
+    # The reference's Triton kernels form the offset of a cache block as block_id * stride in 32-bit
+    # (kvcore/model/attn_backend/triton_paged.py:66-80, 159-165: both factors are 32-bit integers), and
+    # all layers share one tensor of blocks: with blocks of 16 tokens x 8 heads x 128 it can address
+    # block ids below 2^31 / 16384 = 131,072.  Batch 8 x 8,192 tokens x 32 layers needs ids up to 131,840;
+    # run at that size its kernel made an illegal memory access.  The arm therefore never gives it a
+    # pool it cannot address: where the stated context does not fit, it runs the largest context (a
+    # multiple of 64) that does, and says so in its line.
+    block_elems = BLOCK_SIZE * shape["num_key_value_heads"] * shape["head_dim"]
+    addressable = (1 << 31) // block_elems - 1                 # largest pool (null block included) whose ids are safe
+    extra = steps + warmup + 4
+    per_pair = addressable // (layers * batch) - 2             # blocks a (request, layer) pair may use, two to spare
+    stated_context = context
+    if -(-(context + extra) // BLOCK_SIZE) > per_pair:
+        context = (per_pair * BLOCK_SIZE - extra) // 64 * 64
+        if context <= 0:
+            raise RuntimeError(f"the reference cannot address a cache for batch {batch} at {layers} layers")
+    max_len = context + extra + 60
+    blocks = min(layers * batch * (-(-(context + extra) // BLOCK_SIZE) + 2) + 1, addressable)
+    assert (blocks - 1) * block_elems < (1 << 31)
+    config = KVCoreConfig(
+        model_config=ModelConfig(model="unused", hf_config=hf, dtype=torch.bfloat16, max_model_len=max_len),
+        cache_config=CacheConfig(block_size=BLOCK_SIZE, num_gpu_blocks=blocks, profile_kv_cache=False,
+                                 enable_caching=False),
+        scheduler_config=SchedulerConfig(max_num_seqs=batch, max_num_scheduled_tokens=PREFILL_TOKENS,
+                                         max_num_partial_prefills=batch, max_long_partial_prefills=batch),
+        device_config=DeviceConfig(device="cuda:0"),
+    )
+    backend = config.model_config.attn_backend        # the reference's own choice on a CUDA device
+    torch.manual_seed(0)
+    previous = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device("cuda:0"):
+            model = Llama3ForCausalLM(config)
+    finally:
+        torch.set_default_dtype(previous)
+    with torch.no_grad():
+        for name, parameter in model.named_parameters():
+            if name.endswith("norm.weight") or "layernorm" in name:
+                parameter.fill_(1.0)
+            else:
+                parameter.normal_(0.0, 0.02)
+    model.eval()
+
+    core = EngineCore.__new__(EngineCore)      # its __init__ wants a tokenizer and a checkpoint folder
+    core.kvcore_config = config
+    core.model_runner = ModelRunner(config)
+    core.model_runner.model = model
+    core.stop_token_ids = set()
+    core.finished_outputs = {}
+    kv_config = core._build_kv_manager_config()
+    core.scheduler = Scheduler(config, kv_config)
+    core.model_runner.initialize_kv_cache(kv_config)
+
+    generator = torch.Generator().manual_seed(3)
+    for index in range(batch):
+        prompt = torch.randint(0, shape["vocab_size"], (context,), generator=generator).tolist()
+        core.scheduler.add_request(Request(request_id=f"ref-{index}", prompt_token_ids=prompt,
+                                           sampling_params=SamplingParams(max_tokens=1_000_000, temperature=0.0)))
+
+    def sampled(outputs) -> int:
+        return sum(1 for o in outputs.request_outputs if o.sampled_token_id is not None)
+
+    prefill_began = time.perf_counter()
+    guard = 0
+    while sampled(core.step()) < batch:          # its own chunked prefill, untimed
+        guard += 1
+        if guard > 4 * batch * (-(-context // PREFILL_TOKENS)) + 16:
+            raise RuntimeError("the reference did not reach a step in which every request decodes")
+    torch.cuda.synchronize()
+    prefill_seconds = time.perf_counter() - prefill_began
+    for _ in range(warmup):
+        assert sampled(core.step()) == batch
+    sampler = ClockSampler()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    start.record()
+    produced = 0
+    for _ in range(steps):
+        produced += sampled(core.step())
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - began
+    clocks = sampler.stop()
+    assert produced == steps * batch, f"{produced} tokens from {steps} steps of {batch} requests"
+    ms_step = start.elapsed_time(stop) / steps
+    peaks = measured_peaks()
+    numbers = model_numbers(shape, layers)
+    step_bytes = 2.0 * numbers["streamed_params"] + batch * context * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    return {
+        "metric": f"decode tokens/s, {label.replace('-', ' ')}, batch {batch}, bf16",
+        "value": round(batch * 1000.0 / ms_step, 2), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "impl": "reference",
+        "data": "synthetic: random N(0,0.02) weights, seeded uniform-random token ids, cache written by its own prefill",
+        "config": {
+            "model": label, "layers": layers, "layers_of_config": shape["num_hidden_layers"],
+            "hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
+            "kv_heads": shape["num_key_value_heads"], "head_dim": shape["head_dim"],
+            "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+            "tied_embeddings": shape["tie_word_embeddings"], "global_batch": batch, "seq_len": context,
+            "context_len": context, "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single GPU", "attn_backend": backend, "stated_context_len": stated_context,
+            "l2": f"weights of {2e-9 * numbers['streamed_params']:.0f} GB stream every step: inputs larger than L2",
+        },
+        "same_config": context == stated_context,
+        "note": ("" if context == stated_context else
+                 f"the reference's Triton kernels address its shared block tensor with 32-bit offsets (block ids below "
+                 f"{addressable + 1}); {batch} requests of {stated_context} tokens at {layers} layers need more, and run so "
+                 f"its kernel made an illegal memory access, so it is timed at {context} tokens of context, the most it "
+                 f"can address: {100.0 * context / stated_context:.1f} % of the cache bytes, the same weights"),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"],
+                     "bytes_per_step": int(step_bytes)},
+        "clocks": clocks,
+        "e2e": {"value": round(produced / elapsed, 2), "unit": "tokens/s", "ms_per_step": round(1000.0 * elapsed / steps, 3),
+                "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "note": "wall clock around the reference's own EngineCore.step, which uploads its step inputs and reads "
+                        "the sampled tokens back every step"},
+        "reference_prefill_seconds": round(prefill_seconds, 2),
+    }
 
 
 def main() -> int:
@@ -337,6 +580,8 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=None)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="only the headline decode number")
+    parser.add_argument("--check", action=argparse.BooleanOptionalAction, default=True,
+                        help="before timing, compare logits of the model to be timed with the plain implementation")
     parser.add_argument("--only-prefill", action="store_true",
                         help="time the 2,048-token prefill alone and print its line (for profiling)")
     parser.add_argument("--serve", action="store_true",
@@ -381,19 +626,32 @@ def main() -> int:
         print(json.dumps({"prefill_ms": round(ms_prefill, 3), "layers": args.layers,
                           "tokens_per_s": round(PREFILL_TOKENS * 1000.0 / ms_prefill, 1)}))
         return 0
+    checked = check_logits(runner, shape, args.layers) if args.check else {"logits_checked": False}
     sampler = ClockSampler()
     sampler.start()
     launches_before = K.api.launch_count
     ms_step = time_decode(runner, args.batch, args.context, args.steps, args.warmup)
     launches = (K.api.launch_count - launches_before) * args.steps // (args.steps + args.warmup)
     points = {}
+    point_details = {}
     prefill = None
     e2e = None
+
+    def point(name: str, batch: int, context: int) -> None:
+        ms = time_decode(runner, batch, context, args.steps, args.warmup)
+        step_bytes = 2.0 * numbers["streamed_params"] + batch * context * numbers["kv_bytes_per_token"]
+        gbs = step_bytes / (ms * 1e-3) / 1e9
+        points[name] = round(batch * 1000.0 / ms, 2)
+        point_details[name] = {"batch": batch, "context": context, "ms_per_step": round(ms, 4),
+                               "bytes_per_step": int(step_bytes), "achieved_gbs": round(gbs, 1),
+                               "frac": round(gbs / peaks["hbm_gbs"], 4)}
+
     if not args.skip_points:
         for batch in side_batches:
-            points[f"decode_b{batch}"] = round(batch * 1000.0 / time_decode(runner, batch, args.context, args.steps, args.warmup), 2)
+            point(f"decode_b{batch}", batch, args.context)
+        # the decode workload as the baseline configuration states it: prompts of 1,024 tokens
         for batch in (side_batches[0], args.batch, side_batches[1]):
-            points[f"decode_b{batch}_ctx1024"] = round(batch * 1000.0 / time_decode(runner, batch, 1024, args.steps, args.warmup), 2)
+            point(f"decode_b{batch}_ctx1024", batch, 1024)
         ms_prefill = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
         t, h, d = PREFILL_TOKENS, numbers["heads"], numbers["head_dim"]
         flops = 2.0 * t * (args.layers * (numbers["layer_params"] - 2 * numbers["hidden"])) \
@@ -448,6 +706,8 @@ def main() -> int:
         line["e2e"] = e2e
     if points:
         line["points"] = points
+        line["point_details"] = point_details
+    line.update(checked)
     print(json.dumps(line))
     return 0
 

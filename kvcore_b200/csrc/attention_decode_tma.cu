@@ -686,6 +686,7 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
               "decode attention (TMA): page size must be 8, 16, 32 or 64");
   KVB_REQUIRE(H > 0 && KVH > 0 && H % KVH == 0, "decode attention (TMA): H must be a multiple of KVH");
   KVB_REQUIRE(max_query_len * (H / KVH) <= 16, "decode attention (TMA): at most 16 rows per request and kv head");
+  KVB_REQUIRE(num_splits <= KVB_MAX_SPLITS, "decode attention (TMA): at most 1024 splits");
   KVB_REQUIRE((long long)num_reqs * KVH * (num_splits < 1 ? 1 : num_splits) < (1ll << 30),
               "decode attention (TMA): batch too large for one launch");
   KVB_REQUIRE(aligned16(q) && (q_stride % 8) == 0, "decode attention (TMA): q must be 16-byte aligned");

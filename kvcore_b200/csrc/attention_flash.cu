@@ -507,6 +507,7 @@ extern "C" int kvb_flash_paged_attention(void* out, long long out_stride, const 
   const int max_rows = max_query_len * p.G;
   const bool split_mode = max_rows <= 16;
   KVB_REQUIRE(split_mode || num_splits <= 1, "flash attention: splits need at most 16 rows per kv head");
+  KVB_REQUIRE(num_splits <= KVB_MAX_SPLITS, "flash attention: at most 1024 splits");
   p.num_splits = num_splits < 1 ? 1 : num_splits;
   KVB_REQUIRE(p.num_splits == 1 || scratch != nullptr, "flash attention: splits need scratch memory");
   p.partial_o = scratch;
@@ -570,6 +571,7 @@ extern "C" int kvb_flash_paged_attention_static(void* out, long long out_stride,
   KVB_REQUIRE(num_reqs <= 65535 && KVH <= 65535, "static attention: batch too large for one launch");
   KVB_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && (q_stride % 8) == 0,
               "static attention: q and the caches must be 16-byte aligned");
+  KVB_REQUIRE(num_splits <= KVB_MAX_SPLITS, "static attention: at most 1024 splits");
   const int splits = num_splits < 1 ? 1 : num_splits;
   const int max_rows = max_query_len * (H / KVH);
   const bool split_mode = max_rows <= 16;
@@ -581,7 +583,9 @@ extern "C" int kvb_flash_paged_attention_static(void* out, long long out_stride,
   float* scratch = nullptr;
   int* status = nullptr;
   if (int rc = static_arrays(&scratch, &status)) return rc;
-  KVB_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int), stream));  // the one thing that must start at zero
+  // Nothing in the arrays has to be cleared per call: the kernels write every partial result they
+  // later read, and the status word starts at zero with the library image and is cleared by
+  // kvb_static_status, so that a bit set by one call is still there after the calls behind it.
   FlashParams p;
   p.out = (bf16*)out; p.out_stride = out_stride;
   p.q = (const bf16*)q; p.q_stride = q_stride;

@@ -18,6 +18,10 @@
 #define KVB_STATUS_BAD_PAGE 2
 #define KVB_STATUS_WAIT_TIMEOUT 4
 
+// Most chunks a request's keys may be cut into by the split-KV attention entry points (sizes of
+// their scratch are products with this count; the bound keeps them far inside 64 bits).
+#define KVB_MAX_SPLITS 1024
+
 extern "C" int kvb_fail(int code, const char* what, const char* file, int line);
 // Device address of the current device's status word (allocated once per device).
 extern "C" int* kvb_status_word();

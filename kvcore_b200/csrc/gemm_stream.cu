@@ -64,6 +64,10 @@ struct StreamParams {
   // 64 columns to sumsq_out[m * n_tiles + tile].  out itself is not written.
   bf16* residual; float* sumsq_out;
   int silu_pairs;                    // 1: rows n and n+8 of every 16 are a (gate, up) pair: out[m, .] = silu(gate) * up
+  unsigned spin_limit;               // polls after which a wait gives up
+  // Test of the give-up path (kvb_gemm_stream_test_give_up): block test_skip_block never asks for the
+  // copies of its stage test_skip_stage, so that everyone who waits for them runs out of polls.  -1: off.
+  int test_skip_block, test_skip_stage;
 };
 
 __device__ __forceinline__ void gs_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
@@ -83,6 +87,11 @@ __device__ __forceinline__ void gs_mma(float (&c)[4], const unsigned (&a)[4], un
 __device__ __forceinline__ unsigned gs_swz(int row, int k, int rows) {
   const int slab = k >> 6, chunk = (k & 63) >> 3;
   return (unsigned)(slab * rows * 128 + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// A bounded wait with the launch's limit (GS_SPIN_LIMIT polls unless a test lowered it).
+__device__ __forceinline__ bool gs_wait(const StreamParams& p, unsigned long long* bar, unsigned parity) {
+  return kvb_mbar_wait_n(bar, parity, p.spin_limit, 64);
 }
 
 // First stage of block b when `units` stages are dealt to `blocks` blocks.
@@ -140,6 +149,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       // written by no kernel of the step)
       for (int i = 0; i < pre; ++i) {
         const int u = u_begin + i;
+        if (me == p.test_skip_block && i == p.test_skip_stage) continue;
         kvb_mbar_expect_tx(&full_bar[i], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
         kvb_tma_3d(base + i * STAGE_BYTES, &w_map, 0, (u / p.kchunks) * GS_NT, (u % p.kchunks) * GS_KG, &full_bar[i]);
       }
@@ -147,7 +157,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       int issued = 0;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        if (it >= STAGES && !kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
+        if (it >= STAGES && !gs_wait(p, &empty_bar[stage], ((it / STAGES) & 1) ^ 1)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(&flags[0], 1);
           break;
@@ -156,6 +166,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         const int u = u_begin + it;
         const int slab = (u % p.kchunks) * GS_KG;
         unsigned char* wdst = base + stage * STAGE_BYTES;
+        issued = it + 1;
+        if (me == p.test_skip_block && it == p.test_skip_stage) continue;
         if (it >= pre) {
           kvb_mbar_expect_tx(&full_bar[stage], (unsigned)(NORMED ? W_BYTES : STAGE_BYTES));
           kvb_tma_3d(wdst, &w_map, 0, (u / p.kchunks) * GS_NT, slab, &full_bar[stage]);
@@ -166,12 +178,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         } else {
           kvb_tma_3d(wdst + W_BYTES, &x_map, 0, 0, slab, &full_bar[stage]);
         }
-        issued = it + 1;
       }
       if (*reinterpret_cast<volatile int*>(&flags[0])) {   // gave up: let the copies in flight land
         for (int j = max(0, issued - STAGES); j < issued; ++j) {
-          kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&full_bar[j % STAGES], (j / STAGES) & 1);
-          if (NORMED) kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xraw_bar[j % STAGES], (j / STAGES) & 1);
+          gs_wait(p, &full_bar[j % STAGES], (j / STAGES) & 1);
+          if (NORMED) gs_wait(p, &xraw_bar[j % STAGES], (j / STAGES) & 1);
         }
       }
     }
@@ -200,7 +211,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       const int total = u_end - u_begin;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
-        int fine = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
+        int fine = gs_wait(p, &xraw_bar[stage], (it / STAGES) & 1) ? 1 : 0;
         fine = __all_sync(0xffffffffu, fine);
         if (!fine) {
           if (lane == 0) {
@@ -265,8 +276,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       }
       for (; u < seg_end; ++u, ++it) {
         const int stage = it % STAGES;
-        bool landed = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&full_bar[stage], (it / STAGES) & 1);
-        if (NORMED && landed) landed = kvb_mbar_wait<GS_SPIN_LIMIT, 64>(&xready_bar[stage], (it / STAGES) & 1);
+        bool landed = gs_wait(p, &full_bar[stage], (it / STAGES) & 1);
+        if (NORMED && landed) landed = gs_wait(p, &xready_bar[stage], (it / STAGES) & 1);
         if (!__all_sync(0xffffffffu, landed)) {
           atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
           atomicExch(&flags[0], 1);
@@ -346,7 +357,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
               const int batch = parts - c0 < 4 ? parts - c0 : 4;
               float part[4][MBLK][4];
               bool there = false;
-              for (unsigned spin = 0; spin < GS_SPIN_LIMIT && !there; ++spin) {
+              for (unsigned spin = 0; spin < p.spin_limit && !there; ++spin) {
                 if (spin > 256) __nanosleep(64);               // the blocks finish together: spin first
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -532,6 +543,19 @@ static int gs_launch(const void* w, const void* x, long long ldx, StreamParams& 
   return 0;
 }
 
+// For the test of the give-up path only: the NEXT launch of kvb_gemm_stream_bf16 gives up waiting
+// after `spin_limit` polls instead of GS_SPIN_LIMIT, and its block `block` never asks for the copies
+// of its stage `stage`.  The consumers of that block, and the owners of tiles it shares, then run
+// out of polls: they set the status bit KVB_STATUS_WAIT_TIMEOUT, let the copies in flight land and
+// return, leaving wrong values in `out`.  Nothing faults and nothing waits without a limit.
+static int g_gs_test_block = -1, g_gs_test_stage = -1;
+static unsigned g_gs_test_limit = 0;
+extern "C" void kvb_gemm_stream_test_give_up(int block, int stage, unsigned spin_limit) {
+  g_gs_test_block = block;
+  g_gs_test_stage = stage;
+  g_gs_test_limit = spin_limit;
+}
+
 // Largest K whose norm weights (taken as 32-bit) a NORMED launch keeps in shared memory.
 extern "C" int kvb_gemm_stream_norm_max_k() { return GS_NORM_W_BYTES / 4; }
 
@@ -578,6 +602,11 @@ extern "C" int kvb_gemm_stream_bf16(void* out, int out_f32, long long ldo, const
   p.partial = scratch;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "stream gemm: no status word");
+  p.spin_limit = g_gs_test_limit ? g_gs_test_limit : GS_SPIN_LIMIT;
+  p.test_skip_block = g_gs_test_block;
+  p.test_skip_stage = g_gs_test_stage;
+  g_gs_test_block = g_gs_test_stage = -1;      // armed for one launch
+  g_gs_test_limit = 0;
   if (norm_weight != nullptr) {
     if (M <= 8) return gs_launch<1, true>(w, x, ldx, p, sms, stream);
     return gs_launch<2, true>(w, x, ldx, p, sms, stream);

@@ -22,9 +22,12 @@
 //    current, and before any stream capture.
 //  * All calls share the one array, and it keeps whatever the last call left in it.  The
 //    kernels write every partial result they later read, so nothing has to be cleared
-//    except the status word, which the entry point clears on the stream at each call.
+//    between calls.  The status word beside it starts at zero when the library is loaded
+//    and only ever gains bits: a problem reported by one call is still there after any
+//    number of later calls, until kvb_static_status reads and clears it.
 //    Two calls that overlap on the GPU (different streams, no dependency between them)
 //    race on the array: keep calls on one stream, or order them with events.
+//  * num_splits is at most 1024.
 //  * It calls no cudaMalloc, cudaFree, or allocating library routine; inputs and outputs
 //    are the caller's buffers.
 //
@@ -32,8 +35,9 @@
 // caches [pages, KVH, page_size, D], int32 block table, query_start [num_reqs + 1] and
 // context_lens [num_reqs] on the device.  Decode shape only when num_splits > 1:
 // max_query_len * (H / KVH) <= 16.  Returns 0, or a negative code with the message available
-// from kvb_last_error().  kvb_static_status reads (and clears) the status bits of the last
-// calls on the current device; it synchronises the device.
+// from kvb_last_error().  kvb_static_status reads (and clears) the status bits that all calls
+// since its last use have set on the current device (2: a page id outside the cache); it
+// synchronises the device.
 #pragma once
 
 #include <cuda_runtime.h>

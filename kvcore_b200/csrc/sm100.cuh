@@ -44,6 +44,14 @@ __device__ __forceinline__ bool kvb_mbar_wait(unsigned long long* bar, unsigned 
   }
   return false;
 }
+// The same with the limit chosen at run time.
+__device__ __forceinline__ bool kvb_mbar_wait_n(unsigned long long* bar, unsigned parity, unsigned limit, unsigned spin) {
+  for (unsigned poll = 0; poll < limit; ++poll) {
+    if (kvb_mbar_try_wait(bar, parity)) return true;
+    if (poll > spin) __nanosleep(64);
+  }
+  return false;
+}
 // Generic-proxy writes to shared memory made visible to the async proxy (TMA, tensor cores).
 __device__ __forceinline__ void kvb_fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 

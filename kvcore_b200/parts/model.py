@@ -72,6 +72,12 @@ class DecoderModel:
         for part in self._parts():
             part.finalize_weights()
 
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        """The model's tensors under their checkpoint names and in their checkpoint shapes, on the
+        model's device (packed matrices are split and scattered rows gathered again; copies where a
+        slot is a strided view)."""
+        return {slot.name: slot.dest.reshape(slot.shape) for slot in self.weight_slots()}
+
     def weight_bytes(self) -> int:
         seen: set[int] = set()
         total = 0

@@ -1,6 +1,8 @@
 """Writes tests/golden/reference_logits.{json,safetensors}: logits of the reference's own
-model code (Baizx98/KVCore, unmodified, imported from a checkout) on two tiny random Llama
-configurations, on the CPU in float32.  tests/test_plain_vs_golden.py checks the plain
+model code (Baizx98/KVCore, unmodified, imported from a checkout) on three tiny random Llama
+configurations, on the CPU in float32: A and B as the baseline states them, and one with biases on
+every projection, full multi-head attention and a logit scale, all of which the reference implements
+(kvcore/model/models/llama3.py:62-74, kvcore/sample/logits_processor.py:46-54).  tests/test_plain_vs_golden.py checks the plain
 implementation (tests/plain_llama.py) against these numbers.
 
 Usage:  python tests/golden/make_golden.py /path/to/KVCore
@@ -45,11 +47,17 @@ CONFIGS = {
         rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                           original_max_position_embeddings=64),
     ),
+    "BIAS": dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=300, hidden_size=80,
+        intermediate_size=112, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+        max_position_embeddings=128, tie_word_embeddings=False, rms_norm_eps=1e-5, rope_theta=10000.0,
+        hidden_act="silu", attention_bias=True, mlp_bias=True, logit_scale=0.25,
+    ),
 }
-SEEDS = {"A": 0, "B": 1}
-LENGTHS = {"A": (7, 13), "B": (5, 19, 40)}
-BLOCK = {"A": 16, "B": 8}
-BUDGET = {"A": 512, "B": 6}
+SEEDS = {"A": 0, "B": 1, "BIAS": 2}
+LENGTHS = {"A": (7, 13), "B": (5, 19, 40), "BIAS": (11, 30)}
+BLOCK = {"A": 16, "B": 8, "BIAS": 4}
+BUDGET = {"A": 512, "B": 6, "BIAS": 9}
 
 
 def state_dict_hash(tensors: dict) -> str:

@@ -105,7 +105,7 @@ def rope_inv_freq(config: dict) -> torch.Tensor:
 
 def embed(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     # kvcore/model/models/llama3.py:178-180
-    return table[token_ids.long()]
+    return table[token_ids.long().to(table.device)]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, rnd=lambda t: t) -> torch.Tensor:
@@ -127,7 +127,7 @@ def apply_rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fr
     The angle is formed in 32-bit as the reference does (positions.float() * inv_freq.float()).
     ``faithful_tables`` rounds cos/sin themselves as a bfloat16 run of the reference would.
     """
-    angles = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+    angles = positions.to(q.device, torch.float32)[:, None] * inv_freq.to(q.device, torch.float32)[None, :]
     emb = torch.cat((angles, angles), dim=-1).to(q.dtype)
     cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
     if faithful_tables:
@@ -146,7 +146,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     tokens, heads, _ = q.shape
     group = heads // k.shape[1]
     out = torch.empty_like(q)
-    index = torch.arange(tokens)
+    index = torch.arange(tokens, device=q.device)
     visible = index[None, :] <= index[:, None]
     if window is not None:
         visible &= index[None, :] > index[:, None] - window
@@ -177,10 +177,18 @@ def swiglu_mlp(x, gate_w, up_w, down_w, gate_b=None, up_b=None, down_b=None, rnd
 
 # ---- the model -------------------------------------------------------------------------------
 def forward_logits(config: dict, weights: dict, token_ids, *, compute=torch.float32,
-                   round_to=None, window: int | None = None) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence (kvcore/model/models/llama3.py:124-142, 182-200, 245-247)."""
+                   round_to=None, window: int | None = None, rows=None, device=None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence (kvcore/model/models/llama3.py:124-142, 182-200, 245-247).
+
+    ``rows``: only these positions go through the final norm and the head (the result is
+    ``[len(rows), V]``); the layers always run the whole sequence.  ``device``: where the same
+    elementary operations run (default: where the weights are); a large model is evaluated on the
+    GPU in 32- or 64-bit, where torch's matrix products keep full precision (no reduced-precision
+    matrix mode is switched on)."""
     rnd = _rounder(round_to)
-    w = {name: t.to(compute) for name, t in weights.items()}
+    if device is not None and torch.device(device).type == "cuda":
+        assert not torch.backends.cuda.matmul.allow_tf32, "the plain implementation needs full-precision products"
+    w = {name: t.to(device=device, dtype=compute) for name, t in weights.items()}
     if round_to is not None:
         w = {name: rnd(t) for name, t in w.items()}
     ids = torch.as_tensor(token_ids, dtype=torch.long)
@@ -222,7 +230,10 @@ def forward_logits(config: dict, weights: dict, token_ids, *, compute=torch.floa
             maybe(f"{p}.mlp.gate_proj.bias"), maybe(f"{p}.mlp.up_proj.bias"), maybe(f"{p}.mlp.down_proj.bias"),
             rnd,
         )
-    final = rms_norm(rnd(h + residual), w["model.norm.weight"], eps, rnd)  # llama3.py:199
+    last = rnd(h + residual)
+    if rows is not None:
+        last = last[torch.as_tensor(list(rows), dtype=torch.long, device=last.device)]
+    final = rms_norm(last, w["model.norm.weight"], eps, rnd)  # llama3.py:199
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
     logits = final @ head.T  # llama3.py:219, 245-247; kept unrounded: the engine emits 32-bit logits
     scale_out = float(config.get("logit_scale", 1.0))

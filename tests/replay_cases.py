@@ -30,6 +30,16 @@ TINY_B = dict(
     rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=64),
 )
+# the baseline's second configuration exactly as stated: vocabulary 512, no biases, pages of 8 tokens
+# (TINY_B above is its superset with an odd vocabulary and biases on every projection)
+TINY_B_AS_STATED = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=512, hidden_size=96,
+    intermediate_size=160, num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1,
+    head_dim=32, max_position_embeddings=256, tie_word_embeddings=True, rms_norm_eps=1e-6,
+    rope_theta=500000.0, hidden_act="silu",
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=64),
+)
 # a third shape: head size 48 (a step of 16, no power of two), 6 heads in 3 groups, odd widths
 TINY_C = dict(
     architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=301, hidden_size=120,
@@ -54,8 +64,10 @@ TINY_E = dict(
     head_dim=64, max_position_embeddings=1024, tie_word_embeddings=True, rms_norm_eps=1e-6,
     rope_theta=10000.0, hidden_act="silu",
 )
-TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "B8": TINY_B_AS_STATED}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "B8": 1}
+# tokens a cache page holds in the replay tests of each configuration
+TINY_PAGE_SIZES = {"A": 16, "B": 16, "C": 16, "D": 16, "E": 16, "B8": 8}
 
 
 def random_tokens(vocab: int, length: int, seed: int) -> list[int]:
@@ -155,6 +167,24 @@ def peak_tokens(steps: list[dict], page: int = 64) -> int:
     return peak
 
 
+def keep_wants(steps: list[dict], keep: dict[str, set[int]]) -> list[dict]:
+    """The same steps asking for logits only at the positions (counted within each request) that
+    ``keep`` names: for models whose vocabulary makes logits at every position too much to write."""
+    seen: dict[str, int] = {}
+    out = []
+    for step in steps:
+        entries = []
+        for entry in step["entries"]:
+            base = seen.get(entry["id"], 0)
+            wanted = [w for w in entry["want"] if base + w in keep.get(entry["id"], ())]
+            entries.append(dict(entry, want=wanted))
+            seen[entry["id"]] = base + len(entry["tokens"])
+        for rid in step["end"]:
+            seen.pop(rid, None)
+        out.append(dict(step, entries=entries))
+    return out
+
+
 # ---- running --------------------------------------------------------------------------------------
 def collect(steps: list[dict], out_dir: Path, vocab: int) -> dict[tuple[str, int], np.ndarray]:
     """Map (request id, position in the request) -> logits row, from the written files."""
@@ -189,6 +219,17 @@ def run_inprocess(model_dir, dtype: str, steps: list[dict], out_dir: Path, max_t
     kv.check_invariants()
     assert not kv.live_requests()
     return step_function, kv
+
+
+def run_on(step_function, kv, steps: list[dict], out_dir: Path) -> None:
+    """Replay ``steps`` on a step function that is there already (a large model is loaded once)."""
+    from kvcore_b200.engine.trace_replay import replay_stream
+
+    done: list[str] = []
+    replay_stream(step_function, kv, [json.dumps(step) for step in steps], Path(out_dir), done.append)
+    assert done == [f"done {step['step']}" for step in steps]
+    kv.check_invariants()
+    assert not kv.live_requests()
 
 
 def run_subprocess(model_dir, dtype: str, steps: list[dict], out_dir: Path, max_tokens: int, env=None):

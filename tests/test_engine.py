@@ -199,6 +199,51 @@ def test_seeded_sampling_is_reproducible_and_independent_of_the_batch(device, tm
     assert len(unseeded[0].output_token_ids) == 4
 
 
+def test_the_second_baseline_configuration_as_stated(device, tmp_path):
+    """Vocabulary 512, tied, llama3 scaling, pages of 8 tokens; requests of 5, 19 and 40 tokens, at most
+    6 tokens a step, 12 tokens each at temperature 0.8 with a seed.  Every logits row the sampler is
+    given is the plain implementation's row at that position, and every token is the one the plain
+    statement of the sampling rule draws from it."""
+    config = rc.TINY_CONFIGS["B8"]
+    folder = rc.write_model(tmp_path / "m", config, 1, "bfloat16")
+    weights = plain_llama.load_weights(folder)
+    prompts = {f"r{i}": rc.random_tokens(512, n, 50 + i) for i, n in enumerate((5, 19, 40))}
+    engine = LLMEngine(engine_config(folder, device, block_size=8, num_gpu_blocks=40,
+                                     scheduler=dict(max_num_scheduled_tokens=6)))
+    runner = engine.engine_core.model_runner
+    seen = []
+    sample = runner.sampler.sample
+
+    def recording(logits, params, seeds, token_indices):
+        tokens = sample(logits, params, seeds, token_indices)
+        seen.append((logits.float().cpu().clone(), list(seeds), list(token_indices), tokens.cpu().tolist()))
+        return tokens
+
+    runner.sampler.sample = recording
+    outputs = engine.generate([GenerationRequest(rid, SamplingParams(max_tokens=12, temperature=0.8, seed=1000 + i), tuple(p))
+                               for i, (rid, p) in enumerate(prompts.items())])
+    generated = {o.request_id: list(o.output_token_ids) for o in outputs}
+    assert all(len(tokens) == 12 for tokens in generated.values())
+    assert engine.engine_core.model_runner.step_function.num_steps >= 12 + 7       # 64 prompt tokens in portions of 6
+    rows_checked = 0
+    for rid, prompt in prompts.items():
+        seed = 1000 + int(rid[1:])
+        reference = plain_llama.forward_logits(config, weights, prompt + generated[rid]).numpy()
+        for index, token in enumerate(generated[rid]):
+            want = torch.from_numpy(reference[len(prompt) + index - 1])
+            rows = [(logits[row], tokens[row]) for logits, seeds, indices, tokens in seen
+                    for row in range(len(seeds)) if seeds[row] == seed and indices[row] == index]
+            assert len(rows) == 1, "one sampler call per token of a request"
+            got, sampled = rows[0]
+            assert sampled == token
+            assert float((got - want).abs().max()) <= 2e-5 * float(np.abs(reference).max())
+            assert plain_kernels.sample_row(got, 0.8, 512, 1.0, seed, index)[0] == token
+            assert plain_kernels.sample_row(want, 0.8, 512, 1.0, seed, index)[0] == token
+            rows_checked += 1
+    assert rows_checked == 36
+    runner.kv_manager.check_invariants()
+
+
 def test_running_one_step_ahead_changes_no_output(device, tmp_path):
     """With a step kept in flight the engine returns the tokens it returns without: requests that end
     by length, requests that stop on a token (seen a step late, the extra token dropped), seeded

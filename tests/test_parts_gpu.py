@@ -114,7 +114,7 @@ def test_attention_mixer_part(dtype, heads, kv_heads, dim, window):
     table = (torch.randperm(pages) + 1).to(torch.int32).view(1, pages).to(DEV)
     k_cache = torch.zeros(pages + 1, kv_heads, page, dim, dtype=dtype, device=DEV)
     v_cache = torch.zeros_like(k_cache)
-    cache = LayerCache(group=0, k=k_cache, v=v_cache, owner=True, state=None, page_size=page)
+    cache = LayerCache(group=0, planes=(k_cache, v_cache), owner=True, state=None, page_size=page)
     first = 97
     out = torch.cat([part.forward(x[:first].contiguous(), Ctx([(0, first)], table), cache),
                      part.forward(x[first:].contiguous(), Ctx([(first, tokens - first)], table), cache)])
@@ -188,8 +188,8 @@ def test_block_part(dtype, name, tokens):
     page = 16
     heads, kvh, dim = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
     table = torch.tensor([[2, 1, 3]], dtype=torch.int32, device=DEV)
-    cache = LayerCache(0, torch.zeros(4, kvh, page, dim, dtype=dtype, device=DEV),
-                       torch.zeros(4, kvh, page, dim, dtype=dtype, device=DEV), True, None, page)
+    cache = LayerCache(0, (torch.zeros(4, kvh, page, dim, dtype=dtype, device=DEV),
+                           torch.zeros(4, kvh, page, dim, dtype=dtype, device=DEV)), True, None, page)
     h, res = randn(tokens, raw["hidden_size"], dtype=dtype, seed=12), randn(tokens, raw["hidden_size"], dtype=dtype, seed=13)
     h0, r0 = h.float().cpu(), res.float().cpu()
     out_h, out_res = part.forward(h, res, Ctx([(0, tokens)], table), cache)

@@ -1,6 +1,7 @@
 """The plain implementation against the reference's own model code: tests/golden/ holds logits
-that Baizx98/KVCore's Llama3ForCausalLM produced on two tiny random models (made by
-tests/golden/make_golden.py).  Also checks the plain implementation against itself: float64,
+that Baizx98/KVCore's Llama3ForCausalLM produced on three tiny random models (made by
+tests/golden/make_golden.py): the baseline's two configurations and one with biases, full multi-head
+attention and a logit scale.  Also checks the plain implementation against itself: float64,
 and the sampling masks."""
 from __future__ import annotations
 
@@ -23,13 +24,19 @@ def golden():
     return record, SafetensorsFile(GOLDEN / "reference_logits.safetensors")
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "BIAS"])
 def test_plain_matches_reference_model_code(golden, name):
     record, logits = golden
     config = record["configs"][name]
     weights = random_state_dict(config, record["seeds"][name], 0.02, "float32")
-    if state_dict_hash(weights) != record["weights_sha256"][name]:
-        pytest.skip("this torch draws other random weights than the one that made the golden file")
+    # the golden file holds logits, not weights: they are drawn again from the seed, and if this torch
+    # draws other numbers than the one that made the file, the anchor is gone and must be made again
+    assert state_dict_hash(weights) == record["weights_sha256"][name], (
+        f"torch {torch.__version__} draws other random weights than torch {record['torch']}, which made the golden "
+        "file: run tests/golden/make_golden.py against a checkout of the reference again")
+    if name == "BIAS":
+        assert any(key.endswith("q_proj.bias") for key in weights) and any(key.endswith("down_proj.bias") for key in weights)
+        assert config["logit_scale"] != 1.0
     for index, tokens in enumerate(record["tokens"][name]):
         want = logits.tensor(f"{name}/seq{index}")
         got = plain_llama.forward_logits(config, weights, tokens)
@@ -48,7 +55,7 @@ def test_plain_float64_and_bf16_rounding_bracket_float32():
     scale = float(f64.abs().max())
     assert float((f32.double() - f64).abs().max()) < 2e-6 * scale
     err = float((bf16 - f32).abs().max()) / scale
-    assert 1e-4 < err < 1e-2  # what a faithful bfloat16 run loses; the bf16 GPU tests allow 2e-2
+    assert 1e-4 < err < 1e-2  # what a faithful bfloat16 run loses; the bf16 GPU tests allow 1.2e-2 on the tiny models
 
 
 def test_window_changes_only_far_positions():

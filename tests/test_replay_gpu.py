@@ -15,15 +15,24 @@ import replay_cases as rc
 pytestmark = pytest.mark.gpu
 
 # largest |difference| allowed, as a fraction of the largest |logit| of the request.
-# bfloat16: a faithful bfloat16 evaluation of the same formulas differs from 32-bit by about
-# 0.5% of the largest logit on these models; the bound is four times that.
-TOLERANCE = {"float32": 2e-5, "bfloat16": 2e-2}
+# bfloat16: measured on these models (all configurations, whole / tail / mixed cuttings), the engine
+# lies within 4.3e-3 to 7.3e-3 of the 32-bit plain model and within 5.1e-3 to 7.3e-3 of the plain model
+# evaluated with bfloat16 roundings in the reference's places, which itself lies 4.4e-3 to 7.4e-3 from
+# 32-bit: two bfloat16 evaluations that round in different places (the engine keeps the norm, the
+# activation and the residual sum inside its products) differ from each other as much as each does
+# from 32-bit, so the rounded oracle allows no tighter bound than the exact one.  The bound on a single
+# row is 1.6 times the largest error seen; beside it the median row error and the largest
+# root-mean-square error of a row over a trace are bounded at about 1.3 and 1.7 times what was measured
+# (3.0e-3 to 3.9e-3, and 1.3e-3 to 2.1e-3): a kernel that is a little wrong everywhere fails those.
+TOLERANCE = {"float32": 2e-5, "bfloat16": 1.2e-2}
+BF16_MEDIAN_TOLERANCE = 5e-3
+BF16_RMS_TOLERANCE = 3.5e-3
 LENGTHS = (45, 70, 33, 101, 64, 17, 128)
 # the two configurations with serving head sizes also get requests that span several key tiles
 LONG_LENGTHS = (45, 300, 33, 161, 64, 17, 520)
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "B8"])
 def model_case(request, tmp_path_factory):
     name = request.param
     config = rc.TINY_CONFIGS[name]
@@ -33,7 +42,8 @@ def model_case(request, tmp_path_factory):
     lengths = LONG_LENGTHS if name in ("D", "E") else LENGTHS
     requests = {f"r{i}": rc.random_tokens(config["vocab_size"], n, 10 + i) for i, n in enumerate(lengths)}
     reference = {rid: plain_llama.forward_logits(config, weights, toks).numpy() for rid, toks in requests.items()}
-    return dict(name=name, config=config, folder=folder, requests=requests, reference=reference)
+    return dict(name=name, config=config, folder=folder, requests=requests, reference=reference,
+                page_size=rc.TINY_PAGE_SIZES[name])
 
 
 def _compare(rows, reference, dtype):
@@ -48,6 +58,12 @@ def _compare(rows, reference, dtype):
                         and np.abs(v - reference[rid][p]).max() / np.abs(reference[rid]).max() > TOLERANCE[dtype])
             raise AssertionError(f"{rid}: first wrong position {first} (error {err:.3e} at {pos})")
         worst = max(worst, err)
+    if dtype == "bfloat16" and len(rows) >= 50:
+        errors = [np.abs(row - reference[rid][pos]).max() / np.abs(reference[rid]).max() for (rid, pos), row in rows.items()]
+        rms = [np.sqrt(np.mean((row - reference[rid][pos]) ** 2)) / np.abs(reference[rid]).max()
+               for (rid, pos), row in rows.items()]
+        assert np.median(errors) <= BF16_MEDIAN_TOLERANCE, f"median row error {np.median(errors):.3e}"
+        assert max(rms) <= BF16_RMS_TOLERANCE, f"largest root-mean-square row error {max(rms):.3e}"
     return worst
 
 
@@ -68,7 +84,7 @@ def test_cuttings_match_plain_implementation(model_case, dtype, tmp_path):
         peak = rc.peak_tokens(steps)
         # the mixed trace reuses pages: there every page that lost its holder is overwritten with a
         # large value before the next step, so stale contents that a kernel let through would show
-        rc.run_inprocess(model_case["folder"], dtype, steps, out, peak,
+        rc.run_inprocess(model_case["folder"], dtype, steps, out, peak, page_size=model_case["page_size"],
                          fill_freed_pages="poison" if name == "mixed" else None)
         rows = rc.collect(steps, out, vocab)
         assert len(rows) == expected_rows
@@ -87,9 +103,10 @@ def test_pages_are_used_again(model_case, tmp_path):
     """The mixed trace needs more pages over its life than the pool has."""
     steps = rc.trace_mixed(model_case["requests"], max_live=4, seed=3)
     peak = rc.peak_tokens(steps)
-    total = sum(-(-len(t) // 16) for t in model_case["requests"].values())
-    assert total * 16 > peak, "the trace would fit without reuse; make it longer"
-    step_function, kv = rc.run_inprocess(model_case["folder"], "float32", steps, tmp_path / "o", peak)
+    page = model_case["page_size"]
+    total = sum(-(-len(t) // page) for t in model_case["requests"].values())
+    assert total * page > peak, "the trace would fit without reuse; make it longer"
+    step_function, kv = rc.run_inprocess(model_case["folder"], "float32", steps, tmp_path / "o", peak, page_size=page)
     assert kv.pools[0].num_free == kv.pools[0].num_usable
 
 

@@ -4,8 +4,11 @@ forbid cudaMalloc inside it, others sit on a path where the allocator's device-w
 synchronisation is not acceptable.  For them the split-KV attention keeps its scratch in an
 array built into the library.  This test calls that entry point through its exported C symbol,
 twice in a row on different inputs (the second call finds the first call's leftovers in the
-shared array), and checks each result against the regular entry point, which takes caller
-scratch; it also checks that a request larger than the built-in array is refused.
+shared array; one pair is ordered so that the second call has more requests and more splits than
+the first and therefore reads rows of the array the first never wrote), and checks each result
+against the regular entry point, which takes caller scratch, and against the plain statement of
+paged attention in tests/plain_kernels.py.  It also checks that a request larger than the built-in
+array is refused, and that a problem one call reports is still on record after a later, clean call.
 
 Collected last on purpose: a run that stops at the first failure has then run everything else.
 """
@@ -80,27 +83,54 @@ def _call_static(lib, qkv, k, v, table, ctx, heads, kv_heads, dim, scale, window
     return code, out
 
 
-def test_static_scratch_entry_point_matches_the_regular_one():
+def test_static_scratch_entry_point_matches_the_regular_one_and_the_plain_statement():
+    import plain_kernels
+
     K, lib = _library()
     shapes = [
-        (11, 32, 8, 128, 16, [(1000, 1), (17, 1), (4095, 1), (0, 1)], 0, 7),
-        (12, 8, 2, 64, 8, [(300, 2), (64, 1), (2000, 3)], 0, 5),     # other sizes: leftovers of call one lie underneath
-        (13, 8, 2, 128, 16, [(900, 1), (70, 1)], 100, 4),             # window
-        (14, 6, 2, 96, 16, [(5, 150), (0, 3)], 0, 1),                 # one split, tile shape: no scratch used
+        (10, 8, 2, 128, 16, [(260, 1), (40, 1)], 0, 2),              # small: few rows of the array written
+        (11, 32, 8, 128, 16, [(700, 1), (17, 1), (1500, 1), (0, 1), (333, 1)], 0, 7),   # more requests, heads and
+                                                                     # splits: reads rows the call before never wrote
+        (12, 8, 2, 64, 8, [(300, 2), (64, 1), (900, 3)], 0, 5),      # other sizes: leftovers of call two lie underneath
+        (13, 8, 2, 128, 16, [(900, 1), (70, 1)], 100, 4),            # window
+        (14, 6, 2, 96, 16, [(5, 150), (0, 3)], 0, 1),                # one split, tile shape: no scratch used
     ]
     for seed, heads, kv_heads, dim, page, lens, window, splits in shapes:
         qkv, k, v, table, ctx = _case(seed, heads, kv_heads, dim, page, lens)
         scale = dim ** -0.5
         want = K.paged_attention(qkv, k, v, table, ctx, heads, kv_heads, dim, scale, window or None,
                                  num_splits=splits, use_tma=False)
+        plain = plain_kernels.paged_attention_plain(qkv.float(), k.float(), v.float(), table, ctx.positions,
+                                                    ctx.req_index, heads, kv_heads, dim, scale, window or None)
         for _ in range(2):  # two calls in a row
             code, got = _call_static(lib, qkv, k, v, table, ctx, heads, kv_heads, dim, scale, window, splits)
             assert code == 0, lib.kvb_last_error().decode()
             torch.cuda.synchronize()
             assert torch.isfinite(got.float()).all()
             torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+            torch.testing.assert_close(got.float(), plain, rtol=2e-2, atol=2e-2)
         status = ctypes.c_int(-1)
         assert lib.kvb_static_status(ctypes.byref(status)) == 0 and status.value == 0
+
+
+def test_a_reported_problem_outlives_the_calls_behind_it():
+    """A page id outside the cache is not read: the kernel skips it and sets a status bit.  The bit is
+    still there after a later call that had nothing to report, and is cleared by reading it."""
+    K, lib = _library()
+    heads, kv_heads, dim, page = 8, 2, 128, 16
+    qkv, k, v, table, ctx = _case(21, heads, kv_heads, dim, page, [(200, 1), (90, 1)])
+    broken = table.clone()
+    broken[0, 3] = k.shape[0] + 5
+    code, _ = _call_static(lib, qkv, k, v, broken, ctx, heads, kv_heads, dim, dim ** -0.5, 0, 3)
+    assert code == 0
+    code, got = _call_static(lib, qkv, k, v, table, ctx, heads, kv_heads, dim, dim ** -0.5, 0, 3)
+    assert code == 0
+    status = ctypes.c_int(-1)
+    assert lib.kvb_static_status(ctypes.byref(status)) == 0 and status.value == 2
+    assert lib.kvb_static_status(ctypes.byref(status)) == 0 and status.value == 0
+    assert torch.isfinite(got.float()).all()
+    code, _ = _call_static(lib, qkv, k, v, table, ctx, heads, kv_heads, dim, dim ** -0.5, 0, 5000)
+    assert code != 0 and "at most 1024 splits" in lib.kvb_last_error().decode()
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
