@@ -228,7 +228,7 @@ def check_logits(runner, shape: dict, layers: int, batch: int = 8) -> dict:
     operations on the weights read back from the model).  Two requests of 333 and 700 tokens go
     through the step function in portions of 256 beside each other, six short ones beside them, then
     three decode steps of the whole batch (run eagerly, captured, replayed); the logits at the end of
-    both prompts and at every decode step must lie within 2e-2 of the request's largest |logit|."""
+    the prompts and at every decode step of three of the requests are compared."""
     import torch
 
     sys.path.insert(0, str(ROOT / "tests"))
@@ -278,23 +278,38 @@ def check_logits(runner, shape: dict, layers: int, batch: int = 8) -> dict:
         raise RuntimeError(f"a kernel reported status {status} during the logits check")
     config = {k: v for k, v in dict(shape, num_hidden_layers=layers).items() if v is not None}
     weights = runner.model.state_dict()
-    worst, checked = 0.0, 0
+    worst = oracle_worst = rms_worst = oracle_rms_worst = 0.0
+    checked = 0
     with torch.no_grad():
         for index in (0, 1, batch - 1):
             rows = sorted(pos for i, pos in got if i == index)
-            want = plain_llama.forward_logits(config, weights, tokens[index][:done[index]], compute=torch.float32,
-                                              rows=rows, device="cuda:0").float().cpu()
-            scale = float(want.abs().max())
+            sequence = tokens[index][:done[index]]
+            exact = plain_llama.forward_logits(config, weights, sequence, compute=torch.float32, rows=rows,
+                                               device="cuda:0").float().cpu()
+            rounded = plain_llama.forward_logits(config, weights, sequence, compute=torch.float32, rows=rows,
+                                                 device="cuda:0", round_to=torch.bfloat16).float().cpu()
+            scale = float(exact.abs().max())
             for row, pos in enumerate(rows):
-                worst = max(worst, float((got[(index, pos)] - want[row]).abs().max()) / scale)
+                mine, theirs = got[(index, pos)] - exact[row], rounded[row] - exact[row]
+                worst = max(worst, float(mine.abs().max()) / scale)
+                oracle_worst = max(oracle_worst, float(theirs.abs().max()) / scale)
+                rms_worst = max(rms_worst, float(mine.pow(2).mean().sqrt()) / scale)
+                oracle_rms_worst = max(oracle_rms_worst, float(theirs.pow(2).mean().sqrt()) / scale)
                 checked += 1
     del weights
     torch.cuda.empty_cache()
-    tolerance = 2e-2
-    if not worst <= tolerance:
-        raise RuntimeError(f"logits of the benchmark model differ from the plain implementation: "
-                           f"{worst:.3e} of the largest logit (allowed {tolerance})")
-    return {"logits_checked": True, "logits_max_err": round(worst, 5), "logits_tolerance": tolerance,
+    # What bfloat16 costs grows with depth (random weights: 1.4e-2 of the largest logit at 2 layers,
+    # 6e-2 at 32), so the yardstick is the plain implementation itself evaluated with bfloat16
+    # roundings in the reference's places: the engine may stray from 32-bit at most 1.5 times as far as
+    # that evaluation does in its worst entry, and 1.3 times in the worst row's root mean square
+    # (measured: 0.98 to 1.09, and 1.00 to 1.06, at 2 to 32 layers).
+    if not (worst <= 1.5 * oracle_worst and rms_worst <= 1.3 * oracle_rms_worst):
+        raise RuntimeError(
+            f"logits of the benchmark model stray from the plain implementation: worst entry {worst:.3e} of the "
+            f"largest logit (a faithful bfloat16 evaluation: {oracle_worst:.3e}), worst row rms {rms_worst:.3e} "
+            f"(faithful: {oracle_rms_worst:.3e})")
+    return {"logits_checked": True, "logits_max_err": round(worst, 5), "logits_max_err_faithful_bf16": round(oracle_worst, 5),
+            "logits_rms_err": round(rms_worst, 5), "logits_rms_err_faithful_bf16": round(oracle_rms_worst, 5),
             "logits_rows_checked": checked}
 
 

@@ -1,40 +1,39 @@
 // Paged flash attention for prompt portions on the 5th-generation tensor cores (sm_100a):
 // tcgen05.mma with accumulators in tensor memory, operands staged by TMA.  bf16, head size 128.
 //
-// A block owns 128 query rows of one (request, kv head); a row is a (token, query head of the
-// group) pair, so the G heads that share a kv head reuse every K/V tile.  It walks the keys in
-// tiles of 128.  Eleven warps:
-//   warps 0-7  softmax, two warpgroups: threads t and t+128 share row t = TMEM lane t and take
-//              columns [0,64) and [64,128) of it, each for itself: a thread keeps the running max
-//              and sum (32-bit) of its own columns and has an accumulator of its own,
-//              O_h = sum over tiles of P_h(j).V_h(j) (its half of the probabilities times the 64
-//              keys that go with it); the two meet once, at the end, and the row's output is
-//              O_A and O_B put on a common maximum and divided by the common sum.  So the two
-//              warps of a scheduler are not in step, and one's waits on tensor memory are the
-//              other's working time.  Per tile a thread reads its half row of S = Q.K^T from TMEM
-//              (tcgen05.ld), masks, writes P = exp2(...) as packed bf16 over the columns it read
-//              (tcgen05.st: the A operand of the second product is read from tensor memory, so P
-//              never touches shared memory), and rescales its row of O_h when its max moved.
-//              (The softmax is the bottleneck: ~2,300 cycles of exp2 and conversions per tile
-//              against ~1,200 cycles of MMA.)
+// A block owns TWO tiles of 128 query rows of one (request, kv head), A and B, one behind the other;
+// a row is a (token, query head of the group) pair, so the G heads that share a kv head reuse every
+// K/V tile, and every K/V tile that TMA brings is used by both query tiles.  The block walks the
+// keys in tiles of 128.  Eleven warps:
+//   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B: thread t of a warpgroup owns row t
+//              of its tile (= TMEM lane t) and the whole of it, so nothing is exchanged between
+//              threads.  Per key tile it reads its row of S = Q.K^T from tensor memory (tcgen05.ld,
+//              128 columns), masks where the tile needs it, keeps a running maximum and sum in 32-bit,
+//              writes P = exp2(...) as packed bf16 over the columns it read S from (tcgen05.st: the
+//              A operand of the second product is read from tensor memory, so P never touches shared
+//              memory), and rescales its row of O when its maximum moved by more than 2^8.
+//              The two warps of a scheduler belong to different query tiles: while one waits for
+//              tensor memory or for the tensor pipe, the other works.
 //   warps 8, 9 producers of K and of V (separate, so that a wait for a V stage never holds back
 //              the next K tile): each looks pages up in the block table (batched, a batch ahead)
 //              and issues the tiled TMA copies (two 64-column boxes per page, 128-byte swizzle)
 //              into its two-stage ring.
-//   warp 10    one thread issues the MMAs: S(0) and S(1) at once; then per tile O_A += P_A(j).V_A(j)
-//              and O_B += P_B(j).V_B(j) as the halves of P arrive (P from tensor memory, V from
-//              shared memory as an MN-major operand), and S(j+2) = Q.K(j+2)^T behind them into the
-//              buffer that held S(j) and P(j): the tensor pipe takes its instructions in order.
-// mbarriers, indexed by tile parity so that no waiter can fall two phases behind:
-// k_full/k_empty, v_full/v_empty (TMA <-> MMA), s_full (MMA -> softmax, two S buffers), p_ready
-// (softmax -> MMA, per half and buffer), pv_done (MMA -> softmax), x_ready (the partners' one
-// exchange).  tcgen05.commit arrives on the barriers that follow MMAs.  Every wait is bounded: on a
-// time-out the thread sets the WAIT_TIMEOUT status bit and the block drains and frees its tensor
-// memory before it returns.
+//   warp 10    one thread issues the MMAs, alternating between the tiles so that the products of one
+//              run under the softmax of the other:
+//                S_A(0), S_B(0); then per key tile j:  O_A += P_A(j).V(j), S_A(j+1) = Q_A.K(j+1)^T,
+//                O_B += P_B(j).V(j), S_B(j+1) = Q_B.K(j+1)^T
+//              (P from tensor memory, V from shared memory as an MN-major operand).  S_X(j+1) goes
+//              into the columns that held S_X(j) and P_X(j): the tensor pipe takes its instructions
+//              in order, so it has read P_X(j) by then.
+// mbarriers: k_full/k_empty, v_full/v_empty (TMA <-> MMA, two stages each), and per query tile
+// s_full (MMA -> softmax), p_ready (softmax -> MMA), pv_done (MMA -> softmax, the last product).
+// tcgen05.commit arrives on the barriers that follow MMAs.  Every wait is bounded: on a time-out the
+// thread sets the WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it
+// returns.
 //
-// Tensor memory: 512 columns = S0 [0,128) | S1 [128,256) | O_A [256,384) | O_B [384,512); P(j) lies
-// over S(j): half h as 32 columns of two bf16 each at column 64 h of the buffer.
-// Shared memory: Q 32 KB | K 2x32 KB | V 2x32 KB (all 1024-byte aligned, 128B swizzle).
+// Tensor memory: 512 columns = S_A [0,128) | S_B [128,256) | O_A [256,384) | O_B [384,512); P_X lies
+// over the first 64 columns of S_X (two bf16 a column).
+// Shared memory: Q_A, Q_B 32 KB each | K 2x32 KB | V 2x32 KB (all 1024-byte aligned, 128B swizzle).
 #include <cuda.h>
 #include <string.h>
 
@@ -71,43 +70,46 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   KVB_KERNEL_PROLOGUE(KVB_TAG_PREFILL_TC5);
   extern __shared__ __align__(1024) unsigned char t5_dyn[];
   unsigned char* base = t5_dyn;   // the swizzled tiles need 1024-byte alignment (checked below)
-  unsigned char* q_smem = base;
-  unsigned char* k_smem = q_smem + T5_TILE_BYTES;           // 2 stages
+  unsigned char* q_smem = base;                              // tile A, tile B
+  unsigned char* k_smem = q_smem + 2 * T5_TILE_BYTES;       // 2 stages
   unsigned char* v_smem = k_smem + 2 * T5_TILE_BYTES;       // 2 stages
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_smem + 2 * T5_TILE_BYTES);
-  unsigned long long* k_full = bars;        // [2]
+  unsigned long long* k_full = bars;        // [2 stages]
   unsigned long long* k_empty = bars + 2;   // [2]
   unsigned long long* v_full = bars + 4;    // [2]
   unsigned long long* v_empty = bars + 6;   // [2]
-  unsigned long long* s_full = bars + 8;    // [2]
-  unsigned long long* p_ready = bars + 10;  // [2 halves][2]: half h of P(j) is in tensor memory
-  unsigned long long* pv_done = bars + 14;  // [2]
-  unsigned long long* x_ready = bars + 16;  // [1]: the partners' final exchange
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 18);
+  unsigned long long* s_full = bars + 8;    // [2 query tiles]
+  unsigned long long* p_ready = bars + 10;  // [2 query tiles]
+  unsigned long long* pv_done = bars + 12;  // [2 query tiles]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  float* x_buf = reinterpret_cast<float*>(bars + 20);   // [2 parities][2 halves][128 rows]
 
   // later query tiles see more keys: hand them out first so the long blocks do not form the tail
-  const int req = blockIdx.z, kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  const int req = blockIdx.z, kvh = blockIdx.y, pair = gridDim.x - 1 - blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_begin = p.query_start[req];
   const int q_len = p.query_start[req + 1] - q_begin;
   const int context = p.context_lens[req];
   const int rows_total = q_len * p.G;
-  const int row0 = tile * T5_BM;
+  const int row0 = pair * 2 * T5_BM;
   if (row0 >= rows_total) return;  // whole block, before any barrier or allocation
   if (kvb_smem(base) & 1023u) {     // cannot happen with the alignment asked for; never run misaligned
     if (threadIdx.x == 0) atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
     return;
   }
 
-  const int last_row = min(row0 + T5_BM, rows_total) - 1;
-  const int first_pos = context + row0 / p.G;
-  const int last_pos = context + last_row / p.G;
-  const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-  const int key_hi = last_pos + 1;
+  // keys of the two tiles: tile X sees [lo_X, hi_X); both walk the key tiles from tile_begin (the
+  // first tile of A, whose rows come first), tile X through n_X of them
+  const bool has_b = row0 + T5_BM < rows_total;
+  const int last_row_a = min(row0 + T5_BM, rows_total) - 1;
+  const int last_row_b = min(row0 + 2 * T5_BM, rows_total) - 1;
+  const int first_pos_a = context + row0 / p.G;
+  const int key_lo = p.window > 0 ? max(0, first_pos_a - p.window + 1) : 0;
   const int tile_begin = key_lo / T5_BN;
-  const int num_tiles = (key_hi + T5_BN - 1) / T5_BN - tile_begin;   // >= 1
+  const int n_a = (context + last_row_a / p.G + T5_BN) / T5_BN - tile_begin;             // >= 1
+  const int n_b = has_b ? (context + last_row_b / p.G + T5_BN) / T5_BN - tile_begin : 0; // >= n_a when tile B exists
+  const int num_tiles = max(n_a, n_b);
+  const int key_hi = context + (has_b ? last_row_b : last_row_a) / p.G + 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -117,9 +119,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       kvb_mbar_init(&v_empty[i], 1);
       kvb_mbar_init(&s_full[i], 1);
       kvb_mbar_init(&p_ready[i], 128);
-      kvb_mbar_init(&p_ready[2 + i], 128);
       kvb_mbar_init(&pv_done[i], 1);
-      kvb_mbar_init(&x_ready[i], 256);
     }
     *abort_flag = 0;
     kvb_mbar_init_fence();
@@ -127,18 +127,19 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   if (warp == 10) {  // tensor memory: 512 columns for this block
     kvb_tc5_alloc(tmem_slot, 512u);
   }
-  // Q rows -> shared memory in the swizzled K-major operand layout (thread t of warps 0-3: row t)
-  if (warp < 4) {
-    const int r = threadIdx.x;
-    const int flat = row0 + r;
+  // Q rows -> shared memory in the swizzled K-major operand layout (thread t of warpgroup X: row t of tile X)
+  if (warp < 8) {
+    const int r = threadIdx.x & 127, x = threadIdx.x >> 7;
+    const int flat = row0 + x * T5_BM + r;
     const bool valid = flat < rows_total;
     const bf16* src = p.q + (size_t)(q_begin + (valid ? flat / p.G : 0)) * p.q_stride +
                       (size_t)(kvh * p.G + (valid ? flat % p.G : 0)) * T5_D;
+    unsigned char* dst = q_smem + x * T5_TILE_BYTES;
 #pragma unroll
     for (int c = 0; c < 16; ++c) {
       uint4 v = make_uint4(0, 0, 0, 0);
       if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-      *reinterpret_cast<uint4*>(q_smem + t5_chunk_off(r, c)) = v;
+      *reinterpret_cast<uint4*>(dst + t5_chunk_off(r, c)) = v;
     }
     kvb_fence_async_shared();  // generic writes -> visible to the MMA's reads
   }
@@ -146,7 +147,6 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   __syncthreads();
   kvb_tc5_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_o = tmem_base + 256;   // two accumulators of 128 columns: one per half of the keys of a tile
 
   if (warp == 8 || warp == 9) {
     // ================= producers: warp 8 streams K tiles, warp 9 streams V tiles =================
@@ -210,51 +210,54 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       // instruction descriptors: f32 accumulate, bf16 x bf16, M = 128, N = 128
       const unsigned idesc_s = kvb_tc5_idesc(T5_BM, T5_BN, false);   // A, B both K-major
       const unsigned idesc_pv = kvb_tc5_idesc(T5_BM, T5_BN, true);   // B (= V) MN-major
-      const unsigned q_addr = kvb_smem(q_smem);
       bool ok = true;
-      auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
+      auto issue_s = [&](int x, int j) {   // S_x(j) = Q_x . K(j)^T
+        const unsigned q_addr = kvb_smem(q_smem + x * T5_TILE_BYTES);
         const unsigned k_addr = kvb_smem(k_smem + (j & 1) * T5_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < T5_D / 16; ++kk) {
           const unsigned off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;
-          kvb_tc5_mma(tmem_base + (j & 1) * T5_BN, kvb_tc5_desc(q_addr + off, 16, 1024), kvb_tc5_desc(k_addr + off, 16, 1024),
-                 idesc_s, kk > 0);
+          kvb_tc5_mma(tmem_base + x * T5_BN, kvb_tc5_desc(q_addr + off, 16, 1024), kvb_tc5_desc(k_addr + off, 16, 1024),
+                      idesc_s, kk > 0);
         }
-        kvb_tc5_commit(&s_full[j & 1]);
-        kvb_tc5_commit(&k_empty[j & 1]);
+        kvb_tc5_commit(&s_full[x]);
       };
-      // S(0) and S(1) at once; then, tile by tile, the two halves of O += P(j).V(j) as their halves of
-      // P arrive, and S(j+2) behind them into the buffer that held S(j) and P(j) (the tensor pipe
-      // takes its instructions in order, so it has read P(j) by then)
-      for (int n = 0; n < 2 && n < num_tiles && ok; ++n) {
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[n], 0)) { ok = false; break; }
+      auto issue_pv = [&](int x, int j) {  // O_x += P_x(j) . V(j): 16 keys per MMA (8 columns of P, 16 key rows of V)
+        const unsigned v_addr = kvb_smem(v_smem + (j & 1) * T5_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < T5_BN / 16; ++kk)
+          kvb_tc5_mma_ts(tmem_base + 256 + x * T5_D, tmem_base + x * T5_BN + kk * 8,
+                         kvb_tc5_desc(v_addr + kk * 16 * 128, T5_HALF_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        kvb_tc5_commit(&pv_done[x]);
+      };
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[0], 0)) ok = false;
+      if (ok) {
         kvb_tc5_fence_after();
-        issue_s(n);
+        issue_s(0, 0);
+        if (has_b) issue_s(1, 0);
+        kvb_tc5_commit(&k_empty[0]);
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
-        const int b = j & 1;
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[b], (j >> 1) & 1)) { ok = false; break; }
-        const unsigned v_addr = kvb_smem(v_smem + b * T5_TILE_BYTES);
-        const unsigned p_tmem = tmem_base + b * T5_BN;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[2 * half + b], (j >> 1) & 1)) { ok = false; break; }
+        const int st = j & 1, par = (j >> 1) & 1;
+        const bool more = j + 1 < num_tiles;
+        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[st], par)) { ok = false; break; }
+        if (j < n_a) {
+          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[0], j & 1)) { ok = false; break; }
           kvb_tc5_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < T5_BN / 32; ++kk) {   // 16 keys per MMA: 8 columns of P, 16 key rows of V
-            const unsigned b_off = (half * 4 + kk) * 16 * 128;
-            kvb_tc5_mma_ts(tmem_o + half * T5_D, p_tmem + half * 64 + kk * 8,
-                           kvb_tc5_desc(v_addr + b_off, T5_HALF_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-          }
+          issue_pv(0, j);
         }
-        if (!ok) break;
-        kvb_tc5_commit(&pv_done[b]);
-        kvb_tc5_commit(&v_empty[b]);
-        const int n = j + 2;
-        if (n < num_tiles) {
-          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[b], (n >> 1) & 1)) { ok = false; break; }
+        if (more && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[st ^ 1], ((j + 1) >> 1) & 1)) { ok = false; break; }
+        if (more) kvb_tc5_fence_after();
+        if (j + 1 < n_a) issue_s(0, j + 1);
+        if (j < n_b) {
+          if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[1], j & 1)) { ok = false; break; }
           kvb_tc5_fence_after();
-          issue_s(n);
+          issue_pv(1, j);
+        }
+        kvb_tc5_commit(&v_empty[st]);
+        if (more) {
+          if (j + 1 < n_b) issue_s(1, j + 1);
+          kvb_tc5_commit(&k_empty[st ^ 1]);
         }
       }
       if (!ok) {
@@ -263,44 +266,41 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       }
     }
   } else {
-    // ================= softmax: threads t and t+128 own row t, 64 columns each =================
-    // The two partners of a row do not talk to each other until the end: each keeps a running maximum
-    // and sum of its own 64 columns of every tile and its own accumulator O_h = sum over tiles of
-    // P_h(j).V_h(j) (P_h: its half of the probabilities, V_h: the 64 keys that go with it), so the two
-    // warps of a scheduler drift apart and one's waits (tensor-memory loads and stores) are the other's
-    // working time.  The half row of S is read from TMEM once and kept in registers: pass 1 finds
-    // its maximum, pass 2 forms P = 2^(s*scale - m), sums it and writes it as bf16 over the columns it
-    // read S from.  Masks are applied only on tiles that need them (the diagonal, a window, rows beyond
-    // the batch).  The running maximum m is moved (and O_h rescaled) only when some row of the warp
-    // would grow by more than 2^8: until then P may exceed 1, which bf16 and the 32-bit sums hold
-    // easily, and O_h and the row sum stay consistent because both are taken against the same m.
+    // ================= softmax: thread t of warpgroup X owns row t of query tile X =================
+    // The row of S is read from TMEM once and kept in registers: pass 1 finds its maximum, pass 2 forms
+    // P = 2^(s*scale - m), sums it and writes it as bf16 over the columns S was read from.  Masks are
+    // applied only on tiles that need them (the diagonal, a window, rows beyond the batch).  The running
+    // maximum m is moved (and O rescaled) only when some row of the warp would grow by more than 2^8:
+    // until then P may exceed 1, which bf16 and the 32-bit sums hold easily, and O and the row sum stay
+    // consistent because both are taken against the same m.
     const int r = threadIdx.x & 127;
-    const int half = threadIdx.x >> 7;                    // which 64 columns of the row
-    const int flat = row0 + r;
+    const int x = threadIdx.x >> 7;                       // which query tile
+    const int n_mine = x == 0 ? n_a : n_b;
+    const int flat = row0 + x * T5_BM + r;
     const bool row_valid = flat < rows_total;
     const int pos = context + (row_valid ? flat / p.G : 0);
     const int row_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first_pos = context + (row0 + x * T5_BM) / p.G;   // position of the tile's first row
     const unsigned lane_addr = ((unsigned)((warp & 3) * 32) << 16);
-    const bool ragged = row0 + T5_BM > rows_total;        // block holds rows beyond the batch
-    const unsigned my_o = tmem_o + lane_addr + half * T5_D;
+    const bool ragged = row0 + (x + 1) * T5_BM > rows_total;     // the tile holds rows beyond the batch
+    const unsigned s_addr = tmem_base + lane_addr + x * T5_BN;
+    const unsigned o_addr = tmem_base + lane_addr + 256 + x * T5_D;
     float row_max = -INFINITY, row_sum = 0.0f;            // row_max in the scaled (log2) domain
     bool ok = true;
-    for (int j = 0; j < num_tiles; ++j) {
-      const int b = j & 1;
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&s_full[b], (j >> 1) & 1)) { ok = false; break; }
+    for (int j = 0; j < n_mine; ++j) {
+      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&s_full[x], j & 1)) { ok = false; break; }
       kvb_tc5_fence_after();
-      const int key0 = (tile_begin + j) * T5_BN + half * 64;
-      const bool need_mask = ragged || p.window > 0 || (tile_begin + j) * T5_BN + T5_BN - 1 > first_pos;
-      const unsigned s_addr = tmem_base + lane_addr + b * T5_BN + half * 64;
-      float s[2][32];
-      kvb_tc5_ld32(s_addr, s[0]);
-      kvb_tc5_ld32(s_addr + 32, s[1]);
+      const int key0 = (tile_begin + j) * T5_BN;
+      const bool need_mask = ragged || p.window > 0 || key0 + T5_BN - 1 > first_pos;
+      float s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kvb_tc5_ld32(s_addr + c * 32, s[c]);
       kvb_tc5_wait_ld();
-      // ---- pass 1: maximum of the raw scores of this half row ----
+      // ---- pass 1: maximum of the raw scores of the row ----
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
@@ -310,7 +310,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
         }
@@ -325,11 +325,11 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         row_max = new_max;
       }
       const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
-      // ---- pass 2: P = 2^(s*scale - m), partial row sum, packed bf16 into tensor memory ----
+      // ---- pass 2: P = 2^(s*scale - m), row sum, packed bf16 into tensor memory, 32 keys at a time ----
       float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      float packed[32];                              // 64 keys of this half row, two bf16 a register
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
+        float packed[16];                            // 32 keys, two bf16 a register
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float e0, e1;
@@ -340,73 +340,51 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           // Two bf16 in a register, the lower key in the lower half.  Rounded by adding half a step
           // and cutting (integer pipe: the conversion instruction shares the exp2 unit, which is
           // the busiest unit of this kernel); P >= 0 and finite, so this is round-half-up.
-          packed[c * 16 + i / 2] = __uint_as_float(
+          packed[i / 2] = __uint_as_float(
               __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632));
         }
+        // P(j) lies over the first half of the columns S(j) was read from; S(j+1) is written there only
+        // after the tensor pipe has taken P(j)
+        kvb_tc5_st16(s_addr + c * 16, packed);
       }
-      // P(j) lies over the first half of the columns this thread read S(j) from; S(j+2) is written there
-      // only after the tensor pipe has taken P(j)
-      kvb_tc5_st32(s_addr, packed);
       row_sum = row_sum * correction + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
-      if (move && j > 0) {       // rescale this thread's row of its accumulator: PV(j-1) must have landed first
-        if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { ok = false; break; }
-        kvb_tc5_fence_after();
+      if (move && j > 0) {
+        // rescale this thread's row of O.  The product P(j-1).V(j-1) has landed: it was issued before
+        // S(j), whose arrival this thread has seen, and the tensor pipe finishes in order.
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           float o[32];
-          kvb_tc5_ld32(my_o + c * 32, o);
+          kvb_tc5_ld32(o_addr + c * 32, o);
           kvb_tc5_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= correction;
-          kvb_tc5_st32(my_o + c * 32, o);
+          kvb_tc5_st32(o_addr + c * 32, o);
         }
       }
       kvb_tc5_wait_st();
       kvb_tc5_fence_before();
-      kvb_mbar_arrive(&p_ready[2 * half + b]);
+      kvb_mbar_arrive(&p_ready[x]);
     }
-    if (ok && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) ok = false;
-    float scale_a = 0.0f, scale_b = 0.0f;   // what O_A and O_B of this row are multiplied by
-    if (ok) {
-      // the partners meet once: maxima and sums of the two halves of the row
-      x_buf[half * 128 + r] = row_max;
-      x_buf[256 + half * 128 + r] = row_sum;
-      kvb_mbar_arrive(&x_ready[0]);
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&x_ready[0], 0)) ok = false;
-      if (ok) {
-        const float other_max = x_buf[(half ^ 1) * 128 + r], other_sum = x_buf[256 + (half ^ 1) * 128 + r];
-        const float m = fmaxf(row_max, other_max);
-        const float mine = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - m);
-        const float theirs = (other_max == -INFINITY) ? 0.0f : exp2f(other_max - m);
-        const float total = row_sum * mine + other_sum * theirs;
-        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-        scale_a = (half == 0 ? mine : theirs) * inv;
-        scale_b = (half == 0 ? theirs : mine) * inv;
-      }
-    }
-    if (ok) {
+    if (ok && n_mine > 0 && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[x], (n_mine - 1) & 1)) ok = false;
+    if (ok && n_mine > 0) {
       kvb_tc5_fence_after();
+      const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
       bf16* dst = nullptr;
       if (row_valid)
-        dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D +
-              half * 64;
+        dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {   // this thread stores columns [64 half, +64) of the row: both accumulators' share
-        float oa[32], ob[32];
-        kvb_tc5_ld32(tmem_o + lane_addr + half * 64 + c * 32, oa);
-        kvb_tc5_ld32(tmem_o + lane_addr + T5_D + half * 64 + c * 32, ob);
+      for (int c = 0; c < 4; ++c) {
+        float o[32];
+        kvb_tc5_ld32(o_addr + c * 32, o);
         kvb_tc5_wait_ld();
         if (row_valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = oa[i + e] * scale_a + ob[i + e] * scale_b;
             uint4 packed;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[0], v[1]);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[2], v[3]);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[4], v[5]);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[6], v[7]);
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
             packed.x = *reinterpret_cast<unsigned*>(&t0);
             packed.y = *reinterpret_cast<unsigned*>(&t1);
             packed.z = *reinterpret_cast<unsigned*>(&t2);
@@ -415,7 +393,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
           }
         }
       }
-    } else {
+    } else if (!ok) {
       atomicOr(p.status, KVB_STATUS_WAIT_TIMEOUT);
       atomicExch(abort_flag, 1);
     }
@@ -481,14 +459,14 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   alignas(64) CUtensorMap k_map, v_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
-  constexpr size_t SMEM = 5 * T5_TILE_BYTES + 20 * 8 + 2 * 2 * 128 * sizeof(float);
+  constexpr size_t SMEM = 6 * T5_TILE_BYTES + 16 * 8;
   static bool configured = false;
   if (!configured) {
     KVB_CHECK_CUDA(cudaFuncSetAttribute(flash_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     configured = true;
   }
   const int max_rows = max_query_len * p.G;
-  dim3 grid((max_rows + T5_BM - 1) / T5_BM, KVH, num_reqs);
+  dim3 grid((max_rows + 2 * T5_BM - 1) / (2 * T5_BM), KVH, num_reqs);   // a block takes two query tiles
   KVB_CHECK_CUDA(kvb_launch((flash_prefill_tc5_kernel), dim3(grid), dim3(T5_THREADS), SMEM, stream, true, k_map, v_map, p));
   KVB_CHECK_LAUNCH();
   return 0;
