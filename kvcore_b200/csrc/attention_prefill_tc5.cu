@@ -25,7 +25,10 @@
 //              (P from tensor memory, V from shared memory as an MN-major operand).  S_X(j+1) goes
 //              into the columns that held S_X(j) and P_X(j): the tensor pipe takes its instructions
 //              in order, so it has read P_X(j) by then.
-// mbarriers: k_full/k_empty, v_full/v_empty (TMA <-> MMA, two stages each), and per query tile
+// The query tiles come by TMA too when the group size divides 128 (a 4-D map over [token, kv head,
+// head of the group, 64 columns] lands the rows of a tile in (token, head) order); otherwise the softmax
+// threads copy their rows.
+// mbarriers: q_full, k_full/k_empty, v_full/v_empty (TMA <-> MMA, two stages each), and per query tile
 // s_full (MMA -> softmax), p_ready (softmax -> MMA), pv_done (MMA -> softmax, the last product).
 // tcgen05.commit arrives on the barriers that follow MMAs.  Every wait is bounded: on a time-out the
 // thread sets the WAIT_TIMEOUT status bit and the block drains and frees its tensor memory before it
@@ -56,6 +59,7 @@ struct Tc5Params {
   int num_reqs, H, KVH, G, page_size, num_pages, window;
   float scale_log2;
   int* status;
+  int q_by_tma;                // the query tiles are brought by TMA (q_map is valid)
 };
 
 // Byte offset of the 16-byte chunk `chunk16` (0..15 across the 128 columns) of row `r` in a
@@ -64,9 +68,35 @@ __device__ __forceinline__ unsigned t5_chunk_off(int r, int chunk16) {
   return (unsigned)((chunk16 >> 3) * T5_HALF_BYTES + r * 128 + (((chunk16 & 7) ^ (r & 7)) << 4));
 }
 
+// max(a, b, c) in one instruction.
+__device__ __forceinline__ float t5_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (d0, d1) = (a0, a1) * b + c: one packed instruction for two elements.
+__device__ __forceinline__ void t5_fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{.reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %4};\n mov.b64 rc, {%5, %5};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;}\n"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (s0, s1) += (a0, a1), packed.
+__device__ __forceinline__ void t5_add2(float& s0, float& s1, float a0, float a1) {
+  asm("{.reg .b64 ra, rb, rd;\n mov.b64 ra, {%0, %1};\n mov.b64 rb, {%2, %3};\n add.rn.f32x2 rd, ra, rb;\n"
+      " mov.b64 {%0, %1}, rd;}\n"
+      : "+f"(s0), "+f"(s1) : "f"(a0), "f"(a1));
+}
+
+// P is cut to bf16, not rounded, and to make up for it every exponent gets log2(1 + 2^-9) added: the
+// cut value is then off by at most half a bf16 step either way, as a rounded one would be, and it takes
+// one byte permutation for two values instead of two additions and a permutation.  The row sum is taken
+// of the same (raised) values, so the output is divided by sum / (1 + 2^-9).
+#define T5_ROUND_SHIFT 0.0028150156f          // log2(1 + 2^-9)
+#define T5_ROUND_FACTOR 1.001953125f          // 1 + 2^-9
+
 __global__ void __launch_bounds__(T5_THREADS, 1)
 flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                         const Tc5Params p) {
+                         const __grid_constant__ CUtensorMap q_map, const Tc5Params p) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_PREFILL_TC5);
   extern __shared__ __align__(1024) unsigned char t5_dyn[];
   unsigned char* base = t5_dyn;   // the swizzled tiles need 1024-byte alignment (checked below)
@@ -81,11 +111,13 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   unsigned long long* s_full = bars + 8;    // [2 query tiles]
   unsigned long long* p_ready = bars + 10;  // [2 query tiles]
   unsigned long long* pv_done = bars + 12;  // [2 query tiles]
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+  unsigned long long* q_full = bars + 14;   // [1]: the query tiles have landed (TMA)
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
-  // later query tiles see more keys: hand them out first so the long blocks do not form the tail
-  const int req = blockIdx.z, kvh = blockIdx.y, pair = gridDim.x - 1 - blockIdx.x;
+  // Later query tiles see more keys: they are handed out first, for all kv heads and requests (the
+  // pair index is the slowest of the grid), so that the long blocks do not form the tail.
+  const int req = blockIdx.y, kvh = blockIdx.x, pair = gridDim.z - 1 - blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_begin = p.query_start[req];
   const int q_len = p.query_start[req + 1] - q_begin;
@@ -111,24 +143,21 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const int num_tiles = max(n_a, n_b);
   const int key_hi = context + (has_b ? last_row_b : last_row_a) / p.G + 1;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      kvb_mbar_init(&k_full[i], 1);
-      kvb_mbar_init(&k_empty[i], 1);
-      kvb_mbar_init(&v_full[i], 1);
-      kvb_mbar_init(&v_empty[i], 1);
-      kvb_mbar_init(&s_full[i], 1);
-      kvb_mbar_init(&p_ready[i], 128);
-      kvb_mbar_init(&pv_done[i], 1);
-    }
-    *abort_flag = 0;
+  // the fifteen barriers, one thread each (p_ready counts the 128 threads of a softmax warpgroup)
+  if (threadIdx.x < 15) {
+    kvb_mbar_init(&bars[threadIdx.x], (threadIdx.x == 10 || threadIdx.x == 11) ? 128u : 1u);
+    if (threadIdx.x == 0) *abort_flag = 0;
     kvb_mbar_init_fence();
+  }
+  if (warp == 8 && lane < 3) {   // the tensor maps are fetched while the block sets up
+    const CUtensorMap* which = lane == 0 ? &k_map : lane == 1 ? &v_map : &q_map;
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<unsigned long long>(which)) : "memory");
   }
   if (warp == 10) {  // tensor memory: 512 columns for this block
     kvb_tc5_alloc(tmem_slot, 512u);
   }
   // Q rows -> shared memory in the swizzled K-major operand layout (thread t of warpgroup X: row t of tile X)
-  if (warp < 8) {
+  if (warp < 8 && !p.q_by_tma) {
     const int r = threadIdx.x & 127, x = threadIdx.x >> 7;
     const int flat = row0 + x * T5_BM + r;
     const bool valid = flat < rows_total;
@@ -143,6 +172,28 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
     kvb_fence_async_shared();  // generic writes -> visible to the MMA's reads
   }
+  // the producers look their first pages up before the block meets, so that the first copies leave
+  // right behind the barrier
+  const int* pages = p.table + (size_t)req * p.table_stride;
+  const int ppt = T5_BN / p.page_size;          // pages per tile: 2..16
+  const int first_entry = tile_begin * ppt;
+  const int total_entries = num_tiles * ppt;
+  auto fetch = [&](int entry) -> int {
+    if (entry >= total_entries) return 0;
+    const int index = first_entry + entry;
+    if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
+    const int page = pages[index];
+    if (page < 0 || page >= p.num_pages) {
+      atomicOr(p.status, KVB_STATUS_BAD_PAGE);
+      return 0;
+    }
+    return page;
+  };
+  int cur = 0, nxt = 0;
+  if (warp == 8 || warp == 9) {
+    cur = fetch(lane);
+    nxt = fetch(32 + lane);
+  }
   kvb_tc5_fence_before();
   __syncthreads();
   kvb_tc5_fence_after();
@@ -155,22 +206,17 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     unsigned char* ring = is_k ? k_smem : v_smem;
     unsigned long long* full = is_k ? k_full : v_full;
     unsigned long long* empty = is_k ? k_empty : v_empty;
-    const int* pages = p.table + (size_t)req * p.table_stride;
-    const int ppt = T5_BN / p.page_size;          // pages per tile: 2..16
-    const int first_entry = tile_begin * ppt;
-    const int total_entries = num_tiles * ppt;
-    auto fetch = [&](int entry) -> int {
-      if (entry >= total_entries) return 0;
-      const int index = first_entry + entry;
-      if (index >= p.table_stride || index * p.page_size >= key_hi) return 0;
-      const int page = pages[index];
-      if (page < 0 || page >= p.num_pages) {
-        atomicOr(p.status, KVB_STATUS_BAD_PAGE);
-        return 0;
+    if (is_k && lane == 0 && p.q_by_tma) {
+      // the query tiles: rows in (token, head of the group) order, 128 / G tokens a tile, as two boxes
+      // of 64 columns each; tokens beyond the batch arrive as zeros
+      const int tokens_per_tile = T5_BM / p.G;
+      const int token0 = q_begin + row0 / p.G;
+      kvb_mbar_expect_tx(q_full, (has_b ? 2u : 1u) * T5_TILE_BYTES);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x) {
+        kvb_tma_4d(q_smem + x * T5_TILE_BYTES, &q_map, 0, 0, kvh, token0 + x * tokens_per_tile, q_full);
+        kvb_tma_4d(q_smem + x * T5_TILE_BYTES + T5_HALF_BYTES, &q_map, 64, 0, kvh, token0 + x * tokens_per_tile, q_full);
       }
-      return page;
-    };
-    int cur = fetch(lane), nxt = fetch(32 + lane);
+    }
     int issued = 0;
     for (int j = 0; j < num_tiles; ++j) {
       const int s = j & 1;
@@ -203,6 +249,7 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     if (lane == 0 && *reinterpret_cast<volatile int*>(abort_flag)) {
       // let the copies that were issued land before the block may exit
       for (int j = max(0, issued - 2); j < issued; ++j) kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&full[j & 1], (j >> 1) & 1);
+      if (is_k && p.q_by_tma) kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(q_full, 0);
     }
   } else if (warp == 10) {
     // ================= MMA issuer =================
@@ -230,7 +277,8 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
                          kvb_tc5_desc(v_addr + kk * 16 * 128, T5_HALF_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         kvb_tc5_commit(&pv_done[x]);
       };
-      if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[0], 0)) ok = false;
+      if (p.q_by_tma && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(q_full, 0)) ok = false;
+      if (ok && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[0], 0)) ok = false;
       if (ok) {
         kvb_tc5_fence_after();
         issue_s(0, 0);
@@ -299,20 +347,30 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       // ---- pass 1: maximum of the raw scores of the row ----
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
+        // keys of this tile the row sees: indices [lo, hi] within the tile (none if the row is beyond the batch)
+        const int hi = row_valid ? pos - key0 : -1;
+        const int lo = row_lo - key0;
+        if (p.window > 0) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            if (!(row_valid && key <= pos && key >= row_lo)) s[c][i] = -INFINITY;
-            mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > hi || c * 32 + i < lo) s[c][i] = -INFINITY;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > hi) s[c][i] = -INFINITY;
           }
         }
-      } else {
+      }
+      {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], s[c][i]);
+          for (int i = 0; i < 32; i += 2) mx[(i >> 1) & 3] = t5_max3(mx[(i >> 1) & 3], s[c][i], s[c][i + 1]);
         }
       }
       const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;   // scale > 0; -inf stays -inf
@@ -324,24 +382,23 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         correction = (row_max == -INFINITY) ? 0.0f : exp2f(row_max - new_max);
         row_max = new_max;
       }
-      const float m_used = (row_max == -INFINITY) ? 0.0f : row_max;
+      const float shift = ((row_max == -INFINITY) ? 0.0f : -row_max) + T5_ROUND_SHIFT;
       // ---- pass 2: P = 2^(s*scale - m), row sum, packed bf16 into tensor memory, 32 keys at a time ----
+      // (the softmax warps are bound by instruction issue, not by the exp2 unit: the scaling and the sums
+      // are packed two elements an instruction, and the conversion is one byte permutation for two)
       float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float packed[16];                            // 32 keys, two bf16 a register
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0, e1;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(s[c][i], p.scale_log2, -m_used)));       // masked: -inf
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(s[c][i + 1], p.scale_log2, -m_used)));
-          sm[i & 2] += e0;
-          sm[(i & 2) + 1] += e1;
-          // Two bf16 in a register, the lower key in the lower half.  Rounded by adding half a step
-          // and cutting (integer pipe: the conversion instruction shares the exp2 unit, which is
-          // the busiest unit of this kernel); P >= 0 and finite, so this is round-half-up.
-          packed[i / 2] = __uint_as_float(
-              __byte_perm(__float_as_uint(e0) + 0x8000u, __float_as_uint(e1) + 0x8000u, 0x7632));
+          float a0, a1, e0, e1;
+          t5_fma2(a0, a1, s[c][i], s[c][i + 1], p.scale_log2, shift);      // masked entries stay -inf
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
+          t5_add2(sm[i & 2], sm[(i & 2) + 1], e0, e1);
+          // two bf16 in a register, the lower key in the lower half (cut: see T5_ROUND_SHIFT)
+          packed[i / 2] = __uint_as_float(__byte_perm(__float_as_uint(e0), __float_as_uint(e1), 0x7632));
         }
         // P(j) lies over the first half of the columns S(j) was read from; S(j+1) is written there only
         // after the tensor pipe has taken P(j)
@@ -368,23 +425,24 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     if (ok && n_mine > 0 && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&pv_done[x], (n_mine - 1) & 1)) ok = false;
     if (ok && n_mine > 0) {
       kvb_tc5_fence_after();
-      const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+      const float inv = row_sum > 0.0f ? T5_ROUND_FACTOR / row_sum : 0.0f;
       bf16* dst = nullptr;
       if (row_valid)
         dst = p.out + (size_t)(q_begin + flat / p.G) * p.out_stride + (size_t)(kvh * p.G + flat % p.G) * T5_D;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float o[32];
-        kvb_tc5_ld32(o_addr + c * 32, o);
-        kvb_tc5_wait_ld();
-        if (row_valid) {
+      float o[4][32];                               // the whole row at once: one round trip to tensor memory
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kvb_tc5_ld32(o_addr + c * 32, o[c]);
+      kvb_tc5_wait_ld();
+      if (row_valid) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 packed;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(o[c][i] * inv, o[c][i + 1] * inv);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(o[c][i + 2] * inv, o[c][i + 3] * inv);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(o[c][i + 4] * inv, o[c][i + 5] * inv);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(o[c][i + 6] * inv, o[c][i + 7] * inv);
             packed.x = *reinterpret_cast<unsigned*>(&t0);
             packed.y = *reinterpret_cast<unsigned*>(&t1);
             packed.z = *reinterpret_cast<unsigned*>(&t2);
@@ -432,11 +490,12 @@ extern "C" int kvb_make_kv_half_tensor_map(void* map_out, const void* cache, lon
   return 0;
 }
 
+// q [num_tokens, >= H * 128] bf16 with row stride q_stride (elements): the step's queries, rotated already.
 extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void* q, long long q_stride,
                                      const void* k_map_host, const void* v_map_host, const int* table,
                                      int table_stride, const int* query_start, const int* context_lens,
-                                     int num_reqs, int max_query_len, int H, int KVH, int D, int page_size,
-                                     int num_pages, float scale, int window, cudaStream_t stream) {
+                                     int num_reqs, int max_query_len, int num_tokens, int H, int KVH, int D,
+                                     int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(D == T5_D, "prefill attention (tcgen05): head_dim must be 128");
   KVB_REQUIRE(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64,
@@ -456,9 +515,27 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = kvb_status_word();
   KVB_REQUIRE(p.status != nullptr, "prefill attention (tcgen05): no status word");
-  alignas(64) CUtensorMap k_map, v_map;
+  alignas(64) CUtensorMap k_map, v_map, q_map;
   memcpy(&k_map, k_map_host, sizeof(CUtensorMap));
   memcpy(&v_map, v_map_host, sizeof(CUtensorMap));
+  // The queries as [token][kv head][head of the group][128] with boxes of [128 / G tokens][1][G][64 columns]:
+  // a box is one 64-column half of a query tile, its rows in (token, head) order.  Needs G to divide 128.
+  memset(&q_map, 0, sizeof(q_map));
+  p.q_by_tma = 0;
+  if (T5_BM % p.G == 0 && num_tokens > 0) {
+    KvbEncodeTiledFn encode = kvb_encode_tiled_fn();
+    KVB_REQUIRE(encode != nullptr, "prefill attention (tcgen05): the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[4] = {(cuuint64_t)T5_D, (cuuint64_t)p.G, (cuuint64_t)KVH, (cuuint64_t)num_tokens};
+    const cuuint64_t strides[3] = {(cuuint64_t)T5_D * sizeof(bf16), (cuuint64_t)p.G * T5_D * sizeof(bf16),
+                                   (cuuint64_t)q_stride * sizeof(bf16)};
+    const cuuint32_t box[4] = {64, (cuuint32_t)p.G, 1, (cuuint32_t)(T5_BM / p.G)};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult rc = encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box,
+                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KVB_REQUIRE(rc == CUDA_SUCCESS, "prefill attention (tcgen05): cuTensorMapEncodeTiled failed for the queries");
+    p.q_by_tma = 1;
+  }
   constexpr size_t SMEM = 6 * T5_TILE_BYTES + 16 * 8;
   static bool configured = false;
   if (!configured) {
@@ -466,8 +543,10 @@ extern "C" int kvb_flash_prefill_tc5(void* out, long long out_stride, const void
     configured = true;
   }
   const int max_rows = max_query_len * p.G;
-  dim3 grid((max_rows + 2 * T5_BM - 1) / (2 * T5_BM), KVH, num_reqs);   // a block takes two query tiles
-  KVB_CHECK_CUDA(kvb_launch((flash_prefill_tc5_kernel), dim3(grid), dim3(T5_THREADS), SMEM, stream, true, k_map, v_map, p));
+  const int pairs = (max_rows + 2 * T5_BM - 1) / (2 * T5_BM);            // a block takes two query tiles
+  KVB_REQUIRE(pairs <= 65535, "prefill attention (tcgen05): portion too long for one launch");
+  dim3 grid(KVH, num_reqs, pairs);
+  KVB_CHECK_CUDA(kvb_launch((flash_prefill_tc5_kernel), dim3(grid), dim3(T5_THREADS), SMEM, stream, true, k_map, v_map, q_map, p));
   KVB_CHECK_LAUNCH();
   return 0;
 }

@@ -70,6 +70,14 @@ __device__ __forceinline__ void kvb_tma_3d(void* dst, const CUtensorMap* map, in
         "r"(kvb_smem(bar))
       : "memory");
 }
+__device__ __forceinline__ void kvb_tma_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                           unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+      ::"r"(kvb_smem(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+        "r"(kvb_smem(bar))
+      : "memory");
+}
 // Untiled copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from global to shared memory.
 __device__ __forceinline__ void kvb_bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"

@@ -52,7 +52,7 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_flash_decode_tma": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
                                  _int, _int, _int, _float, _int, _int, _vp, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_make_kv_half_tensor_map": [_vp, _vp, _ll, _int, _int, _int],
-        "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int,
+        "kvb_flash_prefill_tc5": [_vp, _ll, _vp, _ll, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int, _int,
                                   _int, _int, _int, _float, _int, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
@@ -536,7 +536,7 @@ def paged_attention(
             _call("kvb_flash_prefill_tc5", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
                   ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
                   ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
-                  num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
+                  tokens, num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
                   _stream())
             return out
         splits = 1
