@@ -258,23 +258,35 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       const unsigned idesc_s = kvb_tc5_idesc(T5_BM, T5_BN, false);   // A, B both K-major
       const unsigned idesc_pv = kvb_tc5_idesc(T5_BM, T5_BN, true);   // B (= V) MN-major
       bool ok = true;
+      // The operand descriptors of a tile differ from step to step only in their address field (bits
+      // 0-13, in units of 16 bytes; shared memory ends below 256 KB, so the field never overflows): the
+      // six bases are made once and a step adds a constant.  This thread issues 32 MMAs per key tile and
+      // is on the critical path of both query tiles: with the descriptors built per MMA it needed ~90
+      // cycles an instruction, more than the 64 the tensor pipe takes.
+      const unsigned long long q_desc[2] = {kvb_tc5_desc(kvb_smem(q_smem), 16, 1024),
+                                            kvb_tc5_desc(kvb_smem(q_smem + T5_TILE_BYTES), 16, 1024)};
+      const unsigned long long k_desc[2] = {kvb_tc5_desc(kvb_smem(k_smem), 16, 1024),
+                                            kvb_tc5_desc(kvb_smem(k_smem + T5_TILE_BYTES), 16, 1024)};
+      const unsigned long long v_desc[2] = {kvb_tc5_desc(kvb_smem(v_smem), T5_HALF_BYTES, 1024),
+                                            kvb_tc5_desc(kvb_smem(v_smem + T5_TILE_BYTES), T5_HALF_BYTES, 1024)};
       auto issue_s = [&](int x, int j) {   // S_x(j) = Q_x . K(j)^T
-        const unsigned q_addr = kvb_smem(q_smem + x * T5_TILE_BYTES);
-        const unsigned k_addr = kvb_smem(k_smem + (j & 1) * T5_TILE_BYTES);
+        const unsigned long long qd = q_desc[x], kd = k_desc[j & 1];
+        const unsigned d = tmem_base + x * T5_BN;
 #pragma unroll
         for (int kk = 0; kk < T5_D / 16; ++kk) {
-          const unsigned off = (kk >> 2) * T5_HALF_BYTES + (kk & 3) * 32;
-          kvb_tc5_mma(tmem_base + x * T5_BN, kvb_tc5_desc(q_addr + off, 16, 1024), kvb_tc5_desc(k_addr + off, 16, 1024),
-                      idesc_s, kk > 0);
+          constexpr unsigned HALF16 = T5_HALF_BYTES >> 4;
+          const unsigned long long off = (unsigned long long)((kk >> 2) * HALF16 + (kk & 3) * 2);   // 32 bytes a step, then the other half
+          kvb_tc5_mma(d, qd + off, kd + off, idesc_s, kk > 0);
         }
         kvb_tc5_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {  // O_x += P_x(j) . V(j): 16 keys per MMA (8 columns of P, 16 key rows of V)
-        const unsigned v_addr = kvb_smem(v_smem + (j & 1) * T5_TILE_BYTES);
+        const unsigned long long vd = v_desc[j & 1];
+        const unsigned d = tmem_base + 256 + x * T5_D, a = tmem_base + x * T5_BN;
+        const unsigned first = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < T5_BN / 16; ++kk)
-          kvb_tc5_mma_ts(tmem_base + 256 + x * T5_D, tmem_base + x * T5_BN + kk * 8,
-                         kvb_tc5_desc(v_addr + kk * 16 * 128, T5_HALF_BYTES, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          kvb_tc5_mma_ts(d, a + kk * 8, vd + (unsigned long long)(kk * 128), idesc_pv, kk > 0 ? 1u : first);   // 16 key rows = 2,048 bytes
         kvb_tc5_commit(&pv_done[x]);
       };
       if (p.q_by_tma && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(q_full, 0)) ok = false;

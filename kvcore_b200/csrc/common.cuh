@@ -141,7 +141,6 @@ struct KvbTrace {
 #define KVB_TAG_GEMM_F32 12
 #define KVB_TAG_GEMM_STREAM 13
 #define KVB_TAG_SAMPLE 14
-#define KVB_TAG_GEMM_STREAM_TC5 15
 #define KVB_TAG_FEED_TOKENS 16
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).

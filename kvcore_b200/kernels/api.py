@@ -57,8 +57,6 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _int, _vp],
-        "kvb_gemm_stream_tc5_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
-                                 _int, _vp, _vp, _vp, _vp, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_feed_tokens": [_vp, _vp, _vp, _int, _int, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
@@ -80,11 +78,6 @@ def ensure_built(verbose: bool = False) -> str:
     lib.kvb_gemm_stream_norm_max_k.restype = _int
     lib.kvb_gemm_stream_scratch_marker.argtypes = []
     lib.kvb_gemm_stream_scratch_marker.restype = ctypes.c_uint
-    for name in ("kvb_gemm_stream_tc5_scratch_floats", "kvb_gemm_stream_tc5_flag_ints"):
-        getattr(lib, name).argtypes = [_int]
-        getattr(lib, name).restype = _ll
-    lib.kvb_gemm_stream_tc5_norm_max_k.argtypes = []
-    lib.kvb_gemm_stream_tc5_norm_max_k.restype = _int
     _lib = lib
     return str(path)
 
@@ -148,11 +141,8 @@ def read_status(reset: bool = True) -> int:
     if out.value & 4:
         # a kernel gave up a wait: the hand-over areas of the streaming kernels may hold parts that
         # nobody took; put them back into their state between launches
-        for (kind, _), (scratch, flags) in _stream_scratch.items():
-            if kind == "mma":
-                scratch.view(torch.int32).fill_(int(_lib.kvb_gemm_stream_scratch_marker()))
-            elif flags is not None:
-                flags.zero_()
+        for scratch in _stream_scratch.values():
+            scratch.view(torch.int32).fill_(int(_lib.kvb_gemm_stream_scratch_marker()))
         for counters in _decode_work_counters.values():
             counters.zero_()
     return out.value
@@ -566,22 +556,14 @@ _mm_out_dtype_ok: bool | None = None
 # KVCORE_B200_STREAM_ROWS overrides the bound (0: never).
 STREAM_MAX_ROWS = 16
 STREAM_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_ROWS", "16"))
-# A second streaming kernel takes up to STREAM_TC5_MAX_ROWS tokens with its product on tcgen05
-# (tokens as accumulator lanes, the same fused epilogues).  It is correct but not the default:
-# measured on B200 at Llama 3.1 8B shapes and 64 tokens it needs 62 us for the gate/up product
-# against 43 us of the library product (the fix-up of tiles shared between blocks moves 64 KB
-# parts and costs ~15 us a launch), so batches above STREAM_AUTO_ROWS go to the library unless
-# KVCORE_B200_STREAM_TC5_ROWS raises the bound.
-STREAM_TC5_MAX_ROWS = 128
-STREAM_TC5_AUTO_ROWS = int(os.environ.get("KVCORE_B200_STREAM_TC5_ROWS", "0"))
-_stream_scratch: dict[tuple[str, int], tuple[torch.Tensor, torch.Tensor | None]] = {}
+_stream_scratch: dict[int, torch.Tensor] = {}
 
 
 TRACE_TAGS = {1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
-              11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 15: "gemm_stream_tc5", 16: "feed_tokens"}
+              11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
-                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "gemm_stream_tc5")
+                "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream")
 _trace_buffer: torch.Tensor | None = None
 
 
@@ -638,11 +620,9 @@ def set_overlapped_launch(enabled: bool) -> None:
 
 
 def linear_stream(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
-                  out_dtype: torch.dtype | None = None, silu_pairs: bool = False,
-                  kind: str | None = None) -> torch.Tensor:
-    """``x @ weight.T`` for a decode-sized batch of bf16 ``x``, K a multiple of 64: a balanced
-    weight-streaming kernel (one block per SM, every block the same number of bytes).  ``kind``
-    "mma" (at most 16 rows, mma.sync) or "tc5" (at most 128 rows, tcgen05); None: by the row count.
+                  out_dtype: torch.dtype | None = None, silu_pairs: bool = False) -> torch.Tensor:
+    """``x @ weight.T`` for a decode-sized batch of bf16 ``x`` (at most 16 rows), K a multiple of 64: a
+    balanced weight-streaming kernel (one block per SM, every block the same number of bytes).
 
     ``silu_pairs``: the rows of ``weight`` alternate in runs of 8 gate rows and 8 up rows; the
     result is ``[M, N/2]``, ``silu(gate) * up``, with the roundings of the unfused path."""
@@ -650,17 +630,14 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     _check(weight, "weight", dtype=torch.bfloat16)
     m, k = x.shape
     n = weight.shape[0]
-    if kind is None:
-        kind = "mma" if m <= STREAM_MAX_ROWS else "tc5"
-    limit = STREAM_TC5_MAX_ROWS if kind == "tc5" else STREAM_MAX_ROWS
-    if kind not in ("mma", "tc5") or not 0 < m <= limit or k % 64 or x.stride(1) != 1 or x.stride(0) % 8:
-        raise KernelError(f"linear_stream ({kind}): unsupported shape x {tuple(x.shape)} strides {x.stride()}")
+    if not 0 < m <= STREAM_MAX_ROWS or k % 64 or x.stride(1) != 1 or x.stride(0) % 8:
+        raise KernelError(f"linear_stream: unsupported shape x {tuple(x.shape)} strides {x.stride()}")
     if bias is not None:
         _check(bias, "bias", dtype=torch.bfloat16)
     if silu_pairs and (n % 16 or out_dtype not in (None, torch.bfloat16)):
         raise KernelError("linear_stream: gated pairs need an output width that is a multiple of 16 and a bf16 result")
     out = torch.empty((m, n // 2 if silu_pairs else n), dtype=out_dtype or torch.bfloat16, device=x.device)
-    _stream_call(kind, x.device, out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
+    _stream_call(x.device, out.data_ptr(), int(out.dtype == torch.float32), out.stride(0),
                  x.data_ptr(), x.stride(0), weight.data_ptr(), None if bias is None else bias.data_ptr(),
                  m, n, k, int(silu_pairs), None, 0, 0.0, None, 0, None, None)
     return out
@@ -695,9 +672,8 @@ def linear(
         return out
     # Decode-sized batches: the layer is one pass over the weights, which this library's own
     # streaming kernel does, overlapping its start with the kernels in front of it.
-    kind = _stream_kind(x, weight)
-    if kind is not None:
-        return linear_stream(x, weight, bias, out_dtype=out_dtype, kind=kind)
+    if _stream_ok(x, weight):
+        return linear_stream(x, weight, bias, out_dtype=out_dtype)
     if out_dtype == torch.float32:
         if _mm_out_dtype_ok is None:
             try:
@@ -715,63 +691,36 @@ def linear(
     return torch.nn.functional.linear(x, weight, bias)
 
 
-def _stream_buffers(device: torch.device, kind: str = "mma") -> tuple[torch.Tensor, torch.Tensor | None]:
-    """Scratch (and, for the tcgen05 kernel, flags that are zero between launches) of a streaming
-    kernel; kept for good, since a captured graph holds their addresses.  The ``mma.sync`` kernel has
-    no flags: every word of its scratch holds a marker between launches."""
+def _stream_buffers(device: torch.device) -> torch.Tensor:
+    """Scratch of the streaming kernel; kept for good, since a captured graph holds its address.  Every
+    word holds a marker between launches."""
     index = device.index or 0
-    buffers = _stream_scratch.get((kind, index))
-    if buffers is None:
-        if kind == "tc5":
-            floats = int(_lib.kvb_gemm_stream_tc5_scratch_floats(sm_count(device)))
-            ints = int(_lib.kvb_gemm_stream_tc5_flag_ints(sm_count(device)))
-            buffers = (torch.empty(floats, dtype=torch.float32, device=device),
-                       torch.zeros(ints, dtype=torch.int32, device=device))
-        else:
-            floats = int(_lib.kvb_gemm_stream_scratch_floats(sm_count(device)))
-            marker = int(_lib.kvb_gemm_stream_scratch_marker())
-            words = torch.full((floats,), marker, dtype=torch.int32, device=device)
-            buffers = (words.view(torch.float32), None)
-        _stream_scratch[(kind, index)] = buffers
-    return buffers
-
-
-def _stream_kind(x: torch.Tensor, weight: torch.Tensor) -> str | None:
-    """Which streaming kernel takes ``x @ weight.T``: "mma" (at most STREAM_AUTO_ROWS tokens),
-    "tc5" (at most STREAM_TC5_AUTO_ROWS) or None (the library product)."""
-    m, k = x.shape
-    if not (x.dtype == torch.bfloat16 and k % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
-            and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and m > 0):
-        return None
-    if m <= min(STREAM_AUTO_ROWS, STREAM_MAX_ROWS):
-        return "mma"
-    if m <= min(STREAM_TC5_AUTO_ROWS, STREAM_TC5_MAX_ROWS):
-        return "tc5"
-    return None
+    scratch = _stream_scratch.get(index)
+    if scratch is None:
+        floats = int(_lib.kvb_gemm_stream_scratch_floats(sm_count(device)))
+        marker = int(_lib.kvb_gemm_stream_scratch_marker())
+        words = torch.full((floats,), marker, dtype=torch.int32, device=device)
+        scratch = _stream_scratch[index] = words.view(torch.float32)
+    return scratch
 
 
 def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return _stream_kind(x, weight) is not None
+    """Whether the streaming kernel takes ``x @ weight.T`` (at most STREAM_AUTO_ROWS tokens); otherwise
+    the library product does.  A streaming kernel on tcgen05 for 17 to 128 tokens existed and was
+    taken out: in whole decode steps at Llama 3.1 8B layer sizes it was 29 % slower than the library
+    product at 20 and 32 tokens and 39 to 47 % slower at 48 and 64."""
+    m, k = x.shape
+    return (x.dtype == torch.bfloat16 and k % 64 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and 0 < m <= min(STREAM_AUTO_ROWS, STREAM_MAX_ROWS))
 
 
-def _stream_piece(kind: str) -> int:
-    """Columns of the residual whose squares one piece of ``sumsq`` holds."""
-    return 32 if kind == "tc5" else 64
+_STREAM_PIECE = 64   # columns of the residual whose squares one piece of ``sumsq`` holds
 
 
-def _stream_norm_max_k(kind: str) -> int:
-    fn = _lib.kvb_gemm_stream_tc5_norm_max_k if kind == "tc5" else _lib.kvb_gemm_stream_norm_max_k
-    return int(fn())
-
-
-def _stream_call(kind: str, device: torch.device, *args) -> None:
-    """``kvb_gemm_stream(_tc5)_bf16`` with ``args`` up to ``sumsq_out``; scratch, flags, SM count and
-    stream are appended."""
-    scratch, flags = _stream_buffers(device, kind)
-    if kind == "tc5":
-        _call("kvb_gemm_stream_tc5_bf16", *args, scratch.data_ptr(), flags.data_ptr(), sm_count(device), _stream())
-    else:
-        _call("kvb_gemm_stream_bf16", *args, scratch.data_ptr(), sm_count(device), _stream())
+def _stream_call(device: torch.device, *args) -> None:
+    """``kvb_gemm_stream_bf16`` with ``args`` up to ``sumsq_out``; scratch, SM count and stream are appended."""
+    _call("kvb_gemm_stream_bf16", *args, _stream_buffers(device).data_ptr(), sm_count(device), _stream())
 
 
 def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
@@ -782,9 +731,8 @@ def linear_silu_mul(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | 
     its epilogue; everything else is the matrix product followed by ``silu_mul``."""
     _check(x, "x", contiguous=False)
     _check(weight, "weight", dtype=x.dtype)
-    kind = _stream_kind(x, weight) if x.dim() == 2 else None
-    if group == 8 and kind is not None and weight.shape[0] % 16 == 0:
-        return linear_stream(x, weight, bias, silu_pairs=True, kind=kind)
+    if group == 8 and x.dim() == 2 and _stream_ok(x, weight) and weight.shape[0] % 16 == 0:
+        return linear_stream(x, weight, bias, silu_pairs=True)
     return silu_mul(linear(x, weight, bias), group)
 
 
@@ -806,9 +754,8 @@ def norm_linear(h: torch.Tensor | None, residual: torch.Tensor | None, norm_weig
         _check(residual, "residual", contiguous=False)
         m, k = residual.shape
         weight_bytes = 4 if norm_weight.dtype == torch.float32 else 2
-        kind = _stream_kind(residual, weight)
-        if (sumsq is not None and kind is not None
-                and k * weight_bytes <= 4 * _stream_norm_max_k(kind)
+        if (sumsq is not None and _stream_ok(residual, weight)
+                and k * weight_bytes <= 4 * int(_lib.kvb_gemm_stream_norm_max_k())
                 and norm_weight.dtype in (torch.bfloat16, torch.float32) and norm_weight.is_contiguous()
                 and norm_weight.data_ptr() % 16 == 0
                 and sumsq.dtype == torch.float32 and sumsq.is_contiguous() and sumsq.shape[0] == m
@@ -818,7 +765,7 @@ def norm_linear(h: torch.Tensor | None, residual: torch.Tensor | None, norm_weig
                 _check(bias, "bias", dtype=torch.bfloat16)
             n = weight.shape[0]
             out = torch.empty((m, n // 2 if silu_group else n), dtype=torch.bfloat16, device=residual.device)
-            _stream_call(kind, residual.device, out.data_ptr(), 0, out.stride(0), residual.data_ptr(),
+            _stream_call(residual.device, out.data_ptr(), 0, out.stride(0), residual.data_ptr(),
                          residual.stride(0), weight.data_ptr(), None if bias is None else bias.data_ptr(), m, n, k,
                          int(bool(silu_group)), norm_weight.data_ptr(), int(norm_weight.dtype == torch.float32),
                          float(eps), sumsq.data_ptr(), sumsq.shape[1], None, None)
@@ -838,10 +785,9 @@ def linear_add_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
 
     Decode-sized bf16 batches: the streaming product adds its (bf16-rounded) result into ``residual``
     in place and returns ``(None, sumsq)``, ``sumsq [T, ceil(N / 64)]`` being the squares of the new
-    rows of ``residual``, 64 (32 above 16 tokens) columns a piece, for the norm that follows.  Otherwise returns
+    rows of ``residual``, 64 columns a piece, for the norm that follows.  Otherwise returns
     ``(out, None)``: the sum is left to that norm, as the deferred-residual scheme has it."""
-    kind = _stream_kind(x, weight) if x.dim() == 2 else None
-    if (residual is not None and kind is not None
+    if (residual is not None and x.dim() == 2 and _stream_ok(x, weight)
             and weight.shape[0] % 8 == 0 and residual.dtype == torch.bfloat16 and residual.is_contiguous()
             and tuple(residual.shape) == (x.shape[0], weight.shape[0]) and residual.data_ptr() % 16 == 0):
         _check(weight, "weight", dtype=torch.bfloat16)
@@ -849,8 +795,8 @@ def linear_add_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tenso
             _check(bias, "bias", dtype=torch.bfloat16)
         m, k = x.shape
         n = weight.shape[0]
-        sumsq = torch.empty((m, -(-n // _stream_piece(kind))), dtype=torch.float32, device=x.device)
-        _stream_call(kind, x.device, None, 0, n, x.data_ptr(), x.stride(0), weight.data_ptr(),
+        sumsq = torch.empty((m, -(-n // _STREAM_PIECE)), dtype=torch.float32, device=x.device)
+        _stream_call(x.device, None, 0, n, x.data_ptr(), x.stride(0), weight.data_ptr(),
                      None if bias is None else bias.data_ptr(), m, n, k, 0, None, 0, 0.0, None, 0,
                      residual.data_ptr(), sumsq.data_ptr())
         return None, sumsq

@@ -24,7 +24,7 @@ def _arm(K, block, stage, polls=4000):
 
 
 def _scratch_is_clean(K) -> bool:
-    scratch, _ = K.api._stream_scratch[("mma", torch.device(DEV).index or 0)]
+    scratch = K.api._stream_scratch[torch.device(DEV).index or 0]
     marker = int(K.api._lib.kvb_gemm_stream_scratch_marker())
     marker = marker - (1 << 32) if marker >= (1 << 31) else marker
     return bool((scratch.view(torch.int32) == marker).all())

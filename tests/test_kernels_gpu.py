@@ -552,82 +552,30 @@ def test_linear_stream(m, n, k, bias):
     assert K().read_status() == 0
 
 
-@pytest.mark.parametrize("m,n,k", [
-    (17, 64, 128), (64, 4096, 4096), (33, 6144, 4096), (20, 515, 1024), (128, 130, 64), (5, 300, 192),
-    (100, 1024, 2048), (32, 96, 14336), (64, 4096, 1024), (48, 28672, 1024), (65, 70, 576),
-    (64, 4096, 14336), (128, 4100, 1088), (31, 33, 3136), (64, 256, 64), (64, 40000, 128),
-])
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 128), (8, 14336, 4096), (5, 200, 576), (16, 1000, 256), (3, 8, 64)])
 @pytest.mark.parametrize("bias", [False, True])
-def test_linear_stream_on_tcgen05(m, n, k, bias):
-    """The streaming kernel for 17 to 128 tokens: whole tiles, tiles shared by many blocks (small N,
-    large K), ragged N and M, more blocks than stages."""
-    x = randn(m, k, dtype=torch.bfloat16, seed=20)
-    w = randn(n, k, dtype=torch.bfloat16, seed=21, scale=0.05)
-    b = randn(n, dtype=torch.bfloat16, seed=22) if bias else None
-    want = x.float() @ w.float().T + (b.float() if bias else 0)
-    got = K().linear_stream(x, w, b, kind="tc5")
-    assert got.dtype == torch.bfloat16
-    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=2e-2)
-    wide = K().linear_stream(x, w, b, out_dtype=torch.float32, kind="tc5")
-    torch.testing.assert_close(wide, want, rtol=1e-3, atol=2e-3)
-    for _ in range(2):   # parts are added in a fixed order; the flags are down again after a launch
-        again = K().linear_stream(x, w, b, out_dtype=torch.float32, kind="tc5")
-        assert torch.equal(wide, again)
-    assert K().read_status() == 0
-
-
-def test_linear_stream_on_tcgen05_finds_a_single_weight():
-    """One large weight far inside K and one in the last row: every (row, k) reaches its output."""
-    m, n, k = 40, 700, 2048
-    x = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV)
-    w = torch.zeros(n, k, dtype=torch.bfloat16, device=DEV)
-    x[37, 1999] = 2.0
-    x[3, 64] = -1.0
-    w[699, 1999] = 3.0
-    w[255, 64] = 5.0
-    w[256, 64] = 7.0
-    got = K().linear_stream(x, w, kind="tc5").float()
-    want = torch.zeros(m, n, device=DEV)
-    want[37, 699] = 6.0
-    want[3, 255] = -5.0
-    want[3, 256] = -7.0
-    assert torch.equal(got, want)
-    assert K().read_status() == 0
-
-
-@pytest.mark.parametrize("m,inter,k,kind", [(1, 64, 128, "mma"), (8, 14336, 4096, "mma"), (5, 200, 576, "mma"),
-                                            (16, 1000, 256, "mma"), (3, 8, 64, "mma"), (64, 14336, 4096, "tc5"),
-                                            (17, 200, 576, "tc5"), (128, 1000, 256, "tc5"), (40, 8, 64, "tc5"),
-                                            (33, 136, 1024, "tc5")])
-@pytest.mark.parametrize("bias", [False, True])
-def test_linear_stream_with_gated_epilogue(m, inter, k, kind, bias):
+def test_linear_stream_with_gated_epilogue(m, inter, k, bias):
     """Rows in runs of 8 gate / 8 up: the activation in the epilogue equals product + silu_mul."""
     x = randn(m, k, dtype=torch.bfloat16, seed=30)
     w = randn(2 * inter, k, dtype=torch.bfloat16, seed=31, scale=0.05)
     b = randn(2 * inter, dtype=torch.bfloat16, seed=32) if bias else None
-    got = K().linear_stream(x, w, b, silu_pairs=True, kind=kind)
+    got = K().linear_stream(x, w, b, silu_pairs=True)
     assert got.shape == (m, inter) and got.dtype == torch.bfloat16
     products = (x.float() @ w.float().T + (b.float() if bias else 0)).to(torch.bfloat16)
     want = P.silu_mul(products, 8)
     torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-2)
     routed = K().linear_silu_mul(x, w, b, group=8)      # the kernels above for decode-sized batches
-    if m <= (K().api.STREAM_TC5_AUTO_ROWS if kind == "tc5" else K().api.STREAM_AUTO_ROWS):
-        assert torch.equal(got, routed)
-    else:
-        torch.testing.assert_close(got.float(), routed.float(), rtol=1.6e-2, atol=2e-2)
+    assert torch.equal(got, routed)
     assert K().read_status() == 0
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 6144, 4096), (5, 200, 576), (16, 4096, 1088), (3, 48, 4096),
-                                   (17, 128, 64), (64, 6144, 4096), (33, 200, 576), (128, 4096, 1088),
-                                   (50, 48, 4096)])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 6144, 4096), (5, 200, 576), (16, 4096, 1088), (3, 48, 4096)])
 @pytest.mark.parametrize("weight_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("gated", [False, True])
-def test_residual_stream_kernels(m, n, k, weight_dtype, gated, monkeypatch):
+def test_residual_stream_kernels(m, n, k, weight_dtype, gated):
     """A sub-layer's exit (product added into the residual, squares left for the norm) and the next
     sub-layer's entry (rows normalised inside the product) equal the separate steps."""
-    monkeypatch.setattr(K().api, "STREAM_TC5_AUTO_ROWS", 128)
-    piece = 64 if m <= 16 else 32
+    piece = 64
     x = randn(m, 192, dtype=torch.bfloat16, seed=39)
     w_out = randn(k, 192, dtype=torch.bfloat16, seed=38, scale=0.05)
     b_out = randn(k, dtype=torch.bfloat16, seed=37)
@@ -679,7 +627,7 @@ def test_linear_stream_refuses_what_it_cannot_take():
     with pytest.raises(K().KernelError):
         K().linear_stream(x, w)            # more than 128 rows
     with pytest.raises(K().KernelError):
-        K().linear_stream(x[:17], w, kind="mma")   # more than 16 rows for the mma.sync kernel
+        K().linear_stream(x[:17], w)   # more than 16 rows
     with pytest.raises(K().KernelError):
         K().linear_stream(x[:4, :72], w[:, :72].contiguous())   # K no multiple of 64
     # the general entry point takes both (library product)
