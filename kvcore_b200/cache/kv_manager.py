@@ -100,8 +100,10 @@ class KVManager:
         self._version = 0
         self._requests: dict[str, _RequestState] = {}
         self._fresh_slots: list[int] = []
-        # prefix reuse needs one table that keeps every key (a windowed group has given pages back)
-        self.prefix_caching = bool(enable_prefix_caching) and len(self.groups) == 1 and self.groups[0].window is None
+        # prefix reuse needs tables that keep every key (a windowed group has given pages back); with
+        # several such groups a prefix counts only as far as every group still holds its pages
+        self.prefix_caching = (bool(enable_prefix_caching) and len(self.groups) >= 1
+                               and all(group.window is None for group in self.groups))
         self.num_prefix_hits = 0          # pages taken over instead of computed
         # per group, the pages that nobody holds any more since take_released_pages() was last called
         # (kept only on request: the debug fill of freed pages reads it)
@@ -156,7 +158,7 @@ class KVManager:
     def pages_needed(self, request_id: str, num_new_tokens: int) -> list[int]:
         return self._new_pages_needed(self._requests.get(request_id), num_new_tokens)
 
-    def can_fit(self, request_id: str, num_new_tokens: int, prefix_pages: Sequence[int] = ()) -> bool:
+    def can_fit(self, request_id: str, num_new_tokens: int, prefix_pages: Sequence[Sequence[int]] = ()) -> bool:
         """Whether ``num_new_tokens`` more tokens of the request can be given pages (and, for a
         request not yet seen, a state slot) right now.  Admission math as the reference's
         ``can_fit`` (kv_manager.py:179-201) per group instead of per layer: new pages, plus the
@@ -171,8 +173,11 @@ class KVManager:
             if state is not None or not self.prefix_caching:
                 return False
             target = -(-(computed + num_new_tokens) // self.page_size)
-            queued = sum(1 for page in prefix_pages if self.pools[0].is_queued(page))
-            return target - len(prefix_pages) + queued <= self.pools[0].num_free
+            for g, pool in enumerate(self.pools):
+                queued = sum(1 for pages in prefix_pages if pool.is_queued(pages[g]))
+                if target - len(prefix_pages) + queued > pool.num_free:
+                    return False
+            return True
         needed = self._new_pages_needed(state, num_new_tokens)
         return all(need <= pool.num_free for need, pool in zip(needed, self.pools))
 
@@ -180,19 +185,20 @@ class KVManager:
     def _chain_key(self, previous: bytes, tokens: Sequence[int]) -> bytes:
         return hashlib.sha256(previous + np.asarray(tokens, dtype=np.int64).tobytes()).digest()
 
-    def find_prefix(self, token_ids: Sequence[int]) -> list[int]:
-        """Pages whose registered contents are the leading full pages of ``token_ids``; at least
-        the last token is left to compute."""
+    def find_prefix(self, token_ids: Sequence[int]) -> list[tuple[int, ...]]:
+        """Pages whose registered contents are the leading full pages of ``token_ids``: one entry per
+        page position, holding that position's page id in every group (a position counts only if
+        every group still has it); at least the last token is left to compute."""
         if not self.prefix_caching:
             return []
-        pages: list[int] = []
+        pages: list[tuple[int, ...]] = []
         key = b""
         for block in range((len(token_ids) - 1) // self.page_size):
             key = self._chain_key(key, token_ids[block * self.page_size : (block + 1) * self.page_size])
-            page = self.pools[0].lookup(key)
-            if page is None:
+            found = tuple(pool.lookup(key) for pool in self.pools)
+            if any(page is None for page in found):
                 break
-            pages.append(page)
+            pages.append(found)
         return pages
 
     def register_full_pages(self, request_id: str, token_ids: Sequence[int]) -> None:
@@ -203,19 +209,20 @@ class KVManager:
         if state is None:
             return
         full = min(state.num_computed, len(token_ids)) // self.page_size
-        row = self.tables[0][state.slot]
         while len(state.page_keys) < full:
             block = len(state.page_keys)
             previous = state.page_keys[-1] if state.page_keys else b""
             key = self._chain_key(previous, token_ids[block * self.page_size : (block + 1) * self.page_size])
             state.page_keys.append(key)
-            self.pools[0].register(int(row[block]), key)   # a key already taken stays with its page
+            for g, pool in enumerate(self.pools):
+                pool.register(int(self.tables[g][state.slot][block]), key)   # a key already taken stays with its page
 
     # ---- changes ---------------------------------------------------------------------------
-    def allocate_slots(self, request_id: str, num_new_tokens: int, prefix_pages: Sequence[int] = ()) -> bool:
+    def allocate_slots(self, request_id: str, num_new_tokens: int,
+                       prefix_pages: Sequence[Sequence[int]] = ()) -> bool:
         """Give the request pages for ``num_new_tokens`` tokens beyond those computed.
         ``prefix_pages`` (a new request only, from ``find_prefix``): pages taken over as its
-        first ones; their tokens count as computed.  Returns False (and changes nothing) if
+        first ones, in every group; their tokens count as computed.  Returns False (and changes nothing) if
         the pages do not fit."""
         if num_new_tokens <= 0:
             raise ValueError(f"num_new_tokens must be positive, got {num_new_tokens}")
@@ -235,11 +242,12 @@ class KVManager:
                 table[slot, :] = NULL_PAGE
             self._touch(slot)
             if prefix_pages:
-                for page in prefix_pages:
-                    self.pools[0].share(page)
                 count = len(prefix_pages)
-                self.tables[0][slot, :count] = list(prefix_pages)
-                state.num_blocks[0] = count
+                for g, pool in enumerate(self.pools):
+                    for pages in prefix_pages:
+                        pool.share(pages[g])
+                    self.tables[g][slot, :count] = [pages[g] for pages in prefix_pages]
+                    state.num_blocks[g] = count
                 state.num_computed = count * self.page_size
                 self.num_prefix_hits += count
         needed = self._new_pages_needed(state, num_new_tokens)

@@ -239,7 +239,7 @@ class Scheduler:
             if is_prefill and not self._can_schedule_partial_prefill(request, partial, long_partial):
                 return None
             # a request that starts (or starts again): pages that already hold its first tokens
-            prefix_pages: list[int] = []
+            prefix_pages: list[tuple[int, ...]] = []
             if (from_waiting and request.num_computed_tokens == 0
                     and not request.sampling_params.skip_reading_prefix_cache):
                 prefix_pages = self.kv_manager.find_prefix(request.all_token_ids)

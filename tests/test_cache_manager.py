@@ -191,14 +191,14 @@ def test_prefix_pages_are_taken_over_by_a_later_request():
     a_pages = kv.block_ids("a")[0]
     second = first[:9] + [7, 8, 9]                   # shares two full pages (8 tokens)
     hit = kv.find_prefix(second)
-    assert hit == list(a_pages[:2])
+    assert hit == [(page,) for page in a_pages[:2]]
     assert kv.allocate_slots("b", len(second) - 8, hit)
     assert kv.num_computed("b") == 8 and kv.block_ids("b")[0][:2] == a_pages[:2]
     assert kv.block_ids("b")[0][2] not in a_pages
     kv.check_invariants()
     kv.free("a")                                      # shared pages stay with b
     kv.check_invariants()
-    assert all(kv.pools[0].is_held(p) for p in hit)
+    assert all(kv.pools[0].is_held(p) for (p,) in hit)
     kv.advance("b", len(second) - 8)
     kv.register_full_pages("b", second)
     kv.free("b")
@@ -206,7 +206,7 @@ def test_prefix_pages_are_taken_over_by_a_later_request():
     assert kv.num_free_pages() == [16]
     # everything is free, yet still findable: a third request takes pages over out of the queue
     again = kv.find_prefix(first)
-    assert again == list(a_pages[:3])
+    assert again == [(page,) for page in a_pages[:3]]
     assert kv.can_fit("c", 2, again) and kv.allocate_slots("c", 2, again)
     assert kv.num_computed("c") == 12 and kv.num_prefix_hits == 5
     kv.check_invariants()
@@ -243,6 +243,33 @@ def test_prefix_reuse_is_off_without_the_flag_and_with_windows():
     windowed = KVManager([CacheGroupSpec(0, (0,), 2, 2, 16, 8)], num_pages=9, page_size=4, max_num_seqs=2,
                          max_model_len=64, enable_prefix_caching=True)
     assert not windowed.prefix_caching
+
+
+def test_prefix_reuse_over_two_groups_counts_only_what_both_still_hold():
+    """Two groups that keep every key (say, layers with different head sizes): a prefix is taken over in
+    both tables, and only as far as both pools still have the page."""
+    kv = KVManager([CacheGroupSpec(0, (0,), 2, 2, 16, None), CacheGroupSpec(1, (1,), 1, 1, 24, None)], num_pages=[17, 17],
+                   page_size=4, max_num_seqs=4, max_model_len=64, enable_prefix_caching=True)
+    assert kv.prefix_caching
+    tokens = list(range(50, 63))                     # 13 tokens: 3 full pages
+    assert kv.allocate_slots("a", 13)
+    kv.advance("a", 13)
+    kv.register_full_pages("a", tokens)
+    a_pages = kv.block_ids("a")
+    hit = kv.find_prefix(tokens)
+    assert hit == [(a_pages[0][i], a_pages[1][i]) for i in range(3)]
+    assert kv.allocate_slots("b", 2, hit[:2])
+    assert kv.num_computed("b") == 8
+    assert kv.block_ids("b")[0][:2] == a_pages[0][:2] and kv.block_ids("b")[1][:2] == a_pages[1][:2]
+    kv.check_invariants()
+    kv.free("a")
+    kv.free("b")
+    kv.check_invariants()
+    # the second group's queue hands its pages out again: the prefix is gone in that group, so it is gone
+    taken = kv.pools[1].allocate(kv.pools[1].num_free)
+    assert kv.find_prefix(tokens) == []
+    kv.pools[1].free(taken)
+    kv.check_invariants()
 
 
 @pytest.mark.parametrize("seed", range(4))
