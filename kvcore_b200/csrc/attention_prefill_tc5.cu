@@ -270,23 +270,14 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
       const unsigned long long v_desc[2] = {kvb_tc5_desc(kvb_smem(v_smem), T5_HALF_BYTES, 1024),
                                             kvb_tc5_desc(kvb_smem(v_smem + T5_TILE_BYTES), T5_HALF_BYTES, 1024)};
       auto issue_s = [&](int x, int j) {   // S_x(j) = Q_x . K(j)^T
-        const unsigned long long qd = q_desc[x], kd = k_desc[j & 1];
-        const unsigned d = tmem_base + x * T5_BN;
-#pragma unroll
-        for (int kk = 0; kk < T5_D / 16; ++kk) {
-          constexpr unsigned HALF16 = T5_HALF_BYTES >> 4;
-          const unsigned long long off = (unsigned long long)((kk >> 2) * HALF16 + (kk & 3) * 2);   // 32 bytes a step, then the other half
-          kvb_tc5_mma(d, qd + off, kd + off, idesc_s, kk > 0);
-        }
+        // 32 bytes (2 units) a step of 16 columns; after four steps on to the other 64-column half
+        constexpr int HALF16 = T5_HALF_BYTES >> 4;
+        kvb_tc5_mma8_ss<2, HALF16 - 6, 2, HALF16 - 6>(tmem_base + x * T5_BN, q_desc[x], k_desc[j & 1], idesc_s, 0u);
         kvb_tc5_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j) {  // O_x += P_x(j) . V(j): 16 keys per MMA (8 columns of P, 16 key rows of V)
-        const unsigned long long vd = v_desc[j & 1];
-        const unsigned d = tmem_base + 256 + x * T5_D, a = tmem_base + x * T5_BN;
-        const unsigned first = j > 0 ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < T5_BN / 16; ++kk)
-          kvb_tc5_mma_ts(d, a + kk * 8, vd + (unsigned long long)(kk * 128), idesc_pv, kk > 0 ? 1u : first);   // 16 key rows = 2,048 bytes
+        // 16 keys a step: 8 columns of P, 16 key rows (2,048 bytes = 128 units) of V
+        kvb_tc5_mma8_ts<8, 128>(tmem_base + 256 + x * T5_D, tmem_base + x * T5_BN, v_desc[j & 1], idesc_pv, j > 0 ? 1u : 0u);
         kvb_tc5_commit(&pv_done[x]);
       };
       if (p.q_by_tma && !kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(q_full, 0)) ok = false;

@@ -123,6 +123,60 @@ __device__ __forceinline__ void kvb_tc5_mma_ts(unsigned tmem_d, unsigned tmem_a,
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
       ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// Eight MMAs of one 128-wide k-range in ONE instruction sequence: D[tmem] (+)= A . B with the operands'
+// descriptors advanced by constants (in units of 16 bytes) from step to step: a_step / b_step per k-step of
+// 16, and a_jump / b_jump added once after the fourth step (the second 64-column half of a swizzled tile).
+// The first product overwrites D unless `accumulate`; the others add.  Written as one block so that the
+// issuing thread, which is alone in its warp and pays several cycles for every dependent instruction, has
+// nothing but eight tcgen05.mma and their descriptor additions to execute.
+template <int A_STEP, int A_JUMP, int B_STEP, int B_JUMP>
+__device__ __forceinline__ void kvb_tc5_mma8_ss(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                                unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, q;\n.reg .b64 a, b;\n"
+      "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "add.u64 a, %1, %5;\nadd.u64 b, %2, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %5;\nadd.u64 b, b, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %5;\nadd.u64 b, b, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %6;\nadd.u64 b, b, %8;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %5;\nadd.u64 b, b, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %5;\nadd.u64 b, b, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n"
+      "add.u64 a, a, %5;\nadd.u64 b, b, %7;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, q;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate),
+        "n"(A_STEP), "n"(A_JUMP), "n"(B_STEP), "n"(B_JUMP) : "memory");
+}
+// The same with A in tensor memory: its address advances by A_COLS columns a step, B's descriptor by B_STEP.
+template <int A_COLS, int B_STEP>
+__device__ __forceinline__ void kvb_tc5_mma8_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc,
+                                                unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, q;\n.reg .b64 b;\n.reg .b32 a;\n"
+      "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, 0, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "add.u32 a, %1, %5;\nadd.u64 b, %2, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n"
+      "add.u32 a, a, %5;\nadd.u64 b, b, %6;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, q;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "n"(A_COLS), "n"(B_STEP) : "memory");
+}
 // The barrier gets an arrival when every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void kvb_tc5_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(kvb_smem(bar)) : "memory");
