@@ -236,6 +236,18 @@ class StepFunction:
             raise ValueError("a step needs at least one entry")
         if num_reqs > self.max_num_seqs:
             raise ValueError(f"{num_reqs} requests in one step exceed max_num_seqs {self.max_num_seqs}")
+        # Inside the step the requests stand longest portion first (a stable order: a decode-only step
+        # keeps the caller's), so that a mixer can hand the portions of prompts and the single decoded
+        # tokens to different kernels as two contiguous runs of requests.  The wanted rows keep the
+        # caller's order of entries: ``caller_order[i]`` is where the caller's entry i stands.
+        if any(len(entry.token_ids) != len(entries[0].token_ids) for entry in entries):
+            by_length = sorted(range(num_reqs), key=lambda i: -len(entries[i].token_ids))
+            caller_order = [0] * num_reqs
+            for place, index in enumerate(by_length):
+                caller_order[index] = place
+            entries = [entries[index] for index in by_length]
+        else:
+            caller_order = None
         query_lens = [len(entry.token_ids) for entry in entries]
         num_tokens = sum(query_lens)
         if num_tokens > self.max_num_tokens:
@@ -320,6 +332,7 @@ class StepFunction:
                         )
                     logit_rows.append(row)
         else:
+            rows_of: list[list[int]] = []
             for row, (entry, n, context) in enumerate(zip(entries, query_lens, context_lens)):
                 ids = np.asarray(entry.token_ids, dtype=np.int64)
                 if ids.min() < 0 or ids.max() >= self.vocab_size:
@@ -331,13 +344,18 @@ class StepFunction:
                     context, context + n, dtype=np.int32
                 )
                 host[off_req_index + cursor : off_req_index + cursor + n] = row
+                wanted = []
                 for place in entry.want:
                     if not 0 <= place < n:
                         raise ValueError(
                             f"request {entry.request_id!r} wants logits at place {place} of {n} tokens"
                         )
-                    logit_rows.append(cursor + int(place))
+                    wanted.append(cursor + int(place))
+                rows_of.append(wanted)
                 cursor += n
+            # the logits come back in the caller's order of entries
+            for place in (caller_order if caller_order is not None else range(num_reqs)):
+                logit_rows.extend(rows_of[place])
         if logit_rows:
             host[off_logits : off_logits + num_logits] = logit_rows
         fed = any(entry.fed_from is not None for entry in entries)

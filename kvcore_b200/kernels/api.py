@@ -499,54 +499,98 @@ def paged_attention(
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if not force_general and flash_attention_supported(qkv.dtype, head_dim) and qkv.stride(0) % 8 == 0:
         group = num_heads // num_kv_heads
-        split_mode = ctx.max_query_len * group <= 16
-        bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
-        if split_mode and use_tma and tma_decode_supported(qkv.dtype, head_dim, page_size):
-            sms = sm_count(qkv.device)
-            splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound, sms)
-            scratch = None
-            if splits > 1:
-                scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
-                                      dtype=torch.float32, device=qkv.device)
-            k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache)
-            _call("kvb_flash_decode_tma", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
-                  ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
-                  ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
-                  num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-                  splits, None if scratch is None else scratch.data_ptr(),
-                  None if cos_sin is None else cos_sin.data_ptr(),
-                  k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None,
-                  _decode_work(qkv.device).data_ptr() if TMA_DECODE_SHARED_WORK else None,
-                  sms * TMA_DECODE_BLOCKS_PER_SM, _stream(),
-                  kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
-            return out
-        if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
-                and out.stride(0) % 8 == 0):
-            k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache, "half")
-            _call("kvb_flash_prefill_tc5", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
-                  ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
-                  ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
-                  tokens, num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-                  _stream())
-            return out
-        splits = 1
-        if split_mode:
-            splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound, sm_count(qkv.device))
-        scratch = None
-        if splits > 1:
-            scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
-                                  dtype=torch.float32, device=qkv.device)
-        _call("kvb_flash_paged_attention", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
-              k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
-              ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
-              num_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale), int(window or 0),
-              splits, None if scratch is None else scratch.data_ptr(), _stream(), kernels=2 if splits > 1 else 1)
+        geometry = (num_heads, num_kv_heads, head_dim, float(scale), int(window or 0))
+        # A mixed step (portions of prompts beside single decoded tokens) is two kinds of work: the
+        # portions fill query tiles of 128 rows, a decoded token has at most 16 rows a kv head and would
+        # leave such a tile almost empty while walking all its keys.  When the batch says how long each
+        # request's portion is and stands longest first (the step function packs it so), the two runs of
+        # requests go to the kernel made for each.
+        lens = getattr(ctx, "host_query_lens", None)
+        contexts = getattr(ctx, "host_context_lens", None)
+        if (write_kv is None and num_splits is None and lens and contexts and len(lens) == ctx.num_reqs
+                and ctx.max_query_len * group > 16):
+            long_count = sum(1 for n in lens if n * group > 16)
+            if 0 < long_count < ctx.num_reqs and all(n * group > 16 for n in lens[:long_count]):
+                for begin, end in ((0, long_count), (long_count, ctx.num_reqs)):
+                    part = _RequestRun(ctx, begin, end)
+                    _flash_attention_into(out, qkv, k_cache, v_cache, table[begin:end], part, geometry,
+                                          None, use_tma, use_tc5, None, None)
+                return out
+        _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_splits, use_tma, use_tc5,
+                              cos_sin, write_kv)
         return out
     _call("kvb_paged_attention_rows", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
           k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
           ctx.positions.data_ptr(), ctx.req_index.data_ptr(), tokens, num_heads, num_kv_heads,
           head_dim, page_size, num_pages, float(scale), int(window or 0), _dtype_code(qkv), _stream())
     return out
+
+
+class _RequestRun:
+    """Requests ``[begin, end)`` of a step's batch, as the attention kernels need a batch described:
+    views of the per-request arrays (query starts are token offsets into the whole step, so outputs
+    land in the rows of the whole step's tensors) and the lengths that size the launch."""
+
+    def __init__(self, ctx, begin: int, end: int) -> None:
+        lens, contexts = ctx.host_query_lens[begin:end], ctx.host_context_lens[begin:end]
+        self.num_reqs = end - begin
+        self.max_query_len = max(lens)
+        self.max_seq_len = max(c + n for c, n in zip(contexts, lens))
+        self.max_seq_len_bound = 0
+        self.query_start = ctx.query_start[begin : end + 1]
+        self.context_lens = ctx.context_lens[begin:end]
+
+
+def _flash_attention_into(out, qkv, k_cache, v_cache, table, ctx, geometry, num_splits, use_tma, use_tc5,
+                          cos_sin, write_kv) -> None:
+    """The tensor-core attention kernels on one batch (or one run of requests of a batch): the TMA
+    decode kernel for at most 16 rows a kv head, the tcgen05 kernel for portions of prompts, the
+    ``mma.sync`` kernel for the shapes those two do not take."""
+    num_heads, num_kv_heads, head_dim, scale, window = geometry
+    num_pages, _, page_size, _ = k_cache.shape
+    group = num_heads // num_kv_heads
+    split_mode = ctx.max_query_len * group <= 16
+    bound = getattr(ctx, "max_seq_len_bound", 0) or ctx.max_seq_len
+    if split_mode and use_tma and tma_decode_supported(qkv.dtype, head_dim, page_size):
+        sms = sm_count(qkv.device)
+        splits = num_splits or decode_splits_tma(ctx.num_reqs, num_kv_heads, bound, sms)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
+                                  dtype=torch.float32, device=qkv.device)
+        k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache)
+        _call("kvb_flash_decode_tma", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+              ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
+              ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+              num_heads, num_kv_heads, head_dim, page_size, num_pages, scale, window,
+              splits, None if scratch is None else scratch.data_ptr(),
+              None if cos_sin is None else cos_sin.data_ptr(),
+              k_cache.data_ptr() if write_kv else None, v_cache.data_ptr() if write_kv else None,
+              _decode_work(qkv.device).data_ptr() if TMA_DECODE_SHARED_WORK else None,
+              sms * TMA_DECODE_BLOCKS_PER_SM, _stream(),
+              kernels=2 if splits > 1 else 1)   # the splits are merged by a second kernel
+        return
+    if (not split_mode and use_tc5 and tc5_prefill_supported(qkv.dtype, head_dim, page_size)
+            and out.stride(0) % 8 == 0):
+        k_map, v_map = _kv_tensor_map_pair(k_cache, v_cache, "half")
+        _call("kvb_flash_prefill_tc5", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+              ctypes.addressof(k_map), ctypes.addressof(v_map), table.data_ptr(), table.stride(0),
+              ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+              qkv.shape[0], num_heads, num_kv_heads, head_dim, page_size, num_pages, scale, window,
+              _stream())
+        return
+    splits = 1
+    if split_mode:
+        splits = num_splits or decode_splits(ctx.num_reqs, num_kv_heads, bound, sm_count(qkv.device))
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(ctx.num_reqs * num_kv_heads * splits * 16 * (head_dim + 2),
+                              dtype=torch.float32, device=qkv.device)
+    _call("kvb_flash_paged_attention", out.data_ptr(), out.stride(0), qkv.data_ptr(), qkv.stride(0),
+          k_cache.data_ptr(), v_cache.data_ptr(), table.data_ptr(), table.stride(0),
+          ctx.query_start.data_ptr(), ctx.context_lens.data_ptr(), ctx.num_reqs, ctx.max_query_len,
+          num_heads, num_kv_heads, head_dim, page_size, num_pages, scale, window,
+          splits, None if scratch is None else scratch.data_ptr(), _stream(), kernels=2 if splits > 1 else 1)
 
 
 _mm_out_dtype_ok: bool | None = None

@@ -292,6 +292,42 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     assert all(not counters.any() for counters in K().api._decode_work_counters.values())
 
 
+MIXED_SHAPES = [
+    # heads, kv_heads, dim, page, [(context, query), ...] longest portion first, window
+    (32, 8, 128, 16, [(100, 300), (0, 64), (777, 1), (17, 1), (2047, 1), (0, 1)], None),   # tcgen05 + TMA decode
+    (8, 2, 128, 16, [(5, 150), (900, 2), (64, 1), (33, 1)], None),                         # 2 tokens x 4 heads: still decode
+    (6, 2, 128, 8, [(0, 70), (40, 9), (500, 5), (63, 1)], None),                           # 3 heads a group: 9 tokens are long
+    (16, 4, 64, 8, [(10, 200), (300, 3), (77, 1)], None),                                  # mma.sync tile + TMA decode (D = 64)
+    (6, 3, 48, 16, [(17, 130), (100, 2), (0, 1)], None),                                   # mma.sync tile + mma.sync split
+    (8, 2, 128, 32, [(0, 400), (350, 1), (120, 1)], 100),                                  # window
+]
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page,lens,window", MIXED_SHAPES)
+def test_mixed_batches_go_to_two_kernels_and_give_one_result(heads, kv_heads, dim, page, lens, window):
+    """A batch that says how long each request's portion is (longest first, as the step function packs
+    it): portions of prompts and decoded tokens are handed to different kernels as two runs of requests,
+    and every row is what the plain statement says (and what the one-kernel path gives)."""
+    dtype = torch.bfloat16
+    case = _cache_case(dtype, heads, kv_heads, dim, page, lens, seed=11)
+    scale = dim ** -0.5
+    ctx = _Ctx(case)
+    one = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                              heads, kv_heads, dim, scale, window)
+    launches = K().api.launch_count
+    ctx.host_query_lens = [q for _, q in lens]
+    ctx.host_context_lens = [c for c, _ in lens]
+    two = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                              heads, kv_heads, dim, scale, window)
+    assert K().api.launch_count - launches >= 2          # two kernels (and a merge where the decode run is split)
+    want = P.paged_attention_plain(case["qkv"], case["k_cache"], case["v_cache"], case["table"],
+                                   case["positions"], case["req_index"], heads, kv_heads, dim, scale, window)
+    assert torch.isfinite(two.float()).all()
+    torch.testing.assert_close(two.float(), want.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(two.float(), one.float(), rtol=2e-2, atol=2e-2)
+    assert K().read_status() == 0
+
+
 ROTATING_DECODE_SHAPES = [
     # heads, kv_heads, dim, page, [(context, query), ...], window, forced splits
     (32, 8, 128, 16, [(1000, 1), (17, 1), (4095, 1), (0, 1)], None, None),
