@@ -292,6 +292,49 @@ def test_flash_paged_attention(heads, kv_heads, dim, page, lens, window, splits)
     assert all(not counters.any() for counters in K().api._decode_work_counters.values())
 
 
+@pytest.mark.parametrize("seed", range(14))
+def test_prompt_attention_on_tcgen05_random_batches(seed):
+    """Batches drawn at random for the tcgen05 prompt kernel (head size 128): group sizes that divide 128
+    (queries by TMA) and 3 (queries copied), every page size, windows, contexts that end anywhere in a key
+    tile, portions that leave the second query tile of a block empty, partly filled, or one key tile behind
+    the first.  Against the general kernel (itself checked against the plain statement), the first seeds
+    against the plain statement as well."""
+    import random
+
+    rng = random.Random(1000 + seed)
+    group = rng.choice([1, 2, 4, 8, 3, 4])
+    kv_heads = rng.choice([1, 2])
+    heads, dim = group * kv_heads, 128
+    page = rng.choice([8, 16, 32, 64])
+    window = rng.choice([None, None, rng.randint(20, 300)])
+    lens = [(rng.choice([0, rng.randint(1, 700), 128 * rng.randint(0, 3), 127, 129]),
+             rng.choice([rng.randint(17, 400), 32, 64, 65, 128 // group + 1]))
+            for _ in range(rng.randint(1, 4))]
+    lens[0] = (lens[0][0], max(lens[0][1], 16 // group + 1))         # at least one portion of more than 16 rows
+    case = _cache_case(torch.bfloat16, heads, kv_heads, dim, page, lens, seed=seed)
+    owned = set(case["table"].flatten().tolist()) | {0}
+    case["k_cache"][0] = 0
+    case["v_cache"][0] = 0
+    for page_id in range(case["k_cache"].shape[0]):
+        if page_id not in owned:
+            case["k_cache"][page_id] = float("nan")
+            case["v_cache"][page_id] = float("nan")
+    scale = dim ** -0.5
+    ctx = _Ctx(case)
+    assert K().tc5_prefill_supported(torch.bfloat16, dim, page) and ctx.max_query_len * group > 16
+    got = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                              heads, kv_heads, dim, scale, window)
+    general = K().paged_attention(case["qkv"], case["k_cache"], case["v_cache"], case["table"], ctx,
+                                  heads, kv_heads, dim, scale, window, force_general=True)
+    assert torch.isfinite(got.float()).all(), (group, kv_heads, page, window, lens)
+    torch.testing.assert_close(got.float(), general.float(), rtol=2e-2, atol=2e-2, msg=str((group, kv_heads, page, window, lens)))
+    if seed < 3:
+        want = P.paged_attention_plain(case["qkv"], case["k_cache"], case["v_cache"], case["table"],
+                                       case["positions"], case["req_index"], heads, kv_heads, dim, scale, window)
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert K().read_status() == 0
+
+
 MIXED_SHAPES = [
     # heads, kv_heads, dim, page, [(context, query), ...] longest portion first, window
     (32, 8, 128, 16, [(100, 300), (0, 64), (777, 1), (17, 1), (2047, 1), (0, 1)], None),   # tcgen05 + TMA decode
