@@ -288,7 +288,39 @@ flash_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         if (has_b) issue_s(1, 0);
         kvb_tc5_commit(&k_empty[0]);
       }
-      for (int j = 0; j < num_tiles && ok; ++j) {
+      int j = 0;
+      // Pairs of key tiles well inside the block's run, where both query tiles are at work and nothing ends:
+      // the ring places, barriers and phases of a pair are constants, so that this thread, which alone feeds
+      // the tensor pipe, runs next to nothing between two groups of products.
+      if (has_b) {
+        unsigned ph = 0;
+        for (; j + 3 < n_a && ok; j += 2, ph ^= 1u) {
+#define T5_HALF_STEP(ST, PPAR, KPAR, ACC)                                                                  \
+          {                                                                                               \
+            if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[ST], ph)) { ok = false; break; }              \
+            if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[0], PPAR)) { ok = false; break; }            \
+            kvb_tc5_fence_after();                                                                        \
+            kvb_tc5_mma8_ts<8, 128>(tmem_base + 256, tmem_base, v_desc[ST], idesc_pv, ACC);               \
+            kvb_tc5_commit(&pv_done[0]);                                                                  \
+            if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&k_full[(ST) ^ 1], KPAR)) { ok = false; break; }      \
+            kvb_tc5_fence_after();                                                                        \
+            kvb_tc5_mma8_ss<2, (T5_HALF_BYTES >> 4) - 6, 2, (T5_HALF_BYTES >> 4) - 6>(tmem_base, q_desc[0], k_desc[(ST) ^ 1], idesc_s, 0u); \
+            kvb_tc5_commit(&s_full[0]);                                                                   \
+            if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&p_ready[1], PPAR)) { ok = false; break; }            \
+            kvb_tc5_fence_after();                                                                        \
+            kvb_tc5_mma8_ts<8, 128>(tmem_base + 256 + T5_D, tmem_base + T5_BN, v_desc[ST], idesc_pv, ACC); \
+            kvb_tc5_commit(&pv_done[1]);                                                                  \
+            kvb_tc5_commit(&v_empty[ST]);                                                                 \
+            kvb_tc5_mma8_ss<2, (T5_HALF_BYTES >> 4) - 6, 2, (T5_HALF_BYTES >> 4) - 6>(tmem_base + T5_BN, q_desc[1], k_desc[(ST) ^ 1], idesc_s, 0u); \
+            kvb_tc5_commit(&s_full[1]);                                                                   \
+            kvb_tc5_commit(&k_empty[(ST) ^ 1]);                                                           \
+          }
+          T5_HALF_STEP(0, 0u, ph, j > 0 ? 1u : 0u)
+          T5_HALF_STEP(1, 1u, ph ^ 1u, 1u)
+#undef T5_HALF_STEP
+        }
+      }
+      for (; j < num_tiles && ok; ++j) {
         const int st = j & 1, par = (j >> 1) & 1;
         const bool more = j + 1 < num_tiles;
         if (!kvb_mbar_wait<T5_SPIN_LIMIT, 4096>(&v_full[st], par)) { ok = false; break; }
