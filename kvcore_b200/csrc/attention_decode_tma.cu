@@ -348,7 +348,9 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     // write both into the cache, keep them to lay over the tile that holds their (old) slots
     if (p.k_cache != nullptr) {
       const int new_tokens = q_len < 16 ? q_len : 16;
-      for (int i = threadIdx.x; i < new_tokens * 2 * PAIRS; i += TD_CONSUMERS * 32) {
+      // (dealt out from the last thread downwards: the first threads are the ones with query rows to
+      // fetch, and the two fetches then wait for memory side by side instead of one after the other)
+      for (int i = TD_CONSUMERS * 32 - 1 - (int)threadIdx.x; i < new_tokens * 2 * PAIRS; i += TD_CONSUMERS * 32) {
         const int t = i / (2 * PAIRS), which = (i / PAIRS) & 1, gq = i % PAIRS;   // which: 0 key, 1 value
         const int pos = context + t;
         if (pos < key_lo || pos >= key_hi) continue;
@@ -543,26 +545,33 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(TD_CONSUMERS * 32));
       const int rows_here = min(4, rows_total - 4 * c);
-      for (int i = threadIdx.x; i < rows_here * D; i += TD_CONSUMERS * 32) {
-        const int r4 = i / D, d = i % D, r = 4 * c + r4;
+      // a thread takes four neighbouring columns of one row (D / 4 threads a row)
+      const int r4 = threadIdx.x / (D / 4), d = (threadIdx.x % (D / 4)) * 4, r = 4 * c + r4;
+      if (r4 < rows_here) {
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < TD_CONSUMERS; ++w) m = fmaxf(m, merge_ml[(w * 4 + r4) * 2]);
-        float total = 0.0f, acc = 0.0f;
+        float total = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int w = 0; w < TD_CONSUMERS; ++w) {
           const float mw = merge_ml[(w * 4 + r4) * 2];
           const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - m);
           total += merge_ml[(w * 4 + r4) * 2 + 1] * f;
-          acc += merge_o[((size_t)(w * 4 + r4)) * D + d] * f;
+          const float4 part = *reinterpret_cast<const float4*>(merge_o + ((size_t)(w * 4 + r4)) * D + d);
+          acc.x += part.x * f; acc.y += part.y * f; acc.z += part.z * f; acc.w += part.w * f;
         }
         if (p.num_splits == 1) {
           const int token = q_begin + r / p.G, head = kvh * p.G + r % p.G;
-          p.out[(size_t)token * p.out_stride + (size_t)head * D + d] =
-              __float2bfloat16_rn(total > 0.0f ? acc / total : 0.0f);
+          if (!(total > 0.0f)) { acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f); total = 1.0f; }
+          __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x / total, acc.y / total), hi = __floats2bfloat162_rn(acc.z / total, acc.w / total);
+          uint2 packed;
+          packed.x = *reinterpret_cast<unsigned*>(&lo);
+          packed.y = *reinterpret_cast<unsigned*>(&hi);
+          *reinterpret_cast<uint2*>(p.out + (size_t)token * p.out_stride + (size_t)head * D + d) = packed;
         } else {
           const size_t slot = ((size_t)req * p.KVH + kvh) * p.num_splits + split;
-          p.partial_o[(slot * 16 + r) * D + d] = acc;
+          *reinterpret_cast<float4*>(p.partial_o + (slot * 16 + r) * D + d) = acc;
           if (d == 0) {
             p.partial_ml[(slot * 16 + r) * 2 + 0] = m;
             p.partial_ml[(slot * 16 + r) * 2 + 1] = total;
@@ -690,6 +699,7 @@ extern "C" int kvb_flash_decode_tma(void* out, long long out_stride, const void*
   KVB_REQUIRE((long long)num_reqs * KVH * (num_splits < 1 ? 1 : num_splits) < (1ll << 30),
               "decode attention (TMA): batch too large for one launch");
   KVB_REQUIRE(aligned16(q) && (q_stride % 8) == 0, "decode attention (TMA): q must be 16-byte aligned");
+  KVB_REQUIRE(aligned16(out) && (out_stride % 8) == 0, "decode attention (TMA): out must be 16-byte aligned");
   KVB_REQUIRE(k_map_host != nullptr && v_map_host != nullptr, "decode attention (TMA): tensor maps are missing");
   DecodeParams p;
   p.out = (bf16*)out; p.out_stride = out_stride;
