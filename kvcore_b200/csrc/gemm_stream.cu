@@ -94,6 +94,17 @@ __device__ __forceinline__ bool gs_wait(const StreamParams& p, unsigned long lon
   return kvb_mbar_wait_n(bar, parity, p.spin_limit, 64);
 }
 
+// Named barrier ID of THREADS threads that also tells everyone whether anyone brought `mine`: the way the
+// warps of a role leave together when one of them has given up (a plain barrier followed by a look at a
+// flag lets one warp leave and another stay, and the one that stays then waits at the next barrier for good).
+template <int ID, int THREADS>
+__device__ __forceinline__ bool gs_bar_any(bool mine) {
+  unsigned any;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.or.pred q, %2, %3, p;\nselp.u32 %0, 1, 0, q;\n}\n"
+               : "=r"(any) : "r"((unsigned)mine), "n"(ID), "n"(THREADS) : "memory");
+  return any != 0;
+}
+
 // First stage of block b when `units` stages are dealt to `blocks` blocks.
 __device__ __forceinline__ int gs_range_start(int units, int blocks, int b) {
   return (int)(((long long)units * b) / blocks);
@@ -319,8 +330,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           for (int e = 0; e < 4; ++e) halves[(j * 4 + e) * 128 + tid] = acc[0][j][e];
         }
       }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32));
-      if (*reinterpret_cast<volatile int*>(&flags[0])) break;   // somebody gave up waiting
+      if (gs_bar_any<1, GS_CONSUMERS * 32>(*reinterpret_cast<volatile int*>(&flags[0]) != 0)) break;   // somebody gave up waiting
       if (kh == 0) {
 #pragma unroll
         for (int j = 0; j < MBLK; ++j) {
@@ -401,8 +411,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                 }
               }
             }
-            asm volatile("bar.sync 2, 128;\n");
-            if (*reinterpret_cast<volatile int*>(&flags[0])) complete = false;
+            if (gs_bar_any<2, 128>(*reinterpret_cast<volatile int*>(&flags[0]) != 0)) complete = false;
           }
           if (complete) {
             // ---- bias, activation, then through shared memory: the tile leaves as whole 128-byte runs ----
@@ -493,8 +502,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         }
       }
       // warps 0-3 have read the halves before they are written again
-      asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32));
-      if (*reinterpret_cast<volatile int*>(&flags[0])) break;
+      if (gs_bar_any<1, GS_CONSUMERS * 32>(*reinterpret_cast<volatile int*>(&flags[0]) != 0)) break;
     }
   }
 }
