@@ -21,6 +21,7 @@ prints a line of its own.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import statistics
 import subprocess
@@ -337,12 +338,18 @@ def time_e2e(config, runner, batch: int, context: int, steps: int, warmup: int) 
         engine.step()
     torch.cuda.synchronize()
     used_before = runner.step_function.num_steps
-    begin = time.perf_counter()
-    produced = 0
-    for _ in range(steps):
-        produced += sum(1 for o in engine.step().request_outputs if o.sampled_token_id is not None)
-    torch.cuda.synchronize()
-    elapsed = time.perf_counter() - begin
+    # (as `timeit` does: no collection of host garbage inside the few timed milliseconds)
+    gc.collect()
+    gc.disable()
+    try:
+        begin = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += sum(1 for o in engine.step().request_outputs if o.sampled_token_id is not None)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - begin
+    finally:
+        gc.enable()
     # with a step kept in flight, one more step than has been read is launched at either end
     assert abs(runner.step_function.num_steps - used_before - steps) <= 1
     assert produced == steps * batch, f"{produced} tokens from {steps} steps of {batch} requests"
