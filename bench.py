@@ -541,14 +541,19 @@ def _run_reference(args, ref: Path) -> dict:
     sampler.start()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
-    began = time.perf_counter()
-    start.record()
-    produced = 0
-    for _ in range(steps):
-        produced += sampled(core.step())
-    stop.record()
-    torch.cuda.synchronize()
-    elapsed = time.perf_counter() - began
+    gc.collect()          # the same for both arms: no collection of host garbage inside the timed steps
+    gc.disable()
+    try:
+        began = time.perf_counter()
+        start.record()
+        produced = 0
+        for _ in range(steps):
+            produced += sampled(core.step())
+        stop.record()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - began
+    finally:
+        gc.enable()
     clocks = sampler.stop()
     assert produced == steps * batch, f"{produced} tokens from {steps} steps of {batch} requests"
     ms_step = start.elapsed_time(stop) / steps
