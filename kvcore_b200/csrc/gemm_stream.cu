@@ -209,16 +209,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       kvb_grid_wait();
       // 1 / rms of this warp's token rows from the pieces of their sums of squares: every lane adds
       // its pieces in order, the lanes are added by a butterfly, so the value depends on the pieces alone
+      // (the pieces of all of this warp's rows are asked for before any of them is added: one trip to L2,
+      // not one a row, between the end of the kernel in front and the first normalised stage)
       constexpr int ROWS = MB / GS_NORMALISERS;
-      float inv[ROWS];
+      float inv[ROWS], part[ROWS];
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        const int m = nw + i * GS_NORMALISERS;
-        float part = 0.0f;
-        if (m < p.M)
-          for (int t = lane; t < p.sumsq_pieces; t += 32) part += __ldcg(p.sumsq_in + (size_t)m * p.sumsq_pieces + t);
-        inv[i] = 1.0f / sqrtf(warp_sum(part) / (float)p.K + p.eps);
+      for (int i = 0; i < ROWS; ++i) part[i] = 0.0f;
+      for (int t = lane; t < p.sumsq_pieces; t += 32) {
+        float piece[ROWS];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+          const int m = nw + i * GS_NORMALISERS;
+          piece[i] = m < p.M ? __ldcg(p.sumsq_in + (size_t)m * p.sumsq_pieces + t) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) part[i] += piece[i];
       }
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) inv[i] = 1.0f / sqrtf(warp_sum(part[i]) / (float)p.K + p.eps);
       const int total = u_end - u_begin;
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
