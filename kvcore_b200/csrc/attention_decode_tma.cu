@@ -36,7 +36,7 @@
 #define TD_GROUP_WARPS 4   // warps of a group; warp w of a group scores keys [16w, 16w+16) of a tile
 #define TD_CONSUMERS (TD_GROUPS * TD_GROUP_WARPS)
 #define TD_THREADS ((TD_CONSUMERS + 1) * 32)
-#define TD_SPIN_LIMIT (1u << 22)
+#define TD_SPIN_LIMIT (1u << 20)
 
 struct DecodeParams {
   bf16* out; long long out_stride;

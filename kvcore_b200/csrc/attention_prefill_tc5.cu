@@ -47,7 +47,7 @@
 #define T5_BN 128
 #define T5_D 128
 #define T5_THREADS 352
-#define T5_SPIN_LIMIT (1u << 22)
+#define T5_SPIN_LIMIT (1u << 20)
 #define T5_HALF_BYTES (128 * 128)        // one 64-column half of a 128-row operand tile
 #define T5_TILE_BYTES (2 * T5_HALF_BYTES)
 

@@ -42,7 +42,7 @@
 #define GS_CONSUMERS 8
 #define GS_THREADS ((GS_CONSUMERS + 1) * 32)
 #define GS_STAGES 5
-#define GS_SPIN_LIMIT (1u << 22)
+#define GS_SPIN_LIMIT (1u << 20)
 #define GS_NORM_W_BYTES (16 * 1024)   // norm weights a NORMED kernel keeps in shared memory
 #define GS_NORMALISERS 4               // NORMED: warps that normalise the token rows of each stage
 #define GS_SCRATCH_MARKER 0x7FC0DEADu  // every word of scratch between launches: a NaN no sum can be (sums that are NaN are 0x7FFFFFFF)
